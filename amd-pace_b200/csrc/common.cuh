@@ -1,0 +1,186 @@
+// Shared device/host helpers for the sm_100a KV-cache kernels.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "pace_b200.h"
+
+namespace pace {
+
+// ---------------------------------------------------------------------------
+// Error plumbing (host)
+// ---------------------------------------------------------------------------
+void set_cuda_error(cudaError_t e, const char* where);
+
+#define PACE_CUDA_TRY(expr)                         \
+  do {                                              \
+    cudaError_t _e = (expr);                        \
+    if (_e != cudaSuccess) {                        \
+      ::pace::set_cuda_error(_e, #expr);            \
+      return PACE_ERR_CUDA;                         \
+    }                                               \
+  } while (0)
+
+#define PACE_LAUNCH_CHECK(name)                     \
+  do {                                              \
+    cudaError_t _e = cudaGetLastError();            \
+    if (_e != cudaSuccess) {                        \
+      ::pace::set_cuda_error(_e, name);             \
+      return PACE_ERR_CUDA;                         \
+    }                                               \
+  } while (0)
+
+// ---------------------------------------------------------------------------
+// What a kernel needs to find K/V rows.  Covers the paged pool (block table,
+// per-slot lengths) and a dense [B][Hkv][L][D] tensor (identity table, one
+// "page" of L tokens per batch row).
+// ---------------------------------------------------------------------------
+struct KVView {
+  const __nv_bfloat16* k;       // base of this layer's K pages
+  const __nv_bfloat16* v;       // base of this layer's V pages
+  const int32_t* block_table;   // [max_seqs][max_pages_per_seq] or nullptr (page = slot)
+  const int32_t* seq_ids;       // [batch] or nullptr (slot = batch index)
+  const int32_t* seq_len;       // this layer's [max_seqs] lengths or nullptr (use fixed_len)
+  int32_t* status;              // sticky device status word or nullptr
+  int32_t fixed_len;
+  int32_t page_tokens;
+  int32_t n_kv_heads;
+  int32_t head_dim;
+  int32_t max_pages_per_seq;
+  int32_t max_seqs;
+  int32_t n_pages;
+};
+
+inline KVView make_view(const pace_kv_pool_t* p, int layer, const int32_t* seq_ids) {
+  KVView v;
+  const size_t page_elems = (size_t)p->n_kv_heads * p->page_tokens * p->head_dim;
+  const size_t region = page_elems * (size_t)p->n_pages;
+  const __nv_bfloat16* base = (const __nv_bfloat16*)p->pages;
+  v.k = base + ((size_t)layer * 2 + 0) * region;
+  v.v = base + ((size_t)layer * 2 + 1) * region;
+  v.block_table = p->block_table;
+  v.seq_ids = seq_ids;
+  v.seq_len = p->seq_len + (size_t)layer * p->max_seqs;
+  v.status = p->status;
+  v.fixed_len = 0;
+  v.page_tokens = p->page_tokens;
+  v.n_kv_heads = p->n_kv_heads;
+  v.head_dim = p->head_dim;
+  v.max_pages_per_seq = p->max_pages_per_seq;
+  v.max_seqs = p->max_seqs;
+  v.n_pages = p->n_pages;
+  return v;
+}
+
+#ifdef __CUDACC__
+
+__device__ __forceinline__ void raise_status(int32_t* status, int bits) {
+  if (status) atomicOr(status, bits);
+}
+
+// slot of batch row b, or -1 when out of range (status raised)
+__device__ __forceinline__ int view_slot(const KVView& kv, int b) {
+  int s = kv.seq_ids ? kv.seq_ids[b] : b;
+  if (s < 0 || s >= kv.max_seqs) {
+    raise_status(kv.status, PACE_DEV_BAD_INDEX);
+    return -1;
+  }
+  return s;
+}
+__device__ __forceinline__ int view_len(const KVView& kv, int slot) {
+  return kv.seq_len ? kv.seq_len[slot] : kv.fixed_len;
+}
+// physical page of logical page lp of a slot, or -1
+__device__ __forceinline__ int view_page(const KVView& kv, int slot, int lp) {
+  if (!kv.block_table) return slot;
+  if (lp < 0 || lp >= kv.max_pages_per_seq) return -1;
+  int p = kv.block_table[(size_t)slot * kv.max_pages_per_seq + lp];
+  if (p < 0 || p >= kv.n_pages) return -1;
+  return p;
+}
+// element offset of row `row` of head h in physical page p
+__device__ __forceinline__ size_t view_row_offset(const KVView& kv, int page, int h, int row) {
+  return (((size_t)page * kv.n_kv_heads + h) * kv.page_tokens + row) * (size_t)kv.head_dim;
+}
+
+// ---------------------------------------------------------------------------
+// mbarrier + bulk-copy (TMA) wrappers.  Every wait is bounded.
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_inval(uint64_t* bar) {
+  asm volatile("mbarrier.inval.shared::cta.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+// make the initialised barriers visible to the async (TMA) proxy
+__device__ __forceinline__ void fence_mbar_init() {
+  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void fence_proxy_async() {
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait: true when the phase completed, false when it gave up
+// (roughly a quarter of a second of polling).
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+  for (int i = 0; i < 2048; ++i)
+    if (mbar_try_wait(bar, parity)) return true;
+  for (int i = 0; i < (1 << 21); ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    __nanosleep(64);
+  }
+  return false;
+}
+// global -> shared bulk copy through the TMA unit, completion on an mbarrier.
+// Both addresses 16-byte aligned, bytes a multiple of 16.
+__device__ __forceinline__ void bulk_g2s(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                   smem_u32(smem_dst)),
+               "l"(gsrc), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
+}
+
+// bf16 pair (packed in a 32-bit word, low element first) -> two floats
+__device__ __forceinline__ float2 bf2_to_f2(uint32_t w) {
+  float2 r;
+  r.x = __uint_as_float(w << 16);
+  r.y = __uint_as_float(w & 0xffff0000u);
+  return r;
+}
+__device__ __forceinline__ uint32_t f2_to_bf2(float a, float b) {
+  __nv_bfloat162 t = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&t);
+}
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+#endif  // __CUDACC__
+
+constexpr float kLog2e = 1.4426950408889634f;
+
+}  // namespace pace

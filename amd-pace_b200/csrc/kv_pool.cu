@@ -1,0 +1,557 @@
+// Device-resident paged KV pool: allocator, block tables, append / rollback /
+// beam-gather kernels and their C ABI.
+//
+// Stands in for the reference's per-layer torch buffers and Python bookkeeping
+// (pace/llm/cache.py:126-400).  All state lives in device memory and is mutated
+// by stream-ordered kernels; the host never copies a table.
+#include <cstdio>
+#include <cstring>
+
+#include "common.cuh"
+
+namespace pace {
+
+static thread_local char g_err[512] = "";
+void set_cuda_error(cudaError_t e, const char* where) {
+  snprintf(g_err, sizeof(g_err), "%s: %s (%s)", where, cudaGetErrorName(e), cudaGetErrorString(e));
+}
+
+namespace {
+
+constexpr int kCounterFree = 0;    // number of free pages
+constexpr int kCounterTicket = 1;  // append kernel: blocks finished
+
+__host__ __device__ inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+
+struct MetaLayout {
+  size_t block_table, seq_len, seq_pages, page_ref, free_stack, counters, status, table_tmp, total;
+};
+
+MetaLayout meta_layout(const pace_kv_pool_t* g) {
+  MetaLayout m;
+  size_t off = 0;
+  auto take = [&](size_t n_int32) {
+    size_t o = off;
+    off = align_up(off + n_int32 * sizeof(int32_t), 256);
+    return o;
+  };
+  const size_t S = g->max_seqs, MP = g->max_pages_per_seq, L = g->n_layers, NP = g->n_pages;
+  m.block_table = take(S * MP);
+  m.seq_len = take(L * S);
+  m.seq_pages = take(S);
+  m.page_ref = take(NP);
+  m.free_stack = take(NP);
+  m.counters = take(8);
+  m.status = take(4);
+  m.table_tmp = take(S * (MP + 4) + L * S);
+  m.total = off;
+  return m;
+}
+
+bool geometry_ok(const pace_kv_pool_t* g) {
+  if (!g) return false;
+  if (g->n_layers <= 0 || g->n_kv_heads <= 0 || g->page_tokens <= 0 || g->n_pages <= 0 || g->max_seqs <= 0 ||
+      g->max_pages_per_seq <= 0)
+    return false;
+  if (g->head_dim != 64 && g->head_dim != 128) return false;
+  return true;
+}
+
+// ---------------------------------------------------------------------------
+// kernels
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ int pop_page(const pace_kv_pool_t& p) {
+  int idx = atomicSub(&p.counters[kCounterFree], 1) - 1;
+  if (idx < 0) {
+    atomicAdd(&p.counters[kCounterFree], 1);
+    return -1;
+  }
+  return p.free_stack[idx];
+}
+__device__ __forceinline__ void push_page(const pace_kv_pool_t& p, int page) {
+  int idx = atomicAdd(&p.counters[kCounterFree], 1);
+  p.free_stack[idx] = page;
+}
+// drop one reference; the last owner returns the page to the free list
+__device__ __forceinline__ void unref_page(const pace_kv_pool_t& p, int page) {
+  if (page < 0 || page >= p.n_pages) return;
+  if (atomicSub(&p.page_ref[page], 1) == 1) push_page(p, page);
+}
+
+__global__ void reset_kernel(pace_kv_pool_t p) {
+  const size_t tid = blockIdx.x * (size_t)blockDim.x + threadIdx.x;
+  const size_t nth = (size_t)gridDim.x * blockDim.x;
+  const size_t nt = (size_t)p.max_seqs * p.max_pages_per_seq;
+  for (size_t i = tid; i < nt; i += nth) p.block_table[i] = -1;
+  for (size_t i = tid; i < (size_t)p.n_layers * p.max_seqs; i += nth) p.seq_len[i] = 0;
+  for (size_t i = tid; i < (size_t)p.max_seqs; i += nth) p.seq_pages[i] = 0;
+  for (size_t i = tid; i < (size_t)p.n_pages; i += nth) {
+    p.page_ref[i] = 0;
+    p.free_stack[i] = p.n_pages - 1 - (int)i;  // page 0 is handed out first
+  }
+  if (tid < 8) p.counters[tid] = (tid == kCounterFree) ? p.n_pages : 0;
+  if (tid < 4) p.status[tid] = 0;
+}
+
+// One block.  Phase 1 (thread 0, sequential): copy-on-write of shared pages the
+// coming append writes into.  Phase 2 (all threads): pop pages up to the needed
+// count.  Phase 3 (all threads): copy the live rows of copied-on-write pages.
+__global__ void reserve_kernel(pace_kv_pool_t p, int layer, const int32_t* __restrict__ seq_ids, int batch,
+                               int n_new, const int32_t* __restrict__ n_per) {
+  __shared__ int cow_count;
+  int32_t* cow = p.table_tmp;  // triples (src page, dst page, rows)
+  const int P = p.page_tokens;
+  if (threadIdx.x == 0) {
+    cow_count = 0;
+    for (int b = 0; b < batch; ++b) {
+      const int slot = seq_ids[b];
+      if (slot < 0 || slot >= p.max_seqs) continue;
+      int n = n_per ? min(n_per[b], n_new) : n_new;
+      if (n <= 0) continue;
+      const int len = p.seq_len[(size_t)layer * p.max_seqs + slot];
+      const int have = p.seq_pages[slot];
+      const int need = min((len + n + P - 1) / P, p.max_pages_per_seq);
+      int32_t* row = p.block_table + (size_t)slot * p.max_pages_per_seq;
+      const int first = len / P;
+      for (int lp = first; lp < min(have, need); ++lp) {
+        const int pg = row[lp];
+        if (pg < 0 || pg >= p.n_pages) continue;
+        if (p.page_ref[pg] > 1) {
+          const int np = pop_page(p);
+          if (np < 0) {
+            raise_status(p.status, PACE_DEV_POOL_EXHAUSTED);
+            break;
+          }
+          p.page_ref[np] = 1;
+          p.page_ref[pg] -= 1;
+          row[lp] = np;
+          const int rows = (lp == first) ? len - first * P : 0;
+          if (rows > 0) {
+            cow[3 * cow_count + 0] = pg;
+            cow[3 * cow_count + 1] = np;
+            cow[3 * cow_count + 2] = rows;
+            ++cow_count;
+          }
+        }
+      }
+    }
+  }
+  __syncthreads();
+  for (int b = threadIdx.x; b < batch; b += blockDim.x) {
+    const int slot = seq_ids[b];
+    if (slot < 0 || slot >= p.max_seqs) {
+      raise_status(p.status, PACE_DEV_BAD_INDEX);
+      continue;
+    }
+    int n = n_per ? min(n_per[b], n_new) : n_new;
+    if (n <= 0) continue;
+    const int len = p.seq_len[(size_t)layer * p.max_seqs + slot];
+    int need = (len + n + P - 1) / P;
+    if (need > p.max_pages_per_seq) {
+      raise_status(p.status, PACE_DEV_TABLE_FULL);
+      need = p.max_pages_per_seq;
+    }
+    int have = p.seq_pages[slot];
+    int32_t* row = p.block_table + (size_t)slot * p.max_pages_per_seq;
+    while (have < need) {
+      const int np = pop_page(p);
+      if (np < 0) {
+        raise_status(p.status, PACE_DEV_POOL_EXHAUSTED);
+        break;
+      }
+      p.page_ref[np] = 1;
+      row[have++] = np;
+    }
+    p.seq_pages[slot] = have;
+  }
+  __syncthreads();
+  const int nc = cow_count;
+  if (nc == 0) return;
+  // rows of a page are contiguous per head: copy rows*D elements for every (layer, K|V, head)
+  const size_t page_elems = (size_t)p.n_kv_heads * P * p.head_dim;
+  const size_t region = page_elems * (size_t)p.n_pages;
+  uint4* base = reinterpret_cast<uint4*>(p.pages);
+  const int vec_per_row = p.head_dim / 8;
+  for (int c = 0; c < nc; ++c) {
+    const int src = cow[3 * c], dst = cow[3 * c + 1], rows = cow[3 * c + 2];
+    const size_t per_head = (size_t)rows * vec_per_row;
+    const size_t total = (size_t)p.n_layers * 2 * p.n_kv_heads * per_head;
+    for (size_t i = threadIdx.x; i < total; i += blockDim.x) {
+      const size_t lk = i / (p.n_kv_heads * per_head);
+      const size_t rem = i % (p.n_kv_heads * per_head);
+      const size_t h = rem / per_head, o = rem % per_head;
+      const size_t head_off = (h * P) * (size_t)p.head_dim / 8;
+      const size_t s = (lk * region + (size_t)src * page_elems) / 8 + head_off + o;
+      const size_t d = (lk * region + (size_t)dst * page_elems) / 8 + head_off + o;
+      base[d] = base[s];
+    }
+  }
+}
+
+// One warp per (sequence, new token, kv head): lanes [0, D/8) move the K row,
+// lanes [16, 16 + D/8) the V row, 16 bytes per lane.  The last block to finish
+// advances the per-layer lengths.
+__global__ void __launch_bounds__(256)
+    append_kernel(pace_kv_pool_t p, int layer, const int32_t* __restrict__ seq_ids, int batch, int n_new,
+                  const int32_t* __restrict__ n_per, const __nv_bfloat16* __restrict__ k_new,
+                  const __nv_bfloat16* __restrict__ v_new, int64_t sb, int64_t sh, int64_t st) {
+  const int lane = threadIdx.x & 31;
+  const int warps_per_block = blockDim.x >> 5;
+  const long long total = (long long)batch * n_new * p.n_kv_heads;
+  const int P = p.page_tokens, D = p.head_dim;
+  const int vec_per_row = D / 8;
+  const size_t page_elems = (size_t)p.n_kv_heads * P * D;
+  const size_t region = page_elems * (size_t)p.n_pages;
+  __nv_bfloat16* kbase = reinterpret_cast<__nv_bfloat16*>(p.pages) + ((size_t)layer * 2) * region;
+  __nv_bfloat16* vbase = kbase + region;
+  const int32_t* lens = p.seq_len + (size_t)layer * p.max_seqs;
+
+  for (long long w = (long long)blockIdx.x * warps_per_block + (threadIdx.x >> 5); w < total;
+       w += (long long)gridDim.x * warps_per_block) {
+    const int h = (int)(w % p.n_kv_heads);
+    const int t = (int)((w / p.n_kv_heads) % n_new);
+    const int b = (int)(w / ((long long)p.n_kv_heads * n_new));
+    const int slot = seq_ids[b];
+    if (slot < 0 || slot >= p.max_seqs) continue;  // reported by reserve
+    const int n = n_per ? min(n_per[b], n_new) : n_new;
+    if (t >= n) continue;
+    const int pos = lens[slot] + t;
+    const int lp = pos / P;
+    int page = -1;
+    if (lp < p.max_pages_per_seq) page = p.block_table[(size_t)slot * p.max_pages_per_seq + lp];
+    if (page < 0 || page >= p.n_pages) {
+      if (lane == 0) raise_status(p.status, PACE_DEV_BAD_INDEX);
+      continue;
+    }
+    const size_t dst = (((size_t)page * p.n_kv_heads + h) * P + (pos - lp * P)) * (size_t)D;
+    const size_t src = (size_t)b * sb + (size_t)h * sh + (size_t)t * st;
+    const int half = lane >> 4, l16 = lane & 15;
+    if (l16 < vec_per_row) {
+      const uint4* s = reinterpret_cast<const uint4*>((half ? v_new : k_new) + src) + l16;
+      uint4* d = reinterpret_cast<uint4*>((half ? vbase : kbase) + dst) + l16;
+      *d = __ldg(s);
+    }
+  }
+  // ---- last block advances the lengths ----
+  __shared__ int is_last;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    const int ticket = atomicAdd(&p.counters[kCounterTicket], 1);
+    is_last = (ticket == (int)gridDim.x - 1);
+  }
+  __syncthreads();
+  if (is_last) {
+    for (int b = threadIdx.x; b < batch; b += blockDim.x) {
+      const int slot = seq_ids[b];
+      if (slot < 0 || slot >= p.max_seqs) continue;
+      const int n = n_per ? min(n_per[b], n_new) : n_new;
+      if (n > 0) p.seq_len[(size_t)layer * p.max_seqs + slot] += n;
+    }
+    if (threadIdx.x == 0) p.counters[kCounterTicket] = 0;
+  }
+}
+
+__global__ void truncate_kernel(pace_kv_pool_t p, int layer_begin, int layer_end, const int32_t* __restrict__ seq_ids,
+                                int batch, int remove_len, const int32_t* __restrict__ remove_per) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  const int n_l = layer_end - layer_begin;
+  if (i >= batch * n_l) return;
+  const int b = i % batch, layer = layer_begin + i / batch;
+  const int slot = seq_ids[b];
+  if (slot < 0 || slot >= p.max_seqs) {
+    raise_status(p.status, PACE_DEV_BAD_INDEX);
+    return;
+  }
+  const int r = remove_per ? remove_per[b] : remove_len;
+  int32_t* len = p.seq_len + (size_t)layer * p.max_seqs + slot;
+  if (r < 0 || r > *len) {
+    raise_status(p.status, PACE_DEV_OVER_REMOVE);
+    return;
+  }
+  *len -= r;
+}
+
+__global__ void release_kernel(pace_kv_pool_t p, const int32_t* __restrict__ seq_ids, int batch) {
+  for (int b = blockIdx.x; b < batch; b += gridDim.x) {
+    const int slot = seq_ids[b];
+    if (slot < 0 || slot >= p.max_seqs) {
+      if (threadIdx.x == 0) raise_status(p.status, PACE_DEV_BAD_INDEX);
+      continue;
+    }
+    int32_t* row = p.block_table + (size_t)slot * p.max_pages_per_seq;
+    const int have = p.seq_pages[slot];
+    for (int lp = threadIdx.x; lp < have; lp += blockDim.x) {
+      unref_page(p, row[lp]);
+      row[lp] = -1;
+    }
+    for (int l = threadIdx.x; l < p.n_layers; l += blockDim.x) p.seq_len[(size_t)l * p.max_seqs + slot] = 0;
+    __syncthreads();
+    if (threadIdx.x == 0) p.seq_pages[slot] = 0;
+    __syncthreads();
+  }
+}
+
+// One block.  Row i of the batch becomes old row beam_idx[i]: snapshot the source
+// rows, take references on them, drop the references of the rows being replaced,
+// then write the snapshot back.
+__global__ void gather_kernel(pace_kv_pool_t p, const int32_t* __restrict__ seq_ids,
+                              const int64_t* __restrict__ beam_idx, int batch) {
+  const int MP = p.max_pages_per_seq;
+  int32_t* tmp_rows = p.table_tmp;                         // [batch][MP + 1] (last = page count)
+  int32_t* tmp_len = p.table_tmp + (size_t)p.max_seqs * (MP + 4);  // [n_layers][batch]
+  __shared__ int bad;
+  if (threadIdx.x == 0) bad = 0;
+  __syncthreads();
+  for (int i = threadIdx.x; i < batch; i += blockDim.x) {
+    const long long j = beam_idx[i];
+    const int dst = seq_ids[i];
+    if (j < 0 || j >= batch || dst < 0 || dst >= p.max_seqs) bad = 1;
+    else {
+      const int src = seq_ids[j];
+      if (src < 0 || src >= p.max_seqs) bad = 1;
+    }
+  }
+  __syncthreads();
+  if (bad) {
+    if (threadIdx.x == 0) raise_status(p.status, PACE_DEV_BAD_INDEX);
+    return;
+  }
+  for (int i = 0; i < batch; ++i) {
+    const int src = seq_ids[beam_idx[i]];
+    const int have = p.seq_pages[src];
+    for (int lp = threadIdx.x; lp < MP; lp += blockDim.x)
+      tmp_rows[(size_t)i * (MP + 1) + lp] = lp < have ? p.block_table[(size_t)src * MP + lp] : -1;
+    if (threadIdx.x == 0) tmp_rows[(size_t)i * (MP + 1) + MP] = have;
+    for (int l = threadIdx.x; l < p.n_layers; l += blockDim.x)
+      tmp_len[(size_t)l * batch + i] = p.seq_len[(size_t)l * p.max_seqs + src];
+  }
+  __syncthreads();
+  for (int i = 0; i < batch; ++i) {
+    const int have = tmp_rows[(size_t)i * (MP + 1) + MP];
+    for (int lp = threadIdx.x; lp < have; lp += blockDim.x) {
+      const int pg = tmp_rows[(size_t)i * (MP + 1) + lp];
+      if (pg >= 0 && pg < p.n_pages) atomicAdd(&p.page_ref[pg], 1);
+    }
+  }
+  __syncthreads();
+  for (int i = 0; i < batch; ++i) {
+    const int dst = seq_ids[i];
+    const int have = p.seq_pages[dst];
+    for (int lp = threadIdx.x; lp < have; lp += blockDim.x) unref_page(p, p.block_table[(size_t)dst * MP + lp]);
+  }
+  __syncthreads();
+  for (int i = 0; i < batch; ++i) {
+    const int dst = seq_ids[i];
+    for (int lp = threadIdx.x; lp < MP; lp += blockDim.x)
+      p.block_table[(size_t)dst * MP + lp] = tmp_rows[(size_t)i * (MP + 1) + lp];
+    if (threadIdx.x == 0) p.seq_pages[dst] = tmp_rows[(size_t)i * (MP + 1) + MP];
+    for (int l = threadIdx.x; l < p.n_layers; l += blockDim.x)
+      p.seq_len[(size_t)l * p.max_seqs + dst] = tmp_len[(size_t)l * batch + i];
+  }
+}
+
+// Dense read-back: one 16-byte vector per thread.
+__global__ void read_dense_kernel(pace_kv_pool_t p, int layer, const int32_t* __restrict__ seq_ids, int batch,
+                                  uint4* __restrict__ k_out, uint4* __restrict__ v_out, int cap) {
+  const int P = p.page_tokens, D = p.head_dim, H = p.n_kv_heads;
+  const int vpr = D / 8;
+  const size_t total = (size_t)batch * H * cap * vpr;
+  const size_t page_elems = (size_t)H * P * D;
+  const size_t region = page_elems * (size_t)p.n_pages;
+  const uint4* kbase = reinterpret_cast<const uint4*>(reinterpret_cast<__nv_bfloat16*>(p.pages) +
+                                                      ((size_t)layer * 2) * region);
+  const uint4* vbase = kbase + region / 8;
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    const int c = (int)(i % vpr);
+    const int t = (int)((i / vpr) % cap);
+    const int h = (int)((i / ((size_t)vpr * cap)) % H);
+    const int b = (int)(i / ((size_t)vpr * cap * H));
+    uint4 kv = make_uint4(0, 0, 0, 0), vv = kv;
+    const int slot = seq_ids[b];
+    if (slot >= 0 && slot < p.max_seqs) {
+      const int lp = t / P;
+      if (lp < p.seq_pages[slot] && lp < p.max_pages_per_seq) {
+        const int pg = p.block_table[(size_t)slot * p.max_pages_per_seq + lp];
+        if (pg >= 0 && pg < p.n_pages) {
+          const size_t off = ((((size_t)pg * H + h) * P + (t - lp * P)) * D) / 8 + c;
+          kv = kbase[off];
+          vv = vbase[off];
+        }
+      }
+    }
+    k_out[i] = kv;
+    v_out[i] = vv;
+  }
+}
+
+bool pool_ok(const pace_kv_pool_t* p) {
+  return geometry_ok(p) && p->pages && p->block_table && p->seq_len && p->seq_pages && p->page_ref &&
+         p->free_stack && p->counters && p->status && p->table_tmp;
+}
+
+}  // namespace
+}  // namespace pace
+
+using namespace pace;
+
+extern "C" {
+
+const char* pace_last_cuda_error(void) { return g_err; }
+const char* pace_version(void) { return "pace_b200 0.1 (sm_100a)"; }
+
+int pace_kv_pool_bytes(const pace_kv_pool_t* g, uint64_t* pages_bytes, uint64_t* meta_bytes) {
+  if (!geometry_ok(g) || !pages_bytes || !meta_bytes) return PACE_ERR_INVALID;
+  *pages_bytes = (uint64_t)g->n_layers * 2 * g->n_pages * g->n_kv_heads * g->page_tokens * g->head_dim * 2;
+  *meta_bytes = meta_layout(g).total;
+  return PACE_OK;
+}
+
+int pace_kv_pool_bind(pace_kv_pool_t* p, void* pages_mem, void* meta_mem) {
+  if (!geometry_ok(p) || !pages_mem || !meta_mem) return PACE_ERR_INVALID;
+  if (((uintptr_t)pages_mem & 255) || ((uintptr_t)meta_mem & 255)) return PACE_ERR_INVALID;
+  const MetaLayout m = meta_layout(p);
+  char* b = static_cast<char*>(meta_mem);
+  p->pages = pages_mem;
+  p->block_table = reinterpret_cast<int32_t*>(b + m.block_table);
+  p->seq_len = reinterpret_cast<int32_t*>(b + m.seq_len);
+  p->seq_pages = reinterpret_cast<int32_t*>(b + m.seq_pages);
+  p->page_ref = reinterpret_cast<int32_t*>(b + m.page_ref);
+  p->free_stack = reinterpret_cast<int32_t*>(b + m.free_stack);
+  p->counters = reinterpret_cast<int32_t*>(b + m.counters);
+  p->status = reinterpret_cast<int32_t*>(b + m.status);
+  p->table_tmp = reinterpret_cast<int32_t*>(b + m.table_tmp);
+  p->owns_memory = 0;
+  return PACE_OK;
+}
+
+int pace_kv_pool_create(pace_kv_pool_t* p) {
+  uint64_t pb = 0, mb = 0;
+  if (pace_kv_pool_bytes(p, &pb, &mb) != PACE_OK) return PACE_ERR_INVALID;
+  void *pages = nullptr, *meta = nullptr;
+  PACE_CUDA_TRY(cudaMalloc(&pages, pb));
+  cudaError_t e = cudaMalloc(&meta, mb);
+  if (e != cudaSuccess) {
+    cudaFree(pages);
+    set_cuda_error(e, "cudaMalloc(meta)");
+    return PACE_ERR_CUDA;
+  }
+  pace_kv_pool_bind(p, pages, meta);
+  p->owns_memory = 1;
+  return pace_kv_pool_reset(p, nullptr);
+}
+
+int pace_kv_pool_destroy(pace_kv_pool_t* p) {
+  if (!p) return PACE_ERR_INVALID;
+  if (p->owns_memory) {
+    PACE_CUDA_TRY(cudaFree(p->pages));
+    PACE_CUDA_TRY(cudaFree(p->block_table));  // first array of the meta block
+  }
+  p->pages = nullptr;
+  p->block_table = p->seq_len = p->seq_pages = p->page_ref = p->free_stack = nullptr;
+  p->counters = p->status = p->table_tmp = nullptr;
+  p->owns_memory = 0;
+  return PACE_OK;
+}
+
+int pace_kv_pool_reset(const pace_kv_pool_t* p, void* stream) {
+  if (!pool_ok(p)) return PACE_ERR_INVALID;
+  reset_kernel<<<148, 256, 0, (cudaStream_t)stream>>>(*p);
+  PACE_LAUNCH_CHECK("reset_kernel");
+  return PACE_OK;
+}
+
+int pace_kv_pool_query(const pace_kv_pool_t* p, int32_t out[4], void* stream) {
+  if (!pool_ok(p) || !out) return PACE_ERR_INVALID;
+  cudaStream_t s = (cudaStream_t)stream;
+  int32_t st = 0, fr = 0;
+  PACE_CUDA_TRY(cudaMemcpyAsync(&st, p->status, sizeof(int32_t), cudaMemcpyDeviceToHost, s));
+  PACE_CUDA_TRY(cudaMemcpyAsync(&fr, p->counters, sizeof(int32_t), cudaMemcpyDeviceToHost, s));
+  PACE_CUDA_TRY(cudaStreamSynchronize(s));
+  out[0] = st;
+  out[1] = fr;
+  out[2] = out[3] = 0;
+  return PACE_OK;
+}
+
+int pace_kv_pool_clear_status(const pace_kv_pool_t* p, void* stream) {
+  if (!pool_ok(p)) return PACE_ERR_INVALID;
+  PACE_CUDA_TRY(cudaMemsetAsync(p->status, 0, 4 * sizeof(int32_t), (cudaStream_t)stream));
+  return PACE_OK;
+}
+
+int pace_kv_seq_release(const pace_kv_pool_t* p, const int32_t* seq_ids, int32_t batch, void* stream) {
+  if (!pool_ok(p) || !seq_ids || batch < 0) return PACE_ERR_INVALID;
+  if (batch == 0) return PACE_OK;
+  release_kernel<<<batch < 148 ? batch : 148, 128, 0, (cudaStream_t)stream>>>(*p, seq_ids, batch);
+  PACE_LAUNCH_CHECK("release_kernel");
+  return PACE_OK;
+}
+
+int pace_kv_reserve(const pace_kv_pool_t* p, int32_t layer, const int32_t* seq_ids, int32_t batch, int32_t n_new,
+                    const int32_t* n_per, void* stream) {
+  if (!pool_ok(p) || !seq_ids || batch < 0 || batch > p->max_seqs || n_new < 0 || layer < 0 ||
+      layer >= p->n_layers)
+    return PACE_ERR_INVALID;
+  if (batch == 0 || n_new == 0) return PACE_OK;
+  reserve_kernel<<<1, 256, 0, (cudaStream_t)stream>>>(*p, layer, seq_ids, batch, n_new, n_per);
+  PACE_LAUNCH_CHECK("reserve_kernel");
+  return PACE_OK;
+}
+
+int pace_kv_append(const pace_kv_pool_t* p, int32_t layer, const int32_t* seq_ids, int32_t batch, int32_t n_new,
+                   const int32_t* n_per, const void* k_new, const void* v_new, int64_t sb, int64_t sh, int64_t st,
+                   void* stream) {
+  if (!pool_ok(p) || !seq_ids || batch < 0 || batch > p->max_seqs || n_new < 0 || layer < 0 ||
+      layer >= p->n_layers)
+    return PACE_ERR_INVALID;
+  if (batch == 0 || n_new == 0) return PACE_OK;
+  if (!k_new || !v_new) return PACE_ERR_INVALID;
+  // 16-byte vector moves: bases and strides must keep rows 16-byte aligned
+  if (((uintptr_t)k_new & 15) || ((uintptr_t)v_new & 15) || (sb & 7) || (sh & 7) || (st & 7)) return PACE_ERR_INVALID;
+  const long long warps = (long long)batch * n_new * p->n_kv_heads;
+  long long blocks = (warps + 7) / 8;
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  append_kernel<<<(int)blocks, 256, 0, (cudaStream_t)stream>>>(
+      *p, layer, seq_ids, batch, n_new, n_per, (const __nv_bfloat16*)k_new, (const __nv_bfloat16*)v_new, sb, sh, st);
+  PACE_LAUNCH_CHECK("append_kernel");
+  return PACE_OK;
+}
+
+int pace_kv_truncate(const pace_kv_pool_t* p, int32_t layer_begin, int32_t layer_end, const int32_t* seq_ids,
+                     int32_t batch, int32_t remove_len, const int32_t* remove_per, void* stream) {
+  if (!pool_ok(p) || !seq_ids || batch < 0 || layer_begin < 0 || layer_end > p->n_layers ||
+      layer_begin > layer_end || (!remove_per && remove_len < 0))
+    return PACE_ERR_INVALID;
+  const int n = batch * (layer_end - layer_begin);
+  if (n == 0) return PACE_OK;
+  truncate_kernel<<<(n + 255) / 256, 256, 0, (cudaStream_t)stream>>>(*p, layer_begin, layer_end, seq_ids, batch,
+                                                                    remove_len, remove_per);
+  PACE_LAUNCH_CHECK("truncate_kernel");
+  return PACE_OK;
+}
+
+int pace_kv_gather(const pace_kv_pool_t* p, const int32_t* seq_ids, const int64_t* beam_idx, int32_t batch,
+                   void* stream) {
+  if (!pool_ok(p) || !seq_ids || !beam_idx || batch < 0 || batch > p->max_seqs) return PACE_ERR_INVALID;
+  if (batch == 0) return PACE_OK;
+  gather_kernel<<<1, 256, 0, (cudaStream_t)stream>>>(*p, seq_ids, beam_idx, batch);
+  PACE_LAUNCH_CHECK("gather_kernel");
+  return PACE_OK;
+}
+
+int pace_kv_read_dense(const pace_kv_pool_t* p, int32_t layer, const int32_t* seq_ids, int32_t batch, void* k_out,
+                       void* v_out, int32_t cap, void* stream) {
+  if (!pool_ok(p) || !seq_ids || batch < 0 || cap < 0 || layer < 0 || layer >= p->n_layers) return PACE_ERR_INVALID;
+  if (batch == 0 || cap == 0) return PACE_OK;
+  if (!k_out || !v_out || ((uintptr_t)k_out & 15) || ((uintptr_t)v_out & 15)) return PACE_ERR_INVALID;
+  const size_t total = (size_t)batch * p->n_kv_heads * cap * (p->head_dim / 8);
+  size_t blocks = (total + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  read_dense_kernel<<<(int)blocks, 256, 0, (cudaStream_t)stream>>>(*p, layer, seq_ids, batch, (uint4*)k_out,
+                                                                  (uint4*)v_out, cap);
+  PACE_LAUNCH_CHECK("read_dense_kernel");
+  return PACE_OK;
+}
+
+}  // extern "C"

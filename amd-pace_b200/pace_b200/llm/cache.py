@@ -1,0 +1,537 @@
+"""KV-cache manager and per-layer cache objects on a device-resident paged pool.
+
+Drop-in for the reference's pace/llm/cache.py (same class and method names, same
+argument meaning, same errors):
+
+    KVCacheType, get_kv_cache_class            cache.py:18-45
+    KVCacheManager                             cache.py:48-123
+    BMCKVCache / DynamicKVCache                cache.py:170-400
+
+What differs underneath: K/V live in one paged pool per manager
+(``[layer][K|V][page][kv_head][page_tokens][head_dim]`` bf16 in HBM) with the block
+table, lengths and free list in device memory; append / rollback / beam gather are
+CUDA kernels (csrc/kv_pool.cu) and the latter two move no K/V bytes.  The page
+size equals the reference's ``tokens_per_split`` so ``capacity`` follows the BMC
+growth trace exactly.  ``update_cache`` returns handles (``PagedKV``) instead of
+dense tensors; ``MultiHeadAttention`` consumes them directly.  The host keeps
+integer mirrors of lengths and capacities because the reference API is
+synchronous about them (``len(manager)``, ``ValueError`` on over-removal).
+
+Extensions the reference does not have (its batch shares one length): ragged
+per-sequence appends and rollbacks (``n_new_per_seq=``, list-valued
+``remove_cache``) and a shared long-lived pool (``pool=``).
+"""
+import ctypes as C
+import math
+import os
+from abc import ABC, abstractmethod
+from enum import Enum
+from typing import List, Optional, Sequence, Tuple, Union
+
+import torch
+
+from pace_b200 import _C
+
+OVER_REMOVE_MSG = "Cannot remove more tokens than available in cache."
+DYNAMIC_PAGE_TOKENS = 64
+
+
+class KVCacheType(Enum):
+    """Cache policies, as in the reference (cache.py:18-33)."""
+
+    DYNAMIC = "dynamic"
+    BMC = "bmc"
+
+    @staticmethod
+    def get_kv_cache_type(cache_type: Union[str, "KVCacheType"]) -> "KVCacheType":
+        if isinstance(cache_type, str):
+            return KVCacheType(cache_type)
+        return cache_type
+
+
+def get_kv_cache_class(cache_type: Union[str, KVCacheType]):
+    cache_type = KVCacheType.get_kv_cache_type(cache_type)
+    if cache_type == KVCacheType.DYNAMIC:
+        return DynamicKVCache
+    if cache_type == KVCacheType.BMC:
+        return BMCKVCache
+    raise ValueError(f"Invalid cache type: {cache_type}")
+
+
+def bmc_tokens_per_split(max_seq_length: int) -> int:
+    """Segment size of the BMC policy; honours PACE_BMC_NUM_SPLITS (cache.py:177-181)."""
+    num_splits = int(os.getenv("PACE_BMC_NUM_SPLITS", int(math.sqrt(max_seq_length))))
+    return max_seq_length // num_splits
+
+
+def _stream_ptr(device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+class KVPool:
+    """Device memory + descriptor of one paged pool (C struct pace_kv_pool_t)."""
+
+    def __init__(self, n_layers: int, n_kv_heads: int, head_dim: int, page_tokens: int, n_pages: int,
+                 max_seqs: int, max_pages_per_seq: int, device):
+        device = torch.device(device)
+        if device.type != "cuda":
+            raise RuntimeError("pace_b200 KV pools live in CUDA memory; got device " + str(device))
+        self.device = device
+        self.desc = _C.KVPoolStruct(n_layers=n_layers, n_kv_heads=n_kv_heads, head_dim=head_dim,
+                                    page_tokens=page_tokens, n_pages=n_pages, max_seqs=max_seqs,
+                                    max_pages_per_seq=max_pages_per_seq)
+        pb, mb = C.c_uint64(), C.c_uint64()
+        _C.check(_C.lib.pace_kv_pool_bytes(C.byref(self.desc), C.byref(pb), C.byref(mb)), "pace_kv_pool_bytes")
+        # zero-filled like the reference's fresh segments (cache.py:255-256)
+        self.pages = torch.zeros(pb.value, dtype=torch.uint8, device=device)
+        self.meta = torch.zeros(mb.value, dtype=torch.uint8, device=device)
+        _C.check(_C.lib.pace_kv_pool_bind(C.byref(self.desc), self.pages.data_ptr(), self.meta.data_ptr()),
+                 "pace_kv_pool_bind")
+        with torch.cuda.device(device):
+            _C.check(_C.lib.pace_kv_pool_reset(C.byref(self.desc), _stream_ptr(device)), "pace_kv_pool_reset")
+        self.n_layers, self.n_kv_heads, self.head_dim = n_layers, n_kv_heads, head_dim
+        self.page_tokens, self.n_pages = page_tokens, n_pages
+        self.max_seqs, self.max_pages_per_seq = max_seqs, max_pages_per_seq
+        self._free_slots = list(range(max_seqs - 1, -1, -1))
+        self.host_pages = [0] * max_seqs          # host mirror of seq_pages (admission control)
+        self.host_free_pages = n_pages
+        self.shared_pages = False                 # set by a beam gather: appends may copy-on-write
+
+    @property
+    def ref(self):
+        return C.byref(self.desc)
+
+    # -- slots -------------------------------------------------------------
+    def alloc_slots(self, n: int) -> List[int]:
+        if n > len(self._free_slots):
+            raise RuntimeError(f"KV pool has {len(self._free_slots)} free sequence slots, {n} requested")
+        return [self._free_slots.pop() for _ in range(n)]
+
+    def release_slots(self, slots: Sequence[int], slots_dev: Optional[torch.Tensor] = None) -> None:
+        if not slots:
+            return
+        if slots_dev is None:
+            slots_dev = torch.tensor(list(slots), dtype=torch.int32, device=self.device)
+        with torch.cuda.device(self.device):
+            _C.check(_C.lib.pace_kv_seq_release(self.ref, slots_dev.data_ptr(), len(slots), _stream_ptr(self.device)),
+                     "pace_kv_seq_release")
+        for s in slots:
+            if not self.shared_pages:
+                self.host_free_pages += self.host_pages[s]
+            self.host_pages[s] = 0
+            self._free_slots.append(s)
+
+    # -- status ------------------------------------------------------------
+    def query(self) -> Tuple[int, int]:
+        """(sticky status bits, free pages); synchronises the current stream."""
+        out = (C.c_int32 * 4)()
+        with torch.cuda.device(self.device):
+            _C.check(_C.lib.pace_kv_pool_query(self.ref, C.byref(out), _stream_ptr(self.device)), "pace_kv_pool_query")
+        return int(out[0]), int(out[1])
+
+    def check_status(self) -> None:
+        bits, _ = self.query()
+        if bits:
+            raise _C.PaceError("KV pool device status: " + _C.describe_status(bits))
+
+    def clear_status(self) -> None:
+        with torch.cuda.device(self.device):
+            _C.check(_C.lib.pace_kv_pool_clear_status(self.ref, _stream_ptr(self.device)), "pace_kv_pool_clear_status")
+
+    # raw views for tests / debugging (device tensors, no copies)
+    def _meta_view(self, ptr: int, n: int) -> torch.Tensor:
+        off = ptr - self.meta.data_ptr()
+        return self.meta[off: off + 4 * n].view(torch.int32)
+
+    def block_table(self) -> torch.Tensor:
+        return self._meta_view(self.desc.block_table, self.max_seqs * self.max_pages_per_seq).view(
+            self.max_seqs, self.max_pages_per_seq)
+
+    def seq_len(self) -> torch.Tensor:
+        return self._meta_view(self.desc.seq_len, self.n_layers * self.max_seqs).view(self.n_layers, self.max_seqs)
+
+    def seq_pages(self) -> torch.Tensor:
+        return self._meta_view(self.desc.seq_pages, self.max_seqs)
+
+    def page_ref(self) -> torch.Tensor:
+        return self._meta_view(self.desc.page_ref, self.n_pages)
+
+
+class PagedKV:
+    """What ``update_cache`` returns for K (or V): a view of one layer of the pool.
+
+    Quacks like the dense ``[B, H, capacity, D]`` tensor the reference returns
+    (cache.py:326) as far as shape queries go; ``dense()`` materialises it.
+    """
+
+    def __init__(self, cache: "KVCacheBase", which: str):
+        self.cache = cache
+        self.which = which
+
+    @property
+    def shape(self) -> torch.Size:
+        return self.cache._reported_shape()
+
+    def size(self, dim: Optional[int] = None):
+        return self.shape if dim is None else self.shape[dim]
+
+    def dim(self) -> int:
+        return len(self.shape)
+
+    @property
+    def dtype(self):
+        return torch.bfloat16
+
+    @property
+    def device(self):
+        return self.cache.pool.device
+
+    def contiguous(self):
+        return self
+
+    def dense(self) -> torch.Tensor:
+        k, v = self.cache.read_dense()
+        return k if self.which == "k" else v
+
+    def __repr__(self):
+        return f"PagedKV({self.which}, layer={self.cache.layer}, shape={tuple(self.shape)})"
+
+
+class KVCacheManager:
+    """One cache object per layer over a shared pool (reference: cache.py:48-123)."""
+
+    def __init__(self, config, max_seq_length: int, cache_type: KVCacheType, pool: Optional[KVPool] = None,
+                 extra_tokens: int = 0):
+        self.num_layers = config.num_hidden_layers
+        self.cache_type = KVCacheType.get_kv_cache_type(cache_type)
+        self.kv_cache_class = get_kv_cache_class(self.cache_type)
+        self.max_seq_length = max_seq_length
+        self.extra_tokens = extra_tokens
+        self.pool: Optional[KVPool] = pool
+        self._owns_pool = pool is None
+        self.slots: Optional[List[int]] = None
+        self.slots_dev: Optional[torch.Tensor] = None
+        self.cache_objects: List[KVCacheBase] = [
+            self.kv_cache_class(max_seq_length, manager=self, layer=i) for i in range(self.num_layers)
+        ]
+
+    # -- pool creation on first use (shapes are only known then) -----------------
+    def _ensure_pool(self, batch: int, n_kv_heads: int, head_dim: int, device) -> None:
+        if self.slots is not None:
+            return
+        page_tokens = self.cache_objects[0].page_tokens
+        if self.pool is None:
+            # capacity can exceed max_seq_length by up to one segment (cache.py:300-313), PARD adds drafts
+            max_tokens = self.max_seq_length + self.extra_tokens + 2 * page_tokens
+            max_pages = (max_tokens + page_tokens - 1) // page_tokens + 1
+            self.pool = KVPool(self.num_layers, n_kv_heads, head_dim, page_tokens, n_pages=batch * max_pages + batch,
+                               max_seqs=batch, max_pages_per_seq=max_pages, device=device)
+        else:
+            p = self.pool
+            if (p.n_layers, p.n_kv_heads, p.head_dim, p.page_tokens) != (self.num_layers, n_kv_heads, head_dim,
+                                                                        page_tokens):
+                raise ValueError("shared KV pool geometry does not match this manager")
+        self.slots = self.pool.alloc_slots(batch)
+        self.slots_dev = torch.tensor(self.slots, dtype=torch.int32, device=self.pool.device)
+
+    def __len__(self) -> int:
+        return int(self.cache_objects[0].seq_len)
+
+    def __getitem__(self, idx: int) -> "KVCacheBase":
+        return self.cache_objects[idx]
+
+    def update_mask(self, attn_mask: torch.Tensor, input_size: int) -> torch.Tensor:
+        return self.cache_objects[0].update_mask(attn_mask, input_size)
+
+    def update_cache_with_beam_indices(self, beam_idx: torch.Tensor) -> None:
+        """Beam gather (cache.py:106-116): ONE index-only kernel for all layers."""
+        if self.slots is None:
+            return
+        pool = self.pool
+        idx = beam_idx.to(device=pool.device, dtype=torch.int64).contiguous()
+        if idx.numel() != len(self.slots):
+            raise ValueError("beam_idx must have one entry per cached sequence")
+        with torch.cuda.device(pool.device):
+            _C.check(_C.lib.pace_kv_gather(pool.ref, self.slots_dev.data_ptr(), idx.data_ptr(), len(self.slots),
+                                           _stream_ptr(pool.device)), "pace_kv_gather")
+        pool.shared_pages = True
+        order = beam_idx.tolist()
+        pages = [pool.host_pages[self.slots[j]] for j in order]
+        for i, s in enumerate(self.slots):
+            pool.host_pages[s] = pages[i]
+        for c in self.cache_objects:
+            if c._lens:
+                c._lens = [c._lens[j] for j in order]
+
+    def remove_cache(self, remove_len) -> None:
+        """Rollback on every layer (cache.py:118-123): one kernel, no K/V bytes moved."""
+        live = [c for c in self.cache_objects if c.key is not None]
+        if not live:
+            return
+        per_seq = live[0]._normalise_remove(remove_len)
+        for c in live:
+            c._check_remove(per_seq)
+        pool = self.pool
+        if len(live) == self.num_layers:
+            scalar, dev = live[0]._remove_args(per_seq)
+            with torch.cuda.device(pool.device):
+                _C.check(_C.lib.pace_kv_truncate(pool.ref, 0, self.num_layers, self.slots_dev.data_ptr(),
+                                                 len(self.slots), scalar, dev, _stream_ptr(pool.device)),
+                         "pace_kv_truncate")
+            for c in live:
+                c._apply_remove(per_seq)
+        else:
+            for c in live:
+                c.remove_cache(remove_len)
+
+    def release(self) -> None:
+        if self.pool is not None and self.slots is not None:
+            if not self._owns_pool:
+                self.pool.release_slots(self.slots, self.slots_dev)
+            self.slots = None
+            self.slots_dev = None
+        if self._owns_pool:
+            self.pool = None
+
+    def __del__(self):
+        try:
+            self.release()
+        except Exception:
+            pass
+
+
+class KVCacheBase(ABC):
+    """Common machinery of the two policies (reference: cache.py:126-167)."""
+
+    policy_page_tokens: int
+
+    def __init__(self, max_seq_length: int, manager: Optional[KVCacheManager] = None, layer: int = 0):
+        if manager is None:  # a free-standing layer cache, as the reference's tests build them
+            class _Cfg:
+                num_hidden_layers = 1
+            manager = KVCacheManager.__new__(KVCacheManager)
+            manager.num_layers, manager.cache_type = 1, None
+            manager.max_seq_length, manager.extra_tokens = max_seq_length, 0
+            manager.pool, manager._owns_pool, manager.slots, manager.slots_dev = None, True, None, None
+            manager.cache_objects = [self]
+        self.manager = manager
+        self.layer = layer
+        self.key: Optional[PagedKV] = None
+        self.value: Optional[PagedKV] = None
+        self.concat_dim: Optional[int] = None
+        self._lens: List[int] = []        # host mirror, one entry per batch row
+        self._capacity = 0                # tokens, as the reference's buffer size along concat_dim
+        self._ndim = 4
+
+    # -- reference attributes --------------------------------------------------
+    @property
+    def pool(self) -> KVPool:
+        return self.manager.pool
+
+    @property
+    def seq_len(self) -> int:
+        if not self._lens:
+            return 0
+        return self._lens[0] if len(set(self._lens)) == 1 else max(self._lens)
+
+    @property
+    def seq_lens(self) -> List[int]:
+        return list(self._lens)
+
+    @property
+    def capacity(self) -> int:
+        return self._capacity
+
+    @abstractmethod
+    def _capacity_after(self, updated: int) -> int:
+        ...
+
+    def _reported_shape(self) -> torch.Size:
+        b, h, d = len(self._lens), self.pool.n_kv_heads, self.pool.head_dim
+        if self._ndim == 3:
+            return torch.Size((b, self._capacity, d))
+        return torch.Size((b, h, self._capacity, d))
+
+    def update_mask(self, attn_mask: torch.Tensor, input_size: int) -> torch.Tensor:
+        return attn_mask
+
+    # -- append ------------------------------------------------------------------
+    def update_cache(self, key_states: torch.Tensor, value_states: torch.Tensor, concat_dim: int,
+                     n_new_per_seq: Optional[Sequence[int]] = None) -> Tuple[PagedKV, PagedKV]:
+        """Append ``[B, H, n, D]`` new keys/values (cache.py:268-326 / 370-400)."""
+        if self.concat_dim is None:
+            self.concat_dim = concat_dim
+        elif self.concat_dim != concat_dim:
+            raise AssertionError("concat_dim should be the same for all updates")
+        if key_states.device.type != "cuda":
+            raise RuntimeError("pace_b200 caches take CUDA tensors (there is no CPU path)")
+        if key_states.dtype != torch.bfloat16 or value_states.dtype != torch.bfloat16:
+            raise TypeError("pace_b200 caches hold bf16 keys/values")
+        if key_states.shape != value_states.shape:
+            raise ValueError("key_states and value_states must have the same shape")
+        if key_states.dim() == 3 and concat_dim == 1:      # [B, n, D]: one KV head
+            self._ndim = 3
+            key_states, value_states = key_states.unsqueeze(1), value_states.unsqueeze(1)
+        elif key_states.dim() == 4 and concat_dim == 2:
+            self._ndim = 4
+        else:
+            raise ValueError("expected [B, H, n, D] with concat_dim=2 (or [B, n, D] with concat_dim=1)")
+        B, H, n, D = key_states.shape
+        mgr = self.manager
+        mgr._ensure_pool(B, H, D, key_states.device)
+        pool = self.pool
+        if (H, D) != (pool.n_kv_heads, pool.head_dim) or B != len(mgr.slots):
+            raise ValueError(f"update_cache got [B={B},H={H},D={D}], the cache holds "
+                             f"[B={len(mgr.slots)},H={pool.n_kv_heads},D={pool.head_dim}]")
+        if key_states.stride(3) != 1 or value_states.stride(3) != 1 or key_states.stride() != value_states.stride():
+            key_states, value_states = key_states.contiguous(), value_states.contiguous()
+        if any(s % 8 for s in key_states.stride()[:3]) or key_states.data_ptr() % 16 or value_states.data_ptr() % 16:
+            key_states, value_states = key_states.contiguous().clone(), value_states.contiguous().clone()
+        if not self._lens:
+            self._lens = [0] * B
+        counts = [n] * B if n_new_per_seq is None else [int(x) for x in n_new_per_seq]
+        if len(counts) != B or any(c < 0 or c > n for c in counts):
+            raise ValueError("n_new_per_seq must hold B counts in [0, n]")
+        n_dev = None
+        if n_new_per_seq is not None:
+            n_dev = torch.tensor(counts, dtype=torch.int32, device=pool.device)
+        # host mirror: pages (shared by all layers) and capacity
+        P = pool.page_tokens
+        grow = False
+        for b, slot in enumerate(mgr.slots):
+            need = (self._lens[b] + counts[b] + P - 1) // P
+            if need > pool.max_pages_per_seq:
+                raise RuntimeError(f"sequence needs {need} pages, the pool's table rows hold {pool.max_pages_per_seq}")
+            if need > pool.host_pages[slot]:
+                pool.host_free_pages -= need - pool.host_pages[slot]
+                pool.host_pages[slot] = need
+                grow = True
+        if pool.host_free_pages < 0 and not pool.shared_pages:
+            raise RuntimeError("KV pool exhausted")
+        sp = _stream_ptr(pool.device)
+        nptr = n_dev.data_ptr() if n_dev is not None else None
+        with torch.cuda.device(pool.device):
+            # after a beam gather pages may be shared: the first layer's reserve un-shares (copies on
+            # write) whatever this append is about to write into, for all layers at once
+            if grow or (pool.shared_pages and self.layer == 0):
+                _C.check(_C.lib.pace_kv_reserve(pool.ref, self.layer, mgr.slots_dev.data_ptr(), B, n, nptr, sp),
+                         "pace_kv_reserve")
+            sb, sh, st, _ = key_states.stride()
+            _C.check(_C.lib.pace_kv_append(pool.ref, self.layer, mgr.slots_dev.data_ptr(), B, n, nptr,
+                                           key_states.data_ptr(), value_states.data_ptr(), sb, sh, st, sp),
+                     "pace_kv_append")
+        for b in range(B):
+            self._lens[b] += counts[b]
+        self._capacity = self._capacity_after(max(self._lens))
+        if self.key is None:
+            self.key, self.value = PagedKV(self, "k"), PagedKV(self, "v")
+        return self.key, self.value
+
+    # -- rollback ----------------------------------------------------------------
+    def _normalise_remove(self, remove_len) -> List[int]:
+        if isinstance(remove_len, torch.Tensor):
+            remove_len = remove_len.tolist()
+        if isinstance(remove_len, (list, tuple)):
+            out = [int(x) for x in remove_len]
+            if len(out) != len(self._lens):
+                raise ValueError("per-sequence remove lengths must match the batch")
+            return out
+        return [int(remove_len)] * len(self._lens)
+
+    def _check_remove(self, per_seq: List[int]) -> None:
+        for r, have in zip(per_seq, self._lens):
+            if r > have:
+                raise ValueError(OVER_REMOVE_MSG)
+            if r < 0:
+                raise ValueError("remove_len must be non-negative")
+
+    def _remove_args(self, per_seq: List[int]):
+        if len(set(per_seq)) <= 1:
+            return (per_seq[0] if per_seq else 0), None
+        dev = torch.tensor(per_seq, dtype=torch.int32, device=self.pool.device)
+        self._keepalive = dev
+        return 0, dev.data_ptr()
+
+    def _apply_remove(self, per_seq: List[int]) -> None:
+        self._lens = [have - r for have, r in zip(self._lens, per_seq)]
+        self._after_remove()
+
+    def _after_remove(self) -> None:
+        pass
+
+    def remove_cache(self, remove_len) -> None:
+        """Forget the last tokens (cache.py:224-240 / 352-368): lengths only, pages kept."""
+        if self.key is None:
+            return  # silent no-op on an empty cache, as the reference
+        per_seq = self._normalise_remove(remove_len)
+        self._check_remove(per_seq)
+        pool, mgr = self.pool, self.manager
+        scalar, dev = self._remove_args(per_seq)
+        with torch.cuda.device(pool.device):
+            _C.check(_C.lib.pace_kv_truncate(pool.ref, self.layer, self.layer + 1, mgr.slots_dev.data_ptr(),
+                                             len(mgr.slots), scalar, dev, _stream_ptr(pool.device)),
+                     "pace_kv_truncate")
+        self._apply_remove(per_seq)
+
+    # -- gather --------------------------------------------------------------------
+    def update_cache_with_beam_indices(self, beam_idx: torch.Tensor) -> None:
+        """Per-layer form of the reference API (cache.py:161-167).  The block table is
+        shared by all layers, so the gather is done once by the manager; calling it
+        on a layer object directly is only valid for a free-standing single layer."""
+        if self.key is None:
+            return
+        if self.manager.num_layers != 1:
+            raise RuntimeError("beam gather permutes the table shared by all layers: call it on the manager")
+        self.manager.update_cache_with_beam_indices(beam_idx)
+
+    # -- read-back -------------------------------------------------------------------
+    def read_dense(self) -> Tuple[torch.Tensor, torch.Tensor]:
+        """Dense ``[B, H, capacity, D]`` K and V, i.e. what the reference's update_cache returns."""
+        pool, mgr = self.pool, self.manager
+        B, cap = len(self._lens), self._capacity
+        k = torch.empty(B, pool.n_kv_heads, cap, pool.head_dim, dtype=torch.bfloat16, device=pool.device)
+        v = torch.empty_like(k)
+        if cap:
+            with torch.cuda.device(pool.device):
+                _C.check(_C.lib.pace_kv_read_dense(pool.ref, self.layer, mgr.slots_dev.data_ptr(), B, k.data_ptr(),
+                                                   v.data_ptr(), cap, _stream_ptr(pool.device)), "pace_kv_read_dense")
+        if self._ndim == 3:
+            return k[:, 0], v[:, 0]
+        return k, v
+
+
+class BMCKVCache(KVCacheBase):
+    """Segmented growth: capacity rises in whole ``tokens_per_split`` steps (cache.py:170-326)."""
+
+    def __init__(self, max_seq_length: int, manager: Optional[KVCacheManager] = None, layer: int = 0):
+        super().__init__(max_seq_length, manager, layer)
+        self.tokens_per_split = bmc_tokens_per_split(max_seq_length)
+        self.page_tokens = self.tokens_per_split
+
+    def _capacity_after(self, updated: int) -> int:
+        # a fresh buffer is made when none exists or the new length reaches the capacity (cache.py:292-313)
+        if self._capacity == 0 or updated >= self._capacity:
+            return ((updated - 1) // self.tokens_per_split + 1) * self.tokens_per_split
+        return self._capacity
+
+    def update_mask(self, attn_mask: torch.Tensor, input_size: int) -> torch.Tensor:
+        """Pad the mask with finfo.min up to the capacity (cache.py:195-222)."""
+        segment_idx = (input_size - 1) // self.tokens_per_split
+        shape = list(attn_mask.shape)
+        shape[-1] = (segment_idx + 1) * self.tokens_per_split - input_size
+        pad = torch.full(shape, torch.finfo(attn_mask.dtype).min, dtype=attn_mask.dtype, device=attn_mask.device)
+        return torch.cat([attn_mask, pad], dim=-1)
+
+
+class DynamicKVCache(KVCacheBase):
+    """No padding: the reported buffer is exactly the cached length (cache.py:329-400)."""
+
+    def __init__(self, max_seq_length: int, manager: Optional[KVCacheManager] = None, layer: int = 0):
+        super().__init__(max_seq_length, manager, layer)
+        self.page_tokens = DYNAMIC_PAGE_TOKENS
+
+    def _capacity_after(self, updated: int) -> int:
+        return updated
+
+    def _after_remove(self) -> None:
+        self._capacity = max(self._lens) if self._lens else 0

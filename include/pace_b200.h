@@ -1,0 +1,176 @@
+/*
+ * pace_b200.h - C ABI of the B200 (sm_100a) KV-cache hot path.
+ *
+ * Every entry point takes plain pointers and sizes, returns an int status
+ * (PACE_OK == 0) and never throws.  Device pointers are marked "device";
+ * `stream` is a cudaStream_t passed as void*.  All work is stream-ordered: no
+ * call synchronises unless it says so.
+ *
+ * The library replaces, for CUDA callers, what the reference does on the CPU in
+ *   pace/llm/cache.py            (append, growth, rollback, beam gather)
+ *   csrc/ops/attention.cpp       (the pace::attention custom op)
+ *   csrc/ops/kernels/attention_kernels.cpp (the four-primitive SDPA sequence)
+ * Each declaration cites the reference interface it stands in for.
+ */
+#ifndef PACE_B200_H_
+#define PACE_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- return codes (host side) ------------------------------------------ */
+#define PACE_OK 0
+#define PACE_ERR_INVALID 1     /* an argument failed validation; nothing was launched */
+#define PACE_ERR_CUDA 2        /* the CUDA runtime reported an error (see pace_last_cuda_error) */
+#define PACE_ERR_UNSUPPORTED 3 /* valid request outside what the kernels are built for */
+
+/* ---- sticky device status bits (pool->status[0]) ----------------------- */
+#define PACE_DEV_POOL_EXHAUSTED 1 /* reserve: free list ran dry                    */
+#define PACE_DEV_OVER_REMOVE 2    /* truncate: remove_len > cached length          */
+#define PACE_DEV_BAD_INDEX 4      /* a sequence slot / page id was out of range    */
+#define PACE_DEV_TABLE_FULL 8     /* a sequence needs more pages than its table row*/
+#define PACE_DEV_WAIT_TIMEOUT 16  /* a bounded in-kernel wait gave up               */
+
+/*
+ * Paged KV pool descriptor.  Geometry + device pointers; plain data, copied by
+ * value into kernels.  Storage may come from pace_kv_pool_create() or from the
+ * caller (pace_kv_pool_bytes + pace_kv_pool_bind, e.g. a torch allocation).
+ *
+ *   pages        bf16 [n_layers][2 (K,V)][n_pages][n_kv_heads][page_tokens][head_dim]
+ *   block_table  int32 [max_seqs][max_pages_per_seq]  logical page -> physical page
+ *   seq_len      int32 [n_layers][max_seqs]  cached tokens, per layer
+ *                (the reference keeps one seq_len per layer object, cache.py:184)
+ *   seq_pages    int32 [max_seqs]   pages a slot owns; capacity = seq_pages*page_tokens
+ *   page_ref     int32 [n_pages]    reference counts (beam gather shares pages)
+ *   free_stack   int32 [n_pages]    free physical pages; counters[0] = number free
+ *   counters     int32 [8]          [0] free pages, [1..] kernel tickets
+ *   status       int32 [4]          [0] sticky PACE_DEV_* bits
+ *   table_tmp    int32 [max_seqs][max_pages_per_seq + 1]   scratch of pace_kv_gather
+ *
+ * page_tokens is the reference's `tokens_per_split` (cache.py:177-181) so that
+ * capacity = pages * page_tokens reproduces the BMC capacity trace exactly.
+ */
+typedef struct pace_kv_pool {
+  int32_t n_layers, n_kv_heads, head_dim, page_tokens;
+  int32_t n_pages, max_seqs, max_pages_per_seq, owns_memory;
+  void* pages;          /* device */
+  int32_t* block_table; /* device */
+  int32_t* seq_len;     /* device */
+  int32_t* seq_pages;   /* device */
+  int32_t* page_ref;    /* device */
+  int32_t* free_stack;  /* device */
+  int32_t* counters;    /* device */
+  int32_t* status;      /* device */
+  int32_t* table_tmp;   /* device */
+} pace_kv_pool_t;
+
+const char* pace_last_cuda_error(void);
+const char* pace_version(void);
+
+/* ---- pool lifetime ------------------------------------------------------
+ * Reference: BMCKVCache.__init__ / _create_new_segment allocate torch buffers
+ * (pace/llm/cache.py:175-193, 242-266); here one pool per model instance is
+ * carved into pages once and segments become block-table entries. */
+int pace_kv_pool_bytes(const pace_kv_pool_t* geom, uint64_t* pages_bytes, uint64_t* meta_bytes);
+int pace_kv_pool_bind(pace_kv_pool_t* pool, void* pages_mem, void* meta_mem); /* host-only pointer carving */
+int pace_kv_pool_create(pace_kv_pool_t* pool);  /* cudaMalloc for pages+meta of the filled-in geometry, then reset */
+int pace_kv_pool_destroy(pace_kv_pool_t* pool); /* frees what pace_kv_pool_create allocated */
+int pace_kv_pool_reset(const pace_kv_pool_t* pool, void* stream); /* all slots empty, all pages free */
+/* Synchronising read of {status bits, free pages, 0, 0}. */
+int pace_kv_pool_query(const pace_kv_pool_t* pool, int32_t out[4], void* stream);
+int pace_kv_pool_clear_status(const pace_kv_pool_t* pool, void* stream);
+
+/* Give back every page of the listed slots and zero their lengths (all layers).
+ * Reference: cache objects are dropped with the manager (generator.py:396-410). */
+int pace_kv_seq_release(const pace_kv_pool_t* pool, const int32_t* seq_ids /*device*/, int32_t batch, void* stream);
+
+/* ---- append -------------------------------------------------------------
+ * Reference: BMCKVCache.update_cache / DynamicKVCache.update_cache
+ * (pace/llm/cache.py:268-326, 370-400).
+ *
+ * pace_kv_reserve makes sure every listed slot owns ceil((seq_len[layer]+n)/page_tokens)
+ * pages (popping the free list; copy-on-write of a shared last page after a beam
+ * gather).  pace_kv_append copies n new K/V rows per sequence into the slots
+ * [seq_len, seq_len+n) and then advances seq_len[layer].  k_new / v_new are bf16
+ * [batch][n_kv_heads][n_new][head_dim] addressed through element strides (the last
+ * dimension is contiguous), so the transposed view a model produces needs no copy.
+ * n_new_per_seq (device, optional) gives ragged counts <= n_new. */
+int pace_kv_reserve(const pace_kv_pool_t* pool, int32_t layer, const int32_t* seq_ids, int32_t batch,
+                    int32_t n_new, const int32_t* n_new_per_seq, void* stream);
+int pace_kv_append(const pace_kv_pool_t* pool, int32_t layer, const int32_t* seq_ids, int32_t batch,
+                   int32_t n_new, const int32_t* n_new_per_seq, const void* k_new, const void* v_new,
+                   int64_t stride_b, int64_t stride_h, int64_t stride_t, void* stream);
+
+/* ---- rollback -------------------------------------------------------------
+ * Reference: BMCKVCache.remove_cache (cache.py:224-240): seq_len -= n, pages kept,
+ * data untouched.  Over-removal leaves the length alone and raises
+ * PACE_DEV_OVER_REMOVE.  layers [layer_begin, layer_end).  remove_per_seq (device,
+ * optional) overrides the scalar per sequence (PARD with per-sequence acceptance). */
+int pace_kv_truncate(const pace_kv_pool_t* pool, int32_t layer_begin, int32_t layer_end,
+                     const int32_t* seq_ids, int32_t batch, int32_t remove_len,
+                     const int32_t* remove_per_seq, void* stream);
+
+/* ---- beam gather ----------------------------------------------------------
+ * Reference: KVCacheBase.update_cache_with_beam_indices (cache.py:161-167):
+ * row i of the batch becomes a copy of old row beam_idx[i].  Index-only here: the
+ * block-table rows and lengths are permuted and page reference counts adjusted. */
+int pace_kv_gather(const pace_kv_pool_t* pool, const int32_t* seq_ids, const int64_t* beam_idx /*device*/,
+                   int32_t batch, void* stream);
+
+/* ---- cache read-back --------------------------------------------------------
+ * Materialises what the reference's update_cache returns (cache.py:326): dense
+ * bf16 [batch][n_kv_heads][cap_tokens][head_dim] K and V, rows beyond a slot's
+ * pages zero-filled. */
+int pace_kv_read_dense(const pace_kv_pool_t* pool, int32_t layer, const int32_t* seq_ids, int32_t batch,
+                       void* k_out, void* v_out, int32_t cap_tokens, void* stream);
+
+/* ---- attention --------------------------------------------------------------
+ * Reference: pace::attention (csrc/ops/attention.cpp:18-97, schema :104-108) and
+ * kernels::attention_kernel Method 1 (csrc/ops/kernels/attention_kernels.cpp:218-257):
+ * softmax(Q K^T / sqrt(D) + mask) V with fp32 accumulation, output in Q's dtype.
+ *
+ * Paged form: K/V come from the pool (layer, slots); the additive mask of the
+ * reference (causal tail + left padding + BMC padding columns, llama.py:294-310)
+ * is expressed by integers: kv_len = seq_len[layer][slot] (the q_len newest
+ * tokens included), query i sees keys [kv_start, kv_len - q_len + i].
+ * q / out are bf16 [batch][n_q_heads][q_len][head_dim] through element strides.
+ * GQA: n_q_heads = G * n_kv_heads, query head h reads KV head h / G, which is
+ * what the reference obtains by repeat_kv before caching (llama.py:152-158). */
+typedef struct pace_attn_args {
+  const pace_kv_pool_t* pool;
+  int32_t layer;
+  int32_t batch;
+  int32_t n_q_heads;
+  int32_t q_len;            /* 1 = decode; d+1 = verify; chunk = prefill */
+  const int32_t* seq_ids;   /* device [batch] */
+  const int32_t* kv_start;  /* device [batch] or NULL (no left padding) */
+  const int32_t* q_lens;    /* device [batch] or NULL: ragged query counts <= q_len */
+  const void* q;
+  int64_t q_stride_b, q_stride_h, q_stride_s;
+  void* out;
+  int64_t o_stride_b, o_stride_h, o_stride_s;
+  float scale;              /* 0 -> 1/sqrt(head_dim) */
+  void* workspace;          /* device scratch, pace_attn_workspace_bytes(); zero it once after allocation */
+  uint64_t workspace_bytes;
+} pace_attn_args_t;
+
+uint64_t pace_attn_workspace_bytes(int32_t batch, int32_t n_q_heads, int32_t n_kv_heads, int32_t head_dim,
+                                   int32_t q_len);
+int pace_attn_decode(const pace_attn_args_t* a, void* stream);  /* q_len == 1, CUDA cores, TMA-streamed cache */
+int pace_attn_verify(const pace_attn_args_t* a, void* stream);  /* short q (PARD verify), tensor-core tiles  */
+int pace_attn_prefill(const pace_attn_args_t* a, void* stream); /* prefill chunks, tensor-core tiles         */
+
+/* Dense form with the reference op's exact operands: q [B,N,S,H], k/v [B,Nkv,L,H]
+ * contiguous bf16, additive mask [B,1,mask_rows,L] (mask_rows 1 or S; bf16 or fp32;
+ * may be NULL), out [B,N,S,H].  Reference: pace::attention, attention.cpp:18-97. */
+int pace_attention_dense(const void* q, const void* k, const void* v, const void* mask, int32_t mask_is_fp32,
+                         int32_t mask_rows, void* out, int32_t B, int32_t N, int32_t Nkv, int32_t S, int32_t L,
+                         int32_t H, void* workspace, uint64_t workspace_bytes, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* PACE_B200_H_ */
