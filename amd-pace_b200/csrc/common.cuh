@@ -182,5 +182,7 @@ __device__ __forceinline__ float fast_exp2(float x) {
 #endif  // __CUDACC__
 
 constexpr float kLog2e = 1.4426950408889634f;
+// head of every attention workspace: int32 arrival counters, zero between launches
+constexpr uint64_t kWorkspaceCounterBytes = 256 * 1024;
 
 }  // namespace pace
