@@ -51,7 +51,8 @@ def kv_start_from_mask(mask: torch.Tensor) -> Optional[torch.Tensor]:
 
 
 def paged_attention(query: torch.Tensor, key: PagedKV, kv_start: Optional[torch.Tensor] = None,
-                    q_lens: Optional[torch.Tensor] = None, scale: Optional[float] = None) -> torch.Tensor:
+                    q_lens: Optional[torch.Tensor] = None, scale: Optional[float] = None,
+                    out: Optional[torch.Tensor] = None) -> torch.Tensor:
     cache = key.cache
     pool, mgr = cache.pool, cache.manager
     if query.device != pool.device:
@@ -67,7 +68,10 @@ def paged_attention(query: torch.Tensor, key: PagedKV, kv_start: Optional[torch.
     if query.stride(3) != 1 or any(s % 8 for s in query.stride()[:3]) or query.data_ptr() % 16:
         query = query.contiguous()
     # [B, S, Hq, D] storage so the caller's transpose(1, 2).reshape(B, S, Hq*D) is a view
-    out = torch.empty(B, S, Hq, D, dtype=torch.bfloat16, device=query.device).transpose(1, 2)
+    if out is None:
+        out = torch.empty(B, S, Hq, D, dtype=torch.bfloat16, device=query.device).transpose(1, 2)
+    elif out.shape != query.shape or out.dtype != torch.bfloat16 or out.stride(3) != 1 or out.device != query.device:
+        raise ValueError("out must be a bf16 [B, Hq, S, D] tensor (any strides, last dim contiguous) on the same device")
     nbytes = _C.lib.pace_attn_workspace_bytes(B, Hq, pool.n_kv_heads, D, S)
     ws = workspace(query.device, nbytes)
     a = _C.AttnArgs()
@@ -132,13 +136,14 @@ def dense_attention(query: torch.Tensor, key: torch.Tensor, value: torch.Tensor,
 
 class B200Attention(BackendBase):
     def execute(self, query: torch.Tensor, key, value, attention_mask: Optional[torch.Tensor] = None,
-                kv_start: Optional[torch.Tensor] = None, q_lens: Optional[torch.Tensor] = None) -> torch.Tensor:
+                kv_start: Optional[torch.Tensor] = None, q_lens: Optional[torch.Tensor] = None,
+                out: Optional[torch.Tensor] = None) -> torch.Tensor:
         if isinstance(key, PagedKV):
             if not isinstance(value, PagedKV) or value.cache is not key.cache:
                 raise ValueError("key and value must come from the same update_cache call")
             if kv_start is None and attention_mask is not None:
                 kv_start = kv_start_from_mask(attention_mask)
-            return paged_attention(query, key, kv_start=kv_start, q_lens=q_lens)
+            return paged_attention(query, key, kv_start=kv_start, q_lens=q_lens, out=out)
         return dense_attention(query, key, value, attention_mask)
 
 

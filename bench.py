@@ -1,0 +1,326 @@
+#!/usr/bin/env python
+"""Benchmark of the KV-cache hot path: per-step K/V append + GQA decode attention.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Workload (N = 1): the decode phase of a Llama-3.1-8B-shaped model - 32 layers,
+32 query / 8 KV heads, head_dim 128, bf16 - batch 32, 512-token prompts already in
+the cache, one token appended per sequence per step.  One "step" is one pass of the
+hot path over the batch: for each of the 32 layers, append the new K/V rows and
+attend over the whole cache.  The projections / MLP around it are not part of the
+path and are not run.  K/V/Q are seeded N(0,1) synthetic tensors.
+
+Prints ONE JSON line (rank 0).  `value` is decode tokens/s with inputs resident in
+HBM (CUDA-graph replay of the step); `e2e` is the same through host buffers (pinned
+H2D of the step's K/V/Q, D2H of the attention outputs, inside the timed region);
+`roofline` is the decode-attention kernel against the measured HBM copy bandwidth;
+`cpu_baseline` is the CPU restatement of the reference's path on this host's cores.
+With N > 1 every rank runs the same per-GPU workload on its own sequences (requests
+are sharded, no collective on the path): weak scaling.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+sys.path.insert(0, os.path.join(ROOT, "amd-pace_b200"))
+
+import torch  # noqa: E402
+
+CFG = dict(n_layers=32, batch=32, hq=32, hkv=8, d=128, prompt=512, max_new=256)
+WORKLOAD = "llama31_8b_shape_decode_b32_prompt512_kv_append+gqa_attention_32layers"
+FALLBACK_HBM_GBS = 6650.0
+
+
+def measured_hbm_peak():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        try:
+            return float(json.load(open(p))["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return FALLBACK_HBM_GBS, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons of one GPU while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.rows = []
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            f = [x.strip() for x in r.split(",")]
+            if len(f) < 7:
+                continue
+            try:
+                sm.append(float(f[0]))
+                mx.append(float(f[1]))
+            except ValueError:
+                continue
+            for n, v in zip(names, f[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def cpu_reference_line(steps: int, warmup: int, sample_layers: int):
+    from oracle.cpu_path import time_decode_tokens_per_s
+    cores = torch.get_num_threads()
+    tps, step_s = time_decode_tokens_per_s(CFG["n_layers"], sample_layers, CFG["batch"], CFG["hq"], CFG["hkv"],
+                                           CFG["d"], CFG["prompt"], CFG["prompt"] + CFG["max_new"], steps, warmup)
+    sample = (f"{steps} decode steps over {sample_layers} of {CFG['n_layers']} layers (reference layout: BMC append + "
+              f"repeat_kv + torch CPU SDPA with additive mask), scaled to {CFG['n_layers']} layers")
+    return tps, step_s, cores, sample
+
+
+def run_reference(args, rank):
+    if rank != 0:
+        return
+    steps = max(1, min(args.steps, 20))
+    tps, step_s, cores, sample = cpu_reference_line(steps, max(1, min(args.warmup, 3)), sample_layers=4)
+    line = {"impl": "reference", "metric": "decode_tokens_per_s", "value": tps, "unit": "tokens/s",
+            "n_gpus": args.gpus, "steps": steps, "warmup": args.warmup, "ms_per_step": step_s * 1e3,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": WORKLOAD, "batch": CFG["batch"], "note": "CPU port of the reference path"},
+            "cpu_baseline": {"value": tps, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": sample},
+            "e2e": {"value": tps, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line), flush=True)
+
+
+def run_ours(args, rank, world, local_rank):
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the hot path has no CPU implementation")
+    from pace_b200.llm.cache import KVCacheManager, KVCacheType
+    from pace_b200.llm.graph import StepGraph
+    from pace_b200.ops import MultiHeadAttention
+    from pace_b200.ops.backends.b200 import workspace
+    from pace_b200 import _C
+    import ctypes as C
+
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(dev)
+    L, B, Hq, Hkv, D, P0 = (CFG[k] for k in ("n_layers", "batch", "hq", "hkv", "d", "prompt"))
+    e2e_steps = min(args.steps, 32)
+    roof_reps = 5
+    needed = 2 + args.warmup + args.steps + 3 + e2e_steps + 2
+    max_new = max(CFG["max_new"], needed)
+
+    class Cfg:
+        num_hidden_layers = L
+
+    g = torch.Generator(device=dev).manual_seed(1234 + rank)
+    mgr = KVCacheManager(Cfg(), P0 + max_new, KVCacheType.BMC)
+    # prompt K/V: appended in 128-token pieces so the staging tensors stay small
+    for _ in range(P0 // 128):
+        for l in range(L):
+            k = torch.randn(B, Hkv, 128, D, device=dev, generator=g, dtype=torch.float32).bfloat16()
+            v = torch.randn(B, Hkv, 128, D, device=dev, generator=g, dtype=torch.float32).bfloat16()
+            mgr[l].update_cache(k, v, concat_dim=2)
+    # the step's inputs, resident on the device: per layer K/V of the new token and the query
+    kvq = torch.randn(L, B, Hkv + Hkv + Hq, D, device=dev, generator=g, dtype=torch.float32).bfloat16()
+    k_new = [kvq[l, :, :Hkv].unsqueeze(2) for l in range(L)]
+    v_new = [kvq[l, :, Hkv:2 * Hkv].unsqueeze(2) for l in range(L)]
+    q_new = [kvq[l, :, 2 * Hkv:].unsqueeze(2) for l in range(L)]
+    out_all = torch.empty(L, B, 1, Hq, D, device=dev, dtype=torch.bfloat16)
+    out_views = [out_all[l].transpose(1, 2) for l in range(L)]   # [B, Hq, 1, D] views the kernel writes through
+    mha = MultiHeadAttention()
+
+    def step_fn():
+        for l in range(L):
+            K, V = mgr[l].update_cache(k_new[l], v_new[l], concat_dim=2)
+            mha(q_new[l], K, V, out=out_views[l])
+        return out_all
+
+    graph = StepGraph(mgr, step_fn, n_new=1, warmup=2)
+    own_launches_per_step = 1 + 2 * L
+
+    def barrier():
+        if world > 1:
+            torch.distributed.barrier()
+
+    for _ in range(args.warmup):
+        graph.replay()
+    torch.cuda.synchronize()
+    barrier()
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    time.sleep(0.25)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        graph.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    barrier()
+    ms = e0.elapsed_time(e1)
+    time.sleep(0.15)
+    clocks = sampler.stop()
+    mgr.pool.check_status()
+    len_after_timed = mgr[0].seq_len
+
+    # ---- end to end: host buffers in, host buffers out, copies inside the timed region ----
+    host_in = torch.empty(kvq.shape, dtype=kvq.dtype).pin_memory()
+    host_in.copy_(kvq.cpu())
+    host_out = torch.empty(out_all.shape, dtype=out_all.dtype).pin_memory()
+    for _ in range(3):
+        kvq.copy_(host_in, non_blocking=True)
+        graph.replay()
+        host_out.copy_(out_all, non_blocking=True)
+    torch.cuda.synchronize()
+    barrier()
+    f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0 = time.perf_counter()
+    f0.record()
+    for _ in range(e2e_steps):
+        kvq.copy_(host_in, non_blocking=True)
+        graph.replay()
+        host_out.copy_(out_all, non_blocking=True)
+        torch.cuda.current_stream().synchronize()      # the caller has the step's result in host memory
+    f1.record()
+    torch.cuda.synchronize()
+    e2e_wall = time.perf_counter() - t0
+    e2e_ms = max(f0.elapsed_time(f1), e2e_wall * 1e3)
+    barrier()
+
+    # ---- roofline of the decode-attention kernel: 32 back-to-back launches, one per layer ----
+    lens_now = mgr[0].seq_len
+    K_handles = [(mgr[l].key, mgr[l].value) for l in range(L)]
+    s = torch.cuda.Stream()
+    s.wait_stream(torch.cuda.current_stream())
+    rg = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(s):
+        for l in range(L):
+            mha(q_new[l], *K_handles[l])
+    s.synchronize()
+    with torch.cuda.graph(rg, stream=s):
+        for l in range(L):
+            mha(q_new[l], *K_handles[l])
+    for _ in range(3):
+        rg.replay()
+    torch.cuda.synchronize()
+    r0, r1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    r0.record()
+    for _ in range(roof_reps):
+        rg.replay()
+    r1.record()
+    torch.cuda.synchronize()
+    attn_us = r0.elapsed_time(r1) * 1e3 / (roof_reps * L)
+    # algorithmic bytes of one launch: K and V rows of every cached token once, q in, o out (bf16, GQA)
+    alg_bytes = B * (2 * Hkv * D * 2 * lens_now) + 2 * B * Hq * D * 2
+    achieved = alg_bytes / (attn_us * 1e-6) / 1e9
+    peak, peak_kind = measured_hbm_peak()
+
+    # ---- reduce over ranks: slowest rank sets the time ----
+    if world > 1:
+        t = torch.tensor([ms, e2e_ms, attn_us], device=dev, dtype=torch.float64)
+        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+        ms, e2e_ms, attn_us = (float(x) for x in t.tolist())
+        achieved = alg_bytes / (attn_us * 1e-6) / 1e9
+    tokens = B * args.steps * world
+    value = tokens / (ms * 1e-3)
+    e2e_value = B * e2e_steps * world / (e2e_ms * 1e-3)
+    if rank != 0:
+        return
+    line = {
+        "metric": "decode_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "batch_per_gpu": B, "global_batch": B * world, "layers": L,
+                   "q_heads": Hq, "kv_heads": Hkv, "head_dim": D, "kv_len_start": len_after_timed - args.steps,
+                   "kv_len_end": len_after_timed, "page_tokens": mgr.pool.page_tokens,
+                   "l2": "inputs_larger_than_l2 (%.1f GB of K/V per step)" % (L * alg_bytes / 1e9),
+                   "parallelism": f"dp{world} (sequences sharded, no collective)",
+                   "launch": "one CUDA graph per step"},
+        "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": host_in.numel() * 2,
+                "d2h_bytes_per_step": host_out.numel() * 2, "steps": e2e_steps, "ms_per_step": e2e_ms / e2e_steps},
+        "gpu_launches": own_launches_per_step * args.steps,
+        "gpu_launches_note": f"{own_launches_per_step} own kernels per step: 1 page reserve + {L} x [append, decode attention]",
+        "clocks": clocks,
+        "roofline": {"bound": "hbm", "kernel": "attn_decode_kernel<128,4>", "achieved": achieved, "peak": peak,
+                     "peak_kind": peak_kind, "unit": "GB/s", "frac": achieved / peak,
+                     "frac_of_nominal_8TBs": achieved / 8000.0, "us_per_launch": attn_us, "kv_len": lens_now,
+                     "alg_bytes_per_launch": alg_bytes, "traffic": None},
+    }
+    if world == 1 and not args.no_cpu_baseline:
+        tps, _, cores, sample = cpu_reference_line(steps=6, warmup=1, sample_layers=4)
+        line["cpu_baseline"] = {"value": tps, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": sample}
+    traffic_file = os.path.join(ROOT, "profiles", "attn_decode_traffic.json")
+    if os.path.exists(traffic_file):
+        try:
+            t = json.load(open(traffic_file))
+            # DRAM bytes of a captured launch scale with the cached tokens it streams
+            line["roofline"]["traffic"] = t["dram_bytes_per_launch"] * (B * lens_now) / t["tokens_per_launch"]
+        except Exception:
+            pass
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--layers", type=int, default=CFG["n_layers"],
+                    help="profiling aid: fewer layers = less device memory; the bench line is only valid at 32")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+    CFG["n_layers"] = args.layers
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, rank)
+        return
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        torch.cuda.set_device(local_rank)
+        torch.distributed.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    try:
+        run_ours(args, rank, world, local_rank)
+    finally:
+        if world > 1:
+            torch.distributed.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
