@@ -1,29 +1,37 @@
-// Entry points shared by the attention kernels: workspace sizing and the dense
-// form of the reference's pace::attention operands (csrc/ops/attention.cpp:18-97).
+// Entry points shared by the attention kernels: workspace sizing and the choice of
+// decode kernel.
+#include <cstdlib>
+#include <cstring>
+
 #include "common.cuh"
 
 namespace pace {
-int run_decode(const KVView& kv, int batch, int n_q_heads, const void* q, int64_t q_sb, int64_t q_sh, void* out,
-               int64_t o_sb, int64_t o_sh, const int32_t* kv_start, float scale, void* workspace,
-               uint64_t workspace_bytes, cudaStream_t stream);
+int decode_cuda_cores(const pace_attn_args_t* a, void* stream);
+int run_mma_paged(const pace_attn_args_t* a, int causal, cudaStream_t stream);
 uint64_t decode_workspace_bytes(int batch, int n_q_heads, int n_kv_heads, int head_dim);
+uint64_t mma_workspace_bytes(int n_q_heads, int n_kv_heads, int head_dim, int q_len);
 }  // namespace pace
 
 using namespace pace;
 
 extern "C" uint64_t pace_attn_workspace_bytes(int32_t batch, int32_t n_q_heads, int32_t n_kv_heads,
                                               int32_t head_dim, int32_t q_len) {
-  (void)q_len;
-  if (batch <= 0 || n_q_heads <= 0 || n_kv_heads <= 0 || head_dim <= 0) return 0;
-  return decode_workspace_bytes(batch, n_q_heads, n_kv_heads, head_dim);
+  if (batch <= 0 || n_q_heads <= 0 || n_kv_heads <= 0 || head_dim <= 0 || q_len <= 0) return 0;
+  const uint64_t a = decode_workspace_bytes(batch, n_q_heads, n_kv_heads, head_dim);
+  const uint64_t b = mma_workspace_bytes(n_q_heads, n_kv_heads, head_dim, q_len);
+  return a > b ? a : b;
 }
 
-// (multi-token kernels land in attn_mma.cu)
-#ifndef PACE_HAVE_MMA
-extern "C" int pace_attn_verify(const pace_attn_args_t*, void*) { return PACE_ERR_UNSUPPORTED; }
-extern "C" int pace_attn_prefill(const pace_attn_args_t*, void*) { return PACE_ERR_UNSUPPORTED; }
-extern "C" int pace_attention_dense(const void*, const void*, const void*, const void*, int32_t, int32_t, void*,
-                                    int32_t, int32_t, int32_t, int32_t, int32_t, int32_t, void*, uint64_t, void*) {
-  return PACE_ERR_UNSUPPORTED;
+// Decode (one query token).  Two kernels compute it: the CUDA-core kernel streams K/V rows
+// through packed fp32 FMAs and costs G * 2 FMAs per cached byte; the tensor-core kernel packs the
+// G grouped query heads into one 16-row MMA tile.  PACE_DECODE_IMPL=cuda|mma forces one of them.
+extern "C" int pace_attn_decode(const pace_attn_args_t* a, void* stream) {
+  if (!a || !a->pool || a->q_len != 1) return PACE_ERR_INVALID;
+  const int G = a->pool->n_kv_heads > 0 ? a->n_q_heads / a->pool->n_kv_heads : 0;
+  bool use_mma = G >= 4 && G <= 16;
+  if (const char* e = getenv("PACE_DECODE_IMPL")) {
+    if (!strcmp(e, "cuda")) use_mma = false;
+    if (!strcmp(e, "mma") && G <= 16) use_mma = true;
+  }
+  return use_mma ? run_mma_paged(a, 1, (cudaStream_t)stream) : decode_cuda_cores(a, stream);
 }
-#endif

@@ -211,126 +211,136 @@ __global__ void __launch_bounds__(kThreads, 1) attn_decode_kernel(const DecodePa
 
   if (warp == kConsumerWarps) {
     // =========================== producer warp ============================
-    // locate the first unit: largest b with prefix[b] <= x0 < prefix[b+1]
+    // Everything that costs (divisions, table walks, the partition arithmetic) is done once
+    // per unit part; the per-chunk loop is a handful of integer operations, one prefetched
+    // page-id load and the copies.
     int lo = 0, hi = p.batch - 1;
-    while (lo < hi) {
+    while (lo < hi) {  // largest b with prefix[b] <= x0
       const int mid = (lo + hi + 1) >> 1;
       if ((long long)prefix[mid] <= x0) lo = mid; else hi = mid - 1;
     }
     int b = lo;
-    while (b < p.batch - 1 && prefix[b + 1] == prefix[b]) ++b;  // never lands on an empty one, kept for safety
     int nch = (prefix[b + 1] - prefix[b]) / Hkv;
     int h = (int)((x0 - prefix[b]) / nch);
     int j = (int)((x0 - prefix[b]) - (long long)h * nch);
-    int slot = view_slot(p.kv, b);
-    int len = view_len(p.kv, slot);
-    int kvs = p.kv_start ? p.kv_start[b] : 0;
-    int cached_lp_base = -1 << 30;  // logical page held by lane 0 of the page cache
-    int cached_page = -1;
+    const bool whole_pages = p.pages_per_chunk > 0;
+    // this lane's copy: K or V of page `pi` of the chunk (whole-page mode) or of the chunk's one page
+    const int pi = whole_pages ? (lane >> 1) : 0;
+    const int is_v = lane & 1;
+    const bool copier = whole_pages ? (lane < 2 * p.pages_per_chunk) : (lane < 2);
+    const __nv_bfloat16* src_base = is_v ? p.kv.v : p.kv.k;
+    const int MP = p.kv.max_pages_per_seq;
     bool ok = true;
-    int issued = 0;
-    for (int i = 0; i < n_my && ok; ++i) {
-      const int s = i % n_stages;
-      if (i >= n_stages) {
-        if (!mbar_wait(&empty_bar[s], ((i / n_stages) - 1) & 1)) { ok = false; break; }
-      }
-      // ---- describe chunk j of unit (b, h) ----
-      int tok0, rows, lp0, row0, n_copy_pages;
-      if (p.pages_per_chunk > 0) {
-        tok0 = j * p.chunk_tokens;
-        rows = min(p.chunk_tokens, len - tok0);
-        lp0 = j * p.pages_per_chunk;
-        row0 = 0;
-        n_copy_pages = (rows + P - 1) / P;
-      } else {
-        const int pg = j / p.chunks_per_page;
-        const int c = j - pg * p.chunks_per_page;
-        row0 = c * kChunkRows;
-        tok0 = pg * P + row0;
-        rows = min(min(kChunkRows, P - row0), len - tok0);
-        lp0 = pg;
-        n_copy_pages = 1;
-      }
-      const long long ub = (long long)prefix[b] + (long long)h * nch;  // unit's first global chunk
-      const bool first = (i == 0) || (j == 0);
-      const bool last = (i == n_my - 1) || (j == nch - 1);
-      // ---- page ids: refill the 32-entry cache when the chunk leaves it ----
-      if (lp0 < cached_lp_base || lp0 + n_copy_pages > cached_lp_base + 32 || first) {
-        cached_lp_base = lp0;
-        cached_page = view_page(p.kv, slot, lp0 + lane);
-      }
-      unsigned char* st = stage_base + (size_t)s * p.stage_bytes;
-      if (lane == 0) {
-        StageMeta* m = reinterpret_cast<StageMeta*>(st + 2 * kv_bytes + G * D * 2);
-        m->rows = rows;
-        m->tok0 = tok0;
-        m->flags = (first ? 1 : 0) | (last ? 2 : 0);
-        m->unit = b * Hkv + h;
-        m->kv_start = kvs;
-        if (last) {
-          const long long ue = ub + nch;  // one past the unit's last global chunk
-          const int c_first = (int)(((ub + 1) * NC + T - 1) / T) - 1;
-          const int c_last = (int)((ue * NC + T - 1) / T) - 1;
-          m->parts = c_last - c_first + 1;
-          m->first_cta = c_first;
-          m->first_slot = (T * c_first / NC == ub) ? 0 : 1;
-          if (c_first == c_last) m->mode = 0;
-          else m->mode = (cta == c_first) ? (m->first_slot ? 2 : 1) : 1;
-        }
-        const uint32_t bytes = 2u * rows * D * 2u + (first ? G * D * 2u : 0u);
-        mbar_arrive_expect_tx(&full_bar[s], bytes);
-      }
-      __syncwarp();
-      // ---- issue the copies: K and V per page, lanes in parallel (at most 32 copies) ----
-      bool page_bad = false;
+    int i = 0, issued = 0;
+    while (i < n_my && ok) {
+      // ------------------------------ unit part ------------------------------
+      const int slot = view_slot(p.kv, b);
+      const int len = view_len(p.kv, slot);
+      const int kvs = p.kv_start ? p.kv_start[b] : 0;
+      const int j_end = min(nch, j + (n_my - i));
+      const int32_t* row_tbl = p.kv.block_table ? p.kv.block_table + (size_t)slot * MP : nullptr;
+      // how the part is finished: whole unit here, or a partial record for the last arriver
+      int mode = 0, parts = 1, first_cta = cta, first_slot = 0;
       {
-        const int pi = lane >> 1, is_v = lane & 1;
-        const int pg = __shfl_sync(0xffffffffu, cached_page, ((lp0 + pi) - cached_lp_base) & 31);
-        if (lane < 2 * n_copy_pages) {
-          const int r_in = (p.pages_per_chunk > 0) ? min(P, rows - pi * P) : rows;
+        const long long ub = (long long)prefix[b] + (long long)h * nch, ue = ub + nch;
+        if (ub < x0 || ue > x1) {
+          first_cta = ub >= x0 ? cta : (int)(((ub + 1) * NC + T - 1) / T) - 1;
+          const int last_cta = ue <= x1 ? cta : (int)((ue * NC + T - 1) / T) - 1;
+          parts = last_cta - first_cta + 1;
+          first_slot = (ub >= x0 ? x0 : T * first_cta / NC) == ub ? 0 : 1;
+          mode = (cta == first_cta) ? (first_slot ? 2 : 1) : 1;
+        }
+      }
+      // chunk -> (logical page, first row): incremental from here on
+      int lp, row0;
+      if (whole_pages) {
+        lp = j * p.pages_per_chunk + pi;
+        row0 = 0;
+      } else {
+        lp = j / p.chunks_per_page;
+        row0 = (j - lp * p.chunks_per_page) * kChunkRows;
+      }
+      auto page_of = [&](int l) -> int {
+        if (!row_tbl) return slot;
+        if (l >= MP) return -1;
+        const int pg = __ldg(row_tbl + l);
+        return (pg < 0 || pg >= p.kv.n_pages) ? -1 : pg;
+      };
+      int pg = copier ? page_of(lp) : 0;
+      for (bool first = true; j < j_end; ++j, ++i, first = false) {
+        // prefetch the next chunk's page id before blocking on the ring
+        int lp_n = lp, row0_n = row0;
+        if (whole_pages) {
+          lp_n = lp + p.pages_per_chunk;
+        } else {
+          row0_n = row0 + kChunkRows;
+          if (row0_n >= P) { row0_n = 0; lp_n = lp + 1; }
+        }
+        const int pg_n = (copier && j + 1 < j_end) ? (lp_n == lp ? pg : page_of(lp_n)) : 0;
+        const int s = i % n_stages;
+        if (i >= n_stages && !mbar_wait(&empty_bar[s], ((i / n_stages) - 1) & 1)) { ok = false; break; }
+        const int tok0 = whole_pages ? j * p.chunk_tokens : lp * P + row0;
+        const int rows = whole_pages ? min(p.chunk_tokens, len - tok0) : min(min(kChunkRows, P - row0), len - tok0);
+        const int my_rows = whole_pages ? max(0, min(P, rows - pi * P)) : rows;
+        const bool last = (j == j_end - 1);
+        unsigned char* st = stage_base + (size_t)s * p.stage_bytes;
+        if (lane == 0) {
+          StageMeta* m = reinterpret_cast<StageMeta*>(st + 2 * kv_bytes + G * D * 2);
+          m->rows = rows;
+          m->tok0 = tok0;
+          m->flags = (first ? 1 : 0) | (last ? 2 : 0);
+          m->kv_start = kvs;
+          if (last) {
+            m->unit = b * Hkv + h;
+            m->mode = mode;
+            m->parts = parts;
+            m->first_cta = first_cta;
+            m->first_slot = first_slot;
+          }
+          mbar_arrive_expect_tx(&full_bar[s], 2u * rows * D * 2u + (first ? G * D * 2u : 0u));
+        }
+        __syncwarp();
+        bool page_bad = false;
+        if (copier && my_rows > 0) {
           if (pg < 0) {
             page_bad = true;
           } else {
-            const __nv_bfloat16* src = (is_v ? p.kv.v : p.kv.k) + view_row_offset(p.kv, pg, h, row0);
+            const __nv_bfloat16* src = src_base + view_row_offset(p.kv, pg, h, row0);
             unsigned char* dst = st + (is_v ? kv_bytes : 0) + (size_t)pi * P * D * 2;
-            bulk_g2s(dst, src, (uint32_t)r_in * D * 2u, &full_bar[s]);
+            bulk_g2s(dst, src, (uint32_t)my_rows * D * 2u, &full_bar[s]);
           }
         }
-      }
-      if (first && lane < G) {
-        const __nv_bfloat16* src = p.q + (size_t)b * p.q_sb + (size_t)(h * G + lane) * p.q_sh;
-        bulk_g2s(st + 2 * kv_bytes + lane * D * 2, src, D * 2u, &full_bar[s]);
-      }
-      if (__any_sync(0xffffffffu, page_bad)) {
-        if (lane == 0) raise_status(p.kv.status, PACE_DEV_BAD_INDEX);
-        ok = false;  // the consumers' bounded wait on this stage will give up
-        break;
-      }
-      ++issued;
-      // ---- advance to the next chunk ----
-      if (++j == nch) {
-        j = 0;
-        if (++h == Hkv) {
-          h = 0;
-          ++b;
-          while (b < p.batch && prefix[b + 1] == prefix[b]) ++b;
-          if (b < p.batch) {
-            nch = (prefix[b + 1] - prefix[b]) / Hkv;
-            slot = view_slot(p.kv, b);
-            len = view_len(p.kv, slot);
-            kvs = p.kv_start ? p.kv_start[b] : 0;
-          }
+        if (first && lane < G) {
+          const __nv_bfloat16* src = p.q + (size_t)b * p.q_sb + (size_t)(h * G + lane) * p.q_sh;
+          bulk_g2s(st + 2 * kv_bytes + lane * D * 2, src, D * 2u, &full_bar[s]);
         }
+        if (__any_sync(0xffffffffu, page_bad)) {
+          if (lane == 0) raise_status(p.kv.status, PACE_DEV_BAD_INDEX);
+          ok = false;  // the consumers' bounded wait on this stage gives up
+          break;
+        }
+        ++issued;
+        pg = pg_n;
+        lp = lp_n;
+        row0 = row0_n;
+      }
+      if (!ok) break;
+      // ---- next unit ----
+      j = 0;
+      if (++h == Hkv) {
+        h = 0;
+        ++b;
+        while (b < p.batch && prefix[b + 1] == prefix[b]) ++b;
+        if (b >= p.batch) break;
+        nch = (prefix[b + 1] - prefix[b]) / Hkv;
       }
     }
-    if (!ok) {
-      if (lane == 0) {
-        misc[0] = 1;
-        raise_status(p.kv.status, PACE_DEV_WAIT_TIMEOUT);
-        // let copies already in flight land before the CTA's shared memory is released
-        const int from = issued > n_stages ? issued - n_stages : 0;
-        for (int i = from; i < issued; ++i) mbar_wait(&full_bar[i % n_stages], (i / n_stages) & 1);
-      }
+    if (!ok && lane == 0) {
+      misc[0] = 1;
+      raise_status(p.kv.status, PACE_DEV_WAIT_TIMEOUT);
+      // let copies already in flight land before the CTA's shared memory is released
+      const int from = issued > n_stages ? issued - n_stages : 0;
+      for (int k = from; k < issued; ++k) mbar_wait(&full_bar[k % n_stages], (k / n_stages) & 1);
     }
     return;
   }
@@ -674,9 +684,8 @@ uint64_t decode_workspace_bytes(int batch, int n_q_heads, int n_kv_heads, int he
 
 }  // namespace pace
 
-using namespace pace;
-
-extern "C" int pace_attn_decode(const pace_attn_args_t* a, void* stream) {
+namespace pace {
+int decode_cuda_cores(const pace_attn_args_t* a, void* stream) {
   if (!a || !a->pool || a->q_len != 1 || a->layer < 0 || a->layer >= a->pool->n_layers || !a->seq_ids)
     return PACE_ERR_INVALID;
   if (a->batch > a->pool->max_seqs) return PACE_ERR_INVALID;
@@ -684,3 +693,4 @@ extern "C" int pace_attn_decode(const pace_attn_args_t* a, void* stream) {
   return run_decode(kv, a->batch, a->n_q_heads, a->q, a->q_stride_b, a->q_stride_h, a->out, a->o_stride_b,
                     a->o_stride_h, a->kv_start, a->scale, a->workspace, a->workspace_bytes, (cudaStream_t)stream);
 }
+}  // namespace pace

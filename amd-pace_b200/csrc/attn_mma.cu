@@ -1,0 +1,873 @@
+// Tensor-core attention over the paged KV pool: short-query verify (PARD), chunked
+// prefill, the dense form of the reference op, and GQA decode with the query-head
+// group packed into one MMA tile.
+//
+// Replaces the reference's four-primitive SDPA sequence
+// (csrc/ops/kernels/attention_kernels.cpp:218-257) for S >= 1 query tokens: the
+// [B,N,S,L] score tensor is never materialised, K/V are read once per query tile.
+//
+// Shape of the kernel:
+//   * the query rows of one (sequence, kv head) are the S tokens x G grouped heads,
+//     row r = s * G + g, cut into tiles of 16 * MT rows;
+//   * persistent grid, one CTA per SM; the global sequence of K/V chunks of all
+//     (sequence, query tile, kv head) units is cut into equal contiguous ranges;
+//   * one producer warp: tiled TMA copies (cp.async.bulk.tensor, 128-byte swizzle)
+//     of K and V pages into a shared-memory ring, per-row bulk copies of the Q tile;
+//   * eight consumer warps arranged MT x NS: warp (mt, ns) owns 16 query rows and
+//     the ns-th slice of every chunk's tokens; S = Q K^T and O += P V are
+//     mma.sync m16n8k16 (bf16 in, fp32 accumulate), online softmax in registers;
+//   * the NS slices of a tile are merged through shared memory; a unit cut by a
+//     range boundary leaves an fp32 partial in the workspace and the last CTA to
+//     arrive merges (no CTA waits on another).
+#include <cuda.h>
+
+#include <climits>
+#include <cstdlib>
+#include <cstring>
+#include <mutex>
+
+#include "common.cuh"
+
+namespace pace {
+namespace {
+
+constexpr int kWarps = 8;
+constexpr int kCThreads = kWarps * 32;
+constexpr int kThreadsM = kCThreads + 32;
+constexpr int kChunk = 64;
+constexpr int kMaxStagesM = 8;
+constexpr int kMaxItems = 4096;
+
+struct MetaM {  // one 64-byte record per ring stage, written by the producer
+  int rows, tok0, flags, kvs;
+  int b, h, r_lo, R;
+  int kv_len, S, mode, parts;
+  int first_cta, first_slot, unit, pad;
+};
+static_assert(sizeof(MetaM) == 64, "MetaM is one 64-byte line");
+
+struct MmaParams {
+  KVView kv;
+  int c3_k, c3_v;  // 4th tensor-map coordinate of the K and of the V region
+  const __nv_bfloat16* q;
+  int64_t q_sb, q_sh, q_ss;
+  __nv_bfloat16* out;
+  int64_t o_sb, o_sh, o_ss;
+  const int32_t* kv_start;
+  const int32_t* q_lens;
+  int batch, q_len, G, n_qt, causal;
+  float scale_log2;
+  float* parts;
+  int32_t* unit_count;
+  int chunk_tokens, pages_per_chunk, chunks_per_page, box_rows, n_stages, stage_bytes;
+  const void* mask;  // additive [B,1,mask_rows,L] or null
+  int mask_fp32, mask_rows;
+  int64_t mask_sb;
+};
+
+__device__ __forceinline__ int chunks_of_m(const MmaParams& p, int len) {
+  if (len <= 0) return 0;
+  if (p.pages_per_chunk > 0) return (len + p.chunk_tokens - 1) / p.chunk_tokens;
+  const int P = p.kv.page_tokens;
+  const int full = len / P, rem = len - full * P;
+  return full * p.chunks_per_page + (rem + kChunk - 1) / kChunk;
+}
+
+__device__ __forceinline__ void csync() { asm volatile("bar.sync 1, %0;" ::"n"(kCThreads) : "memory"); }
+
+__device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+               : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_t(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+               : "r"(addr));
+}
+__device__ __forceinline__ void mma16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void mma1688(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t b0) {
+  asm volatile("mma.sync.aligned.m16n8k8.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5}, {%6}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a0), "r"(a1), "r"(b0));
+}
+// tiled TMA load of one box, completion on an mbarrier (no multicast)
+__device__ __forceinline__ void tma_load_4d(void* smem_dst, const CUtensorMap* tm, int c0, int c1, int c2, int c3,
+                                            uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], "
+      "[%2];" ::"r"(smem_u32(smem_dst)),
+      "l"(tm), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+      : "memory");
+}
+
+template <int D, int MT, int NS>
+__global__ void __launch_bounds__(kThreadsM, 1)
+    attn_mma_kernel(const MmaParams p, const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV) {
+  static_assert(MT * NS == kWarps, "eight consumer warps");
+  constexpr int TW = kChunk / NS;  // tokens of a chunk owned by one warp
+  constexpr int NT = TW / 8;       // score n-tiles per warp
+  constexpr int KS = D / 16;       // k-steps of Q K^T
+  constexpr int ON = D / 8;        // output n-tiles
+  constexpr int HALVES = D / 64;   // 64-element (128-byte) column blocks of a K/V row
+  constexpr int MR = 16 * MT;      // query rows per tile
+  constexpr int QS = D * 2 + 16;   // padded Q row stride in shared memory (bytes)
+  constexpr int KVB = kChunk * D * 2;  // bytes of one K (or V) chunk slot
+  constexpr int HALF_B = kChunk * 128;
+  constexpr int REC = MR * (D + 2);
+
+  extern __shared__ __align__(1024) unsigned char smem[];
+  const int n_stages = p.n_stages;
+  unsigned char* ring = smem;  // [n_stages][K | V | MetaM]
+  unsigned char* qbuf = smem + (size_t)n_stages * p.stage_bytes;
+  float* mg_o = reinterpret_cast<float*>(qbuf + MR * QS);  // [NS][MR][D]
+  float* mg_m = mg_o + NS * MR * D;                        // [NS][MR]
+  float* mg_l = mg_m + NS * MR;                            // [NS][MR]
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(mg_l + NS * MR);
+  uint64_t* empty_bar = full_bar + kMaxStagesM;
+  uint64_t* q_empty = empty_bar + kMaxStagesM;
+  int* misc = reinterpret_cast<int*>(q_empty + 1);
+  int* prefix = misc + 8;  // [items + 1]
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int Hkv = p.kv.n_kv_heads, P = p.kv.page_tokens, G = p.G;
+  const int n_items = p.batch * p.n_qt;
+
+  if (tid == 0) {
+    for (int s = 0; s < n_stages; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], kWarps);
+    }
+    mbar_init(q_empty, kWarps);
+    misc[0] = misc[1] = 0;
+    fence_mbar_init();
+  }
+  // stale shared memory must not hold NaN patterns: rows no copy ever writes are multiplied by p = 0
+  {
+    uint4* z = reinterpret_cast<uint4*>(smem);
+    const int n16 = (int)(((size_t)n_stages * p.stage_bytes + MR * QS) / 16);
+    for (int i = tid; i < n16; i += kThreadsM) z[i] = make_uint4(0, 0, 0, 0);
+  }
+  for (int it = tid; it < n_items; it += kThreadsM) {
+    const int b = it / p.n_qt, qt = it - b * p.n_qt;
+    const int slot = view_slot(p.kv, b);
+    int n = 0;
+    if (slot >= 0) {
+      const int S = p.q_lens ? min(p.q_lens[b], p.q_len) : p.q_len;
+      const int R = S * G;
+      if (qt * MR < R) {
+        const int kv_len = view_len(p.kv, slot);
+        const int s_hi = min(S - 1, ((qt + 1) * MR - 1) / G);
+        const int hi = p.causal ? kv_len - S + s_hi + 1 : kv_len;
+        n = chunks_of_m(p, min(hi, kv_len)) * Hkv;
+      }
+    }
+    prefix[it + 1] = n;
+  }
+  fence_proxy_async();  // the zero fill above precedes TMA writes to the same shared memory
+  __syncthreads();
+  if (warp == 0) {
+    int carry = 0;
+    for (int base = 0; base < n_items; base += 32) {
+      const int i = base + lane;
+      int v = i < n_items ? prefix[i + 1] : 0;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int n = __shfl_up_sync(0xffffffffu, v, o);
+        if (lane >= o) v += n;
+      }
+      if (i < n_items) prefix[i + 1] = v + carry;
+      carry += __shfl_sync(0xffffffffu, v, 31);
+    }
+    if (lane == 0) prefix[0] = 0;
+  }
+  __syncthreads();
+  const long long T = prefix[n_items];
+  const int NC = (long long)gridDim.x < T ? (int)gridDim.x : (int)T;
+  const int cta = blockIdx.x;
+  const long long x0 = cta < NC ? T * cta / NC : 0, x1 = cta < NC ? T * (cta + 1) / NC : 0;
+
+  // query rows that see no key at all (nothing cached) get zeros
+  for (int u = cta; u < n_items * Hkv; u += gridDim.x) {
+    const int it = u / Hkv, h = u - it * Hkv;
+    if (prefix[it + 1] != prefix[it]) continue;
+    const int b = it / p.n_qt, qt = it - b * p.n_qt;
+    const int S = p.q_lens ? min(p.q_lens[b], p.q_len) : p.q_len;
+    const int R = S * G;
+    for (int o = tid; o < MR * D; o += kThreadsM) {
+      const int r = qt * MR + o / D, d = o % D;
+      if (r < R) {
+        const int s = r / G, g = r - s * G;
+        p.out[(size_t)b * p.o_sb + (size_t)(h * G + g) * p.o_sh + (size_t)s * p.o_ss + d] = __float2bfloat16(0.f);
+      }
+    }
+  }
+  if (x1 <= x0) return;
+  const int n_my = (int)(x1 - x0);
+
+  if (warp == kWarps) {
+    // ================================ producer ================================
+    int lo = 0, hi = n_items - 1;
+    while (lo < hi) {
+      const int mid = (lo + hi + 1) >> 1;
+      if ((long long)prefix[mid] <= x0) lo = mid; else hi = mid - 1;
+    }
+    int it = lo;
+    int nch = (prefix[it + 1] - prefix[it]) / Hkv;
+    int h = (int)((x0 - prefix[it]) / nch);
+    int j = (int)((x0 - prefix[it]) - (long long)h * nch);
+    const bool whole_pages = p.pages_per_chunk > 0;
+    const int is_v = lane & 1;
+    const int hf = (lane >> 1) % HALVES;
+    const int pi = whole_pages ? lane / (2 * HALVES) : 0;
+    const bool copier = whole_pages ? (lane < 2 * HALVES * p.pages_per_chunk) : (lane < 2 * HALVES);
+    const CUtensorMap* tm = is_v ? &tmV : &tmK;
+    const int c3 = is_v ? p.c3_v : p.c3_k;
+    const int MPs = p.kv.max_pages_per_seq;
+    const uint32_t box_bytes = (uint32_t)p.box_rows * 128u;
+    bool ok = true;
+    int i = 0, issued = 0, part_idx = 0;
+    while (i < n_my && ok) {
+      const int b = it / p.n_qt, qt = it - b * p.n_qt;
+      const int slot = view_slot(p.kv, b);
+      const int kv_len = view_len(p.kv, slot);
+      const int S = p.q_lens ? min(p.q_lens[b], p.q_len) : p.q_len;
+      const int R = S * G;
+      const int r_lo = qt * MR;
+      const int s_hi = min(S - 1, (r_lo + MR - 1) / G);
+      const int len = min(kv_len, p.causal ? kv_len - S + s_hi + 1 : kv_len);  // keys this tile can see
+      const int kvs = p.kv_start ? p.kv_start[b] : 0;
+      const int j_end = min(nch, j + (n_my - i));
+      const int32_t* row_tbl = p.kv.block_table ? p.kv.block_table + (size_t)slot * MPs : nullptr;
+      int mode = 0, parts = 1, first_cta = cta, first_slot = 0;
+      {
+        const long long ub = (long long)prefix[it] + (long long)h * nch, ue = ub + nch;
+        if (ub < x0 || ue > x1) {
+          first_cta = ub >= x0 ? cta : (int)(((ub + 1) * NC + T - 1) / T) - 1;
+          const int last_cta = ue <= x1 ? cta : (int)((ue * NC + T - 1) / T) - 1;
+          parts = last_cta - first_cta + 1;
+          first_slot = (ub >= x0 ? x0 : T * first_cta / NC) == ub ? 0 : 1;
+          mode = (cta == first_cta) ? (first_slot ? 2 : 1) : 1;
+        }
+      }
+      int lp, row0;
+      if (whole_pages) {
+        lp = j * p.pages_per_chunk + pi;
+        row0 = 0;
+      } else {
+        lp = j / p.chunks_per_page;
+        row0 = (j - lp * p.chunks_per_page) * kChunk;
+      }
+      auto page_of = [&](int l) -> int {
+        if (!row_tbl) return slot;
+        if (l >= MPs) return -1;
+        const int pg = __ldg(row_tbl + l);
+        return (pg < 0 || pg >= p.kv.n_pages) ? -1 : pg;
+      };
+      int pg = copier ? page_of(lp) : 0;
+      for (bool first = true; j < j_end; ++j, ++i, first = false) {
+        int lp_n = lp, row0_n = row0;
+        if (whole_pages) {
+          lp_n = lp + p.pages_per_chunk;
+        } else {
+          row0_n = row0 + kChunk;
+          if (row0_n >= P) { row0_n = 0; lp_n = lp + 1; }
+        }
+        const int pg_n = (copier && j + 1 < j_end) ? (lp_n == lp ? pg : page_of(lp_n)) : 0;
+        const int s = i % n_stages;
+        if (i >= n_stages && !mbar_wait(&empty_bar[s], ((i / n_stages) - 1) & 1)) { ok = false; break; }
+        if (first && part_idx > 0 && !mbar_wait(q_empty, (part_idx - 1) & 1)) { ok = false; break; }
+        const int tok0 = whole_pages ? j * p.chunk_tokens : lp * P + row0;
+        const int rows = whole_pages ? min(p.chunk_tokens, len - tok0) : min(min(kChunk, P - row0), len - tok0);
+        const int n_pages_c = whole_pages ? (rows + P - 1) / P : 1;
+        const bool mine = copier && pi < n_pages_c;
+        const bool last = (j == j_end - 1);
+        const int q_rows = first ? min(MR, R - r_lo) : 0;
+        unsigned char* st = ring + (size_t)s * p.stage_bytes;
+        if (lane == 0) {
+          MetaM* m = reinterpret_cast<MetaM*>(st + 2 * KVB);
+          m->rows = rows;
+          m->tok0 = tok0;
+          m->flags = (first ? 1 : 0) | (last ? 2 : 0);
+          m->kvs = kvs;
+          m->b = b;
+          m->h = h;
+          m->r_lo = r_lo;
+          m->R = R;
+          m->kv_len = kv_len;
+          m->S = S;
+          m->mode = mode;
+          m->parts = parts;
+          m->first_cta = first_cta;
+          m->first_slot = first_slot;
+          m->unit = it * Hkv + h;
+          mbar_arrive_expect_tx(&full_bar[s],
+                                (uint32_t)n_pages_c * 2u * HALVES * box_bytes + (uint32_t)q_rows * D * 2u);
+        }
+        __syncwarp();
+        bool page_bad = false;
+        if (mine) {
+          if (pg < 0) {
+            page_bad = true;
+          } else {
+            unsigned char* dst = st + (is_v ? KVB : 0) + hf * HALF_B + (size_t)pi * P * 128;
+            tma_load_4d(dst, tm, hf * 64, row0, pg * Hkv + h, c3, &full_bar[s]);
+          }
+        }
+        for (int r = lane; r < q_rows; r += 32) {
+          const int rr = r_lo + r, sq = rr / G, g = rr - sq * G;
+          const __nv_bfloat16* src = p.q + (size_t)b * p.q_sb + (size_t)(h * G + g) * p.q_sh + (size_t)sq * p.q_ss;
+          bulk_g2s(qbuf + r * QS, src, D * 2u, &full_bar[s]);
+        }
+        if (__any_sync(0xffffffffu, page_bad)) {
+          if (lane == 0) raise_status(p.kv.status, PACE_DEV_BAD_INDEX);
+          ok = false;
+          break;
+        }
+        ++issued;
+        pg = pg_n;
+        lp = lp_n;
+        row0 = row0_n;
+      }
+      if (!ok) break;
+      ++part_idx;
+      j = 0;
+      if (++h == Hkv) {
+        h = 0;
+        ++it;
+        while (it < n_items && prefix[it + 1] == prefix[it]) ++it;
+        if (it >= n_items) break;
+        nch = (prefix[it + 1] - prefix[it]) / Hkv;
+      }
+    }
+    if (!ok && lane == 0) {
+      misc[0] = 1;
+      raise_status(p.kv.status, PACE_DEV_WAIT_TIMEOUT);
+      const int from = issued > n_stages ? issued - n_stages : 0;
+      for (int k = from; k < issued; ++k) mbar_wait(&full_bar[k % n_stages], (k / n_stages) & 1);
+    }
+    return;
+  }
+
+  // ================================= consumers =================================
+  const int mt = warp / NS, ns = warp - mt * NS;
+  const int qr = lane >> 2, qc = lane & 3;  // fragment row within 8, column pair
+  const int tw0 = ns * TW;
+  uint32_t qa[KS][4];
+  float o[ON][4];
+  float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+  int lim0 = INT_MAX, lim1 = INT_MAX;  // first key NOT visible to my two rows
+  int srow0 = 0, srow1 = 0, bcur = 0;  // query token of my two rows (additive-mask lookup)
+#pragma unroll
+  for (int n = 0; n < ON; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
+#pragma unroll
+  for (int k = 0; k < KS; ++k) qa[k][0] = qa[k][1] = qa[k][2] = qa[k][3] = 0u;
+
+  for (int i = 0; i < n_my; ++i) {
+    const int s = i % n_stages;
+    if (!mbar_wait(&full_bar[s], (i / n_stages) & 1)) {
+      if (lane == 0) raise_status(p.kv.status, PACE_DEV_WAIT_TIMEOUT);
+      return;
+    }
+    const unsigned char* st = ring + (size_t)s * p.stage_bytes;
+    const MetaM* meta = reinterpret_cast<const MetaM*>(st + 2 * KVB);
+    const int rows = meta->rows, tok0 = meta->tok0, flags = meta->flags, kvs = meta->kvs;
+
+    if (flags & 1) {
+      // ---- new unit part: Q fragments to registers, per-row visibility limits ----
+      const uint32_t qb = smem_u32(qbuf) + (uint32_t)(mt * 16) * QS;
+#pragma unroll
+      for (int k = 0; k < KS; ++k) {
+        const int mi = lane >> 3;
+        const int row = (mi & 1) * 8 + (lane & 7);
+        const int cch = k * 2 + (mi >> 1);
+        ldsm_x4(qb + row * QS + cch * 16, qa[k][0], qa[k][1], qa[k][2], qa[k][3]);
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(q_empty);
+      const int R = meta->R, r_lo = meta->r_lo, kv_len = meta->kv_len, S = meta->S;
+      const int r0 = r_lo + mt * 16 + qr, r1 = r0 + 8;
+      srow0 = r0 / G;
+      srow1 = r1 / G;
+      lim0 = (r0 < R) ? (p.causal ? kv_len - S + srow0 + 1 : kv_len) : INT_MAX;
+      lim1 = (r1 < R) ? (p.causal ? kv_len - S + srow1 + 1 : kv_len) : INT_MAX;
+      bcur = meta->b;
+      m0 = m1 = -INFINITY;
+      l0 = l1 = 0.f;
+#pragma unroll
+      for (int n = 0; n < ON; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
+    }
+
+    if (tw0 < rows) {  // this warp's token slice holds live keys
+      const uint32_t kb = smem_u32(st), vb = kb + KVB;
+      // ---- S = Q K^T ----
+      float sc[NT][4];
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt) {
+        sc[nt][0] = sc[nt][1] = sc[nt][2] = sc[nt][3] = 0.f;
+        const int row = tw0 + nt * 8 + (lane & 7);
+#pragma unroll
+        for (int k2 = 0; k2 < KS / 2; ++k2) {
+          const int cg = k2 * 4 + (lane >> 3);
+          uint32_t b0, b1, b2, b3;
+          ldsm_x4(kb + (cg >> 3) * HALF_B + row * 128 + (((cg & 7) ^ (row & 7)) << 4), b0, b1, b2, b3);
+          mma16816(sc[nt], qa[2 * k2], b0, b1);
+          mma16816(sc[nt], qa[2 * k2 + 1], b2, b3);
+        }
+      }
+      // ---- scale, additive mask, visibility ----
+      const int t_base = tok0 + tw0 + 2 * qc;  // key index of sc[0][0]
+      const bool need_mask = (tw0 + TW > rows) || (tok0 + tw0 < kvs) || (tok0 + tw0 + TW > min(lim0, lim1));
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) sc[nt][e] *= p.scale_log2;
+      }
+      if (p.mask) {
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int t = t_base + nt * 8 + (e & 1);
+            const int sq = (e < 2) ? srow0 : srow1;
+            if (t < tok0 + rows && sq < p.q_len) {
+              const size_t off = (size_t)bcur * p.mask_sb + (size_t)(p.mask_rows == 1 ? 0 : sq) * p.kv.fixed_len + t;
+              const float mv = p.mask_fp32 ? reinterpret_cast<const float*>(p.mask)[off]
+                                           : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.mask)[off]);
+              sc[nt][e] += mv * kLog2e;
+            }
+          }
+      }
+      if (need_mask) {
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int t = t_base + nt * 8 + (e & 1);
+            const int lim = (e < 2) ? lim0 : lim1;
+            if (t >= tok0 + rows || t < kvs || t >= lim) sc[nt][e] = -INFINITY;
+          }
+      }
+      // ---- online softmax ----
+      float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt) {
+        mx0 = fmaxf(mx0, fmaxf(sc[nt][0], sc[nt][1]));
+        mx1 = fmaxf(mx1, fmaxf(sc[nt][2], sc[nt][3]));
+      }
+      mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+      mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+      mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+      mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+      const float n0 = fmaxf(m0, mx0), n1 = fmaxf(m1, mx1);
+      const float a0 = (m0 == -INFINITY) ? 0.f : fast_exp2(m0 - n0);
+      const float a1 = (m1 == -INFINITY) ? 0.f : fast_exp2(m1 - n1);
+      const float e0 = (n0 == -INFINITY) ? 0.f : n0, e1 = (n1 == -INFINITY) ? 0.f : n1;
+      m0 = n0;
+      m1 = n1;
+      l0 *= a0;
+      l1 *= a1;
+#pragma unroll
+      for (int n = 0; n < ON; ++n) {
+        o[n][0] *= a0;
+        o[n][1] *= a0;
+        o[n][2] *= a1;
+        o[n][3] *= a1;
+      }
+      uint32_t pk[NT][2];
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt) {
+        const float p00 = fast_exp2(sc[nt][0] - e0), p01 = fast_exp2(sc[nt][1] - e0);
+        const float p10 = fast_exp2(sc[nt][2] - e1), p11 = fast_exp2(sc[nt][3] - e1);
+        l0 += p00 + p01;
+        l1 += p10 + p11;
+        pk[nt][0] = f2_to_bf2(p00, p01);
+        pk[nt][1] = f2_to_bf2(p10, p11);
+      }
+      // ---- O += P V ----
+      if constexpr (NT == 1) {
+#pragma unroll
+        for (int n4 = 0; n4 < ON / 4; ++n4) {
+          const int row = tw0 + (lane & 7);
+          const int cg = n4 * 4 + (lane >> 3);
+          uint32_t b0, b1, b2, b3;
+          ldsm_x4_t(vb + (cg >> 3) * HALF_B + row * 128 + (((cg & 7) ^ (row & 7)) << 4), b0, b1, b2, b3);
+          mma1688(o[n4 * 4 + 0], pk[0][0], pk[0][1], b0);
+          mma1688(o[n4 * 4 + 1], pk[0][0], pk[0][1], b1);
+          mma1688(o[n4 * 4 + 2], pk[0][0], pk[0][1], b2);
+          mma1688(o[n4 * 4 + 3], pk[0][0], pk[0][1], b3);
+        }
+      } else {
+#pragma unroll
+        for (int kb2 = 0; kb2 < NT / 2; ++kb2) {
+          if (tw0 + kb2 * 16 < rows) {  // warp-uniform: skip 16-token blocks past the chunk's keys
+            const uint32_t a[4] = {pk[2 * kb2][0], pk[2 * kb2][1], pk[2 * kb2 + 1][0], pk[2 * kb2 + 1][1]};
+            const int mi = lane >> 3;
+            const int row = tw0 + kb2 * 16 + (mi & 1) * 8 + (lane & 7);
+#pragma unroll
+            for (int n2 = 0; n2 < ON / 2; ++n2) {
+              const int cg = n2 * 2 + (mi >> 1);
+              uint32_t b0, b1, b2, b3;
+              ldsm_x4_t(vb + (cg >> 3) * HALF_B + row * 128 + (((cg & 7) ^ (row & 7)) << 4), b0, b1, b2, b3);
+              mma16816(o[2 * n2], a, b0, b1);
+              mma16816(o[2 * n2 + 1], a, b2, b3);
+            }
+          }
+        }
+      }
+    }
+    const int mb = meta->b, mh = meta->h, r_lo = meta->r_lo, R = meta->R, mode = meta->mode, parts = meta->parts,
+              first_cta = meta->first_cta, first_slot = meta->first_slot, unit = meta->unit;
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&empty_bar[s]);
+
+    if (flags & 2) {
+      // ======================= end of a unit part =======================
+      float lt0 = l0, lt1 = l1;
+      lt0 += __shfl_xor_sync(0xffffffffu, lt0, 1);
+      lt0 += __shfl_xor_sync(0xffffffffu, lt0, 2);
+      lt1 += __shfl_xor_sync(0xffffffffu, lt1, 1);
+      lt1 += __shfl_xor_sync(0xffffffffu, lt1, 2);
+      const int row0 = mt * 16 + qr, row1 = row0 + 8;
+      float* wo = mg_o + (size_t)ns * MR * D;
+#pragma unroll
+      for (int n = 0; n < ON; ++n) {
+        *reinterpret_cast<float2*>(wo + row0 * D + n * 8 + 2 * qc) = make_float2(o[n][0], o[n][1]);
+        *reinterpret_cast<float2*>(wo + row1 * D + n * 8 + 2 * qc) = make_float2(o[n][2], o[n][3]);
+      }
+      if (qc == 0) {
+        mg_m[ns * MR + row0] = m0;
+        mg_m[ns * MR + row1] = m1;
+        mg_l[ns * MR + row0] = lt0;
+        mg_l[ns * MR + row1] = lt1;
+      }
+      csync();
+      const int live = min(MR, R - r_lo);  // query rows of this tile that exist
+      float* rec = p.parts + ((size_t)cta * 2 + (mode == 2 ? 1 : 0)) * REC;
+      for (int oi = tid; oi < live * D; oi += kCThreads) {
+        const int row = oi / D, d = oi - row * D;
+        float M = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < NS; ++w) M = fmaxf(M, mg_m[w * MR + row]);
+        float num = 0.f, den = 0.f;
+        if (M != -INFINITY) {
+#pragma unroll
+          for (int w = 0; w < NS; ++w) {
+            const float mw = mg_m[w * MR + row];
+            const float f = (mw == -INFINITY) ? 0.f : fast_exp2(mw - M);
+            num += mg_o[((size_t)w * MR + row) * D + d] * f;
+            den += mg_l[w * MR + row] * f;
+          }
+        }
+        if (mode == 0) {
+          const int r = r_lo + row, sq = r / G, g = r - sq * G;
+          p.out[(size_t)mb * p.o_sb + (size_t)(mh * G + g) * p.o_sh + (size_t)sq * p.o_ss + d] =
+              __float2bfloat16(den > 0.f ? num / den : 0.f);
+        } else {
+          rec[row * D + d] = num;
+          if (d == 0) {
+            rec[MR * D + row] = M;
+            rec[MR * D + MR + row] = den;
+          }
+        }
+      }
+      if (mode != 0) {
+        __threadfence();
+        csync();
+        if (tid == 0) {
+          const int old = atomicAdd(&p.unit_count[unit], 1);
+          misc[1] = (old == parts - 1);
+          if (old == parts - 1) p.unit_count[unit] = 0;
+        }
+        csync();
+        if (misc[1]) {
+          __threadfence();
+          for (int oi = tid; oi < live * D; oi += kCThreads) {
+            const int row = oi / D, d = oi - row * D;
+            float M = -INFINITY;
+            for (int c = 0; c < parts; ++c) {
+              const float* r = p.parts + ((size_t)(first_cta + c) * 2 + (c == 0 ? first_slot : 0)) * REC;
+              M = fmaxf(M, __ldcg(r + MR * D + row));
+            }
+            float num = 0.f, den = 0.f;
+            if (M != -INFINITY) {
+              for (int c = 0; c < parts; ++c) {
+                const float* r = p.parts + ((size_t)(first_cta + c) * 2 + (c == 0 ? first_slot : 0)) * REC;
+                const float mc = __ldcg(r + MR * D + row);
+                const float f = (mc == -INFINITY) ? 0.f : fast_exp2(mc - M);
+                num += __ldcg(r + row * D + d) * f;
+                den += __ldcg(r + MR * D + MR + row) * f;
+              }
+            }
+            const int rr = r_lo + row, sq = rr / G, g = rr - sq * G;
+            p.out[(size_t)mb * p.o_sb + (size_t)(mh * G + g) * p.o_sh + (size_t)sq * p.o_ss + d] =
+                __float2bfloat16(den > 0.f ? num / den : 0.f);
+          }
+        }
+      }
+      csync();
+    }
+  }
+}
+
+// ------------------------------- host side -------------------------------
+typedef CUresult (*EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                             const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                             CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeFn encode_fn() {
+  static EncodeFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeFn>(ptr);
+  });
+  return fn;
+}
+
+// bf16 tensor seen as [c3][tiles][rows][D]; box = 64 columns x box_rows rows, 128-byte swizzle
+int make_map(CUtensorMap* tm, const void* base, int D, int rows, uint64_t tiles, uint64_t c3, uint64_t c3_stride_elems,
+             int box_rows) {
+  EncodeFn fn = encode_fn();
+  if (!fn) {
+    set_cuda_error(cudaErrorNotSupported, "cuTensorMapEncodeTiled entry point");
+    return PACE_ERR_CUDA;
+  }
+  const cuuint64_t dims[4] = {(cuuint64_t)D, (cuuint64_t)rows, tiles, c3};
+  const cuuint64_t strides[3] = {(cuuint64_t)D * 2, (cuuint64_t)rows * D * 2, c3_stride_elems * 2};
+  const cuuint32_t box[4] = {64, (cuuint32_t)box_rows, 1, 1};
+  const cuuint32_t estr[4] = {1, 1, 1, 1};
+  const CUresult r = fn(tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    set_cuda_error(cudaErrorInvalidValue, "cuTensorMapEncodeTiled");
+    return PACE_ERR_CUDA;
+  }
+  return PACE_OK;
+}
+
+struct PoolMapEntry {
+  const void* pages;
+  int geom[6];
+  CUtensorMap tm;
+};
+std::mutex g_map_mu;
+PoolMapEntry g_maps[16];
+int g_n_maps = 0, g_next_map = 0;
+
+int pool_map(const pace_kv_pool_t* pl, CUtensorMap* out) {
+  const int geom[6] = {pl->n_layers, pl->n_kv_heads, pl->head_dim, pl->page_tokens, pl->n_pages, 0};
+  std::lock_guard<std::mutex> lk(g_map_mu);
+  for (int i = 0; i < g_n_maps; ++i)
+    if (g_maps[i].pages == pl->pages && memcmp(g_maps[i].geom, geom, sizeof(geom)) == 0) {
+      *out = g_maps[i].tm;
+      return PACE_OK;
+    }
+  CUtensorMap tm;
+  const uint64_t tiles = (uint64_t)pl->n_pages * pl->n_kv_heads;
+  const int rc = make_map(&tm, pl->pages, pl->head_dim, pl->page_tokens, tiles, (uint64_t)pl->n_layers * 2,
+                          tiles * pl->page_tokens * pl->head_dim, pl->page_tokens <= kChunk ? pl->page_tokens : kChunk);
+  if (rc != PACE_OK) return rc;
+  PoolMapEntry& e = g_maps[g_next_map];
+  g_next_map = (g_next_map + 1) % 16;
+  if (g_n_maps < 16) ++g_n_maps;
+  e.pages = pl->pages;
+  memcpy(e.geom, geom, sizeof(geom));
+  e.tm = tm;
+  *out = tm;
+  return PACE_OK;
+}
+
+int sm_count_m() {
+  int dev = 0, n = 148;
+  if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+  return n;
+}
+
+template <int D, int MT, int NS>
+int launch_mma(MmaParams& p, const CUtensorMap& tmK, const CUtensorMap& tmV, int grid, cudaStream_t stream) {
+  constexpr int MR = 16 * MT, QS = D * 2 + 16;
+  p.stage_bytes = 2 * kChunk * D * 2 + (int)sizeof(MetaM);
+  // stage slots must keep the 1024-byte alignment the 128-byte swizzle pattern is anchored to
+  p.stage_bytes = (p.stage_bytes + 1023) / 1024 * 1024;
+  const int n_items = p.batch * p.n_qt;
+  const size_t fixed = (size_t)MR * QS + (size_t)NS * MR * (D + 2) * sizeof(float) +
+                       (2 * kMaxStagesM + 1) * sizeof(uint64_t) + 8 * sizeof(int) + (size_t)(n_items + 1) * sizeof(int) +
+                       64;
+  const size_t budget = 224 * 1024;
+  if (fixed + 2 * (size_t)p.stage_bytes > budget) return PACE_ERR_UNSUPPORTED;
+  int ns = (int)((budget - fixed) / p.stage_bytes);
+  if (ns > kMaxStagesM) ns = kMaxStagesM;
+  p.n_stages = ns;
+  size_t smem_bytes = (size_t)ns * p.stage_bytes + fixed;
+  smem_bytes = (smem_bytes + 15) / 16 * 16;
+  PACE_CUDA_TRY(cudaFuncSetAttribute(attn_mma_kernel<D, MT, NS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     226 * 1024));
+  attn_mma_kernel<D, MT, NS><<<grid, kThreadsM, smem_bytes, stream>>>(p, tmK, tmV);
+  PACE_LAUNCH_CHECK("attn_mma_kernel");
+  return PACE_OK;
+}
+
+}  // namespace
+
+uint64_t mma_workspace_bytes(int n_q_heads, int n_kv_heads, int head_dim, int q_len) {
+  const int G = n_q_heads / (n_kv_heads > 0 ? n_kv_heads : 1);
+  const int M = G * q_len;
+  const int MT = M <= 16 ? 1 : M <= 32 ? 2 : M <= 64 ? 4 : 8;
+  return kWorkspaceCounterBytes + (uint64_t)sm_count_m() * 2 * (16 * MT) * (head_dim + 2) * sizeof(float) + 256;
+}
+
+// One launch per slice of the batch small enough for the shared-memory prefix array.
+int run_mma(const KVView& kv, const CUtensorMap& tmK, const CUtensorMap& tmV, int c3_k, int c3_v, int batch,
+            int n_q_heads, int q_len, const void* q, int64_t q_sb, int64_t q_sh, int64_t q_ss, void* out, int64_t o_sb,
+            int64_t o_sh, int64_t o_ss, const int32_t* kv_start, const int32_t* q_lens, int causal, float scale,
+            const void* mask, int mask_fp32, int mask_rows, int64_t mask_sb, void* workspace, uint64_t workspace_bytes,
+            cudaStream_t stream) {
+  const int D = kv.head_dim, Hkv = kv.n_kv_heads;
+  if (batch <= 0 || q_len <= 0) return PACE_OK;
+  if (n_q_heads % Hkv) return PACE_ERR_INVALID;
+  const int G = n_q_heads / Hkv;
+  if (!q || !out || ((uintptr_t)q & 15) || (q_sb & 7) || (q_sh & 7) || (q_ss & 7)) return PACE_ERR_INVALID;
+  if (!workspace || ((uintptr_t)workspace & 15)) return PACE_ERR_INVALID;
+  const int M = G * q_len;
+  const int MT = M <= 16 ? 1 : M <= 32 ? 2 : M <= 64 ? 4 : 8;
+  const int MR = 16 * MT;
+  int grid = sm_count_m();
+  if (const char* g = getenv("PACE_DECODE_GRID")) {  // test hook: other partitions of the same work
+    const int v = atoi(g);
+    if (v > 0 && v < grid) grid = v;
+  }
+  if (workspace_bytes < kWorkspaceCounterBytes + (uint64_t)grid * 2 * MR * (D + 2) * sizeof(float))
+    return PACE_ERR_INVALID;
+
+  MmaParams p;
+  p.kv = kv;
+  p.c3_k = c3_k;
+  p.c3_v = c3_v;
+  p.q_sb = q_sb;
+  p.q_sh = q_sh;
+  p.q_ss = q_ss;
+  p.o_sb = o_sb;
+  p.o_sh = o_sh;
+  p.o_ss = o_ss;
+  p.q_len = q_len;
+  p.G = G;
+  p.n_qt = (M + MR - 1) / MR;
+  p.causal = causal;
+  p.scale_log2 = (scale > 0.f ? scale : 1.0f / sqrtf((float)D)) * kLog2e;
+  p.unit_count = reinterpret_cast<int32_t*>(workspace);
+  p.parts = reinterpret_cast<float*>(static_cast<char*>(workspace) + kWorkspaceCounterBytes);
+  p.mask = mask;
+  p.mask_fp32 = mask_fp32;
+  p.mask_rows = mask_rows;
+  p.mask_sb = mask_sb;
+  const int P = kv.page_tokens;
+  const int HALVES = D / 64;
+  if (P <= kChunk) {
+    const int most = 16 / HALVES;  // one producer lane per (page, K|V, column block)
+    p.pages_per_chunk = kChunk / P < most ? kChunk / P : most;
+    p.chunks_per_page = 0;
+    p.chunk_tokens = p.pages_per_chunk * P;
+    p.box_rows = P;
+  } else {
+    p.pages_per_chunk = 0;
+    p.chunks_per_page = (P + kChunk - 1) / kChunk;
+    p.chunk_tokens = kChunk;
+    p.box_rows = kChunk;
+  }
+  int per_launch = kMaxItems / p.n_qt;
+  if (per_launch < 1) return PACE_ERR_UNSUPPORTED;
+  if ((uint64_t)per_launch * p.n_qt * Hkv * sizeof(int32_t) > kWorkspaceCounterBytes)
+    per_launch = (int)(kWorkspaceCounterBytes / sizeof(int32_t) / ((uint64_t)p.n_qt * Hkv));
+  if (per_launch < 1) return PACE_ERR_UNSUPPORTED;
+  for (int b0 = 0; b0 < batch; b0 += per_launch) {
+    const int nb = batch - b0 < per_launch ? batch - b0 : per_launch;
+    p.batch = nb;
+    p.kv.seq_ids = kv.seq_ids ? kv.seq_ids + b0 : nullptr;
+    if (!kv.seq_ids && b0 > 0) return PACE_ERR_UNSUPPORTED;  // the dense form is never that large
+    p.q = (const __nv_bfloat16*)q + (size_t)b0 * q_sb;
+    p.out = (__nv_bfloat16*)out + (size_t)b0 * o_sb;
+    p.kv_start = kv_start ? kv_start + b0 : nullptr;
+    p.q_lens = q_lens ? q_lens + b0 : nullptr;
+    int rc = PACE_ERR_UNSUPPORTED;
+#define PACE_MMA_CASE(DD, MM, NN) \
+  if (D == DD && MT == MM) rc = launch_mma<DD, MM, NN>(p, tmK, tmV, grid, stream);
+    PACE_MMA_CASE(128, 1, 8)
+    PACE_MMA_CASE(128, 2, 4)
+    PACE_MMA_CASE(128, 4, 2)
+    PACE_MMA_CASE(128, 8, 1)
+    PACE_MMA_CASE(64, 1, 8)
+    PACE_MMA_CASE(64, 2, 4)
+    PACE_MMA_CASE(64, 4, 2)
+    PACE_MMA_CASE(64, 8, 1)
+#undef PACE_MMA_CASE
+    if (rc != PACE_OK) return rc;
+  }
+  return PACE_OK;
+}
+
+int run_mma_paged(const pace_attn_args_t* a, int causal, cudaStream_t stream) {
+  if (!a || !a->pool || a->q_len < 1 || a->layer < 0 || a->layer >= a->pool->n_layers || !a->seq_ids)
+    return PACE_ERR_INVALID;
+  if (a->batch > a->pool->max_seqs) return PACE_ERR_INVALID;
+  CUtensorMap tm;
+  const int rc = pool_map(a->pool, &tm);
+  if (rc != PACE_OK) return rc;
+  const KVView kv = make_view(a->pool, a->layer, a->seq_ids);
+  return run_mma(kv, tm, tm, a->layer * 2, a->layer * 2 + 1, a->batch, a->n_q_heads, a->q_len, a->q, a->q_stride_b,
+                 a->q_stride_h, a->q_stride_s, a->out, a->o_stride_b, a->o_stride_h, a->o_stride_s, a->kv_start,
+                 a->q_lens, causal, a->scale, nullptr, 0, 1, 0, a->workspace, a->workspace_bytes, stream);
+}
+
+}  // namespace pace
+
+using namespace pace;
+
+extern "C" int pace_attn_verify(const pace_attn_args_t* a, void* stream) {
+  return run_mma_paged(a, 1, (cudaStream_t)stream);
+}
+extern "C" int pace_attn_prefill(const pace_attn_args_t* a, void* stream) {
+  return run_mma_paged(a, 1, (cudaStream_t)stream);
+}
+
+extern "C" int pace_attention_dense(const void* q, const void* k, const void* v, const void* mask,
+                                    int32_t mask_is_fp32, int32_t mask_rows, void* out, int32_t B, int32_t N,
+                                    int32_t Nkv, int32_t S, int32_t L, int32_t H, void* workspace,
+                                    uint64_t workspace_bytes, void* stream) {
+  if (!q || !k || !v || !out || B <= 0 || N <= 0 || Nkv <= 0 || S <= 0 || L <= 0) return PACE_ERR_INVALID;
+  if (H != 64 && H != 128) return PACE_ERR_UNSUPPORTED;
+  if (N % Nkv || (mask && mask_rows != 1 && mask_rows != S)) return PACE_ERR_INVALID;
+  if (((uintptr_t)k & 15) || ((uintptr_t)v & 15)) return PACE_ERR_INVALID;
+  KVView kv;
+  kv.k = (const __nv_bfloat16*)k;
+  kv.v = (const __nv_bfloat16*)v;
+  kv.block_table = nullptr;
+  kv.seq_ids = nullptr;
+  kv.seq_len = nullptr;
+  kv.status = nullptr;
+  kv.fixed_len = L;
+  kv.page_tokens = L;
+  kv.n_kv_heads = Nkv;
+  kv.head_dim = H;
+  kv.max_pages_per_seq = 1;
+  kv.max_seqs = B;
+  kv.n_pages = B;
+  CUtensorMap tmK, tmV;
+  const int box_rows = L <= kChunk ? L : kChunk;
+  int rc = make_map(&tmK, k, H, L, (uint64_t)B * Nkv, 1, (uint64_t)B * Nkv * L * H, box_rows);
+  if (rc != PACE_OK) return rc;
+  rc = make_map(&tmV, v, H, L, (uint64_t)B * Nkv, 1, (uint64_t)B * Nkv * L * H, box_rows);
+  if (rc != PACE_OK) return rc;
+  return run_mma(kv, tmK, tmV, 0, 0, B, N, S, q, (int64_t)N * S * H, (int64_t)S * H, H, out, (int64_t)N * S * H,
+                 (int64_t)S * H, H, nullptr, nullptr, /*causal=*/0, 0.f, mask, mask_is_fp32, mask_rows,
+                 (int64_t)mask_rows * L, workspace, workspace_bytes, (cudaStream_t)stream);
+}

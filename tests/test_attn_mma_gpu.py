@@ -1,0 +1,203 @@
+"""Tensor-core attention (verify / prefill / dense op / packed-GQA decode) vs the CPU oracle."""
+import os
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+G_DIR = os.path.join(os.path.dirname(__file__), "golden")
+DEV = "cuda:0"
+MAX_ABS, MEAN_ABS = 2e-2, 2e-3          # parity budget for bf16 caches
+
+
+class Cfg:
+    def __init__(self, n):
+        self.num_hidden_layers = n
+
+
+def _fill(mgr, layer, ks, vs):
+    B = len(ks)
+    Lmax = max(k.shape[1] for k in ks)
+    H, D = ks[0].shape[0], ks[0].shape[2]
+    kp = torch.zeros(B, H, Lmax, D, dtype=torch.bfloat16, device=DEV)
+    vp = torch.zeros_like(kp)
+    for b in range(B):
+        kp[b, :, : ks[b].shape[1]] = ks[b]
+        vp[b, :, : vs[b].shape[1]] = vs[b]
+    return mgr[layer].update_cache(kp, vp, concat_dim=2, n_new_per_seq=[k.shape[1] for k in ks])
+
+
+def _oracle(q, ks, vs, left_pad=None, q_lens=None):
+    """q [B,Hq,S,D]; the S (or q_lens[b]) newest cached tokens are the queries' own."""
+    from oracle.attention_ref import attend_over_cache
+    outs = []
+    for b in range(len(ks)):
+        L = ks[b].shape[1]
+        s = q.shape[2] if q_lens is None else q_lens[b]
+        o = attend_over_cache(q[b:b + 1, :, :s].cpu(), ks[b][None].cpu(), vs[b][None].cpu(), L,
+                              0 if left_pad is None else left_pad[b], "native")[0].float()
+        outs.append(o)
+    return outs
+
+
+def _check(got, want):
+    err = (got.float().cpu() - want).abs()
+    assert err.max().item() < MAX_ABS, f"max-abs {err.max().item()}"
+    assert err.mean().item() < MEAN_ABS, f"mean-abs {err.mean().item()}"
+
+
+def test_verify_matches_reference_golden():
+    from pace_b200.llm.cache import KVCacheManager, KVCacheType
+    from pace_b200.ops import MultiHeadAttention
+    case = torch.load(os.path.join(G_DIR, "verify_case.pt"))
+    B, S = case["B"], case["S"]
+    mgr = KVCacheManager(Cfg(1), case["max_len"], KVCacheType.BMC)
+    ks = [case["k_cache"][b][:, : case["lens"][b]].to(DEV) for b in range(B)]
+    vs = [case["v_cache"][b][:, : case["lens"][b]].to(DEV) for b in range(B)]
+    _fill(mgr, 0, ks, vs)
+    K, V = mgr[0].update_cache(torch.stack(case["k_new"]).to(DEV), torch.stack(case["v_new"]).to(DEV), concat_dim=2)
+    q = torch.stack(case["q"]).to(DEV)
+    kv_start = torch.tensor(case["left_pad"], dtype=torch.int32, device=DEV)
+    out = MultiHeadAttention()(q, K, V, kv_start=kv_start)
+    assert out.shape == q.shape
+    _check(out, torch.stack(case["out"]).float())
+    dk, dv = mgr[0].read_dense()
+    for b in range(B):
+        n = case["lens"][b] + S
+        assert torch.equal(dk[b, :, :n].cpu(), case["k_cache"][b][:, :n])
+    mgr.pool.check_status()
+
+
+CASES = [
+    # B, Hq, Hkv, D, max_len, lens (query tokens included), S
+    (16, 32, 8, 128, 1200, [1033] * 16, 9),                 # PARD verify, config-4 target shape
+    (4, 32, 8, 64, 1200, [1033, 900, 77, 9], 9),            # draft-model head_dim
+    (2, 8, 2, 128, 300, [5, 250], 5),                       # M = 20: 2 x 4 warp grid
+    (2, 8, 2, 128, 300, [2, 250], 2),                       # M = 8: packed into one tile
+    (3, 8, 8, 64, 200, [40, 13, 199], 13),                  # MHA (G = 1)
+    (2, 16, 2, 128, 400, [130, 399], 33),                   # M = 264: several query tiles
+    (2, 32, 8, 128, 2100, [512, 1536], 512),                # a 512-token prefill chunk (first chunk / with past)
+    (1, 8, 2, 64, 700, [601], 130),                         # prefill, D = 64
+    (1, 8, 2, 128, 40000, [20000], 9),                      # long context: unit split over many CTAs
+    (2, 32, 8, 128, 9000, [8190, 4097], 9),                 # page_tokens 94 > 64: sub-page chunks
+]
+
+
+@pytest.mark.parametrize("B,Hq,Hkv,D,max_len,lens,S", CASES)
+def test_multi_query_matches_oracle(B, Hq, Hkv, D, max_len, lens, S):
+    from pace_b200.llm.cache import KVCacheManager, KVCacheType
+    from pace_b200.ops import MultiHeadAttention
+    g = torch.Generator().manual_seed(B * 1000 + Hq + D + S)
+    ks = [torch.randn(Hkv, L, D, generator=g).bfloat16().to(DEV) for L in lens]
+    vs = [torch.randn(Hkv, L, D, generator=g).bfloat16().to(DEV) for L in lens]
+    # model layout: [B, S, Hq, D] storage viewed as [B, Hq, S, D]
+    q = torch.randn(B, S, Hq, D, generator=g).bfloat16().to(DEV).transpose(1, 2)
+    mgr = KVCacheManager(Cfg(2), max_len, KVCacheType.BMC)
+    K, V = _fill(mgr, 1, ks, vs)
+    mha = MultiHeadAttention()
+    out = mha(q, K, V)
+    want = _oracle(q, ks, vs)
+    for b in range(B):
+        _check(out[b], want[b])
+    assert torch.equal(out, mha(q, K, V))
+    mgr.pool.check_status()
+
+
+def test_ragged_query_counts_and_left_padding():
+    from pace_b200.llm.cache import KVCacheManager, KVCacheType
+    from pace_b200.ops import MultiHeadAttention
+    g = torch.Generator().manual_seed(77)
+    B, Hq, Hkv, D, S = 3, 8, 2, 128, 9
+    lens, q_lens, pads = [100, 64, 37], [9, 4, 1], [0, 11, 30]
+    ks = [torch.randn(Hkv, L, D, generator=g).bfloat16().to(DEV) for L in lens]
+    vs = [torch.randn(Hkv, L, D, generator=g).bfloat16().to(DEV) for L in lens]
+    q = torch.randn(B, Hq, S, D, generator=g).bfloat16().to(DEV)
+    mgr = KVCacheManager(Cfg(1), 128, KVCacheType.DYNAMIC)
+    K, V = _fill(mgr, 0, ks, vs)
+    out = MultiHeadAttention()(q, K, V, kv_start=torch.tensor(pads, dtype=torch.int32, device=DEV),
+                               q_lens=torch.tensor(q_lens, dtype=torch.int32, device=DEV))
+    want = _oracle(q, ks, vs, left_pad=pads, q_lens=q_lens)
+    for b in range(B):
+        _check(out[b, :, : q_lens[b]], want[b])
+    mgr.pool.check_status()
+
+
+@pytest.mark.parametrize("impl", ["mma", "cuda"])
+@pytest.mark.parametrize("B,Hq,Hkv,D,max_len,lens", [
+    (4, 32, 8, 128, 1025, [128, 1024, 577, 300]),
+    (32, 32, 8, 128, 768, [513 + i for i in range(32)]),
+    (3, 8, 2, 64, 100, [9, 10, 11]),
+    (1, 8, 2, 128, 40000, [33000]),
+    (2, 32, 4, 128, 500, [200, 437]),
+])
+def test_decode_kernels_agree_with_oracle(monkeypatch, impl, B, Hq, Hkv, D, max_len, lens):
+    from pace_b200.llm.cache import KVCacheManager, KVCacheType
+    from pace_b200.ops import MultiHeadAttention
+    monkeypatch.setenv("PACE_DECODE_IMPL", impl)
+    g = torch.Generator().manual_seed(B + Hq + D)
+    ks = [torch.randn(Hkv, L, D, generator=g).bfloat16().to(DEV) for L in lens]
+    vs = [torch.randn(Hkv, L, D, generator=g).bfloat16().to(DEV) for L in lens]
+    q = torch.randn(B, Hq, 1, D, generator=g).bfloat16().to(DEV)
+    mgr = KVCacheManager(Cfg(1), max_len, KVCacheType.BMC)
+    K, V = _fill(mgr, 0, ks, vs)
+    out = MultiHeadAttention()(q, K, V)
+    want = _oracle(q, ks, vs)
+    for b in range(B):
+        _check(out[b], want[b])
+    mgr.pool.check_status()
+
+
+# ---- the dense form: the reference custom op's operands (reference tests/ops/test_sdpa.py:79-127) ----
+@pytest.mark.parametrize("B,N,S,H,L", [(1, 1, 1, 64, 1), (2, 16, 1, 128, 512), (2, 16, 128, 64, 512),
+                                       (1, 32, 128, 128, 2048), (3, 4, 7, 128, 33), (32, 1, 1, 64, 512)])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_dense_op_matches_reference_restatements(B, N, S, H, L, dtype):
+    from pace_b200.ops import MultiHeadAttention
+    from oracle.attention_ref import sdpa_native, sdpa_jit_restated
+    g = torch.Generator().manual_seed(B + N + S + H + L)
+    q = torch.randn(B, N, S, H, generator=g).to(dtype)
+    k = torch.randn(B, N, L, H, generator=g).to(dtype)
+    v = torch.randn(B, N, L, H, generator=g).to(dtype)
+    m = torch.randn(B, 1, 1, L, generator=g).to(dtype)
+    out = MultiHeadAttention()(q.to(DEV), k.to(DEV), v.to(DEV), attention_mask=m.to(DEV))
+    assert out.dtype == dtype and out.shape == q.shape
+    # the reference pins its op at 1e-1 for bf16 against both of these (test_sdpa.py:113-127);
+    # bf16 inputs are what the kernel computes on, so the fp32 case is compared at bf16 precision
+    qb, kb, vb, mb = (t.bfloat16() for t in (q, k, v, m))
+    for want in (sdpa_native(qb, kb, vb, mb), sdpa_jit_restated(qb, kb, vb, mb)):
+        err = (out.float().cpu() - want.float()).abs()
+        assert err.max().item() < 4e-2 and err.mean().item() < 4e-3, (err.max().item(), err.mean().item())
+
+
+def test_dense_op_full_mask_rows_and_gqa():
+    from pace_b200.ops import MultiHeadAttention
+    from oracle.attention_ref import sdpa_native, repeat_kv, additive_mask_4d
+    g = torch.Generator().manual_seed(9)
+    B, N, Nkv, S, H, L = 2, 8, 2, 6, 128, 70
+    q = torch.randn(B, N, S, H, generator=g).bfloat16()
+    k = torch.randn(B, Nkv, L, H, generator=g).bfloat16()
+    v = torch.randn(B, Nkv, L, H, generator=g).bfloat16()
+    m2 = torch.ones(B, L, dtype=torch.long)
+    m2[1, :9] = 0
+    m4 = additive_mask_4d(m2, S, L, torch.bfloat16)          # [B,1,S,L] causal + padding, as the model builds it
+    out = MultiHeadAttention()(q.to(DEV), k.to(DEV), v.to(DEV), attention_mask=m4.to(DEV))
+    want = sdpa_native(q, repeat_kv(k, 4), repeat_kv(v, 4), m4)
+    _check(out, want.float())
+
+
+def test_dense_op_error_surface():
+    # messages the reference's tests look for (tests/ops/test_sdpa.py:129-208)
+    from pace_b200.ops import MultiHeadAttention
+    mha = MultiHeadAttention()
+    q = torch.randn(2, 4, 8, 64, device=DEV).bfloat16()
+    k = torch.randn(2, 4, 16, 64, device=DEV).bfloat16()
+    m = torch.randn(2, 1, 1, 16, device=DEV).bfloat16()
+    with pytest.raises(RuntimeError, match="attention requires 4D inputs"):
+        mha(q.view(8, 8, 64), k, k, attention_mask=m)
+    with pytest.raises(RuntimeError, match="attention requires 4D inputs"):
+        mha(q, k, k, attention_mask=m.view(2, 16))
+    with pytest.raises(RuntimeError, match="only support the dtypes Float and BF16 types for input"):
+        mha(q.to(torch.int8), k.to(torch.int8), k.to(torch.int8), attention_mask=m)
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        mha(q.cpu(), k.cpu(), k.cpu(), attention_mask=m.cpu())
