@@ -16,7 +16,8 @@ OUT = os.path.join(HERE, "pace_b200", "libpace_b200.so")
 SOURCES = ["kv_pool.cu", "attn_decode.cu", "attn_mma.cu", "attn_api.cu"]
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
-         "--use_fast_math", "-Xcompiler", "-fPIC", "-I", os.path.join(ROOT, "include"), "-I", CSRC]
+         "--use_fast_math", "-Xcompiler", "-fPIC", "-I", os.path.join(ROOT, "include"), "-I", CSRC] + \
+    os.environ.get("PACE_NVCC_EXTRA", "").split()
 
 
 def _newer(a, b):

@@ -229,7 +229,8 @@ __global__ void __launch_bounds__(kThreads, 1) attn_decode_kernel(const DecodePa
     const int is_v = lane & 1;
     const bool copier = whole_pages ? (lane < 2 * p.pages_per_chunk) : (lane < 2);
     const __nv_bfloat16* src_base = is_v ? p.kv.v : p.kv.k;
-    const int MP = p.kv.max_pages_per_seq;
+    PageWindow pw;
+    const int win_step = whole_pages ? (32 / p.pages_per_chunk) * p.pages_per_chunk : 32;
     bool ok = true;
     int i = 0, issued = 0;
     while (i < n_my && ok) {
@@ -238,7 +239,6 @@ __global__ void __launch_bounds__(kThreads, 1) attn_decode_kernel(const DecodePa
       const int len = view_len(p.kv, slot);
       const int kvs = p.kv_start ? p.kv_start[b] : 0;
       const int j_end = min(nch, j + (n_my - i));
-      const int32_t* row_tbl = p.kv.block_table ? p.kv.block_table + (size_t)slot * MP : nullptr;
       // how the part is finished: whole unit here, or a partial record for the last arriver
       int mode = 0, parts = 1, first_cta = cta, first_slot = 0;
       {
@@ -251,22 +251,16 @@ __global__ void __launch_bounds__(kThreads, 1) attn_decode_kernel(const DecodePa
           mode = (cta == first_cta) ? (first_slot ? 2 : 1) : 1;
         }
       }
-      // chunk -> (logical page, first row): incremental from here on
+      // chunk -> (first logical page, first row): incremental from here on
       int lp, row0;
       if (whole_pages) {
-        lp = j * p.pages_per_chunk + pi;
+        lp = j * p.pages_per_chunk;
         row0 = 0;
       } else {
         lp = j / p.chunks_per_page;
         row0 = (j - lp * p.chunks_per_page) * kChunkRows;
       }
-      auto page_of = [&](int l) -> int {
-        if (!row_tbl) return slot;
-        if (l >= MP) return -1;
-        const int pg = __ldg(row_tbl + l);
-        return (pg < 0 || pg >= p.kv.n_pages) ? -1 : pg;
-      };
-      int pg = copier ? page_of(lp) : 0;
+      pw.start(p.kv, slot, lp, win_step, lane);
       for (bool first = true; j < j_end; ++j, ++i, first = false) {
         // prefetch the next chunk's page id before blocking on the ring
         int lp_n = lp, row0_n = row0;
@@ -276,7 +270,6 @@ __global__ void __launch_bounds__(kThreads, 1) attn_decode_kernel(const DecodePa
           row0_n = row0 + kChunkRows;
           if (row0_n >= P) { row0_n = 0; lp_n = lp + 1; }
         }
-        const int pg_n = (copier && j + 1 < j_end) ? (lp_n == lp ? pg : page_of(lp_n)) : 0;
         const int s = i % n_stages;
         if (i >= n_stages && !mbar_wait(&empty_bar[s], ((i / n_stages) - 1) & 1)) { ok = false; break; }
         const int tok0 = whole_pages ? j * p.chunk_tokens : lp * P + row0;
@@ -301,6 +294,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_decode_kernel(const DecodePa
         }
         __syncwarp();
         bool page_bad = false;
+        const int pg = pw.get(lp + pi, lp, lane);
         if (copier && my_rows > 0) {
           if (pg < 0) {
             page_bad = true;
@@ -320,7 +314,6 @@ __global__ void __launch_bounds__(kThreads, 1) attn_decode_kernel(const DecodePa
           break;
         }
         ++issued;
-        pg = pg_n;
         lp = lp_n;
         row0 = row0_n;
       }
@@ -686,8 +679,7 @@ uint64_t decode_workspace_bytes(int batch, int n_q_heads, int n_kv_heads, int he
 
 namespace pace {
 int decode_cuda_cores(const pace_attn_args_t* a, void* stream) {
-  if (!a || !a->pool || a->q_len != 1 || a->layer < 0 || a->layer >= a->pool->n_layers || !a->seq_ids)
-    return PACE_ERR_INVALID;
+  if (!a || !a->pool || a->q_len != 1 || a->layer < 0 || a->layer >= a->pool->n_layers) return PACE_ERR_INVALID;
   if (a->batch > a->pool->max_seqs) return PACE_ERR_INVALID;
   const KVView kv = make_view(a->pool, a->layer, a->seq_ids);
   return run_decode(kv, a->batch, a->n_q_heads, a->q, a->q_stride_b, a->q_stride_h, a->out, a->o_stride_b,

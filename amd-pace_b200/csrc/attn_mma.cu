@@ -33,10 +33,10 @@ namespace {
 
 constexpr int kWarps = 8;
 constexpr int kCThreads = kWarps * 32;
-constexpr int kThreadsM = kCThreads + 32;
+constexpr int kThreadsM = kCThreads + 64;  // + producer warp + epilogue warp
 constexpr int kChunk = 64;
 constexpr int kMaxStagesM = 8;
-constexpr int kMaxItems = 4096;
+constexpr int kMaxItems = 1024;
 
 struct MetaM {  // one 64-byte record per ring stage, written by the producer
   int rows, tok0, flags, kvs;
@@ -59,7 +59,7 @@ struct MmaParams {
   float scale_log2;
   float* parts;
   int32_t* unit_count;
-  int chunk_tokens, pages_per_chunk, chunks_per_page, box_rows, n_stages, stage_bytes;
+  int chunk_tokens, pages_per_chunk, chunks_per_page, box_rows, n_stages, live_max;
   const void* mask;  // additive [B,1,mask_rows,L] or null
   int mask_fp32, mask_rows;
   int64_t mask_sb;
@@ -86,13 +86,13 @@ __device__ __forceinline__ void ldsm_x4_t(uint32_t addr, uint32_t& r0, uint32_t&
                : "r"(addr));
 }
 __device__ __forceinline__ void mma16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-  asm volatile(
+  asm(
       "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
       : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 __device__ __forceinline__ void mma1688(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t b0) {
-  asm volatile("mma.sync.aligned.m16n8k8.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5}, {%6}, {%0,%1,%2,%3};"
+  asm("mma.sync.aligned.m16n8k8.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5}, {%6}, {%0,%1,%2,%3};"
                : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
                : "r"(a0), "r"(a1), "r"(b0));
 }
@@ -104,6 +104,128 @@ __device__ __forceinline__ void tma_load_4d(void* smem_dst, const CUtensorMap* t
       "[%2];" ::"r"(smem_u32(smem_dst)),
       "l"(tm), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
       : "memory");
+}
+
+// Shared-memory carve-up, computed identically on host and device.
+struct SmemPlan {
+  int ring, metas, qbuf, mg, res, bars, misc, per_b, prefix, total;
+  int res_slot_bytes, n_res, mg_stride;
+};
+__host__ __device__ inline SmemPlan plan_smem(int D, int MT, int NS, int n_stages, int live_max, int batch,
+                                              int n_items) {
+  SmemPlan s;
+  const int MR = 16 * MT, QS = D * 2 + 16;
+  int off = 0;
+  auto take = [&](int bytes, int align) {
+    off = (off + align - 1) / align * align;
+    const int o = off;
+    off += bytes;
+    return o;
+  };
+  s.ring = take(n_stages * 2 * kChunk * D * 2, 1024);
+  s.qbuf = take(MR * QS, 128);
+  s.mg_stride = D + 8;  // floats; the pad spreads the rows of a fragment over the banks
+  s.mg = take(NS > 1 ? NS * live_max * (s.mg_stride + 2) * 4 : 16, 16);
+  s.n_res = live_max <= 64 ? 2 : 1;
+  s.res_slot_bytes = (live_max * (D + 2) * 4 + 64 + 15) / 16 * 16;
+  s.res = take(s.n_res * s.res_slot_bytes, 16);
+  s.metas = take(kMaxStagesM * (int)sizeof(MetaM), 64);
+  s.bars = take((2 * kMaxStagesM + 1 + 4) * 8, 8);
+  s.misc = take(8 * 4, 4);
+  s.per_b = take(batch * 4 * 4, 4);
+  s.prefix = take((n_items + 1) * 4, 4);
+  s.total = (off + 15) / 16 * 16;
+  return s;
+}
+
+struct ResMeta {  // trails each result slot
+  int b, h, r_lo, live, mode, parts, first_cta, first_slot, unit, last_part, pad[6];
+};
+static_assert(sizeof(ResMeta) == 64, "ResMeta is one 64-byte line");
+
+// Takes one finished unit part from its shared-memory result slot to global memory: the output
+// rows (mode 0), or an fp32 partial plus the arrival count and, for the last arriver, the merge
+// of all partials.  Run by a group of NTHR threads: one warp (WARP) or the eight consumer warps.
+template <int D, int MR, int NTHR, bool WARP>
+__device__ __forceinline__ void publish_part(const MmaParams& p, const ResMeta& rm, const float* rnum, const float* rM,
+                                             const float* rden, int t, int cta, int* flag) {
+  constexpr int REC = MR * (D + 2);
+  const int G = p.G, live = rm.live;
+  auto group_sync = [&]() {
+    if (WARP) __syncwarp(); else csync();
+  };
+  if (rm.mode == 0) {
+    for (int oi = t * 2; oi < live * D; oi += NTHR * 2) {
+      const int row = oi / D, d = oi - row * D;
+      const float den = rden[row];
+      const float inv = den > 0.f ? 1.0f / den : 0.f;
+      const int r = rm.r_lo + row, sq = r / G, g = r - sq * G;
+      *reinterpret_cast<uint32_t*>(p.out + (size_t)rm.b * p.o_sb + (size_t)(rm.h * G + g) * p.o_sh +
+                                   (size_t)sq * p.o_ss + d) = f2_to_bf2(rnum[oi] * inv, rnum[oi + 1] * inv);
+    }
+    return;
+  }
+  float* rec = p.parts + ((size_t)cta * 2 + (rm.mode == 2 ? 1 : 0)) * REC;
+  for (int oi = t * 2; oi < live * D; oi += NTHR * 2)
+    *reinterpret_cast<float2*>(rec + oi) = *reinterpret_cast<const float2*>(rnum + oi);
+  for (int row = t; row < live; row += NTHR) {
+    rec[MR * D + row] = rM[row];
+    rec[MR * D + MR + row] = rden[row];
+  }
+  __threadfence();
+  group_sync();
+  int is_last = 0;
+  if (t == 0) {
+    const int old = atomicAdd(&p.unit_count[rm.unit], 1);
+    is_last = (old == rm.parts - 1);
+    if (is_last) p.unit_count[rm.unit] = 0;  // ready for the next launch
+    if (!WARP) *flag = is_last;
+  }
+  if (WARP) {
+    is_last = __shfl_sync(0xffffffffu, is_last, 0);
+  } else {
+    csync();
+    is_last = *flag;
+  }
+  if (!is_last) return;
+  __threadfence();
+  for (int oi = t * 2; oi < live * D; oi += NTHR * 2) {
+    const int row = oi / D, d = oi - row * D;
+    float M = -INFINITY, n0 = 0.f, n1 = 0.f, den = 0.f;
+    for (int c0 = 0; c0 < rm.parts; c0 += 4) {  // four partials' loads in flight at a time
+      float mc[4], dc[4];
+      float2 nn[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const int c = c0 + k;
+        mc[k] = -INFINITY;
+        dc[k] = 0.f;
+        nn[k] = make_float2(0.f, 0.f);
+        if (c < rm.parts) {
+          const float* r = p.parts + ((size_t)(rm.first_cta + c) * 2 + (c == 0 ? rm.first_slot : 0)) * REC;
+          mc[k] = __ldcg(r + MR * D + row);
+          dc[k] = __ldcg(r + MR * D + MR + row);
+          nn[k] = __ldcg(reinterpret_cast<const float2*>(r + oi));
+        }
+      }
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const float Mn = fmaxf(M, mc[k]);
+        if (Mn != -INFINITY) {
+          const float a = (M == -INFINITY) ? 0.f : fast_exp2(M - Mn);
+          const float f = (mc[k] == -INFINITY) ? 0.f : fast_exp2(mc[k] - Mn);
+          n0 = n0 * a + nn[k].x * f;
+          n1 = n1 * a + nn[k].y * f;
+          den = den * a + dc[k] * f;
+          M = Mn;
+        }
+      }
+    }
+    const float inv = den > 0.f ? 1.0f / den : 0.f;
+    const int rr = rm.r_lo + row, sq = rr / G, g = rr - sq * G;
+    *reinterpret_cast<uint32_t*>(p.out + (size_t)rm.b * p.o_sb + (size_t)(rm.h * G + g) * p.o_sh + (size_t)sq * p.o_ss +
+                                 d) = f2_to_bf2(n0 * inv, n1 * inv);
+  }
 }
 
 template <int D, int MT, int NS>
@@ -119,58 +241,111 @@ __global__ void __launch_bounds__(kThreadsM, 1)
   constexpr int QS = D * 2 + 16;   // padded Q row stride in shared memory (bytes)
   constexpr int KVB = kChunk * D * 2;  // bytes of one K (or V) chunk slot
   constexpr int HALF_B = kChunk * 128;
+  constexpr int STAGE = 2 * KVB;
   constexpr int REC = MR * (D + 2);
 
   extern __shared__ __align__(1024) unsigned char smem[];
   const int n_stages = p.n_stages;
-  unsigned char* ring = smem;  // [n_stages][K | V | MetaM]
-  unsigned char* qbuf = smem + (size_t)n_stages * p.stage_bytes;
-  float* mg_o = reinterpret_cast<float*>(qbuf + MR * QS);  // [NS][MR][D]
-  float* mg_m = mg_o + NS * MR * D;                        // [NS][MR]
-  float* mg_l = mg_m + NS * MR;                            // [NS][MR]
-  uint64_t* full_bar = reinterpret_cast<uint64_t*>(mg_l + NS * MR);
+  const int n_items = p.batch * p.n_qt;
+  const SmemPlan sp = plan_smem(D, MT, NS, n_stages, p.live_max, p.batch, n_items);
+  unsigned char* ring = smem + sp.ring;  // [n_stages][K | V]
+  MetaM* metas = reinterpret_cast<MetaM*>(smem + sp.metas);
+  unsigned char* qbuf = smem + sp.qbuf;
+  float* mg_o = reinterpret_cast<float*>(smem + sp.mg);          // [NS][live_max][mg_stride]
+  float* mg_m = mg_o + NS * p.live_max * sp.mg_stride;           // [NS][live_max]
+  float* mg_l = mg_m + NS * p.live_max;                          // [NS][live_max]
+  unsigned char* res = smem + sp.res;                            // [n_res] { num[live][D], M[live], den[live], ResMeta }
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + sp.bars);
   uint64_t* empty_bar = full_bar + kMaxStagesM;
   uint64_t* q_empty = empty_bar + kMaxStagesM;
-  int* misc = reinterpret_cast<int*>(q_empty + 1);
-  int* prefix = misc + 8;  // [items + 1]
+  uint64_t* res_full = q_empty + 1;   // [2]
+  uint64_t* res_empty = res_full + 2; // [2]
+  int* misc = reinterpret_cast<int*>(smem + sp.misc);
+  int* sb_slot = reinterpret_cast<int*>(smem + sp.per_b);
+  int* sb_len = sb_slot + p.batch;
+  int* sb_kvs = sb_len + p.batch;
+  int* sb_S = sb_kvs + p.batch;
+  int* prefix = reinterpret_cast<int*>(smem + sp.prefix);  // [items + 1]
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int Hkv = p.kv.n_kv_heads, P = p.kv.page_tokens, G = p.G;
-  const int n_items = p.batch * p.n_qt;
+  // a kernel launched as a programmatic dependent of this one (the next layer's K/V append, which
+  // touches nothing this kernel reads or writes) may start as soon as every CTA is past this point
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+#ifdef PACE_TIMING
+  unsigned long long* stamps = reinterpret_cast<unsigned long long*>(p.parts + (size_t)gridDim.x * 2 * REC) + blockIdx.x * 8;
+#define PACE_STAMP(i) do { unsigned long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_)); stamps[i] = t_; } while (0)
+  unsigned long long* trace = reinterpret_cast<unsigned long long*>(p.parts + (size_t)gridDim.x * 2 * REC) + gridDim.x * 8;
+#define PACE_TRACE(k, i) do { if (blockIdx.x == 7 && (i) < 64) { unsigned long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_)); trace[(k) * 64 + (i)] = t_; } } while (0)
+  if (tid == 0) PACE_STAMP(0);
+#else
+#define PACE_TRACE(k, i) do {} while (0)
+#define PACE_STAMP(i) do {} while (0)
+#endif
 
-  if (tid == 0) {
-    for (int s = 0; s < n_stages; ++s) {
-      mbar_init(&full_bar[s], 1);
-      mbar_init(&empty_bar[s], kWarps);
+  // ---- prologue.  The per-sequence loads go out first; barrier set-up and the zero fill of the V
+  // slots (rows no copy ever writes are multiplied by p = 0 and must not hold NaN patterns) run
+  // under their latency. ----
+  int my_slot[(kMaxItems + kThreadsM - 1) / kThreadsM];
+  int my_len[(kMaxItems + kThreadsM - 1) / kThreadsM];
+#pragma unroll
+  for (int r = 0; r < (kMaxItems + kThreadsM - 1) / kThreadsM; ++r) {
+    const int b = tid + r * kThreadsM;
+    my_slot[r] = -1;
+    my_len[r] = 0;
+    if (b < p.batch) {
+      my_slot[r] = view_slot(p.kv, b);
+      if (my_slot[r] >= 0) my_len[r] = view_len(p.kv, my_slot[r]);
+      sb_kvs[b] = p.kv_start ? p.kv_start[b] : 0;
+      sb_S[b] = p.q_lens ? min(p.q_lens[b], p.q_len) : p.q_len;
     }
-    mbar_init(q_empty, kWarps);
-    misc[0] = misc[1] = 0;
+  }
+  if (tid == 0) PACE_TRACE(3, 0);
+  // one barrier per thread of the last warp (its lanes have no sequences to look up in small batches)
+  if (tid >= kThreadsM - 32) {
+    const int k = tid - (kThreadsM - 32);
+    if (k < n_stages) mbar_init(&full_bar[k], 1);
+    else if (k < 2 * n_stages) mbar_init(&empty_bar[k - n_stages], kWarps);
+    else if (k == 2 * n_stages) mbar_init(q_empty, kWarps);
+    else if (k < 2 * n_stages + 3) mbar_init(&res_full[k - 2 * n_stages - 1], kWarps);
+    else if (k < 2 * n_stages + 5) mbar_init(&res_empty[k - 2 * n_stages - 3], 1);
     fence_mbar_init();
   }
-  // stale shared memory must not hold NaN patterns: rows no copy ever writes are multiplied by p = 0
-  {
-    uint4* z = reinterpret_cast<uint4*>(smem);
-    const int n16 = (int)(((size_t)n_stages * p.stage_bytes + MR * QS) / 16);
-    for (int i = tid; i < n16; i += kThreadsM) z[i] = make_uint4(0, 0, 0, 0);
+  if (tid == 0) PACE_TRACE(3, 1);
+  for (int s = 0; s < n_stages; ++s) {
+    uint4* z = reinterpret_cast<uint4*>(ring + (size_t)s * STAGE + KVB);
+    for (int i = tid; i < KVB / 16; i += kThreadsM) z[i] = make_uint4(0, 0, 0, 0);
   }
+  if (tid == 0) PACE_TRACE(3, 2);
+#pragma unroll
+  for (int r = 0; r < (kMaxItems + kThreadsM - 1) / kThreadsM; ++r) {
+    const int b = tid + r * kThreadsM;
+    if (b < p.batch) {
+      sb_slot[b] = my_slot[r];
+      sb_len[b] = my_len[r];
+    }
+  }
+  fence_proxy_async();  // generic-proxy zero fill before async-proxy (TMA) writes to the same bytes
+  __syncthreads();
+  if (tid == 0) PACE_TRACE(3, 3);
+  int saw_empty = 0;
   for (int it = tid; it < n_items; it += kThreadsM) {
-    const int b = it / p.n_qt, qt = it - b * p.n_qt;
-    const int slot = view_slot(p.kv, b);
+    const int b = p.n_qt == 1 ? it : it / p.n_qt, qt = it - b * p.n_qt;
     int n = 0;
-    if (slot >= 0) {
-      const int S = p.q_lens ? min(p.q_lens[b], p.q_len) : p.q_len;
-      const int R = S * G;
+    if (sb_slot[b] >= 0) {
+      const int S = sb_S[b], R = S * G;
       if (qt * MR < R) {
-        const int kv_len = view_len(p.kv, slot);
+        const int kv_len = sb_len[b];
         const int s_hi = min(S - 1, ((qt + 1) * MR - 1) / G);
         const int hi = p.causal ? kv_len - S + s_hi + 1 : kv_len;
         n = chunks_of_m(p, min(hi, kv_len)) * Hkv;
       }
     }
     prefix[it + 1] = n;
+    saw_empty |= (n == 0);
   }
-  fence_proxy_async();  // the zero fill above precedes TMA writes to the same shared memory
-  __syncthreads();
+  const int any_empty = __syncthreads_or(saw_empty);
+  if (tid == 0) PACE_TRACE(3, 4);
   if (warp == 0) {
     int carry = 0;
     for (int base = 0; base < n_items; base += 32) {
@@ -187,18 +362,27 @@ __global__ void __launch_bounds__(kThreadsM, 1)
     if (lane == 0) prefix[0] = 0;
   }
   __syncthreads();
+  if (tid == 0) PACE_TRACE(3, 5);
   const long long T = prefix[n_items];
   const int NC = (long long)gridDim.x < T ? (int)gridDim.x : (int)T;
   const int cta = blockIdx.x;
-  const long long x0 = cta < NC ? T * cta / NC : 0, x1 = cta < NC ? T * (cta + 1) / NC : 0;
+  // range boundaries floor(T * c / NC); 32-bit arithmetic whenever it cannot overflow
+  const bool small = (T + 1) * (NC + 1) < (1LL << 31);
+  auto range_begin = [&](int c) -> long long {
+    return small ? (long long)((unsigned)T * (unsigned)c / (unsigned)NC) : T * c / NC;
+  };
+  auto cta_of = [&](long long x) -> int {  // the CTA whose range holds chunk x
+    return small ? (int)(((unsigned)(x + 1) * (unsigned)NC + (unsigned)T - 1u) / (unsigned)T) - 1
+                 : (int)(((x + 1) * NC + T - 1) / T) - 1;
+  };
+  const long long x0 = cta < NC ? range_begin(cta) : 0, x1 = cta < NC ? range_begin(cta + 1) : 0;
 
   // query rows that see no key at all (nothing cached) get zeros
-  for (int u = cta; u < n_items * Hkv; u += gridDim.x) {
+  for (int u = cta; any_empty && u < n_items * Hkv; u += gridDim.x) {
     const int it = u / Hkv, h = u - it * Hkv;
     if (prefix[it + 1] != prefix[it]) continue;
     const int b = it / p.n_qt, qt = it - b * p.n_qt;
-    const int S = p.q_lens ? min(p.q_lens[b], p.q_len) : p.q_len;
-    const int R = S * G;
+    const int R = sb_S[b] * G;
     for (int o = tid; o < MR * D; o += kThreadsM) {
       const int r = qt * MR + o / D, d = o % D;
       if (r < R) {
@@ -209,130 +393,119 @@ __global__ void __launch_bounds__(kThreadsM, 1)
   }
   if (x1 <= x0) return;
   const int n_my = (int)(x1 - x0);
+  if (tid == 0) PACE_STAMP(1);
+  if (tid == 0) PACE_TRACE(3, 6);
 
   if (warp == kWarps) {
     // ================================ producer ================================
-    int lo = 0, hi = n_items - 1;
-    while (lo < hi) {
-      const int mid = (lo + hi + 1) >> 1;
-      if ((long long)prefix[mid] <= x0) lo = mid; else hi = mid - 1;
+    // One warp feeds the ring.  Everything costly (table walks, divisions, the partition
+    // arithmetic, the 48-byte part record) happens once per unit part; one iteration of the
+    // chunk loop is a few dozen instructions, because a single warp's dependent instruction
+    // stream is what paces the whole pipeline.
+    // the item holding chunk x0: the last one whose prefix is <= x0; 32 candidates per ballot
+    int it = 0;
+    for (int base = 0; base < n_items; base += 32) {
+      const int k = base + lane;
+      const unsigned m = __ballot_sync(0xffffffffu, k < n_items && (long long)prefix[k] <= x0);
+      if (m == 0) break;
+      it = base + 31 - __clz(m);
+      if (m != 0xffffffffu) break;
     }
-    int it = lo;
     int nch = (prefix[it + 1] - prefix[it]) / Hkv;
-    int h = (int)((x0 - prefix[it]) / nch);
-    int j = (int)((x0 - prefix[it]) - (long long)h * nch);
+    const int rel = (int)(x0 - prefix[it]);
+    int h = rel / nch;
+    int j = rel - h * nch;
     const bool whole_pages = p.pages_per_chunk > 0;
+    if (lane == 0) PACE_TRACE(3, 7);
     const int is_v = lane & 1;
     const int hf = (lane >> 1) % HALVES;
     const int pi = whole_pages ? lane / (2 * HALVES) : 0;
     const bool copier = whole_pages ? (lane < 2 * HALVES * p.pages_per_chunk) : (lane < 2 * HALVES);
     const CUtensorMap* tm = is_v ? &tmV : &tmK;
     const int c3 = is_v ? p.c3_v : p.c3_k;
-    const int MPs = p.kv.max_pages_per_seq;
-    const uint32_t box_bytes = (uint32_t)p.box_rows * 128u;
+    const int c0 = hf * 64;
+    const uint32_t lane_off = (uint32_t)(is_v ? KVB : 0) + hf * HALF_B + (uint32_t)pi * P * 128;
+    PageWindow pw;
+    const int win_step = whole_pages ? (32 / p.pages_per_chunk) * p.pages_per_chunk : 32;
+    const uint32_t box_bytes = (uint32_t)p.box_rows * 128u * 2u * HALVES;  // K and V boxes of one page
+    const int CT = p.chunk_tokens;
+    int i = 0, s = 0, ph = 0, part_idx = 0;
     bool ok = true;
-    int i = 0, issued = 0, part_idx = 0;
     while (i < n_my && ok) {
-      const int b = it / p.n_qt, qt = it - b * p.n_qt;
-      const int slot = view_slot(p.kv, b);
-      const int kv_len = view_len(p.kv, slot);
-      const int S = p.q_lens ? min(p.q_lens[b], p.q_len) : p.q_len;
+      const int b = p.n_qt == 1 ? it : it / p.n_qt, qt = it - b * p.n_qt;
+      const int slot = sb_slot[b];
+      const int kv_len = sb_len[b];
+      const int S = sb_S[b];
       const int R = S * G;
       const int r_lo = qt * MR;
       const int s_hi = min(S - 1, (r_lo + MR - 1) / G);
       const int len = min(kv_len, p.causal ? kv_len - S + s_hi + 1 : kv_len);  // keys this tile can see
-      const int kvs = p.kv_start ? p.kv_start[b] : 0;
       const int j_end = min(nch, j + (n_my - i));
-      const int32_t* row_tbl = p.kv.block_table ? p.kv.block_table + (size_t)slot * MPs : nullptr;
-      int mode = 0, parts = 1, first_cta = cta, first_slot = 0;
-      {
-        const long long ub = (long long)prefix[it] + (long long)h * nch, ue = ub + nch;
-        if (ub < x0 || ue > x1) {
-          first_cta = ub >= x0 ? cta : (int)(((ub + 1) * NC + T - 1) / T) - 1;
-          const int last_cta = ue <= x1 ? cta : (int)((ue * NC + T - 1) / T) - 1;
-          parts = last_cta - first_cta + 1;
-          first_slot = (ub >= x0 ? x0 : T * first_cta / NC) == ub ? 0 : 1;
-          mode = (cta == first_cta) ? (first_slot ? 2 : 1) : 1;
-        }
-      }
-      int lp, row0;
+      int lp, row0;  // the chunk's first logical page (uniform) and first row inside it
       if (whole_pages) {
-        lp = j * p.pages_per_chunk + pi;
+        lp = j * p.pages_per_chunk;
         row0 = 0;
       } else {
         lp = j / p.chunks_per_page;
         row0 = (j - lp * p.chunks_per_page) * kChunk;
       }
-      auto page_of = [&](int l) -> int {
-        if (!row_tbl) return slot;
-        if (l >= MPs) return -1;
-        const int pg = __ldg(row_tbl + l);
-        return (pg < 0 || pg >= p.kv.n_pages) ? -1 : pg;
-      };
-      int pg = copier ? page_of(lp) : 0;
-      for (bool first = true; j < j_end; ++j, ++i, first = false) {
-        int lp_n = lp, row0_n = row0;
-        if (whole_pages) {
-          lp_n = lp + p.pages_per_chunk;
-        } else {
-          row0_n = row0 + kChunk;
-          if (row0_n >= P) { row0_n = 0; lp_n = lp + 1; }
+      pw.start(p.kv, slot, lp, win_step, lane);  // loads in flight while the arithmetic below runs
+      if (lane == 0 && i == 0) PACE_TRACE(3, 8);
+      int mode = 0, parts = 1, first_cta = cta, first_slot = 0;
+      {
+        const long long ub = (long long)prefix[it] + (long long)h * nch, ue = ub + nch;
+        if (ub < x0 || ue > x1) {
+          first_cta = ub >= x0 ? cta : cta_of(ub);
+          const int last_cta = ue <= x1 ? cta : cta_of(ue - 1);
+          parts = last_cta - first_cta + 1;
+          first_slot = (ub >= x0 ? x0 : range_begin(first_cta)) == ub ? 0 : 1;
+          mode = (cta == first_cta) ? (first_slot ? 2 : 1) : 1;
         }
-        const int pg_n = (copier && j + 1 < j_end) ? (lp_n == lp ? pg : page_of(lp_n)) : 0;
-        const int s = i % n_stages;
-        if (i >= n_stages && !mbar_wait(&empty_bar[s], ((i / n_stages) - 1) & 1)) { ok = false; break; }
-        if (first && part_idx > 0 && !mbar_wait(q_empty, (part_idx - 1) & 1)) { ok = false; break; }
-        const int tok0 = whole_pages ? j * p.chunk_tokens : lp * P + row0;
-        const int rows = whole_pages ? min(p.chunk_tokens, len - tok0) : min(min(kChunk, P - row0), len - tok0);
-        const int n_pages_c = whole_pages ? (rows + P - 1) / P : 1;
-        const bool mine = copier && pi < n_pages_c;
+      }
+      const int q_rows = min(MR, R - r_lo);
+      const int c2h = h;
+      if (lane == 0 && i == 0) PACE_TRACE(3, 9);
+      if (part_idx > 0 && !mbar_wait(q_empty, (part_idx - 1) & 1)) { ok = false; break; }
+      for (bool first = true; j < j_end; ++j, ++i, first = false) {
+        if (i >= n_stages && !mbar_wait(&empty_bar[s], ph ^ 1)) { ok = false; break; }
+        const int tok0 = whole_pages ? j * CT : lp * P + row0;
+        const int rows = whole_pages ? min(CT, len - tok0) : min(min(kChunk, P - row0), len - tok0);
+        const int n_pages_c = !whole_pages ? 1 : (rows == CT ? p.pages_per_chunk : (rows + P - 1) / P);
         const bool last = (j == j_end - 1);
-        const int q_rows = first ? min(MR, R - r_lo) : 0;
-        unsigned char* st = ring + (size_t)s * p.stage_bytes;
         if (lane == 0) {
-          MetaM* m = reinterpret_cast<MetaM*>(st + 2 * KVB);
-          m->rows = rows;
-          m->tok0 = tok0;
-          m->flags = (first ? 1 : 0) | (last ? 2 : 0);
-          m->kvs = kvs;
-          m->b = b;
-          m->h = h;
-          m->r_lo = r_lo;
-          m->R = R;
-          m->kv_len = kv_len;
-          m->S = S;
-          m->mode = mode;
-          m->parts = parts;
-          m->first_cta = first_cta;
-          m->first_slot = first_slot;
-          m->unit = it * Hkv + h;
-          mbar_arrive_expect_tx(&full_bar[s],
-                                (uint32_t)n_pages_c * 2u * HALVES * box_bytes + (uint32_t)q_rows * D * 2u);
+          MetaM* m = &metas[s];
+          *reinterpret_cast<int4*>(m) = make_int4(
+              rows, tok0, (first ? 1 : 0) | (last ? 2 : 0) | ((last && i == n_my - 1) ? 4 : 0), sb_kvs[b]);
+          if (first) {
+            *reinterpret_cast<int4*>(&m->b) = make_int4(b, h, r_lo, R);
+            *reinterpret_cast<int4*>(&m->kv_len) = make_int4(kv_len, S, mode, parts);
+            *reinterpret_cast<int4*>(&m->first_cta) = make_int4(first_cta, first_slot, it * Hkv + h, 0);
+          }
+          mbar_arrive_expect_tx(&full_bar[s], (uint32_t)n_pages_c * box_bytes + (first ? (uint32_t)q_rows * D * 2u : 0u));
         }
         __syncwarp();
-        bool page_bad = false;
-        if (mine) {
-          if (pg < 0) {
-            page_bad = true;
-          } else {
-            unsigned char* dst = st + (is_v ? KVB : 0) + hf * HALF_B + (size_t)pi * P * 128;
-            tma_load_4d(dst, tm, hf * 64, row0, pg * Hkv + h, c3, &full_bar[s]);
+        const int pg = pw.get(lp + pi, lp, lane);
+        if (lane == 0 && i == 0) PACE_TRACE(3, 10);
+        if (copier && pi < n_pages_c) {
+          if (pg >= 0) tma_load_4d(ring + (size_t)s * STAGE + lane_off, tm, c0, row0, pg * Hkv + c2h, c3, &full_bar[s]);
+          else raise_status(p.kv.status, PACE_DEV_BAD_INDEX);  // the consumers' bounded wait on this stage gives up
+        }
+        if (first) {
+          for (int r = lane; r < q_rows; r += 32) {
+            const int rr = r_lo + r, sq = rr / G, g = rr - sq * G;
+            const __nv_bfloat16* src = p.q + (size_t)b * p.q_sb + (size_t)(h * G + g) * p.q_sh + (size_t)sq * p.q_ss;
+            bulk_g2s(qbuf + r * QS, src, D * 2u, &full_bar[s]);
           }
+          if (i == 0 && lane == 0) PACE_STAMP(2);
         }
-        for (int r = lane; r < q_rows; r += 32) {
-          const int rr = r_lo + r, sq = rr / G, g = rr - sq * G;
-          const __nv_bfloat16* src = p.q + (size_t)b * p.q_sb + (size_t)(h * G + g) * p.q_sh + (size_t)sq * p.q_ss;
-          bulk_g2s(qbuf + r * QS, src, D * 2u, &full_bar[s]);
+        if (lane == 0) PACE_TRACE(0, i);
+        if (whole_pages) {
+          lp += p.pages_per_chunk;
+        } else {
+          row0 += kChunk;
+          if (row0 >= P) { row0 = 0; ++lp; }
         }
-        if (__any_sync(0xffffffffu, page_bad)) {
-          if (lane == 0) raise_status(p.kv.status, PACE_DEV_BAD_INDEX);
-          ok = false;
-          break;
-        }
-        ++issued;
-        pg = pg_n;
-        lp = lp_n;
-        row0 = row0_n;
+        if (++s == n_stages) { s = 0; ph ^= 1; }
       }
       if (!ok) break;
       ++part_idx;
@@ -346,10 +519,33 @@ __global__ void __launch_bounds__(kThreadsM, 1)
       }
     }
     if (!ok && lane == 0) {
-      misc[0] = 1;
       raise_status(p.kv.status, PACE_DEV_WAIT_TIMEOUT);
-      const int from = issued > n_stages ? issued - n_stages : 0;
-      for (int k = from; k < issued; ++k) mbar_wait(&full_bar[k % n_stages], (k / n_stages) & 1);
+      // let copies already in flight land before the CTA's shared memory is released
+      const int from = i > n_stages ? i - n_stages : 0;
+      for (int k = from; k < i; ++k) mbar_wait(&full_bar[k % n_stages], (k / n_stages) & 1);
+    }
+    return;
+  }
+
+  if (warp == kWarps + 1) {
+    // ================================ epilogue warp ================================
+    // Takes each finished unit part from shared memory to global memory: the output rows, or an
+    // fp32 partial plus the arrival count (and the merge, when this CTA arrives last).  The global
+    // round trips happen here, off the consumers' path.
+    for (int k = 0;; ++k) {
+      const int rs = k % sp.n_res;
+      if (!mbar_wait(&res_full[rs], (k / sp.n_res) & 1)) {
+        if (lane == 0) raise_status(p.kv.status, PACE_DEV_WAIT_TIMEOUT);
+        return;
+      }
+      const float* rnum = reinterpret_cast<const float*>(res + (size_t)rs * sp.res_slot_bytes);
+      const float* rM = rnum + p.live_max * D;
+      const float* rden = rM + p.live_max;
+      const ResMeta rm = *reinterpret_cast<const ResMeta*>(rden + p.live_max);
+      if (rm.last_part) break;  // the CTA's last part is published by the consumer warps themselves
+      publish_part<D, MR, 32, true>(p, rm, rnum, rM, rden, lane, cta, nullptr);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&res_empty[rs]);
     }
     return;
   }
@@ -363,6 +559,9 @@ __global__ void __launch_bounds__(kThreadsM, 1)
   float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
   int lim0 = INT_MAX, lim1 = INT_MAX;  // first key NOT visible to my two rows
   int srow0 = 0, srow1 = 0, bcur = 0;  // query token of my two rows (additive-mask lookup)
+  int n_parts_done = 0;
+  ResMeta fin;  // the current unit part, read from the part record of its first chunk
+  fin.last_part = 0;
 #pragma unroll
   for (int n = 0; n < ON; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
 #pragma unroll
@@ -374,9 +573,12 @@ __global__ void __launch_bounds__(kThreadsM, 1)
       if (lane == 0) raise_status(p.kv.status, PACE_DEV_WAIT_TIMEOUT);
       return;
     }
-    const unsigned char* st = ring + (size_t)s * p.stage_bytes;
-    const MetaM* meta = reinterpret_cast<const MetaM*>(st + 2 * KVB);
+    const unsigned char* st = ring + (size_t)s * STAGE;
+    const MetaM* meta = &metas[s];
     const int rows = meta->rows, tok0 = meta->tok0, flags = meta->flags, kvs = meta->kvs;
+    if (tid == 0 && i == 0) PACE_STAMP(3);
+    if (tid == 0) PACE_TRACE(1, i);
+    if (tid == 0 && i == n_my - 1) PACE_STAMP(4);
 
     if (flags & 1) {
       // ---- new unit part: Q fragments to registers, per-row visibility limits ----
@@ -397,27 +599,52 @@ __global__ void __launch_bounds__(kThreadsM, 1)
       lim0 = (r0 < R) ? (p.causal ? kv_len - S + srow0 + 1 : kv_len) : INT_MAX;
       lim1 = (r1 < R) ? (p.causal ? kv_len - S + srow1 + 1 : kv_len) : INT_MAX;
       bcur = meta->b;
+      fin.b = meta->b;
+      fin.h = meta->h;
+      fin.r_lo = r_lo;
+      fin.live = min(MR, R - r_lo);
+      fin.mode = meta->mode;
+      fin.parts = meta->parts;
+      fin.first_cta = meta->first_cta;
+      fin.first_slot = meta->first_slot;
+      fin.unit = meta->unit;
       m0 = m1 = -INFINITY;
       l0 = l1 = 0.f;
 #pragma unroll
       for (int n = 0; n < ON; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
     }
 
+#ifdef PACE_SKIP_MATH
+    if (false) {
+#else
     if (tw0 < rows) {  // this warp's token slice holds live keys
+#endif
       const uint32_t kb = smem_u32(st), vb = kb + KVB;
       // ---- S = Q K^T ----
+      // (the k-steps of a tile go to CH independent accumulators: a chain of dependent MMAs is the
+      // longest latency in the loop)
+      constexpr int CH = (NT == 1) ? 4 : (NT <= 2 ? 2 : 1);
       float sc[NT][4];
 #pragma unroll
       for (int nt = 0; nt < NT; ++nt) {
-        sc[nt][0] = sc[nt][1] = sc[nt][2] = sc[nt][3] = 0.f;
+        float part[CH][4];
+#pragma unroll
+        for (int c = 0; c < CH; ++c) part[c][0] = part[c][1] = part[c][2] = part[c][3] = 0.f;
         const int row = tw0 + nt * 8 + (lane & 7);
 #pragma unroll
         for (int k2 = 0; k2 < KS / 2; ++k2) {
           const int cg = k2 * 4 + (lane >> 3);
           uint32_t b0, b1, b2, b3;
           ldsm_x4(kb + (cg >> 3) * HALF_B + row * 128 + (((cg & 7) ^ (row & 7)) << 4), b0, b1, b2, b3);
-          mma16816(sc[nt], qa[2 * k2], b0, b1);
-          mma16816(sc[nt], qa[2 * k2 + 1], b2, b3);
+          mma16816(part[(2 * k2) % CH], qa[2 * k2], b0, b1);
+          mma16816(part[(2 * k2 + 1) % CH], qa[2 * k2 + 1], b2, b3);
+        }
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          float t = part[0][e];
+#pragma unroll
+          for (int c = 1; c < CH; ++c) t += part[c][e];
+          sc[nt][e] = t;
         }
       }
       // ---- scale, additive mask, visibility ----
@@ -521,96 +748,107 @@ __global__ void __launch_bounds__(kThreadsM, 1)
         }
       }
     }
-    const int mb = meta->b, mh = meta->h, r_lo = meta->r_lo, R = meta->R, mode = meta->mode, parts = meta->parts,
-              first_cta = meta->first_cta, first_slot = meta->first_slot, unit = meta->unit;
+    if (flags & 2) fin.last_part = (flags & 4) ? 1 : 0;
     __syncwarp();
     if (lane == 0) mbar_arrive(&empty_bar[s]);
+    if (tid == 0) PACE_TRACE(2, i);
 
     if (flags & 2) {
-      // ======================= end of a unit part =======================
+      // ================= end of a unit part: hand the result to the epilogue warp =================
       float lt0 = l0, lt1 = l1;
       lt0 += __shfl_xor_sync(0xffffffffu, lt0, 1);
       lt0 += __shfl_xor_sync(0xffffffffu, lt0, 2);
       lt1 += __shfl_xor_sync(0xffffffffu, lt1, 1);
       lt1 += __shfl_xor_sync(0xffffffffu, lt1, 2);
+      const int live = fin.live;
       const int row0 = mt * 16 + qr, row1 = row0 + 8;
-      float* wo = mg_o + (size_t)ns * MR * D;
+      const int rs = n_parts_done % sp.n_res;
+      float* rnum = reinterpret_cast<float*>(res + (size_t)rs * sp.res_slot_bytes);
+      float* rM = rnum + p.live_max * D;
+      float* rden = rM + p.live_max;
+      bool ok_res = true;
+      if (NS > 1) {
+        // the NS token slices of each row meet in shared memory
+        csync();  // every thread is done reading the merge buffer for the previous part
+        float* wo = mg_o + (size_t)ns * p.live_max * sp.mg_stride;
+        if (row0 < live) {
 #pragma unroll
-      for (int n = 0; n < ON; ++n) {
-        *reinterpret_cast<float2*>(wo + row0 * D + n * 8 + 2 * qc) = make_float2(o[n][0], o[n][1]);
-        *reinterpret_cast<float2*>(wo + row1 * D + n * 8 + 2 * qc) = make_float2(o[n][2], o[n][3]);
-      }
-      if (qc == 0) {
-        mg_m[ns * MR + row0] = m0;
-        mg_m[ns * MR + row1] = m1;
-        mg_l[ns * MR + row0] = lt0;
-        mg_l[ns * MR + row1] = lt1;
-      }
-      csync();
-      const int live = min(MR, R - r_lo);  // query rows of this tile that exist
-      float* rec = p.parts + ((size_t)cta * 2 + (mode == 2 ? 1 : 0)) * REC;
-      for (int oi = tid; oi < live * D; oi += kCThreads) {
-        const int row = oi / D, d = oi - row * D;
-        float M = -INFINITY;
-#pragma unroll
-        for (int w = 0; w < NS; ++w) M = fmaxf(M, mg_m[w * MR + row]);
-        float num = 0.f, den = 0.f;
-        if (M != -INFINITY) {
-#pragma unroll
-          for (int w = 0; w < NS; ++w) {
-            const float mw = mg_m[w * MR + row];
-            const float f = (mw == -INFINITY) ? 0.f : fast_exp2(mw - M);
-            num += mg_o[((size_t)w * MR + row) * D + d] * f;
-            den += mg_l[w * MR + row] * f;
+          for (int n = 0; n < ON; ++n)
+            *reinterpret_cast<float2*>(wo + row0 * sp.mg_stride + n * 8 + 2 * qc) = make_float2(o[n][0], o[n][1]);
+          if (qc == 0) {
+            mg_m[ns * p.live_max + row0] = m0;
+            mg_l[ns * p.live_max + row0] = lt0;
           }
         }
-        if (mode == 0) {
-          const int r = r_lo + row, sq = r / G, g = r - sq * G;
-          p.out[(size_t)mb * p.o_sb + (size_t)(mh * G + g) * p.o_sh + (size_t)sq * p.o_ss + d] =
-              __float2bfloat16(den > 0.f ? num / den : 0.f);
-        } else {
-          rec[row * D + d] = num;
+        if (row1 < live) {
+#pragma unroll
+          for (int n = 0; n < ON; ++n)
+            *reinterpret_cast<float2*>(wo + row1 * sp.mg_stride + n * 8 + 2 * qc) = make_float2(o[n][2], o[n][3]);
+          if (qc == 0) {
+            mg_m[ns * p.live_max + row1] = m1;
+            mg_l[ns * p.live_max + row1] = lt1;
+          }
+        }
+        if (n_parts_done >= sp.n_res) ok_res = mbar_wait(&res_empty[rs], ((n_parts_done / sp.n_res) - 1) & 1);
+        csync();
+        for (int oi = tid; oi < live * D; oi += kCThreads) {
+          const int row = oi / D, d = oi - row * D;
+          float M = -INFINITY;
+#pragma unroll
+          for (int w = 0; w < NS; ++w) M = fmaxf(M, mg_m[w * p.live_max + row]);
+          float num = 0.f, den = 0.f;
+          if (M != -INFINITY) {
+#pragma unroll
+            for (int w = 0; w < NS; ++w) {
+              const float mw = mg_m[w * p.live_max + row];
+              const float f = (mw == -INFINITY) ? 0.f : fast_exp2(mw - M);
+              num += mg_o[((size_t)w * p.live_max + row) * sp.mg_stride + d] * f;
+              den += mg_l[w * p.live_max + row] * f;
+            }
+          }
+          rnum[oi] = num;
           if (d == 0) {
-            rec[MR * D + row] = M;
-            rec[MR * D + MR + row] = den;
+            rM[row] = M;
+            rden[row] = den;
+          }
+        }
+      } else {
+        // one warp owns its 16 rows outright: registers go straight to the result slot
+        if (n_parts_done >= sp.n_res) ok_res = mbar_wait(&res_empty[rs], ((n_parts_done / sp.n_res) - 1) & 1);
+        if (row0 < live) {
+#pragma unroll
+          for (int n = 0; n < ON; ++n)
+            *reinterpret_cast<float2*>(rnum + row0 * D + n * 8 + 2 * qc) = make_float2(o[n][0], o[n][1]);
+          if (qc == 0) {
+            rM[row0] = m0;
+            rden[row0] = lt0;
+          }
+        }
+        if (row1 < live) {
+#pragma unroll
+          for (int n = 0; n < ON; ++n)
+            *reinterpret_cast<float2*>(rnum + row1 * D + n * 8 + 2 * qc) = make_float2(o[n][2], o[n][3]);
+          if (qc == 0) {
+            rM[row1] = m1;
+            rden[row1] = lt1;
           }
         }
       }
-      if (mode != 0) {
-        __threadfence();
-        csync();
-        if (tid == 0) {
-          const int old = atomicAdd(&p.unit_count[unit], 1);
-          misc[1] = (old == parts - 1);
-          if (old == parts - 1) p.unit_count[unit] = 0;
-        }
-        csync();
-        if (misc[1]) {
-          __threadfence();
-          for (int oi = tid; oi < live * D; oi += kCThreads) {
-            const int row = oi / D, d = oi - row * D;
-            float M = -INFINITY;
-            for (int c = 0; c < parts; ++c) {
-              const float* r = p.parts + ((size_t)(first_cta + c) * 2 + (c == 0 ? first_slot : 0)) * REC;
-              M = fmaxf(M, __ldcg(r + MR * D + row));
-            }
-            float num = 0.f, den = 0.f;
-            if (M != -INFINITY) {
-              for (int c = 0; c < parts; ++c) {
-                const float* r = p.parts + ((size_t)(first_cta + c) * 2 + (c == 0 ? first_slot : 0)) * REC;
-                const float mc = __ldcg(r + MR * D + row);
-                const float f = (mc == -INFINITY) ? 0.f : fast_exp2(mc - M);
-                num += __ldcg(r + row * D + d) * f;
-                den += __ldcg(r + MR * D + MR + row) * f;
-              }
-            }
-            const int rr = r_lo + row, sq = rr / G, g = rr - sq * G;
-            p.out[(size_t)mb * p.o_sb + (size_t)(mh * G + g) * p.o_sh + (size_t)sq * p.o_ss + d] =
-                __float2bfloat16(den > 0.f ? num / den : 0.f);
-          }
-        }
+      if (!ok_res) {
+        if (lane == 0) raise_status(p.kv.status, PACE_DEV_WAIT_TIMEOUT);
+        return;
       }
-      csync();
+      if (tid == 0) *reinterpret_cast<ResMeta*>(rden + p.live_max) = fin;
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&res_full[rs]);  // release: the slot's contents are visible to the waiter
+      ++n_parts_done;
+      if (fin.last_part) {
+        // nothing is left to stream: all eight warps take the result out (the epilogue warp only
+        // wakes up to leave), which keeps the kernel's tail short
+        csync();
+        publish_part<D, MR, kCThreads, false>(p, fin, rnum, rM, rden, tid, cta, misc);
+        if (tid == 0) PACE_STAMP(5);
+      }
     }
   }
 }
@@ -695,23 +933,23 @@ int sm_count_m() {
 
 template <int D, int MT, int NS>
 int launch_mma(MmaParams& p, const CUtensorMap& tmK, const CUtensorMap& tmV, int grid, cudaStream_t stream) {
-  constexpr int MR = 16 * MT, QS = D * 2 + 16;
-  p.stage_bytes = 2 * kChunk * D * 2 + (int)sizeof(MetaM);
-  // stage slots must keep the 1024-byte alignment the 128-byte swizzle pattern is anchored to
-  p.stage_bytes = (p.stage_bytes + 1023) / 1024 * 1024;
+  constexpr int MR = 16 * MT;
   const int n_items = p.batch * p.n_qt;
-  const size_t fixed = (size_t)MR * QS + (size_t)NS * MR * (D + 2) * sizeof(float) +
-                       (2 * kMaxStagesM + 1) * sizeof(uint64_t) + 8 * sizeof(int) + (size_t)(n_items + 1) * sizeof(int) +
-                       64;
-  const size_t budget = 224 * 1024;
-  if (fixed + 2 * (size_t)p.stage_bytes > budget) return PACE_ERR_UNSUPPORTED;
-  int ns = (int)((budget - fixed) / p.stage_bytes);
-  if (ns > kMaxStagesM) ns = kMaxStagesM;
+  p.live_max = p.G * p.q_len < MR ? p.G * p.q_len : MR;
+  const int budget = 226 * 1024;
+  int ns = kMaxStagesM;
+  while (ns >= 2 && plan_smem(D, MT, NS, ns, p.live_max, p.batch, n_items).total > budget) --ns;
+  if (ns < 2) return PACE_ERR_UNSUPPORTED;
   p.n_stages = ns;
-  size_t smem_bytes = (size_t)ns * p.stage_bytes + fixed;
-  smem_bytes = (smem_bytes + 15) / 16 * 16;
-  PACE_CUDA_TRY(cudaFuncSetAttribute(attn_mma_kernel<D, MT, NS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                     226 * 1024));
+  const size_t smem_bytes = plan_smem(D, MT, NS, ns, p.live_max, p.batch, n_items).total;
+  static bool configured[16] = {};
+  int dev = 0;
+  PACE_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev >= 16 || !configured[dev]) {
+    PACE_CUDA_TRY(cudaFuncSetAttribute(attn_mma_kernel<D, MT, NS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       budget));
+    if (dev < 16) configured[dev] = true;
+  }
   attn_mma_kernel<D, MT, NS><<<grid, kThreadsM, smem_bytes, stream>>>(p, tmK, tmV);
   PACE_LAUNCH_CHECK("attn_mma_kernel");
   return PACE_OK;
@@ -737,6 +975,7 @@ int run_mma(const KVView& kv, const CUtensorMap& tmK, const CUtensorMap& tmV, in
   if (n_q_heads % Hkv) return PACE_ERR_INVALID;
   const int G = n_q_heads / Hkv;
   if (!q || !out || ((uintptr_t)q & 15) || (q_sb & 7) || (q_sh & 7) || (q_ss & 7)) return PACE_ERR_INVALID;
+  if (((uintptr_t)out & 3) || (o_sb & 1) || (o_sh & 1) || (o_ss & 1)) return PACE_ERR_INVALID;  // bf16 pairs are stored
   if (!workspace || ((uintptr_t)workspace & 15)) return PACE_ERR_INVALID;
   const int M = G * q_len;
   const int MT = M <= 16 ? 1 : M <= 32 ? 2 : M <= 64 ? 4 : 8;
@@ -816,8 +1055,7 @@ int run_mma(const KVView& kv, const CUtensorMap& tmK, const CUtensorMap& tmV, in
 }
 
 int run_mma_paged(const pace_attn_args_t* a, int causal, cudaStream_t stream) {
-  if (!a || !a->pool || a->q_len < 1 || a->layer < 0 || a->layer >= a->pool->n_layers || !a->seq_ids)
-    return PACE_ERR_INVALID;
+  if (!a || !a->pool || a->q_len < 1 || a->layer < 0 || a->layer >= a->pool->n_layers) return PACE_ERR_INVALID;
   if (a->batch > a->pool->max_seqs) return PACE_ERR_INVALID;
   CUtensorMap tm;
   const int rc = pool_map(a->pool, &tm);

@@ -105,6 +105,42 @@ __device__ __forceinline__ size_t view_row_offset(const KVView& kv, int page, in
   return (((size_t)page * kv.n_kv_heads + h) * kv.page_tokens + row) * (size_t)kv.head_dim;
 }
 
+// A producer warp's window onto one sequence's block-table row: lane l holds the physical page of
+// logical page base + l, and the following window is already on its way.  One coalesced load per
+// `step` pages instead of one dependent load per chunk, which would pace the whole pipeline at one
+// chunk per memory latency.  All 32 lanes call every method together.
+struct PageWindow {
+  const int32_t* row;  // nullptr: dense view, every logical page is the slot itself
+  int slot, max_pages, n_pages, base, step, cur, nxt;
+
+  __device__ __forceinline__ int load(int l) const {
+    if (!row) return slot;
+    if (l < 0 || l >= max_pages) return -1;
+    const int pg = __ldg(row + l);
+    return (pg < 0 || pg >= n_pages) ? -1 : pg;
+  }
+  // step: how far the window moves at a time (a multiple of the pages one chunk spans, <= 32)
+  __device__ __forceinline__ void start(const KVView& kv, int slot_, int first_lp, int step_, int lane) {
+    row = kv.block_table ? kv.block_table + (size_t)slot_ * kv.max_pages_per_seq : nullptr;
+    slot = slot_;
+    max_pages = kv.max_pages_per_seq;
+    n_pages = kv.n_pages;
+    base = first_lp;
+    step = step_;
+    cur = load(base + lane);
+    nxt = load(base + step + lane);
+  }
+  // physical page of logical page `lp` (may differ per lane); lp_first is the chunk's first page (uniform)
+  __device__ __forceinline__ int get(int lp, int lp_first, int lane) {
+    while (lp_first >= base + step) {
+      base += step;
+      cur = nxt;
+      nxt = load(base + step + lane);
+    }
+    return __shfl_sync(0xffffffffu, cur, (lp - base) & 31);
+  }
+};
+
 // ---------------------------------------------------------------------------
 // mbarrier + bulk-copy (TMA) wrappers.  Every wait is bounded.
 // ---------------------------------------------------------------------------

@@ -5,6 +5,7 @@
 // (pace/llm/cache.py:126-400).  All state lives in device memory and is mutated
 // by stream-ordered kernels; the host never copies a table.
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 
 #include "common.cuh"
@@ -385,6 +386,12 @@ __global__ void read_dense_kernel(pace_kv_pool_t p, int layer, const int32_t* __
   }
 }
 
+// PACE_PDL=0 turns the programmatic launch of the append kernel off (A/B measurements)
+const bool g_pdl_append = [] {
+  const char* e = getenv("PACE_PDL");
+  return !(e && e[0] == '0');
+}();
+
 bool pool_ok(const pace_kv_pool_t* p) {
   return geometry_ok(p) && p->pages && p->block_table && p->seq_len && p->seq_pages && p->page_ref &&
          p->free_stack && p->counters && p->status && p->table_tmp;
@@ -512,8 +519,23 @@ int pace_kv_append(const pace_kv_pool_t* p, int32_t layer, const int32_t* seq_id
   const long long warps = (long long)batch * n_new * p->n_kv_heads;
   long long blocks = (warps + 7) / 8;
   if (blocks > 148 * 8) blocks = 148 * 8;
-  append_kernel<<<(int)blocks, 256, 0, (cudaStream_t)stream>>>(
-      *p, layer, seq_ids, batch, n_new, n_per, (const __nv_bfloat16*)k_new, (const __nv_bfloat16*)v_new, sb, sh, st);
+  // Programmatic dependent launch: when the kernel in front of this one on the stream announces it
+  // (the attention kernels do, and an append touches nothing they read or write - another layer's
+  // pages and lengths), the append overlaps with it instead of waiting for it to drain.  After any
+  // other kernel the attribute changes nothing.
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)blocks);
+  cfg.blockDim = dim3(256);
+  cfg.dynamicSmemBytes = 0;
+  cfg.stream = (cudaStream_t)stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = g_pdl_append ? 1 : 0;
+  PACE_CUDA_TRY(cudaLaunchKernelEx(&cfg, append_kernel, *p, (int)layer, seq_ids, (int)batch, (int)n_new, n_per,
+                                   (const __nv_bfloat16*)k_new, (const __nv_bfloat16*)v_new, (int64_t)sb, (int64_t)sh,
+                                   (int64_t)st));
   PACE_LAUNCH_CHECK("append_kernel");
   return PACE_OK;
 }

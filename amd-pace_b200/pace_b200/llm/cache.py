@@ -211,6 +211,7 @@ class KVCacheManager:
         self._owns_pool = pool is None
         self.slots: Optional[List[int]] = None
         self.slots_dev: Optional[torch.Tensor] = None
+        self.identity_slots = False
         self.static_launch = False   # frozen launch sequence (CUDA graphs): layer 0 always reserves
         self.capturing = False       # launches are being recorded, not executed: leave the mirror alone
         self.cache_objects: List[KVCacheBase] = [
@@ -235,6 +236,7 @@ class KVCacheManager:
                 raise ValueError("shared KV pool geometry does not match this manager")
         self.slots = self.pool.alloc_slots(batch)
         self.slots_dev = torch.tensor(self.slots, dtype=torch.int32, device=self.pool.device)
+        self.identity_slots = self.slots == list(range(batch))
 
     def __len__(self) -> int:
         return int(self.cache_objects[0].seq_len)
@@ -316,6 +318,7 @@ class KVCacheBase(ABC):
             manager.max_seq_length, manager.extra_tokens = max_seq_length, 0
             manager.pool, manager._owns_pool, manager.slots, manager.slots_dev = None, True, None, None
             manager.static_launch = manager.capturing = False
+            manager.identity_slots = False
             manager.cache_objects = [self]
         self.manager = manager
         self.layer = layer

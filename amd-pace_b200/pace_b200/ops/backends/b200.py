@@ -77,7 +77,8 @@ def paged_attention(query: torch.Tensor, key: PagedKV, kv_start: Optional[torch.
     a = _C.AttnArgs()
     a.pool = C.pointer(pool.desc)
     a.layer, a.batch, a.n_q_heads, a.q_len = cache.layer, B, Hq, S
-    a.seq_ids = mgr.slots_dev.data_ptr()
+    # a manager that owns its pool uses slots 0..B-1: NULL tells the kernels so and saves them a dependent load
+    a.seq_ids = None if mgr.identity_slots else mgr.slots_dev.data_ptr()
     a.kv_start = kv_start.data_ptr() if kv_start is not None else None
     a.q_lens = q_lens.data_ptr() if q_lens is not None else None
     a.q = query.data_ptr()

@@ -145,7 +145,7 @@ typedef struct pace_attn_args {
   int32_t batch;
   int32_t n_q_heads;
   int32_t q_len;            /* 1 = decode; d+1 = verify; chunk = prefill */
-  const int32_t* seq_ids;   /* device [batch] */
+  const int32_t* seq_ids;   /* device [batch]; NULL = slots 0..batch-1 */
   const int32_t* kv_start;  /* device [batch] or NULL (no left padding) */
   const int32_t* q_lens;    /* device [batch] or NULL: ragged query counts <= q_len */
   const void* q;
