@@ -1070,6 +1070,67 @@ int run_mma_paged(const pace_attn_args_t* a, int causal, cudaStream_t stream) {
 
 using namespace pace;
 
+// ---------------------------------------------------------------------------------------------
+// Decode attention for callers that must not allocate device memory.
+//
+// Some hosts of this library cannot call cudaMalloc on the path that runs a decode step: code
+// inside a region that forbids allocation (a serving loop that has handed all of its memory to a
+// fixed arena, a real-time thread, a process whose memory budget was frozen at start-up), or a
+// plug-in loaded into an engine that owns every byte of the device.  pace_attn_decode needs a
+// caller-provided workspace; this entry point instead keeps the scratch in a file-scope device
+// array that every GPU loading the library holds until the process exits.
+//
+// kStaticScratchBytes bounds what it can serve (see the checks below); anything larger is refused
+// with PACE_ERR_UNSUPPORTED.  All calls on a device share the one array, which still holds what
+// the previous call left: the arrival counters the kernel needs at zero are cleared on the stream
+// before every launch, and two calls that overlap on the GPU (different streams) race on it.
+constexpr int kStaticMaxSMs = 192;
+constexpr uint64_t kStaticPartBytes = (uint64_t)kStaticMaxSMs * 2 * 16 * (128 + 2) * sizeof(float);
+constexpr uint64_t kStaticScratchBytes = kWorkspaceCounterBytes + kStaticPartBytes + 256;
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+namespace pace {
+namespace {
+// In host code `g_static_scratch` is only a handle for the runtime, not an address the GPU can
+// use: the device address is asked for once per device, with that device current.
+int static_scratch_ptr(void** out) {
+  static void* ptrs[64] = {};
+  static std::mutex mu;
+  int dev = 0;
+  PACE_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return PACE_ERR_UNSUPPORTED;
+  std::lock_guard<std::mutex> lk(mu);
+  if (!ptrs[dev]) {
+    void* ptr = nullptr;
+    PACE_CUDA_TRY(cudaGetSymbolAddress(&ptr, g_static_scratch));
+    ptrs[dev] = ptr;
+  }
+  *out = ptrs[dev];
+  return PACE_OK;
+}
+}  // namespace
+}  // namespace pace
+
+extern "C" int pace_attn_decode_static(const pace_attn_args_t* a, void* stream) {
+  if (!a || !a->pool || a->q_len != 1 || a->batch < 0) return PACE_ERR_INVALID;
+  const pace_kv_pool_t* pl = a->pool;
+  if (pl->n_kv_heads <= 0 || a->n_q_heads % pl->n_kv_heads) return PACE_ERR_INVALID;
+  const int G = a->n_q_heads / pl->n_kv_heads;
+  // limits of the fixed scratch: one 16-row tile of grouped heads, counters for every (sequence, kv head)
+  if (G > 16 || pl->head_dim > 128) return PACE_ERR_UNSUPPORTED;
+  if ((uint64_t)a->batch * pl->n_kv_heads * sizeof(int32_t) > kWorkspaceCounterBytes) return PACE_ERR_UNSUPPORTED;
+  if (sm_count_m() > kStaticMaxSMs) return PACE_ERR_UNSUPPORTED;
+  if (a->batch == 0) return PACE_OK;
+  void* scratch = nullptr;
+  const int rc = static_scratch_ptr(&scratch);  // first call on a device: resolves the array's device address
+  if (rc != PACE_OK) return rc;
+  PACE_CUDA_TRY(cudaMemsetAsync(scratch, 0, (size_t)a->batch * pl->n_kv_heads * sizeof(int32_t), (cudaStream_t)stream));
+  pace_attn_args_t b = *a;
+  b.workspace = scratch;
+  b.workspace_bytes = kStaticScratchBytes;
+  return run_mma_paged(&b, 1, (cudaStream_t)stream);
+}
+
 extern "C" int pace_attn_verify(const pace_attn_args_t* a, void* stream) {
   return run_mma_paged(a, 1, (cudaStream_t)stream);
 }

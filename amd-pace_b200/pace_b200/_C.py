@@ -63,6 +63,7 @@ _SIGS = {
                                      C.c_void_p]),
     "pace_attn_workspace_bytes": (C.c_uint64, [C.c_int32] * 5),
     "pace_attn_decode": (C.c_int, [C.POINTER(AttnArgs), C.c_void_p]),
+    "pace_attn_decode_static": (C.c_int, [C.POINTER(AttnArgs), C.c_void_p]),
     "pace_attn_verify": (C.c_int, [C.POINTER(AttnArgs), C.c_void_p]),
     "pace_attn_prefill": (C.c_int, [C.POINTER(AttnArgs), C.c_void_p]),
     "pace_attention_dense": (C.c_int, [C.c_void_p] * 4 + [C.c_int32, C.c_int32, C.c_void_p] + [C.c_int32] * 6 +

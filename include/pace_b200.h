@@ -163,6 +163,20 @@ int pace_attn_decode(const pace_attn_args_t* a, void* stream);  /* q_len == 1, C
 int pace_attn_verify(const pace_attn_args_t* a, void* stream);  /* short q (PARD verify), tensor-core tiles  */
 int pace_attn_prefill(const pace_attn_args_t* a, void* stream); /* prefill chunks, tensor-core tiles         */
 
+/* Decode attention without any allocation.  (No counterpart in the reference: its CPU op
+ * allocates its score tensor on every call, attention_kernels.cpp:222-226.)
+ *
+ * For hosts that cannot allocate device memory where a decode step runs - an engine that owns the
+ * whole device and lends this library nothing, a serving loop whose memory was fixed at start-up,
+ * a thread that must not enter the allocator - and so cannot supply pace_attn_decode's workspace.
+ * Same arguments and result as pace_attn_decode; `workspace` / `workspace_bytes` are ignored and
+ * the scratch is a fixed device array inside the library (about 3.4 MB per GPU, held until the
+ * process exits).  Limits, refused with PACE_ERR_UNSUPPORTED beyond them: at most 16 query heads per
+ * KV head, head_dim <= 128, batch * n_kv_heads <= 65536, at most 192 SMs.  The first call on a device
+ * resolves the array's address there (make it before any stream capture).  Calls share the array:
+ * issue them on one stream, or otherwise keep them from overlapping on the GPU. */
+int pace_attn_decode_static(const pace_attn_args_t* a, void* stream);
+
 /* Dense form with the reference op's exact operands: q [B,N,S,H], k/v [B,Nkv,L,H]
  * contiguous bf16, additive mask [B,1,mask_rows,L] (mask_rows 1 or S; bf16 or fp32;
  * may be NULL), out [B,N,S,H].  Reference: pace::attention, attention.cpp:18-97. */
