@@ -1,0 +1,193 @@
+"""Llama decoder re-hosted on CUDA tensors around the B200 KV-cache path.
+
+The caller of the hot path, kept in the reference's shape (pace/llm/models/llama.py): per layer
+q/k/v projection -> RoPE -> ``kv_cache.update_cache`` -> ``MultiHeadAttention`` -> o_proj
+(llama.py:111-170), model forward slicing off what is already cached (llama.py:270-318).
+Parameter names match the reference's state dict, so its weights load unchanged.
+
+Differences that come from the path being on the GPU:
+  * no ``repeat_kv``: the cache holds the KV heads, the attention kernels are GQA-native;
+  * no 4-D additive mask: causality and left padding reach the kernels as per-sequence integers
+    (``kv_start`` = padded positions, the causal tail follows from the cached lengths);
+  * projections, norms, RoPE and the MLP are stock torch CUDA ops (they are not part of the path);
+  * ``forward_tokens`` takes only the NEW tokens and allows ragged counts per sequence, which
+    batched speculative decoding needs; ``forward`` is the reference signature on top of it.
+"""
+import math
+from typing import List, Optional, Sequence
+
+import torch
+import torch.nn.functional as F
+from torch import nn
+
+from pace_b200.llm.cache import KVCacheBase, KVCacheManager
+from pace_b200.llm.outputs import ModelOutput
+from pace_b200.ops import MultiHeadAttention
+
+
+class _FusedLinear(nn.Module):
+    """Holds ``linear.weight`` like the reference's fused linear + activation operators."""
+
+    def __init__(self, in_features: int, out_features: int):
+        super().__init__()
+        self.linear = nn.Linear(in_features, out_features, bias=False)
+
+
+class RMSNorm(nn.Module):
+    def __init__(self, hidden: int, eps: float):
+        super().__init__()
+        self.weight = nn.Parameter(torch.ones(hidden))
+        self.eps = eps
+
+    def forward(self, x):
+        return F.rms_norm(x, (x.shape[-1],), self.weight, self.eps)
+
+
+class LlamaMLP(nn.Module):
+    """down(up(x) * silu(gate(x))) (reference MergedMLP with gate, pace/ops/mlp.py:73-79)."""
+
+    def __init__(self, hidden: int, inter: int):
+        super().__init__()
+        self.up_proj = _FusedLinear(hidden, inter)
+        self.gate_proj = _FusedLinear(hidden, inter)
+        self.down_proj = nn.Linear(inter, hidden, bias=False)
+
+    def forward(self, x):
+        return self.down_proj(self.up_proj.linear(x) * F.silu(self.gate_proj.linear(x)))
+
+
+class RotaryEmbedding(nn.Module):
+    """Default RoPE: fp32 cos/sin table indexed by position, applied NeoX-style in the activations'
+    dtype (reference pace/ops/rotary_embedding.py:60-110, 396-441)."""
+
+    def __init__(self, rotary_dim: int, max_position_embeddings: int, theta: float):
+        super().__init__()
+        inv_freq = 1.0 / (theta ** (torch.arange(0, rotary_dim, 2, dtype=torch.float) / rotary_dim))
+        freqs = torch.einsum("i,j -> ij", torch.arange(max_position_embeddings, dtype=torch.float), inv_freq)
+        self.register_buffer("cos_cache", freqs.cos(), persistent=False)
+        self.register_buffer("sin_cache", freqs.sin(), persistent=False)
+
+    def forward(self, x: torch.Tensor, position_ids: torch.Tensor):
+        idx = position_ids.flatten()
+        cos = self.cos_cache.index_select(0, idx).unflatten(0, position_ids.shape).to(x.dtype).unsqueeze(1)
+        sin = self.sin_cache.index_select(0, idx).unflatten(0, position_ids.shape).to(x.dtype).unsqueeze(1)
+
+        def apply(query, key):
+            def rot(t):
+                t1, t2 = torch.chunk(t, 2, dim=-1)
+                return torch.cat((t1 * cos - t2 * sin, t2 * cos + t1 * sin), dim=-1)
+            return rot(query), rot(key)
+
+        return apply
+
+
+class LlamaAttention(nn.Module):
+    def __init__(self, config):
+        super().__init__()
+        self.hidden_size = config.hidden_size
+        self.num_heads = config.num_attention_heads
+        self.head_dim = self.hidden_size // self.num_heads
+        self.num_key_value_heads = config.num_key_value_heads
+        self.q_proj = nn.Linear(self.hidden_size, self.num_heads * self.head_dim, bias=False)
+        self.k_proj = nn.Linear(self.hidden_size, self.num_key_value_heads * self.head_dim, bias=False)
+        self.v_proj = nn.Linear(self.hidden_size, self.num_key_value_heads * self.head_dim, bias=False)
+        self.o_proj = nn.Linear(self.hidden_size, self.hidden_size, bias=False)
+        self.attention = MultiHeadAttention()
+
+    def forward(self, hidden_states, position_embeddings, kv_cache: KVCacheBase, kv_start=None, n_new=None,
+                q_lens=None):
+        bsz, q_len, _ = hidden_states.size()
+        q = self.q_proj(hidden_states).view(bsz, q_len, self.num_heads, self.head_dim).transpose(1, 2)
+        k = self.k_proj(hidden_states).view(bsz, q_len, self.num_key_value_heads, self.head_dim).transpose(1, 2)
+        v = self.v_proj(hidden_states).view(bsz, q_len, self.num_key_value_heads, self.head_dim).transpose(1, 2)
+        q, k = position_embeddings(query=q, key=k)
+        # the hot path: append, then attend over the cache (llama.py:155-165)
+        key_h, value_h = kv_cache.update_cache(k, v, concat_dim=2, n_new_per_seq=n_new)
+        out = self.attention(q, key_h, value_h, attention_mask=None, kv_start=kv_start, q_lens=q_lens)
+        out = out.transpose(1, 2).reshape(bsz, q_len, -1)
+        return self.o_proj(out)
+
+
+class LlamaDecoderLayer(nn.Module):
+    def __init__(self, config):
+        super().__init__()
+        self.input_layernorm = RMSNorm(config.hidden_size, config.rms_norm_eps)
+        self.self_attn = LlamaAttention(config)
+        self.mlp = LlamaMLP(config.hidden_size, config.intermediate_size)
+        self.post_attention_layernorm = RMSNorm(config.hidden_size, config.rms_norm_eps)
+
+    def forward(self, hidden_states, position_embeddings, kv_cache, kv_start=None, n_new=None, q_lens=None):
+        h = hidden_states + self.self_attn(self.input_layernorm(hidden_states), position_embeddings, kv_cache,
+                                           kv_start, n_new, q_lens)
+        return h + self.mlp(self.post_attention_layernorm(h))
+
+
+class LlamaModel(nn.Module):
+    def __init__(self, config):
+        super().__init__()
+        self.embed_tokens = nn.Embedding(config.vocab_size, config.hidden_size, getattr(config, "pad_token_id", None))
+        self.layers = nn.ModuleList([LlamaDecoderLayer(config) for _ in range(config.num_hidden_layers)])
+        self.rotary_emb = RotaryEmbedding(config.hidden_size // config.num_attention_heads,
+                                          config.max_position_embeddings, config.rope_theta)
+        self.norm = RMSNorm(config.hidden_size, config.rms_norm_eps)
+
+    def forward_tokens(self, new_ids: torch.Tensor, kv_cache: KVCacheManager, position_ids: torch.Tensor,
+                       kv_start: Optional[torch.Tensor] = None, n_new: Optional[Sequence[int]] = None):
+        hidden = self.embed_tokens(new_ids)
+        rope = self.rotary_emb(hidden, position_ids)
+        q_lens = None
+        if n_new is not None:
+            q_lens = torch.tensor(list(n_new), dtype=torch.int32, device=new_ids.device)
+        for idx, layer in enumerate(self.layers):
+            hidden = layer(hidden, rope, kv_cache[idx], kv_start, n_new, q_lens)
+        return self.norm(hidden)
+
+
+class LlamaForCausalLM(nn.Module):
+    def __init__(self, config):
+        super().__init__()
+        self.config = config
+        self.model = LlamaModel(config)
+        self.vocab_size = config.vocab_size
+        self.lm_head = nn.Linear(config.hidden_size, config.vocab_size, bias=False)
+
+    # -- the reference signature (llama.py:428-440) -----------------------------------------
+    def forward(self, input_ids: torch.LongTensor, kv_cache: KVCacheManager, attention_mask: torch.Tensor,
+                inputs_embeds=None) -> ModelOutput:
+        """``input_ids`` is the whole history; what the cache already holds is sliced off
+        (llama.py:284-286).  ``attention_mask`` is the 2-D 0/1 mask; zeros on the left are padding."""
+        if inputs_embeds is not None:
+            raise NotImplementedError("inputs_embeds is not supported")
+        past = len(kv_cache)
+        new_ids = input_ids[:, past:]
+        mask = attention_mask.to(input_ids.device)
+        position_ids = mask.long().cumsum(-1) - 1
+        position_ids.masked_fill_(mask == 0, 1)
+        position_ids = position_ids[:, past: past + new_ids.shape[1]]
+        kv_start = None
+        if bool((mask == 0).any()):
+            kv_start = (mask.cumsum(-1) == 0).sum(-1).to(torch.int32)
+        hidden = self.model.forward_tokens(new_ids, kv_cache, position_ids, kv_start)
+        return ModelOutput(logits=self.lm_head(hidden))
+
+    # -- ragged form used by batched speculative decoding ---------------------------------------
+    def forward_ragged(self, new_ids: torch.Tensor, n_new: Sequence[int], kv_cache: KVCacheManager) -> ModelOutput:
+        """``new_ids`` [B, n_max] holds, left-aligned, ``n_new[b]`` new tokens of sequence b; positions
+        continue from each sequence's cached length."""
+        cached = kv_cache[0].seq_lens if kv_cache[0].seq_lens else [0] * new_ids.shape[0]
+        base = torch.tensor(cached, dtype=torch.long, device=new_ids.device).unsqueeze(1)
+        position_ids = base + torch.arange(new_ids.shape[1], device=new_ids.device).unsqueeze(0)
+        position_ids.clamp_(max=self.config.max_position_embeddings - 1)
+        ragged = None if all(n == new_ids.shape[1] for n in n_new) else list(n_new)
+        hidden = self.model.forward_tokens(new_ids, kv_cache, position_ids, None, ragged)
+        return ModelOutput(logits=self.lm_head(hidden))
+
+
+def random_init_(model: nn.Module, seed: int, std: float = 0.02) -> nn.Module:
+    """N(0, std) weights from a seed (norm weights stay at one): the BASELINE configs' synthetic models."""
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    with torch.no_grad():
+        for p in model.parameters():
+            if p.dim() >= 2:
+                p.copy_((torch.randn(p.shape, generator=g) * std).to(p.dtype))
+    return model
