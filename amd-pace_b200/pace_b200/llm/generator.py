@@ -1,0 +1,153 @@
+"""Generation loop: greedy decoding and PARD speculative decoding over the B200 KV-cache path.
+
+Re-hosts the part of the reference's ``Generator`` (pace/llm/generator.py) that drives the hot path:
+
+  _prepare_kv_cache                    generator.py:396-410   one manager per model, max_new + prompt
+  _prepare_for_pard                    generator.py:412-449   second manager for the draft model
+  _speculate_tokens                    generator.py:638-667   one draft pass over history + (d-1) placeholders
+  _postprocess_speculated_tokens       generator.py:669-713   accept / rollback
+  _generate                            generator.py:715-818   the step loop
+
+What each step does to the caches follows the reference exactly: the draft cache takes
+history + d - 1 tokens and always gives d - 1 back; the target cache takes history + d tokens and
+gives back d - keep + 1 of them unless every compared draft matched (keep == d), in which case nothing
+is removed and the unverified last draft row stays (generator.py:696-706).
+
+Beyond the reference (which asserts batch size 1 for PARD, generator.py:427-430): a batch of
+sequences, each with its own acceptance, so appends and rollbacks are ragged per sequence; and
+acceptance forced by a seeded Bernoulli draw per draft token instead of the token comparison, which
+is how the speculative configuration of the benchmark exercises rollback with random weights.
+"""
+from typing import List, Optional
+
+import torch
+
+from pace_b200.llm.cache import KVCacheManager, KVCacheType
+from pace_b200.llm.configs import PardSpecDecodeConfig, SamplingConfig
+from pace_b200.llm.outputs import GeneratorOutput, SpeculativeStats
+
+
+class Generator:
+    def __init__(self, model, pard_model=None, pard_config: Optional[PardSpecDecodeConfig] = None,
+                 kv_cache_type: KVCacheType = KVCacheType.BMC):
+        self.model = model
+        self.pard_model = pard_model
+        self.pard_config = pard_config if pard_model is not None else None
+        self.kv_cache_type = kv_cache_type
+        self.device = next(model.parameters()).device
+        self.trace: List[list] = []        # (cache, op, n per sequence) - what the tests compare with the reference
+
+    # -- preparation --------------------------------------------------------------------------
+    def _prepare_kv_cache(self, kv_cache_type, input_prompts: torch.Tensor) -> None:
+        max_seq_length = self.sampling_config.max_new_tokens + input_prompts.size(-1)
+        extra = self.pard_config.num_speculative_tokens + 1 if self.pard_config else 0
+        self.kv_cache_manager = KVCacheManager(self.model.config, max_seq_length, kv_cache_type, extra_tokens=extra)
+
+    def _prepare_for_pard(self, input_prompts: torch.Tensor) -> None:
+        if self.pard_config is None:
+            self.draft_size = 0
+            return
+        self.draft_size = self.pard_config.num_speculative_tokens
+        self.total_speculated_tokens: List[int] = []
+        self.pard_kv_cache_manager = KVCacheManager(
+            self.pard_model.config, self.sampling_config.max_new_tokens + input_prompts.size(-1), self.kv_cache_type,
+            extra_tokens=self.draft_size + 1)
+        self._accept_rng = None
+        if self.pard_config.forced_accept_prob is not None:
+            self._accept_rng = torch.Generator().manual_seed(self.pard_config.forced_accept_seed)
+
+    def prepare_for_generate(self, prompts: torch.Tensor, sampling_config: Optional[SamplingConfig] = None):
+        self.sampling_config = sampling_config or SamplingConfig()
+        self._prepare_kv_cache(self.kv_cache_type, prompts)
+        self._prepare_for_pard(prompts)
+        self.trace = []
+        return prompts
+
+    # -- helpers --------------------------------------------------------------------------------
+    def _run_ragged(self, model, manager, tag: str, history: List[List[int]], tail: List[List[int]]):
+        """Feeds every sequence the part of history + tail its cache does not hold yet."""
+        cached = manager[0].seq_lens if manager[0].seq_lens else [0] * len(history)
+        rows = [(history[b] + tail[b])[cached[b]:] for b in range(len(history))]
+        counts = [len(r) for r in rows]
+        n_max = max(counts)
+        new = torch.full((len(rows), n_max), self.sampling_config.pad_token_id, dtype=torch.long)
+        for b, r in enumerate(rows):
+            new[b, : len(r)] = torch.tensor(r, dtype=torch.long)
+        out = model.forward_ragged(new.to(self.device), counts, manager)
+        self.trace.append([tag, "append", counts])
+        return out.logits, counts
+
+    def _speculate_tokens(self, history: List[List[int]]) -> List[List[int]]:
+        d = self.draft_size
+        if self.pard_config is None:
+            return [[] for _ in history]
+        tail = [[self.pard_config.pard_token] * (d - 1) for _ in history]
+        logits, counts = self._run_ragged(self.pard_model, self.pard_kv_cache_manager, "draft", history, tail)
+        drafts = []
+        for b, n in enumerate(counts):
+            drafts.append(logits[b, n - d: n].argmax(dim=-1).tolist())
+        return drafts
+
+    def _postprocess_speculated_tokens(self, next_tokens: List[List[int]], drafts: List[List[int]]) -> List[List[int]]:
+        """Accept leading matches among the first d-1 drafts, always keep one target token, roll the
+        caches back (generator.py:684-706) - per sequence."""
+        if self.pard_config is None:
+            return next_tokens
+        d = self.draft_size
+        kept, target_rm, draft_rm = [], [], []
+        for b in range(len(drafts)):
+            if self._accept_rng is not None:
+                draws = (torch.rand(d - 1, generator=self._accept_rng) < self.pard_config.forced_accept_prob).tolist()
+            else:
+                draws = [i < len(next_tokens[b]) and next_tokens[b][i] == drafts[b][i] for i in range(d - 1)]
+            keep = 0
+            for ok in draws:
+                if not ok:
+                    break
+                keep += 1
+            keep += 1                                   # the target's own token is always kept
+            toks = (drafts[b][: keep - 1] if self._accept_rng is not None else next_tokens[b][: keep - 1])
+            toks = toks + [next_tokens[b][min(keep - 1, len(next_tokens[b]) - 1)]]
+            kept.append(toks)
+            target_rm.append(d - keep + 1 if d - keep > 0 else 0)
+            draft_rm.append(d - 1)
+            self.total_speculated_tokens.append(keep)
+        if any(target_rm):
+            self.kv_cache_manager.remove_cache(target_rm)
+        self.trace.append(["target", "remove", target_rm])
+        self.pard_kv_cache_manager.remove_cache(draft_rm)
+        self.trace.append(["draft", "remove", draft_rm])
+        return kept
+
+    # -- the loop ----------------------------------------------------------------------------------
+    @torch.inference_mode()
+    def _generate(self, inputs: torch.Tensor) -> GeneratorOutput:
+        history = [row.tolist() for row in inputs]
+        prompt_len = inputs.shape[1]
+        max_len = prompt_len + self.sampling_config.max_new_tokens
+        d = self.draft_size
+        while min(len(h) for h in history) < max_len:
+            drafts = self._speculate_tokens(history)
+            logits, counts = self._run_ragged(self.model, self.kv_cache_manager, "target", history, drafts)
+            next_tokens = []
+            for b, n in enumerate(counts):
+                take = min(d + 1, n)
+                next_tokens.append(logits[b, n - take: n].float().argmax(dim=-1).tolist())
+            kept = self._postprocess_speculated_tokens(next_tokens, drafts)
+            for b in range(len(history)):
+                if len(history[b]) < max_len or self.pard_config is not None:
+                    history[b] = history[b] + kept[b]
+        lengths = [len(h) for h in history]
+        out = torch.full((len(history), max(lengths)), self.sampling_config.pad_token_id, dtype=torch.long)
+        for b, h in enumerate(history):
+            out[b, : len(h)] = torch.tensor(h)
+        stats = None
+        if self.pard_config is not None:
+            stats = SpeculativeStats(total_speculated_tokens=sum(self.total_speculated_tokens),
+                                     mean_accepted_tokens=sum(self.total_speculated_tokens) / len(self.total_speculated_tokens))
+        self.kv_cache_manager.pool.check_status()
+        return GeneratorOutput(output_token_ids=out, lengths=lengths, speculative_stats=stats)
+
+    def generate(self, inputs: torch.Tensor, sampling_config: Optional[SamplingConfig] = None) -> GeneratorOutput:
+        self.prepare_for_generate(inputs, sampling_config)
+        return self._generate(inputs)
