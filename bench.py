@@ -274,7 +274,7 @@ def run_ours(args, rank, world, local_rank):
         "gpu_launches": own_launches_per_step * args.steps,
         "gpu_launches_note": f"{own_launches_per_step} own kernels per step: 1 page reserve + {L} x [append, decode attention]",
         "clocks": clocks,
-        "roofline": {"bound": "hbm", "kernel": "attn_decode_kernel<128,4>", "achieved": achieved, "peak": peak,
+        "roofline": {"bound": "hbm", "kernel": "attn_mma_kernel<128,1,8> (GQA decode, 4 query heads packed per MMA tile)", "achieved": achieved, "peak": peak,
                      "peak_kind": peak_kind, "unit": "GB/s", "frac": achieved / peak,
                      "frac_of_nominal_8TBs": achieved / 8000.0, "us_per_launch": attn_us, "kv_len": lens_now,
                      "alg_bytes_per_launch": alg_bytes, "traffic": None},

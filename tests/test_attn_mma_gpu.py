@@ -201,3 +201,21 @@ def test_dense_op_error_surface():
         mha(q.to(torch.int8), k.to(torch.int8), k.to(torch.int8), attention_mask=m)
     with pytest.raises(RuntimeError, match="no CPU path"):
         mha(q.cpu(), k.cpu(), k.cpu(), attention_mask=m.cpu())
+
+
+def test_torch_ops_pace_attention_schema_on_cuda():
+    # the reference's custom-op entry (csrc/ops/attention.cpp:104-108), same call as its tests make
+    import pace_b200.ops  # noqa: F401
+    from oracle.attention_ref import sdpa_native
+    g = torch.Generator().manual_seed(11)
+    q = torch.randn(2, 16, 1, 128, generator=g).bfloat16()
+    k = torch.randn(2, 16, 300, 128, generator=g).bfloat16()
+    v = torch.randn(2, 16, 300, 128, generator=g).bfloat16()
+    m = torch.randn(2, 1, 1, 300, generator=g).bfloat16()
+    for use_kq in (0, 1, False):
+        out = torch.ops.pace.attention(q.to(DEV), k.to(DEV), v.to(DEV), m.to(DEV), use_kq)
+        _check(out, sdpa_native(q, k, v, m).float())
+    with pytest.raises(RuntimeError, match="attention requires use_KQ to be 0 or 1"):
+        torch.ops.pace.attention(q.to(DEV), k.to(DEV), v.to(DEV), m.to(DEV), 7)
+    with pytest.raises(RuntimeError, match="attention requires 4D inputs"):
+        torch.ops.pace.attention(q.to(DEV), k.to(DEV).view(32, 300, 128), v.to(DEV), m.to(DEV), 0)
