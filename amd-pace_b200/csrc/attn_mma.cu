@@ -232,8 +232,13 @@ template <int D, int MT, int NS>
 __global__ void __launch_bounds__(kThreadsM, 1)
     attn_mma_kernel(const MmaParams p, const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV) {
   static_assert(MT * NS == kWarps, "eight consumer warps");
-  constexpr int TW = kChunk / NS;  // tokens of a chunk owned by one warp
-  constexpr int NT = TW / 8;       // score n-tiles per warp
+  // How the NS warps of a row tile share the key stream.  Decode (MT == 1): each chunk's keys are cut
+  // into NS slices, every warp works on every chunk.  Verify tiles (MT, NS >= 2): whole chunks are dealt
+  // round-robin to the NS warp groups, so NS chunks are in flight in the tensor pipe at a time and a
+  // warp's MMA chains have 8 independent tiles to overlap.
+  constexpr bool DEAL_CHUNKS = (MT >= 2 && NS >= 2);
+  constexpr int TW = DEAL_CHUNKS ? kChunk : kChunk / NS;  // keys of a chunk one warp works on
+  constexpr int NT = TW / 8;                              // score n-tiles per warp
   constexpr int KS = D / 16;       // k-steps of Q K^T
   constexpr int ON = D / 8;        // output n-tiles
   constexpr int HALVES = D / 64;   // 64-element (128-byte) column blocks of a K/V row
@@ -553,7 +558,6 @@ __global__ void __launch_bounds__(kThreadsM, 1)
   // ================================= consumers =================================
   const int mt = warp / NS, ns = warp - mt * NS;
   const int qr = lane >> 2, qc = lane & 3;  // fragment row within 8, column pair
-  const int tw0 = ns * TW;
   uint32_t qa[KS][4];
   float o[ON][4];
   float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
@@ -617,7 +621,14 @@ __global__ void __launch_bounds__(kThreadsM, 1)
 #ifdef PACE_SKIP_MATH
     if (false) {
 #else
-    if (tw0 < rows) {  // this warp's token slice holds live keys
+    // The chunk's keys are dealt to the NS warps of a row tile in equal slices of whole 8-key tiles:
+    // a short chunk (a page of 33..63 tokens, a sequence's last chunk) keeps every warp busy instead of
+    // filling the first slices only.  Row tiles made of padding rows only sit the chunk out.
+    int tw = TW;
+    if (!DEAL_CHUNKS && NT > 1 && rows < kChunk) tw = min(TW, (((rows + NS - 1) / NS) + 7) & ~7);
+    const int tw0 = DEAL_CHUNKS ? 0 : ns * tw;
+    const bool mine = !DEAL_CHUNKS || (i % NS) == ns;
+    if (mine && tw0 < rows && mt * 16 < fin.live) {
 #endif
       const uint32_t kb = smem_u32(st), vb = kb + KVB;
       // ---- S = Q K^T ----
@@ -631,25 +642,29 @@ __global__ void __launch_bounds__(kThreadsM, 1)
 #pragma unroll
         for (int c = 0; c < CH; ++c) part[c][0] = part[c][1] = part[c][2] = part[c][3] = 0.f;
         const int row = tw0 + nt * 8 + (lane & 7);
+        if (nt * 8 < tw && tw0 + nt * 8 < rows) {  // warp-uniform: this 8-key tile is in my slice and holds keys
 #pragma unroll
-        for (int k2 = 0; k2 < KS / 2; ++k2) {
-          const int cg = k2 * 4 + (lane >> 3);
-          uint32_t b0, b1, b2, b3;
-          ldsm_x4(kb + (cg >> 3) * HALF_B + row * 128 + (((cg & 7) ^ (row & 7)) << 4), b0, b1, b2, b3);
-          mma16816(part[(2 * k2) % CH], qa[2 * k2], b0, b1);
-          mma16816(part[(2 * k2 + 1) % CH], qa[2 * k2 + 1], b2, b3);
-        }
+          for (int k2 = 0; k2 < KS / 2; ++k2) {
+            const int cg = k2 * 4 + (lane >> 3);
+            uint32_t b0, b1, b2, b3;
+            ldsm_x4(kb + (cg >> 3) * HALF_B + row * 128 + (((cg & 7) ^ (row & 7)) << 4), b0, b1, b2, b3);
+            mma16816(part[(2 * k2) % CH], qa[2 * k2], b0, b1);
+            mma16816(part[(2 * k2 + 1) % CH], qa[2 * k2 + 1], b2, b3);
+          }
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          float t = part[0][e];
+          for (int e = 0; e < 4; ++e) {
+            float t = part[0][e];
 #pragma unroll
-          for (int c = 1; c < CH; ++c) t += part[c][e];
-          sc[nt][e] = t;
+            for (int c = 1; c < CH; ++c) t += part[c][e];
+            sc[nt][e] = t;
+          }
+        } else {
+          sc[nt][0] = sc[nt][1] = sc[nt][2] = sc[nt][3] = -INFINITY;
         }
       }
       // ---- scale, additive mask, visibility ----
       const int t_base = tok0 + tw0 + 2 * qc;  // key index of sc[0][0]
-      const bool need_mask = (tw0 + TW > rows) || (tok0 + tw0 < kvs) || (tok0 + tw0 + TW > min(lim0, lim1));
+      const bool need_mask = (tw0 + tw > rows) || (tok0 + tw0 < kvs) || (tok0 + tw0 + tw > min(lim0, lim1));
 #pragma unroll
       for (int nt = 0; nt < NT; ++nt) {
 #pragma unroll
@@ -732,7 +747,7 @@ __global__ void __launch_bounds__(kThreadsM, 1)
       } else {
 #pragma unroll
         for (int kb2 = 0; kb2 < NT / 2; ++kb2) {
-          if (tw0 + kb2 * 16 < rows) {  // warp-uniform: skip 16-token blocks past the chunk's keys
+          if (kb2 * 16 < tw && tw0 + kb2 * 16 < rows) {  // warp-uniform: skip 16-key blocks outside my slice
             const uint32_t a[4] = {pk[2 * kb2][0], pk[2 * kb2][1], pk[2 * kb2 + 1][0], pk[2 * kb2 + 1][1]};
             const int mi = lane >> 3;
             const int row = tw0 + kb2 * 16 + (mi & 1) * 8 + (lane & 7);

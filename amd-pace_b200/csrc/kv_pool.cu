@@ -21,6 +21,7 @@ namespace {
 
 constexpr int kCounterFree = 0;    // number of free pages
 constexpr int kCounterTicket = 1;  // append kernel: blocks finished
+constexpr int kCounterShared = 2;  // set by a beam gather: pages may have more than one owner
 
 __host__ __device__ inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
@@ -104,7 +105,9 @@ __global__ void reserve_kernel(pace_kv_pool_t p, int layer, const int32_t* __res
   const int P = p.page_tokens;
   if (threadIdx.x == 0) {
     cow_count = 0;
-    for (int b = 0; b < batch; ++b) {
+    // pages are only ever shared after a beam gather; without one this sequential scan is skipped
+    const int n_scan = p.counters[kCounterShared] ? batch : 0;
+    for (int b = 0; b < n_scan; ++b) {
       const int slot = seq_ids[b];
       if (slot < 0 || slot >= p.max_seqs) continue;
       int n = n_per ? min(n_per[b], n_new) : n_new;
@@ -302,7 +305,10 @@ __global__ void gather_kernel(pace_kv_pool_t p, const int32_t* __restrict__ seq_
   int32_t* tmp_rows = p.table_tmp;                         // [batch][MP + 1] (last = page count)
   int32_t* tmp_len = p.table_tmp + (size_t)p.max_seqs * (MP + 4);  // [n_layers][batch]
   __shared__ int bad;
-  if (threadIdx.x == 0) bad = 0;
+  if (threadIdx.x == 0) {
+    bad = 0;
+    p.counters[kCounterShared] = 1;
+  }
   __syncthreads();
   for (int i = threadIdx.x; i < batch; i += blockDim.x) {
     const long long j = beam_idx[i];

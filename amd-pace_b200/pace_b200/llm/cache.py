@@ -10,9 +10,9 @@ argument meaning, same errors):
 What differs underneath: K/V live in one paged pool per manager
 (``[layer][K|V][page][kv_head][page_tokens][head_dim]`` bf16 in HBM) with the block
 table, lengths and free list in device memory; append / rollback / beam gather are
-CUDA kernels (csrc/kv_pool.cu) and the latter two move no K/V bytes.  The page
-size equals the reference's ``tokens_per_split`` so ``capacity`` follows the BMC
-growth trace exactly.  ``update_cache`` returns handles (``PagedKV``) instead of
+CUDA kernels (csrc/kv_pool.cu) and the latter two move no K/V bytes.  ``capacity``
+follows the reference's BMC growth trace exactly (whole ``tokens_per_split`` segments);
+it is bookkeeping on top of the physical pages, which are 64 tokens by default.  ``update_cache`` returns handles (``PagedKV``) instead of
 dense tensors; ``MultiHeadAttention`` consumes them directly.  The host keeps
 integer mirrors of lengths and capacities because the reference API is
 synchronous about them (``len(manager)``, ``ValueError`` on over-removal).
@@ -33,7 +33,23 @@ import torch
 from pace_b200 import _C
 
 OVER_REMOVE_MSG = "Cannot remove more tokens than available in cache."
-DYNAMIC_PAGE_TOKENS = 64
+KV_PAGE_TOKENS = 64
+
+
+def physical_page_tokens(tokens_per_split: Optional[int]) -> int:
+    """Tokens per physical page of the pool.
+
+    64 by default: one page is then exactly one full K/V chunk of the attention kernels (one TMA box
+    of 64 rows per 128-byte column block), whatever the BMC segment size.  The reference's capacity
+    (a multiple of ``tokens_per_split``) is bookkeeping on top of the pages and does not depend on
+    their size.  ``PACE_KV_PAGE_TOKENS=tps`` makes a page one BMC segment instead, an integer forces a size.
+    """
+    v = os.getenv("PACE_KV_PAGE_TOKENS", "")
+    if v == "tps" and tokens_per_split:
+        return int(tokens_per_split)
+    if v.isdigit() and int(v) > 0:
+        return int(v)
+    return KV_PAGE_TOKENS
 
 
 class KVCacheType(Enum):
@@ -524,7 +540,7 @@ class BMCKVCache(KVCacheBase):
     def __init__(self, max_seq_length: int, manager: Optional[KVCacheManager] = None, layer: int = 0):
         super().__init__(max_seq_length, manager, layer)
         self.tokens_per_split = bmc_tokens_per_split(max_seq_length)
-        self.page_tokens = self.tokens_per_split
+        self.page_tokens = physical_page_tokens(self.tokens_per_split)
 
     def _capacity_after(self, updated: int) -> int:
         # a fresh buffer is made when none exists or the new length reaches the capacity (cache.py:292-313)
@@ -546,7 +562,7 @@ class DynamicKVCache(KVCacheBase):
 
     def __init__(self, max_seq_length: int, manager: Optional[KVCacheManager] = None, layer: int = 0):
         super().__init__(max_seq_length, manager, layer)
-        self.page_tokens = DYNAMIC_PAGE_TOKENS
+        self.page_tokens = physical_page_tokens(None)
 
     def _capacity_after(self, updated: int) -> int:
         return updated

@@ -102,6 +102,12 @@ class ClockSampler:
 
 def cpu_reference_line(steps: int, warmup: int, sample_layers: int):
     from oracle.cpu_path import time_decode_tokens_per_s
+    # every host core this process may run on (a launcher such as torchrun sets OMP_NUM_THREADS=1)
+    try:
+        cores = len(os.sched_getaffinity(0))
+    except AttributeError:
+        cores = os.cpu_count() or 1
+    torch.set_num_threads(max(1, cores))
     cores = torch.get_num_threads()
     tps, step_s = time_decode_tokens_per_s(CFG["n_layers"], sample_layers, CFG["batch"], CFG["hq"], CFG["hkv"],
                                            CFG["d"], CFG["prompt"], CFG["prompt"] + CFG["max_new"], steps, warmup)
@@ -271,7 +277,7 @@ def run_ours(args, rank, world, local_rank):
                    "launch": "one CUDA graph per step"},
         "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": host_in.numel() * 2,
                 "d2h_bytes_per_step": host_out.numel() * 2, "steps": e2e_steps, "ms_per_step": e2e_ms / e2e_steps},
-        "gpu_launches": own_launches_per_step * args.steps,
+        "gpu_launches": own_launches_per_step * args.steps * world,
         "gpu_launches_note": f"{own_launches_per_step} own kernels per step: 1 page reserve + {L} x [append, decode attention]",
         "clocks": clocks,
         "roofline": {"bound": "hbm", "kernel": "attn_mma_kernel<128,1,8> (GQA decode, 4 query heads packed per MMA tile)", "achieved": achieved, "peak": peak,
@@ -293,6 +299,74 @@ def run_ours(args, rank, world, local_rank):
     print(json.dumps(line), flush=True)
 
 
+def run_aux(args):
+    """Side measurements of the multi-token attention kernels (not the bench line): PARD verify
+    (config 4: batch 16, 9 query tokens over 1033 cached) and a 512-token prefill chunk (config 3:
+    batch 8, 512 queries over a cache of `--past` + 512).  Times the attention kernel alone over
+    `--layers` layers visited round-robin (cold L2) and prints one JSON line."""
+    from pace_b200.llm.cache import KVCacheManager, KVCacheType
+    from pace_b200.ops import MultiHeadAttention
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    L = min(args.layers, 8)
+    Hq, Hkv, D = CFG["hq"], CFG["hkv"], args.head_dim
+    if args.workload == "verify":
+        B, S, kv_len = 16, 9, 1024 + 9
+    else:
+        B, S, kv_len = 8, 512, args.past + 512
+
+    class Cfg:
+        num_hidden_layers = L
+
+    g = torch.Generator(device=dev).manual_seed(7)
+    mgr = KVCacheManager(Cfg(), kv_len + 64, KVCacheType.BMC)
+    for l in range(L):
+        done = 0
+        while done < kv_len:
+            n = min(512, kv_len - done)
+            k = torch.randn(B, Hkv, n, D, device=dev, generator=g, dtype=torch.float32).bfloat16()
+            mgr[l].update_cache(k, k.flip(2), concat_dim=2)
+            done += n
+    q = torch.randn(B, S, Hq, D, device=dev, generator=g, dtype=torch.float32).bfloat16().transpose(1, 2)
+    mha = MultiHeadAttention()
+    hs = [(mgr[l].key, mgr[l].value) for l in range(L)]
+    out = torch.empty(B, S, Hq, D, dtype=torch.bfloat16, device=dev).transpose(1, 2)
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for l in range(L):
+            mha(q, *hs[l], out=out)
+    side.synchronize()
+    graph = torch.cuda.CUDAGraph()          # back-to-back launches without host gaps
+    with torch.cuda.graph(graph, stream=side):
+        for l in range(L):
+            mha(q, *hs[l], out=out)
+    for _ in range(3):
+        graph.replay()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    reps = max(1, args.steps // 8)
+    e0.record()
+    for _ in range(reps):
+        graph.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    us = e0.elapsed_time(e1) * 1e3 / (reps * L)
+    mgr.pool.check_status()
+    alg_bytes = B * (2 * Hkv * D * 2 * kv_len) + 2 * B * Hq * D * 2 * S
+    # causal: query s sees past + s + 1 keys; 4 flops per (query head, key, dim)
+    flops = sum(4 * Hq * D * (kv_len - S + s + 1) for s in range(S)) * B
+    peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json"))) if os.path.exists(
+        os.path.join(ROOT, "MEASURED_PEAKS.json")) else {"hbm_gbs": FALLBACK_HBM_GBS, "bf16_tflops": 1590.0}
+    line = {"workload": args.workload, "batch": B, "q_len": S, "kv_len": kv_len, "head_dim": D,
+            "page_tokens": mgr.pool.page_tokens, "us_per_launch": us,
+            "hbm": {"alg_bytes": alg_bytes, "achieved_gbs": alg_bytes / us / 1e3,
+                    "frac_of_measured": alg_bytes / us / 1e3 / peaks["hbm_gbs"]},
+            "tensor": {"flops": flops, "achieved_tflops": flops / us / 1e6,
+                       "frac_of_measured_burst": flops / us / 1e6 / peaks["bf16_tflops"]}}
+    print(json.dumps(line), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -302,6 +376,10 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--layers", type=int, default=CFG["n_layers"],
                     help="profiling aid: fewer layers = less device memory; the bench line is only valid at 32")
+    ap.add_argument("--workload", default="decode", choices=["decode", "verify", "prefill"],
+                    help="decode = the bench line; verify / prefill = side measurements of the multi-token kernels")
+    ap.add_argument("--past", type=int, default=3584, help="prefill side measurement: tokens cached before the chunk")
+    ap.add_argument("--head-dim", type=int, default=128, choices=[64, 128])
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     CFG["n_layers"] = args.layers
@@ -310,6 +388,10 @@ def main():
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if args.impl == "reference":
         run_reference(args, rank)
+        return
+    if args.workload != "decode":
+        if rank == 0:
+            run_aux(args)
         return
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
