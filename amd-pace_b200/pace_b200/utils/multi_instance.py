@@ -1,0 +1,94 @@
+"""Multi-instance data-parallel serving: one model instance per GPU, requests sharded by sequence.
+
+    python -m pace_b200.utils.multi_instance --gpus 8 --requests-per-gpu 256 --min-len 256 --max-len 32768
+
+The shape of the reference's examples/multi_instance_pace.py:139-274: N worker processes, each with
+its own model and KV pool on its own device, serve their share of the requests; only request
+indices go in and (tokens, seconds) come out; whole-box throughput = all tokens over the slowest
+instance's time.  Prompts are seeded random token ids with log-uniform lengths, weights are random
+N(0, 0.02) of the given shape: there is no dataset or checkpoint behind it.
+"""
+import argparse
+import json
+import math
+import multiprocessing as mp
+import time
+
+from pace_b200.utils.worker import MultipleProcesses, Worker, box_throughput, shard_requests
+
+
+class _Cfg:
+    def __init__(self, **kw):
+        self.__dict__.update(kw)
+
+
+def make_prompt_lengths(n: int, lo: int, hi: int, seed: int):
+    import torch
+    g = torch.Generator().manual_seed(seed)
+    u = torch.rand(n, generator=g)
+    return [int(round(math.exp(math.log(lo) + float(x) * (math.log(hi) - math.log(lo))))) for x in u]
+
+
+def _init_instance(rank, args):
+    import torch
+    from pace_b200.llm.models.llama import LlamaForCausalLM, random_init_
+    from pace_b200.llm.serving import WaveServer
+    cfg = _Cfg(hidden_size=args.hidden, intermediate_size=args.ffn, num_hidden_layers=args.layers,
+               num_attention_heads=args.heads, num_key_value_heads=args.kv_heads, vocab_size=args.vocab,
+               max_position_embeddings=args.max_len + args.new_tokens + 64, rope_theta=500000.0, rms_norm_eps=1e-5,
+               pad_token_id=0)
+    dev = torch.device("cuda", torch.cuda.current_device())
+    model = random_init_(LlamaForCausalLM(cfg).to(torch.bfloat16), seed=1).to(dev).eval()
+    server = WaveServer(model, pool_tokens=args.pool_tokens, max_batch=args.max_batch,
+                        max_seq_len=args.max_len + args.new_tokens)
+    return {"rank": rank, "server": server, "cfg": cfg}
+
+
+def _serve(state, args, world, out_queue):
+    import torch
+    rank = state["rank"]
+    lengths = make_prompt_lengths(args.requests_per_gpu * world, args.min_len, args.max_len, seed=7)
+    mine = shard_requests(len(lengths), world, rank)
+    g = torch.Generator().manual_seed(100 + rank)
+    prompts = [torch.randint(1, args.vocab, (lengths[i],), generator=g) for i in mine]
+    t0 = time.perf_counter()
+    _, stats = state["server"].run(prompts, args.new_tokens)
+    dt = time.perf_counter() - t0
+    out_queue.put((rank, stats.output_tokens, stats.prompt_tokens, dt, stats.decode_s, stats.waves))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--requests-per-gpu", type=int, default=256)
+    ap.add_argument("--min-len", type=int, default=256)
+    ap.add_argument("--max-len", type=int, default=32768)
+    ap.add_argument("--new-tokens", type=int, default=128)
+    ap.add_argument("--pool-tokens", type=int, default=1 << 20)
+    ap.add_argument("--max-batch", type=int, default=256)
+    ap.add_argument("--layers", type=int, default=32)
+    ap.add_argument("--hidden", type=int, default=4096)
+    ap.add_argument("--ffn", type=int, default=14336)
+    ap.add_argument("--heads", type=int, default=32)
+    ap.add_argument("--kv-heads", type=int, default=8)
+    ap.add_argument("--vocab", type=int, default=128256)
+    args = ap.parse_args()
+    ctx = mp.get_context("spawn")
+    out = ctx.Queue()
+    workers = [Worker(r, None, _init_instance, (r, args), _serve, (args, args.gpus, out), device_index=r, ctx=ctx)
+               for r in range(args.gpus)]
+    pool = MultipleProcesses(workers)
+    pool.run()
+    results = [out.get() for _ in range(args.gpus)]
+    pool.join()
+    agg, ref_style = box_throughput([(r[1], r[3]) for r in results], args.gpus)
+    decode_tps = sum(r[1] for r in results) / max(r[4] for r in results)
+    print(json.dumps({"n_gpus": args.gpus, "requests": args.requests_per_gpu * args.gpus,
+                      "output_tokens": sum(r[1] for r in results), "prompt_tokens": sum(r[2] for r in results),
+                      "box_output_tokens_per_s": agg, "reference_style_tokens_per_s": ref_style,
+                      "box_decode_tokens_per_s": decode_tps, "waves_per_gpu": [r[5] for r in sorted(results)],
+                      "failed_workers": pool.failed()}))
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,50 @@
+"""Wave admission on a shared long-lived pool: ragged chunked prefill, decode, page recycling."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+class Cfg:
+    def __init__(self, **kw):
+        self.__dict__.update(kw)
+
+
+def _model():
+    from pace_b200.llm.models.llama import LlamaForCausalLM, random_init_
+    cfg = Cfg(hidden_size=256, intermediate_size=256, num_hidden_layers=2, num_attention_heads=4,
+              num_key_value_heads=1, vocab_size=97, max_position_embeddings=1024, rope_theta=500000.0,
+              rms_norm_eps=1e-5, pad_token_id=0)
+    return random_init_(LlamaForCausalLM(cfg).to(torch.bfloat16), 3).to(DEV).eval()
+
+
+def test_waves_recycle_pages_and_match_single_request_runs():
+    from pace_b200.llm.serving import WaveServer
+    model = _model()
+    g = torch.Generator().manual_seed(8)
+    lens = [300, 37, 129, 64, 511, 5, 200]
+    prompts = [torch.randint(1, 97, (n,), generator=g) for n in lens]
+    new = 6
+    small = WaveServer(model, pool_tokens=64 * 14, max_batch=4, max_seq_len=600, prefill_chunk=128)
+    free0 = small.pool.query()[1]
+    outs, stats = small.run(prompts, new)
+    assert stats.waves >= 3 and sum(stats.wave_sizes) == len(prompts)       # the pool forced several waves
+    assert stats.prompt_tokens == sum(lens) and stats.output_tokens == new * len(prompts)
+    assert all(len(o) == new for o in outs)
+    bits, free1 = small.pool.query()
+    assert bits == 0 and free1 == free0 and small.pool.host_free_pages == free0   # every page came back
+    # one request at a time on a roomy pool: same first token (later ones may flip on bf16 ties)
+    big = WaveServer(model, pool_tokens=64 * 64, max_batch=1, max_seq_len=600, prefill_chunk=512)
+    agree = 0
+    for i, p in enumerate(prompts):
+        o, _ = big.run([p], new)
+        agree += int(o[0][0] == outs[i][0])
+    assert agree >= len(prompts) - 1
+
+
+def test_request_larger_than_the_pool_is_refused():
+    from pace_b200.llm.serving import WaveServer
+    server = WaveServer(_model(), pool_tokens=64 * 3, max_batch=2, max_seq_len=600)
+    with pytest.raises(RuntimeError, match="does not fit the KV pool"):
+        server.run([torch.randint(1, 97, (400,))], 4)
