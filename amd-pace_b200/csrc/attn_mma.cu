@@ -165,7 +165,23 @@ __device__ __forceinline__ void publish_part(const MmaParams& p, const ResMeta& 
     }
     return;
   }
+  // Fast path for the CTA's last part (the consumer warps' call): it is usually the last of its unit
+  // to arrive, and then its own result never needs to leave shared memory.  One acquiring load of the
+  // arrival count decides; no other CTA can arrive once parts - 1 have.
+  int own = -1;  // index of this CTA's part when it is merged straight from shared memory
+  if (!WARP) {
+    if (t == 0) {
+      int seen;
+      asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(seen) : "l"(p.unit_count + rm.unit) : "memory");
+      *flag = (seen == rm.parts - 1);
+      if (seen == rm.parts - 1) p.unit_count[rm.unit] = 0;  // ready for the next launch
+    }
+    csync();
+    if (*flag) own = cta - rm.first_cta;
+    csync();  // flag is rewritten below
+  }
   float* rec = p.parts + ((size_t)cta * 2 + (rm.mode == 2 ? 1 : 0)) * REC;
+  if (own < 0) {
   for (int oi = t * 2; oi < live * D; oi += NTHR * 2)
     *reinterpret_cast<float2*>(rec + oi) = *reinterpret_cast<const float2*>(rnum + oi);
   for (int row = t; row < live; row += NTHR) {
@@ -189,6 +205,7 @@ __device__ __forceinline__ void publish_part(const MmaParams& p, const ResMeta& 
   }
   if (!is_last) return;
   __threadfence();
+  }  // own < 0
   for (int oi = t * 2; oi < live * D; oi += NTHR * 2) {
     const int row = oi / D, d = oi - row * D;
     float M = -INFINITY, n0 = 0.f, n1 = 0.f, den = 0.f;
@@ -201,7 +218,11 @@ __device__ __forceinline__ void publish_part(const MmaParams& p, const ResMeta& 
         mc[k] = -INFINITY;
         dc[k] = 0.f;
         nn[k] = make_float2(0.f, 0.f);
-        if (c < rm.parts) {
+        if (c == own) {
+          mc[k] = rM[row];
+          dc[k] = rden[row];
+          nn[k] = *reinterpret_cast<const float2*>(rnum + oi);
+        } else if (c < rm.parts) {
           const float* r = p.parts + ((size_t)(rm.first_cta + c) * 2 + (c == 0 ? rm.first_slot : 0)) * REC;
           mc[k] = __ldcg(r + MR * D + row);
           dc[k] = __ldcg(r + MR * D + MR + row);
@@ -288,24 +309,11 @@ __global__ void __launch_bounds__(kThreadsM, 1)
 #define PACE_STAMP(i) do {} while (0)
 #endif
 
-  // ---- prologue.  The per-sequence loads go out first; barrier set-up and the zero fill of the V
-  // slots (rows no copy ever writes are multiplied by p = 0 and must not hold NaN patterns) run
-  // under their latency. ----
-  int my_slot[(kMaxItems + kThreadsM - 1) / kThreadsM];
-  int my_len[(kMaxItems + kThreadsM - 1) / kThreadsM];
-#pragma unroll
-  for (int r = 0; r < (kMaxItems + kThreadsM - 1) / kThreadsM; ++r) {
-    const int b = tid + r * kThreadsM;
-    my_slot[r] = -1;
-    my_len[r] = 0;
-    if (b < p.batch) {
-      my_slot[r] = view_slot(p.kv, b);
-      if (my_slot[r] >= 0) my_len[r] = view_len(p.kv, my_slot[r]);
-      sb_kvs[b] = p.kv_start ? p.kv_start[b] : 0;
-      sb_S[b] = p.q_lens ? min(p.q_lens[b], p.q_len) : p.q_len;
-    }
-  }
-  if (tid == 0) PACE_TRACE(3, 0);
+  // ---- prologue, part 1: what depends on nothing an earlier kernel wrote.  Barrier set-up and the
+  // zero fill of the V slots (rows no copy ever writes are multiplied by p = 0 and must not hold NaN
+  // patterns).  When the kernel is launched as a programmatic dependent this part runs while the
+  // kernel in front of it on the stream drains; griddepcontrol.wait then holds until that kernel has
+  // completed and its writes (the appended rows, the lengths) are visible. ----
   // one barrier per thread of the last warp (its lanes have no sequences to look up in small batches)
   if (tid >= kThreadsM - 32) {
     const int k = tid - (kThreadsM - 32);
@@ -316,11 +324,37 @@ __global__ void __launch_bounds__(kThreadsM, 1)
     else if (k < 2 * n_stages + 5) mbar_init(&res_empty[k - 2 * n_stages - 3], 1);
     fence_mbar_init();
   }
-  if (tid == 0) PACE_TRACE(3, 1);
   for (int s = 0; s < n_stages; ++s) {
     uint4* z = reinterpret_cast<uint4*>(ring + (size_t)s * STAGE + KVB);
     for (int i = tid; i < KVB / 16; i += kThreadsM) z[i] = make_uint4(0, 0, 0, 0);
   }
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  // ---- prologue, part 2: per-sequence lengths -> chunk prefix -> this CTA's range ----
+  int my_slot[(kMaxItems + kThreadsM - 1) / kThreadsM];
+  int my_len[(kMaxItems + kThreadsM - 1) / kThreadsM];
+#pragma unroll
+  for (int r = 0; r < (kMaxItems + kThreadsM - 1) / kThreadsM; ++r) {
+    const int b = tid + r * kThreadsM;
+    my_slot[r] = -1;
+    my_len[r] = 0;
+    if (b < p.batch) {
+      my_slot[r] = view_slot(p.kv, b);
+      if (my_slot[r] >= 0) {
+        my_len[r] = view_len(p.kv, my_slot[r]);
+        // the producer will walk this row of the block table a few microseconds from now: start
+        // bringing its first lines into L2 (the K/V stream of the previous launch has evicted them)
+        if (p.kv.block_table) {
+          const char* row = reinterpret_cast<const char*>(p.kv.block_table + (size_t)my_slot[r] * p.kv.max_pages_per_seq);
+          const int bytes = min(p.kv.max_pages_per_seq * 4, 512);
+          for (int o = 0; o < bytes; o += 128) asm volatile("prefetch.global.L2 [%0];" ::"l"(row + o));
+        }
+      }
+      sb_kvs[b] = p.kv_start ? p.kv_start[b] : 0;
+      sb_S[b] = p.q_lens ? min(p.q_lens[b], p.q_len) : p.q_len;
+    }
+  }
+  if (tid == 0) PACE_TRACE(3, 0);
+  if (tid == 0) PACE_TRACE(3, 1);
   if (tid == 0) PACE_TRACE(3, 2);
 #pragma unroll
   for (int r = 0; r < (kMaxItems + kThreadsM - 1) / kThreadsM; ++r) {
@@ -946,6 +980,15 @@ int sm_count_m() {
   return n;
 }
 
+// PACE_PDL=0 turns programmatic dependent launches off (A/B measurements)
+bool pdl_enabled() {
+  static const bool on = [] {
+    const char* e = getenv("PACE_PDL");
+    return !(e && e[0] == '0');
+  }();
+  return on;
+}
+
 template <int D, int MT, int NS>
 int launch_mma(MmaParams& p, const CUtensorMap& tmK, const CUtensorMap& tmV, int grid, cudaStream_t stream) {
   constexpr int MR = 16 * MT;
@@ -965,7 +1008,17 @@ int launch_mma(MmaParams& p, const CUtensorMap& tmK, const CUtensorMap& tmV, int
                                        budget));
     if (dev < 16) configured[dev] = true;
   }
-  attn_mma_kernel<D, MT, NS><<<grid, kThreadsM, smem_bytes, stream>>>(p, tmK, tmV);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)grid);
+  cfg.blockDim = dim3(kThreadsM);
+  cfg.dynamicSmemBytes = smem_bytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  PACE_CUDA_TRY(cudaLaunchKernelEx(&cfg, attn_mma_kernel<D, MT, NS>, p, tmK, tmV));
   PACE_LAUNCH_CHECK("attn_mma_kernel");
   return PACE_OK;
 }

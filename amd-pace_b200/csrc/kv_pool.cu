@@ -199,6 +199,8 @@ __global__ void __launch_bounds__(256)
     append_kernel(pace_kv_pool_t p, int layer, const int32_t* __restrict__ seq_ids, int batch, int n_new,
                   const int32_t* __restrict__ n_per, const __nv_bfloat16* __restrict__ k_new,
                   const __nv_bfloat16* __restrict__ v_new, int64_t sb, int64_t sh, int64_t st) {
+  // the attention kernel behind this append may set up while the append runs
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const int lane = threadIdx.x & 31;
   const int warps_per_block = blockDim.x >> 5;
   const long long total = (long long)batch * n_new * p.n_kv_heads;
@@ -254,6 +256,10 @@ __global__ void __launch_bounds__(256)
     }
     if (threadIdx.x == 0) p.counters[kCounterTicket] = 0;
   }
+  // Launched as a programmatic dependent, the append overlaps the attention kernel in front of it.
+  // It must not COMPLETE before that kernel does: the attention kernel behind the append orders
+  // itself after the append only, and shares its workspace with the one in front.
+  asm volatile("griddepcontrol.wait;" ::: "memory");
 }
 
 __global__ void truncate_kernel(pace_kv_pool_t p, int layer_begin, int layer_end, const int32_t* __restrict__ seq_ids,
