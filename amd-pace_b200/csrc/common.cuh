@@ -167,23 +167,29 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t by
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
+#ifndef PACE_WAIT_HINT_NS
+#define PACE_WAIT_HINT_NS 1000
+#endif
+// One potentially-blocking probe.  The suspend-time hint lets the hardware park the warp until the
+// phase completes (or the hint runs out) instead of having it spin: a spinning warp keeps taking
+// issue slots from the warps of its scheduler that have work.
 __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
       "selp.u32 %0, 1, 0, p;\n\t}"
       : "=r"(ok)
-      : "r"(smem_u32(bar)), "r"(parity)
+      : "r"(smem_u32(bar)), "r"(parity), "r"((uint32_t)PACE_WAIT_HINT_NS)
       : "memory");
   return ok != 0;
 }
-// Bounded wait: true when the phase completed, false when it gave up
-// (roughly a quarter of a second of polling).
+// Bounded wait: true when the phase completed, false when it gave up (after about a quarter of a
+// second).
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
-  for (int i = 0; i < 2048; ++i)
+  for (int i = 0; i < 64; ++i)
     if (mbar_try_wait(bar, parity)) return true;
-  for (int i = 0; i < (1 << 21); ++i) {
+  for (int i = 0; i < (1 << 18); ++i) {
     if (mbar_try_wait(bar, parity)) return true;
     __nanosleep(64);
   }
