@@ -42,7 +42,7 @@ struct MetaM {  // one 64-byte record per ring stage, written by the producer
   int rows, tok0, flags, kvs;
   int b, h, r_lo, R;
   int kv_len, S, mode, parts;
-  int first_cta, first_slot, unit, pad;
+  int first_cta, first_slot, unit, pad;  // pad: chunks of the unit part (on its first chunk's record)
 };
 static_assert(sizeof(MetaM) == 64, "MetaM is one 64-byte line");
 
@@ -111,8 +111,10 @@ struct SmemPlan {
   int ring, metas, qbuf, mg, res, bars, misc, per_b, prefix, total;
   int res_slot_bytes, n_res, mg_stride;
 };
+// (umma: the tcgen05 variant keeps a swizzled 128-row Q tile instead of the padded Q rows, and needs
+// neither the merge buffer nor the result slots)
 __host__ __device__ inline SmemPlan plan_smem(int D, int MT, int NS, int n_stages, int live_max, int batch,
-                                              int n_items) {
+                                              int n_items, bool umma = false) {
   SmemPlan s;
   const int MR = 16 * MT, QS = D * 2 + 16;
   int off = 0;
@@ -123,14 +125,14 @@ __host__ __device__ inline SmemPlan plan_smem(int D, int MT, int NS, int n_stage
     return o;
   };
   s.ring = take(n_stages * 2 * kChunk * D * 2, 1024);
-  s.qbuf = take(MR * QS, 128);
+  s.qbuf = umma ? take(MR * D * 2, 1024) : take(MR * QS, 128);
   s.mg_stride = D + 8;  // floats; the pad spreads the rows of a fragment over the banks
-  s.mg = take(NS > 1 ? NS * live_max * (s.mg_stride + 2) * 4 : 16, 16);
+  s.mg = take(umma ? 4 * MR * 4 : (NS > 1 ? NS * live_max * (s.mg_stride + 2) * 4 : 16), 16);
   s.n_res = live_max <= 64 ? 2 : 1;
   s.res_slot_bytes = (live_max * (D + 2) * 4 + 64 + 15) / 16 * 16;
-  s.res = take(s.n_res * s.res_slot_bytes, 16);
+  s.res = take(umma ? 16 : s.n_res * s.res_slot_bytes, 16);
   s.metas = take(kMaxStagesM * (int)sizeof(MetaM), 64);
-  s.bars = take((2 * kMaxStagesM + 1 + 4) * 8, 8);
+  s.bars = take((2 * kMaxStagesM + 1 + 4 + 10) * 8, 8);
   s.misc = take(8 * 4, 4);
   s.per_b = take(batch * 4 * 4, 4);
   s.prefix = take((n_items + 1) * 4, 4);
@@ -142,6 +144,12 @@ struct ResMeta {  // trails each result slot
   int b, h, r_lo, live, mode, parts, first_cta, first_slot, unit, last_part, pad[6];
 };
 static_assert(sizeof(ResMeta) == 64, "ResMeta is one 64-byte line");
+
+}  // namespace
+}  // namespace pace
+#include "attn_umma.cuh"
+namespace pace {
+namespace {
 
 // Takes one finished unit part from its shared-memory result slot to global memory: the output
 // rows (mode 0), or an fp32 partial plus the arrival count and, for the last arriver, the merge
@@ -249,10 +257,11 @@ __device__ __forceinline__ void publish_part(const MmaParams& p, const ResMeta& 
   }
 }
 
-template <int D, int MT, int NS>
+template <int D, int MT, int NS, bool UMMA = false>
 __global__ void __launch_bounds__(kThreadsM, 1)
     attn_mma_kernel(const MmaParams p, const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV) {
   static_assert(MT * NS == kWarps, "eight consumer warps");
+  static_assert(!UMMA || (MT == 8 && NS == 1), "the tcgen05 variant works on whole 128-row tiles");
   // How the NS warps of a row tile share the key stream.  Decode (MT == 1): each chunk's keys are cut
   // into NS slices, every warp works on every chunk.  Verify tiles (MT, NS >= 2): whole chunks are dealt
   // round-robin to the NS warp groups, so NS chunks are in flight in the tensor pipe at a time and a
@@ -273,7 +282,7 @@ __global__ void __launch_bounds__(kThreadsM, 1)
   extern __shared__ __align__(1024) unsigned char smem[];
   const int n_stages = p.n_stages;
   const int n_items = p.batch * p.n_qt;
-  const SmemPlan sp = plan_smem(D, MT, NS, n_stages, p.live_max, p.batch, n_items);
+  const SmemPlan sp = plan_smem(D, MT, NS, n_stages, p.live_max, p.batch, n_items, UMMA);
   unsigned char* ring = smem + sp.ring;  // [n_stages][K | V]
   MetaM* metas = reinterpret_cast<MetaM*>(smem + sp.metas);
   unsigned char* qbuf = smem + sp.qbuf;
@@ -286,6 +295,7 @@ __global__ void __launch_bounds__(kThreadsM, 1)
   uint64_t* q_empty = empty_bar + kMaxStagesM;
   uint64_t* res_full = q_empty + 1;   // [2]
   uint64_t* res_empty = res_full + 2; // [2]
+  uint64_t* umma_bars = res_empty + 2; // [10], tcgen05 variant only
   int* misc = reinterpret_cast<int*>(smem + sp.misc);
   int* sb_slot = reinterpret_cast<int*>(smem + sp.per_b);
   int* sb_len = sb_slot + p.batch;
@@ -318,10 +328,18 @@ __global__ void __launch_bounds__(kThreadsM, 1)
   if (tid >= kThreadsM - 32) {
     const int k = tid - (kThreadsM - 32);
     if (k < n_stages) mbar_init(&full_bar[k], 1);
-    else if (k < 2 * n_stages) mbar_init(&empty_bar[k - n_stages], kWarps);
+    else if (k < 2 * n_stages) mbar_init(&empty_bar[k - n_stages], UMMA ? 1 : kWarps);
     else if (k == 2 * n_stages) mbar_init(q_empty, kWarps);
     else if (k < 2 * n_stages + 3) mbar_init(&res_full[k - 2 * n_stages - 1], kWarps);
     else if (k < 2 * n_stages + 5) mbar_init(&res_empty[k - 2 * n_stages - 3], 1);
+    if (UMMA && k == 31) {
+      // s_full[2], p_full[2] (one arrival per warp of the group), o_full[2], q_ready and xch (one
+      // arrival per softmax warp), drain, pub (every softmax thread)
+      for (int j = 0; j < 10; ++j)
+        mbar_init(&umma_bars[j],
+                  (j == 2 || j == 3) ? 4 : (j == 6 || j == 9) ? 8 : (j == 8 ? kUmmaSoftmaxThreads : 1));
+      misc[4] = 0;  // abort flag
+    }
     fence_mbar_init();
   }
   for (int s = 0; s < n_stages; ++s) {
@@ -504,7 +522,7 @@ __global__ void __launch_bounds__(kThreadsM, 1)
       const int q_rows = min(MR, R - r_lo);
       const int c2h = h;
       if (lane == 0 && i == 0) PACE_TRACE(3, 9);
-      if (part_idx > 0 && !mbar_wait(q_empty, (part_idx - 1) & 1)) { ok = false; break; }
+      if (!UMMA && part_idx > 0 && !mbar_wait(q_empty, (part_idx - 1) & 1)) { ok = false; break; }
       for (bool first = true; j < j_end; ++j, ++i, first = false) {
         if (i >= n_stages && !mbar_wait(&empty_bar[s], ph ^ 1)) { ok = false; break; }
         const int tok0 = whole_pages ? j * CT : lp * P + row0;
@@ -518,9 +536,9 @@ __global__ void __launch_bounds__(kThreadsM, 1)
           if (first) {
             *reinterpret_cast<int4*>(&m->b) = make_int4(b, h, r_lo, R);
             *reinterpret_cast<int4*>(&m->kv_len) = make_int4(kv_len, S, mode, parts);
-            *reinterpret_cast<int4*>(&m->first_cta) = make_int4(first_cta, first_slot, it * Hkv + h, 0);
+            *reinterpret_cast<int4*>(&m->first_cta) = make_int4(first_cta, first_slot, it * Hkv + h, j_end - j);
           }
-          mbar_arrive_expect_tx(&full_bar[s], (uint32_t)n_pages_c * box_bytes + (first ? (uint32_t)q_rows * D * 2u : 0u));
+          mbar_arrive_expect_tx(&full_bar[s], (uint32_t)n_pages_c * box_bytes + ((first && !UMMA) ? (uint32_t)q_rows * D * 2u : 0u));
         }
         __syncwarp();
         const int pg = pw.get(lp + pi, lp, lane);
@@ -529,7 +547,7 @@ __global__ void __launch_bounds__(kThreadsM, 1)
           if (pg >= 0) tma_load_4d(ring + (size_t)s * STAGE + lane_off, tm, c0, row0, pg * Hkv + c2h, c3, &full_bar[s]);
           else raise_status(p.kv.status, PACE_DEV_BAD_INDEX);  // the consumers' bounded wait on this stage gives up
         }
-        if (first) {
+        if (first && !UMMA) {  // (the tcgen05 variant's softmax warps write the Q tile themselves, swizzled)
           for (int r = lane; r < q_rows; r += 32) {
             const int rr = r_lo + r, sq = rr / G, g = rr - sq * G;
             const __nv_bfloat16* src = p.q + (size_t)b * p.q_sb + (size_t)(h * G + g) * p.q_sh + (size_t)sq * p.q_ss;
@@ -563,6 +581,37 @@ __global__ void __launch_bounds__(kThreadsM, 1)
       const int from = i > n_stages ? i - n_stages : 0;
       for (int k = from; k < i; ++k) mbar_wait(&full_bar[k % n_stages], (k / n_stages) & 1);
     }
+    return;
+  }
+
+  if constexpr (UMMA) {
+    // ============== tcgen05 variant: softmax warps 0..7 (two groups), MMA issuer warp 9 ==============
+    UmmaCtx uc;
+    uc.ring = ring;
+    uc.metas = metas;
+    uc.qsw = qbuf;
+    uc.full_bar = full_bar;
+    uc.empty_bar = empty_bar;
+    uc.s_full = umma_bars;
+    uc.p_full = umma_bars + 2;
+    uc.o_full = umma_bars + 4;
+    uc.q_ready = umma_bars + 6;
+    uc.drain = umma_bars + 7;
+    uc.pub = umma_bars + 8;
+    uc.xch = umma_bars + 9;
+    uc.xch_m = mg_o;
+    uc.xch_l = mg_o + 2 * kUmmaRows;
+    uc.tmem_slot = reinterpret_cast<uint32_t*>(misc + 5);
+    uc.flag = misc + 6;
+    uc.abort = misc + 4;
+    uc.n_my = n_my;
+    uc.n_stages = n_stages;
+    uc.cta = cta;
+#ifdef PACE_TIMING
+    uc.trace = trace;
+    uc.stamps = stamps;
+#endif
+    umma_consumer<D>(p, uc, tid);
     return;
   }
 
@@ -989,22 +1038,32 @@ bool pdl_enabled() {
   return on;
 }
 
-template <int D, int MT, int NS>
+// Fewest query rows (tokens x grouped heads) for which a tile goes to the tcgen05 variant; 0 = never.
+// PACE_UMMA_MIN_ROWS overrides it (A/B measurements).
+int umma_min_rows() {
+  static const int v = [] {
+    const char* e = getenv("PACE_UMMA_MIN_ROWS");
+    return e ? atoi(e) : 0;
+  }();
+  return v;
+}
+
+template <int D, int MT, int NS, bool UMMA = false>
 int launch_mma(MmaParams& p, const CUtensorMap& tmK, const CUtensorMap& tmV, int grid, cudaStream_t stream) {
   constexpr int MR = 16 * MT;
   const int n_items = p.batch * p.n_qt;
   p.live_max = p.G * p.q_len < MR ? p.G * p.q_len : MR;
   const int budget = 226 * 1024;
   int ns = kMaxStagesM;
-  while (ns >= 2 && plan_smem(D, MT, NS, ns, p.live_max, p.batch, n_items).total > budget) --ns;
+  while (ns >= 2 && plan_smem(D, MT, NS, ns, p.live_max, p.batch, n_items, UMMA).total > budget) --ns;
   if (ns < 2) return PACE_ERR_UNSUPPORTED;
   p.n_stages = ns;
-  const size_t smem_bytes = plan_smem(D, MT, NS, ns, p.live_max, p.batch, n_items).total;
+  const size_t smem_bytes = plan_smem(D, MT, NS, ns, p.live_max, p.batch, n_items, UMMA).total;
   static bool configured[16] = {};
   int dev = 0;
   PACE_CUDA_TRY(cudaGetDevice(&dev));
   if (dev >= 16 || !configured[dev]) {
-    PACE_CUDA_TRY(cudaFuncSetAttribute(attn_mma_kernel<D, MT, NS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    PACE_CUDA_TRY(cudaFuncSetAttribute(attn_mma_kernel<D, MT, NS, UMMA>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        budget));
     if (dev < 16) configured[dev] = true;
   }
@@ -1018,7 +1077,7 @@ int launch_mma(MmaParams& p, const CUtensorMap& tmK, const CUtensorMap& tmV, int
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = pdl_enabled() ? 1 : 0;
-  PACE_CUDA_TRY(cudaLaunchKernelEx(&cfg, attn_mma_kernel<D, MT, NS>, p, tmK, tmV));
+  PACE_CUDA_TRY(cudaLaunchKernelEx(&cfg, attn_mma_kernel<D, MT, NS, UMMA>, p, tmK, tmV));
   PACE_LAUNCH_CHECK("attn_mma_kernel");
   return PACE_OK;
 }
@@ -1028,7 +1087,7 @@ int launch_mma(MmaParams& p, const CUtensorMap& tmK, const CUtensorMap& tmV, int
 uint64_t mma_workspace_bytes(int n_q_heads, int n_kv_heads, int head_dim, int q_len) {
   const int G = n_q_heads / (n_kv_heads > 0 ? n_kv_heads : 1);
   const int M = G * q_len;
-  const int MT = M <= 16 ? 1 : M <= 32 ? 2 : M <= 64 ? 4 : 8;
+  const int MT = (umma_min_rows() > 0 && M >= umma_min_rows()) ? 8 : M <= 16 ? 1 : M <= 32 ? 2 : M <= 64 ? 4 : 8;
   return kWorkspaceCounterBytes + (uint64_t)sm_count_m() * 2 * (16 * MT) * (head_dim + 2) * sizeof(float) + 256;
 }
 
@@ -1046,7 +1105,10 @@ int run_mma(const KVView& kv, const CUtensorMap& tmK, const CUtensorMap& tmV, in
   if (((uintptr_t)out & 3) || (o_sb & 1) || (o_sh & 1) || (o_ss & 1)) return PACE_ERR_INVALID;  // bf16 pairs are stored
   if (!workspace || ((uintptr_t)workspace & 15)) return PACE_ERR_INVALID;
   const int M = G * q_len;
-  const int MT = M <= 16 ? 1 : M <= 32 ? 2 : M <= 64 ? 4 : 8;
+  // 128-row tiles on the 5th-generation tensor cores (no additive mask there; 16-byte output stores)
+  const bool umma = umma_min_rows() > 0 && M >= umma_min_rows() && !mask && !((uintptr_t)out & 15) && !(o_sb & 7) &&
+                    !(o_sh & 7) && !(o_ss & 7);
+  const int MT = umma ? 8 : M <= 16 ? 1 : M <= 32 ? 2 : M <= 64 ? 4 : 8;
   const int MR = 16 * MT;
   int grid = sm_count_m();
   if (const char* g = getenv("PACE_DECODE_GRID")) {  // test hook: other partitions of the same work
@@ -1108,14 +1170,19 @@ int run_mma(const KVView& kv, const CUtensorMap& tmK, const CUtensorMap& tmV, in
     int rc = PACE_ERR_UNSUPPORTED;
 #define PACE_MMA_CASE(DD, MM, NN) \
   if (D == DD && MT == MM) rc = launch_mma<DD, MM, NN>(p, tmK, tmV, grid, stream);
-    PACE_MMA_CASE(128, 1, 8)
-    PACE_MMA_CASE(128, 2, 4)
-    PACE_MMA_CASE(128, 4, 2)
-    PACE_MMA_CASE(128, 8, 1)
-    PACE_MMA_CASE(64, 1, 8)
-    PACE_MMA_CASE(64, 2, 4)
-    PACE_MMA_CASE(64, 4, 2)
-    PACE_MMA_CASE(64, 8, 1)
+    if (umma) {
+      if (D == 128) rc = launch_mma<128, 8, 1, true>(p, tmK, tmV, grid, stream);
+      if (D == 64) rc = launch_mma<64, 8, 1, true>(p, tmK, tmV, grid, stream);
+    } else {
+      PACE_MMA_CASE(128, 1, 8)
+      PACE_MMA_CASE(128, 2, 4)
+      PACE_MMA_CASE(128, 4, 2)
+      PACE_MMA_CASE(128, 8, 1)
+      PACE_MMA_CASE(64, 1, 8)
+      PACE_MMA_CASE(64, 2, 4)
+      PACE_MMA_CASE(64, 4, 2)
+      PACE_MMA_CASE(64, 8, 1)
+    }
 #undef PACE_MMA_CASE
     if (rc != PACE_OK) return rc;
   }

@@ -1,0 +1,523 @@
+// 5th-generation tensor-core path of the multi-token attention kernel (prefill chunks, PARD verify).
+//
+// One 128-row query tile per CTA pass: S = Q K^T and O += P V are tcgen05.mma instructions issued
+// by one elected thread, operands in shared memory (K-major / MN-major, 128-byte swizzle, exactly
+// the layout the tiled TMA copies of K and V produce), accumulators in tensor memory.
+//
+// The chunks of a unit part are dealt alternately to two softmax warpgroups (A: even, B: odd).  Each
+// group has its own score buffer, P tile, running (max, sum) and O accumulator, so the two never
+// wait for one another while the part streams; the two accumulators are merged when the part ends:
+//     TMEM columns [0, 64) / [64, 128)              S_A / S_B   128 x 64 fp32
+//     TMEM columns [128, 128 + D) / [256, 256 + D)  O_A / O_B   128 x D  fp32
+//     TMEM columns [384, 416) / [416, 448)          P_A / P_B   128 x 64 bf16 (two per column)
+// A softmax thread owns one query row (TMEM lane == row): tcgen05.ld the row of S, online softmax in
+// registers, P written back to tensor memory as the A operand of the second MMA (shared memory then
+// carries only Q, K and V: an MMA with both operands in shared memory is bound by its bandwidth).  O is rescaled in TMEM
+// only when a row's running maximum grows by more than 2^8 (the result is exact either way:
+// numerator and denominator share whatever maximum was used).
+//
+// Included by attn_mma.cu, which provides MmaParams, MetaM, the ring and its producer warp.
+#pragma once
+
+namespace pace {
+namespace {
+
+constexpr int kUmmaRows = 128;          // query rows per tile (UMMA M)
+constexpr int kUmmaSoftmaxThreads = 256;  // two warpgroups
+constexpr int kTmemCols = 512;          // S_A, S_B, O_A, O_B
+constexpr float kLazyRescale = 8.0f;    // log2 units
+
+struct UmmaCtx {
+  unsigned char* ring;    // [n_stages][K | V] as the TMA boxes land
+  const MetaM* metas;
+  unsigned char* qsw;     // Q tile, K-major 128-byte-swizzled: [D/64][128 rows][128 B]
+  uint64_t* full_bar;
+  uint64_t* empty_bar;
+  uint64_t* s_full;       // [2] QK^T of a chunk of group A / B has landed in TMEM
+  uint64_t* p_full;       // [2] P of a chunk is in shared memory (and O has been rescaled)
+  uint64_t* o_full;       // [2] PV of a chunk has been accumulated
+  uint64_t* q_ready;      // the Q tile of a unit part is in shared memory (one arrival per softmax warp)
+  uint64_t* drain;        // every MMA this CTA issued has completed
+  uint64_t* pub;          // meeting point of the 256 softmax threads while a cut unit is published
+  uint64_t* xch;          // the two groups have posted their (max, sum) of a part (one arrival per warp)
+  float* xch_m;           // [2][128]
+  float* xch_l;           // [2][128]
+  uint32_t* tmem_slot;    // where tcgen05.alloc wrote the base address
+  int* flag;              // "this CTA arrived last" broadcast
+  volatile int* abort;
+  int n_my, n_stages, cta;
+#ifdef PACE_TIMING
+  unsigned long long* trace;
+  unsigned long long* stamps;
+#endif
+};
+#ifdef PACE_TIMING
+#define PACE_UTRACE(c, k, i) do { if ((c).cta == 7 && (i) < 64) { unsigned long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_)); (c).trace[(k) * 64 + (i)] = t_; } } while (0)
+#else
+#define PACE_UTRACE(c, k, i) do {} while (0)
+#endif
+
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+// shared-memory matrix descriptor, 128-byte swizzle (layout type 2), descriptor version 1
+__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  const uint32_t lo = ((smem_addr >> 4) & 0x3FFFu) | (((lbo_bytes >> 4) & 0x3FFFu) << 16);
+  const uint32_t hi = ((sbo_bytes >> 4) & 0x3FFFu) | (1u << 14) | (2u << 29);
+  return ((uint64_t)hi << 32) | lo;
+}
+// instruction descriptor: bf16 x bf16 -> fp32, M = 128, A K-major
+__host__ __device__ constexpr uint32_t umma_idesc(int n, bool b_mn_major) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((b_mn_major ? 1u : 0u) << 16) | ((uint32_t)(n >> 3) << 17) |
+         ((uint32_t)(kUmmaRows >> 4) << 24);
+}
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                          uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
+      :
+      : "r"(tmem_d), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u)
+      : "memory");
+}
+// A operand in tensor memory (128 lanes x 8 columns of packed bf16 pairs per 16-wide k-step)
+__device__ __forceinline__ void umma_bf16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t b_desc, uint32_t idesc,
+                                             uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, {%5, %5, %5, %5}, p;\n\t}"
+      :
+      : "r"(tmem_d), "r"(tmem_a), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u)
+      : "memory");
+}
+__device__ __forceinline__ uint64_t pack64(uint32_t lo, uint32_t hi) {
+  uint64_t d;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "r"(lo), "r"(hi));
+  return d;
+}
+// arrive on an mbarrier once every tcgen05.mma issued so far by this thread has completed
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+               : "memory");
+}
+// 32 TMEM lanes (this warp's) x 32 consecutive 32-bit columns -> 32 registers per thread
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};" ::"r"(taddr),
+      "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+      "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]),
+      "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]),
+      "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+// Bounded wait that also gives up when another role has raised the abort flag.  Called by whole
+// warps; the answer is the same for every lane (the tcgen05 instructions that follow are .aligned).
+__device__ __forceinline__ bool umma_wait(uint64_t* bar, uint32_t parity, volatile int* abort) {
+  bool ok = false;
+  for (int i = 0; i < (1 << 18); ++i) {
+    if (mbar_try_wait(bar, parity)) {
+      ok = true;
+      break;
+    }
+    if (*abort) break;
+    if (i > 64) __nanosleep(64);
+  }
+  if (!ok) *abort = 1;
+  return __all_sync(0xffffffffu, ok);
+}
+
+
+// ---- the MMA issuer: one warp waits, lane 0 issues ----
+// Within a unit part of n chunks, chunk c (part-relative) belongs to group w = c & 1.  Issue order:
+//   QK(0), QK(1), then for every c: wait P(c) -> PV(c) -> QK(c + 2)
+// so each group's next scores are computed while it works on its current chunk.
+template <int D>
+__device__ __forceinline__ void umma_issuer(const UmmaCtx& c, uint32_t tmem, int lane) {
+  constexpr int KVB = kChunk * D * 2, HALF_B = kChunk * 128, STAGE = 2 * KVB, HALVES = D / 64;
+  constexpr int QHALF = kUmmaRows * 128;
+  constexpr uint32_t IDESC_QK = umma_idesc(kChunk, false), IDESC_PV = umma_idesc(D, true);
+  // Descriptors differ from one instruction to the next only in the start-address field (units of
+  // 16 bytes): everything else is folded into constants, because the scalar instructions between two
+  // tcgen05.mma of the one issuing thread are what limits the issue rate.
+  constexpr uint32_t DESC_HI = (1024u >> 4) | (1u << 14) | (2u << 29);       // SBO 1024 B, version 1, 128-byte swizzle
+  const uint32_t q_lo = (smem_u32(c.qsw) >> 4) | (1u << 16);                 // K-major: LBO unused (1)
+  const uint32_t k_lo0 = (smem_u32(c.ring) >> 4) | (1u << 16);
+  const uint32_t v_lo0 = ((smem_u32(c.ring) + KVB) >> 4) | ((uint32_t)(HALF_B >> 4) << 16);  // MN-major: LBO = next 64 columns
+  auto issue_qk = [&](int i, int s, int w) {
+    const uint32_t k_lo = k_lo0 + (uint32_t)s * (STAGE >> 4);
+    const uint32_t tS = tmem + (uint32_t)w * kChunk;
+#pragma unroll
+    for (int hf = 0; hf < HALVES; ++hf)
+#pragma unroll
+      for (int k = 0; k < 4; ++k)
+        umma_bf16(tS, pack64(q_lo + hf * (QHALF >> 4) + k * 2, DESC_HI), pack64(k_lo + hf * (HALF_B >> 4) + k * 2, DESC_HI),
+                  IDESC_QK, (hf | k) ? 1u : 0u);
+    umma_commit(&c.s_full[w]);
+    PACE_UTRACE(c, 8, i);
+  };
+  int cnt[2] = {0, 0};  // chunks handed to each group so far (the phase of its barriers)
+  int sq = 0, phq = 0;  // ring stage and phase of the next chunk whose QK is issued (QKs go out in chunk order)
+  int sp = 0;           // ring stage of the next chunk whose PV is issued
+  int part = 0, i0 = 0;
+  bool ok = true;
+  auto next_qk = [&](int i, int w) -> bool {
+    if (!umma_wait(&c.full_bar[sq], phq, c.abort)) return false;
+    tc_fence_after();
+    if (lane == 0) issue_qk(i, sq, w);
+    __syncwarp();
+    if (++sq == c.n_stages) {
+      sq = 0;
+      phq ^= 1;
+    }
+    return true;
+  };
+  while (i0 < c.n_my && ok) {
+    ok = umma_wait(&c.full_bar[sq], phq, c.abort) && umma_wait(c.q_ready, part & 1, c.abort);
+    if (!ok) break;
+    ++part;
+    const int n = c.metas[sq].pad;  // chunks of this part
+    if (n < 1) {
+      *c.abort = 1;
+      break;
+    }
+    ok = next_qk(i0, 0) && (n < 2 || next_qk(i0 + 1, 1));
+    if (!ok) break;
+    for (int j = 0; j < n; ++j) {
+      const int w = j & 1;
+      ok = umma_wait(&c.p_full[w], cnt[w] & 1, c.abort);
+      if (!ok) break;
+      ++cnt[w];
+      tc_fence_after();
+      if (lane == 0) {
+        PACE_UTRACE(c, 9, i0 + j);
+        const uint32_t v_lo = v_lo0 + (uint32_t)sp * (STAGE >> 4);
+        const uint32_t tO = tmem + 128 + (uint32_t)w * 128, tP = tmem + 384 + (uint32_t)w * 32;
+        umma_bf16_ts(tO, tP, pack64(v_lo, DESC_HI), IDESC_PV, j < 2 ? 0u : 1u);
+#pragma unroll
+        for (int k = 1; k < 4; ++k)  // 16 keys per instruction
+          umma_bf16_ts(tO, tP + k * 8, pack64(v_lo + k * (2048 >> 4), DESC_HI), IDESC_PV, 1u);
+        umma_commit(&c.empty_bar[sp]);  // K and V of this stage have been consumed
+        umma_commit(&c.o_full[w]);
+        PACE_UTRACE(c, 10, i0 + j);
+      }
+      __syncwarp();
+      if (++sp == c.n_stages) sp = 0;
+      if (j + 2 < n) {
+        ok = next_qk(i0 + j + 2, w);
+        if (!ok) break;
+      }
+    }
+    i0 += n;
+  }
+  // nothing may still be writing tensor memory when it is handed back
+  if (lane == 0) umma_commit(c.drain);
+  __syncwarp();
+  for (int k = 0; k < (1 << 20) && !mbar_try_wait(c.drain, 0); ++k) __nanosleep(64);
+}
+
+// merge of a unit's partials by its last arriver (all softmax threads; every partial is in the workspace)
+template <int D>
+__device__ __forceinline__ void umma_merge(const MmaParams& p, const ResMeta& rm, int t) {
+  constexpr int MR = kUmmaRows, REC = MR * (D + 2);
+  const int G = p.G;
+  for (int oi = t * 2; oi < rm.live * D; oi += kUmmaSoftmaxThreads * 2) {
+    const int row = oi / D, d = oi - row * D;
+    float M = -INFINITY, n0 = 0.f, n1 = 0.f, den = 0.f;
+    for (int c0 = 0; c0 < rm.parts; c0 += 4) {
+      float mc[4], dc[4];
+      float2 nn[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const int c = c0 + k;
+        mc[k] = -INFINITY;
+        dc[k] = 0.f;
+        nn[k] = make_float2(0.f, 0.f);
+        if (c < rm.parts) {
+          const float* r = p.parts + ((size_t)(rm.first_cta + c) * 2 + (c == 0 ? rm.first_slot : 0)) * REC;
+          mc[k] = __ldcg(r + MR * D + row);
+          dc[k] = __ldcg(r + MR * D + MR + row);
+          nn[k] = __ldcg(reinterpret_cast<const float2*>(r + oi));
+        }
+      }
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const float Mn = fmaxf(M, mc[k]);
+        if (Mn != -INFINITY) {
+          const float a = (M == -INFINITY) ? 0.f : fast_exp2(M - Mn);
+          const float f = (mc[k] == -INFINITY) ? 0.f : fast_exp2(mc[k] - Mn);
+          n0 = n0 * a + nn[k].x * f;
+          n1 = n1 * a + nn[k].y * f;
+          den = den * a + dc[k] * f;
+          M = Mn;
+        }
+      }
+    }
+    const float inv = den > 0.f ? 1.0f / den : 0.f;
+    const int rr = rm.r_lo + row, sq = rr / G, g = rr - sq * G;
+    *reinterpret_cast<uint32_t*>(p.out + (size_t)rm.b * p.o_sb + (size_t)(rm.h * G + g) * p.o_sh + (size_t)sq * p.o_ss +
+                                 d) = f2_to_bf2(n0 * inv, n1 * inv);
+  }
+}
+
+// ---- the softmax warps: thread (group w, row r) owns query row r for the chunks dealt to group w ----
+template <int D>
+__device__ __forceinline__ void umma_softmax(const MmaParams& p, const UmmaCtx& c, uint32_t tmem, int tid) {
+  constexpr int MR = kUmmaRows, REC = MR * (D + 2), QHALF = MR * 128;
+  const int wg = tid >> 7, row = tid & 127, lane = tid & 31, G = p.G;
+  const uint32_t t_lane = tmem + ((uint32_t)(row & ~31) << 16);  // this warp's 32 TMEM lanes
+  const uint32_t tS = t_lane + (uint32_t)wg * kChunk;
+  const uint32_t tOa = t_lane + 128, tOb = t_lane + 256, tO = wg ? tOb : tOa;
+  const float scale = p.scale_log2;
+  const uint32_t tP = t_lane + 384 + (uint32_t)wg * 32;  // this group's P tile: 64 keys as 32 columns of bf16 pairs
+  int cnt = 0;  // chunks this group has worked on (the phase of its barriers)
+  int n_pub = 0, n_xch = 0;
+  auto group_sync = [&]() -> bool {  // all softmax threads meet (bounded, unlike bar.sync)
+    mbar_arrive(c.pub);
+    const bool ok = umma_wait(c.pub, n_pub & 1, c.abort);
+    ++n_pub;
+    return ok;
+  };
+
+  for (int i0 = 0; i0 < c.n_my;) {
+    // ---- new unit part: its record, this thread's share of the Q tile (swizzled A operand) ----
+    if (!umma_wait(&c.full_bar[i0 % c.n_stages], (i0 / c.n_stages) & 1, c.abort)) return;
+    ResMeta fin;
+    int n_part, kvs, lim;
+    bool live;
+    __nv_bfloat16* out_row;
+    {
+      const MetaM* meta = &c.metas[i0 % c.n_stages];
+      const int R = meta->R, r_lo = meta->r_lo, kv_len = meta->kv_len, S = meta->S;
+      kvs = meta->kvs;
+      n_part = meta->pad;
+      fin.b = meta->b;
+      fin.h = meta->h;
+      fin.r_lo = r_lo;
+      fin.live = min(MR, R - r_lo);
+      fin.mode = meta->mode;
+      fin.parts = meta->parts;
+      fin.first_cta = meta->first_cta;
+      fin.first_slot = meta->first_slot;
+      fin.unit = meta->unit;
+      const int r = r_lo + row;
+      live = r < R;
+      const int sq = r / G, g = r - sq * G;
+      lim = live ? (p.causal ? kv_len - S + sq + 1 : kv_len) : 0;  // first key this row does NOT see
+      const uint4* src = reinterpret_cast<const uint4*>(p.q + (size_t)fin.b * p.q_sb + (size_t)(fin.h * G + g) * p.q_sh +
+                                                        (size_t)sq * p.q_ss);
+      out_row = p.out + (size_t)fin.b * p.o_sb + (size_t)(fin.h * G + g) * p.o_sh + (size_t)sq * p.o_ss;
+      unsigned char* qrow = c.qsw + row * 128;
+#pragma unroll
+      for (int k = 0; k < D / 16; ++k) {
+        const int cc = wg * (D / 16) + k;
+        const uint4 v = live ? __ldg(src + cc) : make_uint4(0, 0, 0, 0);
+        *reinterpret_cast<uint4*>(qrow + (cc >> 3) * QHALF + (((cc & 7) ^ (row & 7)) << 4)) = v;
+      }
+      fence_proxy_async();  // generic-proxy writes before the tensor core's async-proxy reads
+      tc_fence_before();    // (and this thread's reads of O for the previous part are done)
+      __syncwarp();
+      if (lane == 0) mbar_arrive(c.q_ready);
+    }
+    if (n_part < 1) return;
+    const bool warp_live = (row & ~31) < fin.live;  // a warp of padding rows only keeps the barriers in step
+    float m_used = -INFINITY, l = 0.f;
+
+    for (int j = wg; j < n_part; j += 2) {
+      const int i = i0 + j, s = i % c.n_stages;
+      if (!umma_wait(&c.full_bar[s], (i / c.n_stages) & 1, c.abort)) return;
+      const int rows = c.metas[s].rows, tok0 = c.metas[s].tok0;
+      if (tid == 0) PACE_UTRACE(c, 4, i);
+      if (!umma_wait(&c.s_full[wg], cnt & 1, c.abort)) return;
+      tc_fence_after();
+      if (tid == 0) PACE_UTRACE(c, 5, i);
+      uint32_t pk[32];
+      if (warp_live) {
+        // ---- scores of this chunk: TMEM -> registers ----
+        uint32_t sr[2][32];
+        tmem_ld32(tS, sr[0]);
+        tmem_ld32(tS + 32, sr[1]);
+        tmem_wait_ld();
+        const int lo = max(0, kvs - tok0), hi = min(rows, lim - tok0);  // visible keys of the chunk: [lo, hi)
+        if (!__all_sync(0xffffffffu, lo <= 0 && hi >= kChunk)) {
+#pragma unroll
+          for (int k = 0; k < 64; ++k)
+            if (k < lo || k >= hi) sr[k >> 5][k & 31] = 0xff800000u;  // -inf
+        }
+        float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+        for (int k = 0; k < 64; ++k) mx4[k & 3] = fmaxf(mx4[k & 3], __uint_as_float(sr[k >> 5][k & 31]));
+        const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale;  // scale > 0
+        // ---- running maximum; O is rescaled only when some row of the warp moved by more than 2^8 ----
+        const bool grow = mx > m_used + kLazyRescale;
+        if (__any_sync(0xffffffffu, grow)) {
+          const float m_new = grow ? mx : m_used;
+          const float alpha = grow ? ((m_used == -INFINITY) ? 0.f : fast_exp2(m_used - m_new)) : 1.f;
+          if (j >= 2) {  // O holds the sum of the group's earlier chunks of this part
+            if (!umma_wait(&c.o_full[wg], (cnt - 1) & 1, c.abort)) return;
+            tc_fence_after();
+#pragma unroll
+            for (int d0 = 0; d0 < D; d0 += 32) {
+              uint32_t ov[32];
+              tmem_ld32(tO + d0, ov);
+              tmem_wait_ld();
+#pragma unroll
+              for (int k = 0; k < 32; ++k) ov[k] = __float_as_uint(__uint_as_float(ov[k]) * alpha);
+              tmem_st32(tO + d0, ov);
+            }
+            tmem_wait_st();
+          }
+          l *= alpha;
+          m_used = m_new;
+        }
+        // ---- P = 2^(s * scale - m), row sum, bf16 pairs ----
+        const float ne = (m_used == -INFINITY) ? 0.f : -m_used;
+        float l4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int k = 0; k < 32; ++k) {
+          const float p0 = fast_exp2(fmaf(__uint_as_float(sr[k >> 4][(2 * k) & 31]), scale, ne));
+          const float p1 = fast_exp2(fmaf(__uint_as_float(sr[k >> 4][(2 * k + 1) & 31]), scale, ne));
+          l4[k & 3] += p0 + p1;
+          pk[k] = f2_to_bf2(p0, p1);
+        }
+        l += (l4[0] + l4[1]) + (l4[2] + l4[3]);
+      }
+      if (tid == 0) PACE_UTRACE(c, 6, i);
+      // the P tile (tensor memory) was the A operand of this group's previous PV
+      if (cnt >= 1 && !umma_wait(&c.o_full[wg], (cnt - 1) & 1, c.abort)) return;
+      if (warp_live) {
+        tmem_st32(tP, pk);
+        tmem_wait_st();
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&c.p_full[wg]);
+      if (tid == 0) PACE_UTRACE(c, 7, i);
+      ++cnt;
+    }
+
+    // ================= end of a unit part: the two groups' accumulators meet =================
+    const bool has_mine = n_part > wg;  // (a part of one chunk leaves group B empty-handed)
+    if (has_mine && !umma_wait(&c.o_full[wg], (cnt - 1) & 1, c.abort)) return;
+    c.xch_m[wg * MR + row] = m_used;
+    c.xch_l[wg * MR + row] = l;
+    __syncwarp();
+    if (lane == 0) mbar_arrive(c.xch);
+    if (!umma_wait(c.xch, n_xch & 1, c.abort)) return;
+    ++n_xch;
+    tc_fence_after();
+    const float m_o = c.xch_m[(wg ^ 1) * MR + row], l_o = c.xch_l[(wg ^ 1) * MR + row];
+    const float mA = wg ? m_o : m_used, mB = wg ? m_used : m_o, lA = wg ? l_o : l, lB = wg ? l : l_o;
+    const float M = fmaxf(mA, mB);
+    const float fA = (mA == -INFINITY) ? 0.f : fast_exp2(mA - M), fB = (mB == -INFINITY) ? 0.f : fast_exp2(mB - M);
+    const float den = lA * fA + lB * fB;
+    const bool has_b = n_part > 1;
+    // group A takes the lower half of the head dimension, group B the upper half
+    float* rec = p.parts + ((size_t)c.cta * 2 + (fin.mode == 2 ? 1 : 0)) * REC;
+    if (warp_live) {
+      const float inv = den > 0.f ? 1.0f / den : 0.f;
+      const float sA = fin.mode == 0 ? fA * inv : fA, sB = fin.mode == 0 ? fB * inv : fB;
+#pragma unroll
+      for (int d0 = wg * (D / 2); d0 < (wg + 1) * (D / 2); d0 += 32) {
+        uint32_t oa[32], ob[32];
+        tmem_ld32(tOa + d0, oa);
+        if (has_b) tmem_ld32(tOb + d0, ob);
+        tmem_wait_ld();
+        float v[32];
+#pragma unroll
+        for (int k = 0; k < 32; ++k) {
+          v[k] = __uint_as_float(oa[k]) * sA;
+          if (has_b) v[k] = fmaf(__uint_as_float(ob[k]), sB, v[k]);
+        }
+        if (live) {
+          if (fin.mode == 0) {
+#pragma unroll
+            for (int q4 = 0; q4 < 4; ++q4)
+              *reinterpret_cast<uint4*>(out_row + d0 + q4 * 8) =
+                  make_uint4(f2_to_bf2(v[q4 * 8], v[q4 * 8 + 1]), f2_to_bf2(v[q4 * 8 + 2], v[q4 * 8 + 3]),
+                             f2_to_bf2(v[q4 * 8 + 4], v[q4 * 8 + 5]), f2_to_bf2(v[q4 * 8 + 6], v[q4 * 8 + 7]));
+          } else {
+#pragma unroll
+            for (int q4 = 0; q4 < 8; ++q4)
+              *reinterpret_cast<float4*>(rec + row * D + d0 + q4 * 4) =
+                  make_float4(v[q4 * 4], v[q4 * 4 + 1], v[q4 * 4 + 2], v[q4 * 4 + 3]);
+          }
+        }
+      }
+    }
+    tc_fence_before();
+    i0 += n_part;
+    if (fin.mode == 0) continue;
+    // cut unit: the fp32 partial is in the workspace; arrival count, merge by the last arriver
+    if (live && wg == 0) {
+      rec[MR * D + row] = M;
+      rec[MR * D + MR + row] = den;
+    }
+    __threadfence();
+    if (!group_sync()) return;
+    if (tid == 0) {
+      const int old = atomicAdd(&p.unit_count[fin.unit], 1);
+      const int is_last = (old == fin.parts - 1);
+      if (is_last) p.unit_count[fin.unit] = 0;  // ready for the next launch
+      *c.flag = is_last;
+    }
+    if (!group_sync()) return;
+    const int is_last = *c.flag;
+    if (!group_sync()) return;  // the flag is rewritten by the next cut unit
+    if (is_last) {
+      __threadfence();
+      umma_merge<D>(p, fin, tid);
+    }
+  }
+}
+
+// Entry of warps 0..7 and 9 of a CTA that has work: warp 9 owns the tensor memory and issues the
+// MMAs, warps 0..7 are the two softmax groups.  Every wait inside is bounded and every path ends at
+// the barrier in front of the deallocation: a CTA never exits holding tensor memory.
+template <int D>
+__device__ __forceinline__ void umma_consumer(const MmaParams& p, const UmmaCtx& c, int tid) {
+  const int warp = tid >> 5, lane = tid & 31;
+  const bool issuer = warp == 9;
+  if (issuer) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(c.tmem_slot)),
+                 "r"(kTmemCols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  asm volatile("bar.sync 3, 288;" ::: "memory");
+  tc_fence_after();
+  const uint32_t tmem = *reinterpret_cast<volatile uint32_t*>(c.tmem_slot);
+  if (issuer) umma_issuer<D>(c, tmem, lane);
+  else umma_softmax<D>(p, c, tmem, tid);
+  if (lane == 0 && *c.abort) raise_status(p.kv.status, PACE_DEV_WAIT_TIMEOUT);
+#ifdef PACE_TIMING
+  if (tid == 0) { unsigned long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_)); c.stamps[5] = t_; }
+#endif
+  tc_fence_before();
+  asm volatile("bar.sync 3, 288;" ::: "memory");
+  if (issuer) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols) : "memory");
+  }
+}
+
+}  // namespace
+}  // namespace pace
