@@ -125,14 +125,14 @@ __host__ __device__ inline SmemPlan plan_smem(int D, int MT, int NS, int n_stage
     return o;
   };
   s.ring = take(n_stages * 2 * kChunk * D * 2, 1024);
-  s.qbuf = umma ? take(MR * D * 2, 1024) : take(MR * QS, 128);
+  s.qbuf = take(umma ? 16 : MR * QS, 128);
   s.mg_stride = D + 8;  // floats; the pad spreads the rows of a fragment over the banks
   s.mg = take(umma ? 4 * MR * 4 : (NS > 1 ? NS * live_max * (s.mg_stride + 2) * 4 : 16), 16);
   s.n_res = live_max <= 64 ? 2 : 1;
   s.res_slot_bytes = (live_max * (D + 2) * 4 + 64 + 15) / 16 * 16;
   s.res = take(umma ? 16 : s.n_res * s.res_slot_bytes, 16);
   s.metas = take(kMaxStagesM * (int)sizeof(MetaM), 64);
-  s.bars = take((2 * kMaxStagesM + 1 + 4 + 10) * 8, 8);
+  s.bars = take((2 * kMaxStagesM + 1 + 4 + 12) * 8, 8);
   s.misc = take(8 * 4, 4);
   s.per_b = take(batch * 4 * 4, 4);
   s.prefix = take((n_items + 1) * 4, 4);
@@ -295,7 +295,7 @@ __global__ void __launch_bounds__(kThreadsM, 1)
   uint64_t* q_empty = empty_bar + kMaxStagesM;
   uint64_t* res_full = q_empty + 1;   // [2]
   uint64_t* res_empty = res_full + 2; // [2]
-  uint64_t* umma_bars = res_empty + 2; // [10], tcgen05 variant only
+  uint64_t* umma_bars = res_empty + 2; // [12], tcgen05 variant only
   int* misc = reinterpret_cast<int*>(smem + sp.misc);
   int* sb_slot = reinterpret_cast<int*>(smem + sp.per_b);
   int* sb_len = sb_slot + p.batch;
@@ -333,11 +333,11 @@ __global__ void __launch_bounds__(kThreadsM, 1)
     else if (k < 2 * n_stages + 3) mbar_init(&res_full[k - 2 * n_stages - 1], kWarps);
     else if (k < 2 * n_stages + 5) mbar_init(&res_empty[k - 2 * n_stages - 3], 1);
     if (UMMA && k == 31) {
-      // s_full[2], p_full[2] (one arrival per warp of the group), o_full[2], q_ready and xch (one
+      // s_full[3], p_full[3] (one arrival per warp of the group), o_full[2], q_ready and xch (one
       // arrival per softmax warp), drain, pub (every softmax thread)
-      for (int j = 0; j < 10; ++j)
+      for (int j = 0; j < 12; ++j)
         mbar_init(&umma_bars[j],
-                  (j == 2 || j == 3) ? 4 : (j == 6 || j == 9) ? 8 : (j == 8 ? kUmmaSoftmaxThreads : 1));
+                  (j >= 3 && j < 6) ? 4 : (j == 8 || j == 11) ? 8 : (j == 10 ? kUmmaSoftmaxThreads : 1));
       misc[4] = 0;  // abort flag
     }
     fence_mbar_init();
@@ -589,16 +589,15 @@ __global__ void __launch_bounds__(kThreadsM, 1)
     UmmaCtx uc;
     uc.ring = ring;
     uc.metas = metas;
-    uc.qsw = qbuf;
     uc.full_bar = full_bar;
     uc.empty_bar = empty_bar;
     uc.s_full = umma_bars;
-    uc.p_full = umma_bars + 2;
-    uc.o_full = umma_bars + 4;
-    uc.q_ready = umma_bars + 6;
-    uc.drain = umma_bars + 7;
-    uc.pub = umma_bars + 8;
-    uc.xch = umma_bars + 9;
+    uc.p_full = umma_bars + 3;
+    uc.o_full = umma_bars + 6;
+    uc.q_ready = umma_bars + 8;
+    uc.drain = umma_bars + 9;
+    uc.pub = umma_bars + 10;
+    uc.xch = umma_bars + 11;
     uc.xch_m = mg_o;
     uc.xch_l = mg_o + 2 * kUmmaRows;
     uc.tmem_slot = reinterpret_cast<uint32_t*>(misc + 5);
@@ -1039,11 +1038,12 @@ bool pdl_enabled() {
 }
 
 // Fewest query rows (tokens x grouped heads) for which a tile goes to the tcgen05 variant; 0 = never.
-// PACE_UMMA_MIN_ROWS overrides it (A/B measurements).
+// Below 65 rows half of a 128-row tile or more is padding and the mma.sync kernel's smaller tiles win
+// (measured on PARD verify, 36 rows).  PACE_UMMA_MIN_ROWS overrides it (A/B measurements).
 int umma_min_rows() {
   static const int v = [] {
     const char* e = getenv("PACE_UMMA_MIN_ROWS");
-    return e ? atoi(e) : 0;
+    return e ? atoi(e) : 65;
   }();
   return v;
 }

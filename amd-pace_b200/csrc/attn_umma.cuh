@@ -4,15 +4,16 @@
 // by one elected thread, operands in shared memory (K-major / MN-major, 128-byte swizzle, exactly
 // the layout the tiled TMA copies of K and V produce), accumulators in tensor memory.
 //
-// The chunks of a unit part are dealt alternately to two softmax warpgroups (A: even, B: odd).  Each
-// group has its own score buffer, P tile, running (max, sum) and O accumulator, so the two never
-// wait for one another while the part streams; the two accumulators are merged when the part ends:
-//     TMEM columns [0, 64) / [64, 128)              S_A / S_B   128 x 64 fp32
-//     TMEM columns [128, 128 + D) / [256, 256 + D)  O_A / O_B   128 x D  fp32
-//     TMEM columns [384, 416) / [416, 448)          P_A / P_B   128 x 64 bf16 (two per column)
+// The chunks of a CTA's range are dealt alternately to two softmax warpgroups (A: even, B: odd).
+// Each group has its own running (max, sum) and O accumulator, so the two never wait for one another
+// while a unit part streams; the two accumulators are merged when the part ends.  Tensor memory:
+//     columns [0, 64) [64, 128) [128, 192)    three score buffers, 128 x 64 fp32; chunk i uses i % 3
+//     columns [192, 320) / [320, 448)         O_A / O_B, 128 x D fp32
+//     columns [448, 448 + D / 2)              the Q tile, 128 x D bf16 (two per column)
 // A softmax thread owns one query row (TMEM lane == row): tcgen05.ld the row of S, online softmax in
-// registers, P written back to tensor memory as the A operand of the second MMA (shared memory then
-// carries only Q, K and V: an MMA with both operands in shared memory is bound by its bandwidth).  O is rescaled in TMEM
+// registers, P written over the first 32 columns of the same score buffer as packed bf16 pairs.  Both
+// MMAs take their A operand (Q, P) from tensor memory, so shared memory carries only the K and V
+// stream (an MMA with both operands in shared memory is bound by its bandwidth).  O is rescaled in TMEM
 // only when a row's running maximum grows by more than 2^8 (the result is exact either way:
 // numerator and denominator share whatever maximum was used).
 //
@@ -24,18 +25,23 @@ namespace {
 
 constexpr int kUmmaRows = 128;          // query rows per tile (UMMA M)
 constexpr int kUmmaSoftmaxThreads = 256;  // two warpgroups
-constexpr int kTmemCols = 512;          // S_A, S_B, O_A, O_B
+constexpr int kTmemCols = 512;          // the whole tensor memory of the SM:
+constexpr uint32_t kTmemO = 192;        //   [0, 192) three score buffers, [192, 448) O of group A and B,
+constexpr uint32_t kTmemQ = 448;        //   [448, 512) the Q tile
 constexpr float kLazyRescale = 8.0f;    // log2 units
+#ifndef PACE_SOFTMAX_BACKOFF_NS
+#define PACE_SOFTMAX_BACKOFF_NS 100
+#endif
+constexpr unsigned kSoftmaxBackoffNs = PACE_SOFTMAX_BACKOFF_NS;  // a waiting softmax warp leaves its scheduler's issue slots to the MMA issuer
 
 struct UmmaCtx {
   unsigned char* ring;    // [n_stages][K | V] as the TMA boxes land
   const MetaM* metas;
-  unsigned char* qsw;     // Q tile, K-major 128-byte-swizzled: [D/64][128 rows][128 B]
   uint64_t* full_bar;
   uint64_t* empty_bar;
-  uint64_t* s_full;       // [2] QK^T of a chunk of group A / B has landed in TMEM
-  uint64_t* p_full;       // [2] P of a chunk is in shared memory (and O has been rescaled)
-  uint64_t* o_full;       // [2] PV of a chunk has been accumulated
+  uint64_t* s_full;       // [3] per score buffer: QK^T of a chunk has landed in TMEM
+  uint64_t* p_full;       // [3] per score buffer: P is in place (and O has been rescaled); one arrival per warp of the group
+  uint64_t* o_full;       // [2] per group: PV of a chunk has been accumulated
   uint64_t* q_ready;      // the Q tile of a unit part is in shared memory (one arrival per softmax warp)
   uint64_t* drain;        // every MMA this CTA issued has completed
   uint64_t* pub;          // meeting point of the 256 softmax threads while a cut unit is published
@@ -52,8 +58,10 @@ struct UmmaCtx {
 #endif
 };
 #ifdef PACE_TIMING
-#define PACE_UTRACE(c, k, i) do { if ((c).cta == 7 && (i) < 64) { unsigned long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_)); (c).trace[(k) * 64 + (i)] = t_; } } while (0)
+#define PACE_UTRACE(c, k, i) do { if ((c).cta == 7 && (i) < 64) (c).trace[(k) * 64 + (i)] = (unsigned long long)clock64(); } while (0)
+#define PACE_UCLK(c, k, i, v) do { if ((c).cta == 7 && (i) < 64) (c).trace[(k) * 64 + (i)] = (unsigned long long)(v); } while (0)
 #else
+#define PACE_UCLK(c, k, i, v) do {} while (0)
 #define PACE_UTRACE(c, k, i) do {} while (0)
 #endif
 
@@ -125,6 +133,14 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32
       "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
       : "memory");
 }
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};" ::"r"(taddr),
+      "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+      "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+      : "memory");
+}
 __device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
@@ -138,7 +154,7 @@ __device__ __forceinline__ bool umma_wait(uint64_t* bar, uint32_t parity, volati
       break;
     }
     if (*abort) break;
-    if (i > 64) __nanosleep(64);
+    __nanosleep(i > 64 ? 256 : kSoftmaxBackoffNs);
   }
   if (!ok) *abort = 1;
   return __all_sync(0xffffffffu, ok);
@@ -146,91 +162,121 @@ __device__ __forceinline__ bool umma_wait(uint64_t* bar, uint32_t parity, volati
 
 
 // ---- the MMA issuer: one warp waits, lane 0 issues ----
-// Within a unit part of n chunks, chunk c (part-relative) belongs to group w = c & 1.  Issue order:
-//   QK(0), QK(1), then for every c: wait P(c) -> PV(c) -> QK(c + 2)
-// so each group's next scores are computed while it works on its current chunk.
+// Chunk i of this CTA's range (counted over the whole range, not per unit part) uses score buffer
+// i % 3 and belongs to softmax group i & 1.  Within a unit part of n chunks the issue order is
+//   QK(0), QK(1), QK(2), then for every j: wait P(j) -> PV(j) -> QK(j + 3)
+// so the scores of a group's next chunk are in tensor memory before the group has finished its
+// current one.  QK(j + 3) overwrites the buffer PV(j) reads its P from: the tensor pipe executes the
+// MMAs of this thread in issue order, which is all the protection that reuse needs.
 template <int D>
 __device__ __forceinline__ void umma_issuer(const UmmaCtx& c, uint32_t tmem, int lane) {
-  constexpr int KVB = kChunk * D * 2, HALF_B = kChunk * 128, STAGE = 2 * KVB, HALVES = D / 64;
-  constexpr int QHALF = kUmmaRows * 128;
+  constexpr int KVB = kChunk * D * 2, HALF_B = kChunk * 128, STAGE = 2 * KVB;
   constexpr uint32_t IDESC_QK = umma_idesc(kChunk, false), IDESC_PV = umma_idesc(D, true);
   // Descriptors differ from one instruction to the next only in the start-address field (units of
   // 16 bytes): everything else is folded into constants, because the scalar instructions between two
   // tcgen05.mma of the one issuing thread are what limits the issue rate.
-  constexpr uint32_t DESC_HI = (1024u >> 4) | (1u << 14) | (2u << 29);       // SBO 1024 B, version 1, 128-byte swizzle
-  const uint32_t q_lo = (smem_u32(c.qsw) >> 4) | (1u << 16);                 // K-major: LBO unused (1)
-  const uint32_t k_lo0 = (smem_u32(c.ring) >> 4) | (1u << 16);
+  constexpr uint32_t DESC_HI = (1024u >> 4) | (1u << 14) | (2u << 29);  // SBO 1024 B, version 1, 128-byte swizzle
+  const uint32_t k_lo0 = (smem_u32(c.ring) >> 4) | (1u << 16);          // K-major: LBO unused (1)
   const uint32_t v_lo0 = ((smem_u32(c.ring) + KVB) >> 4) | ((uint32_t)(HALF_B >> 4) << 16);  // MN-major: LBO = next 64 columns
-  auto issue_qk = [&](int i, int s, int w) {
-    const uint32_t k_lo = k_lo0 + (uint32_t)s * (STAGE >> 4);
-    const uint32_t tS = tmem + (uint32_t)w * kChunk;
-#pragma unroll
-    for (int hf = 0; hf < HALVES; ++hf)
-#pragma unroll
-      for (int k = 0; k < 4; ++k)
-        umma_bf16(tS, pack64(q_lo + hf * (QHALF >> 4) + k * 2, DESC_HI), pack64(k_lo + hf * (HALF_B >> 4) + k * 2, DESC_HI),
-                  IDESC_QK, (hf | k) ? 1u : 0u);
-    umma_commit(&c.s_full[w]);
-    PACE_UTRACE(c, 8, i);
-  };
-  int cnt[2] = {0, 0};  // chunks handed to each group so far (the phase of its barriers)
-  int sq = 0, phq = 0;  // ring stage and phase of the next chunk whose QK is issued (QKs go out in chunk order)
-  int sp = 0;           // ring stage of the next chunk whose PV is issued
-  int part = 0, i0 = 0;
-  bool ok = true;
-  auto next_qk = [&](int i, int w) -> bool {
-    if (!umma_wait(&c.full_bar[sq], phq, c.abort)) return false;
-    tc_fence_after();
-    if (lane == 0) issue_qk(i, sq, w);
-    __syncwarp();
-    if (++sq == c.n_stages) {
-      sq = 0;
-      phq ^= 1;
-    }
-    return true;
-  };
-  while (i0 < c.n_my && ok) {
-    ok = umma_wait(&c.full_bar[sq], phq, c.abort) && umma_wait(c.q_ready, part & 1, c.abort);
-    if (!ok) break;
-    ++part;
-    const int n = c.metas[sq].pad;  // chunks of this part
-    if (n < 1) {
+  const uint32_t tQ = tmem + kTmemQ;
+  // Only lane 0 runs the loop: what paces this warp is the latency of its own dependent instruction
+  // stream (barrier probes, descriptor arithmetic, the MMA issues), and votes or shuffles that keep
+  // 32 lanes in agreement would only add to it.
+  if (lane == 0) {
+    int sq = 0, phq = 0;  // ring stage and phase of the next chunk whose QK is issued (QKs go out in chunk order)
+    int bq = 0;           // score buffer of that chunk
+    int sp = 0, bp = 0, php = 0;  // ring stage / score buffer / barrier phase of the next chunk whose PV is issued
+    int part = 0, i0 = 0;
+    bool ok = true;
+    auto wait1 = [&](uint64_t* bar, uint32_t parity) -> bool {
+      for (int k = 0; k < (1 << 20); ++k) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((k & 15) == 15 && *c.abort) break;
+      }
       *c.abort = 1;
-      break;
-    }
-    ok = next_qk(i0, 0) && (n < 2 || next_qk(i0 + 1, 1));
-    if (!ok) break;
-    for (int j = 0; j < n; ++j) {
-      const int w = j & 1;
-      ok = umma_wait(&c.p_full[w], cnt[w] & 1, c.abort);
+      return false;
+    };
+    auto next_qk = [&](int i) -> bool {
+      if (!wait1(&c.full_bar[sq], phq)) return false;
+#ifdef PACE_TIMING
+      const long long ck0 = clock64();
+#endif
+      const uint32_t k_lo = k_lo0 + (uint32_t)sq * (STAGE >> 4);
+      const uint32_t tS = tmem + (uint32_t)bq * kChunk;
+#pragma unroll
+      for (int kk = 0; kk < D / 16; ++kk)
+        umma_bf16_ts(tS, tQ + kk * 8, pack64(k_lo + (kk >> 2) * (HALF_B >> 4) + (kk & 3) * 2, DESC_HI), IDESC_QK,
+                     kk ? 1u : 0u);
+      umma_commit(&c.s_full[bq]);
+#ifdef PACE_TIMING
+      PACE_UCLK(c, 1, i, clock64() - ck0);
+#endif
+      PACE_UTRACE(c, 8, i);
+      if (++sq == c.n_stages) {
+        sq = 0;
+        phq ^= 1;
+      }
+      if (++bq == 3) bq = 0;
+      return true;
+    };
+    while (i0 < c.n_my && ok) {
+      ok = wait1(&c.full_bar[sq], phq) && wait1(c.q_ready, part & 1);
       if (!ok) break;
-      ++cnt[w];
-      tc_fence_after();
-      if (lane == 0) {
+      ++part;
+      const int n = c.metas[sq].pad;  // chunks of this part
+      if (n < 1) {
+        *c.abort = 1;
+        break;
+      }
+      tc_fence_after();  // the Q tile was written with tcgen05.st by the softmax threads
+      ok = next_qk(i0) && (n < 2 || next_qk(i0 + 1)) && (n < 3 || next_qk(i0 + 2));
+      if (!ok) break;
+      for (int j = 0; j < n; ++j) {
+        const int w = (i0 + j) & 1;
+#ifdef PACE_TIMING
+        const long long cw0 = clock64();
+#endif
+        ok = wait1(&c.p_full[bp], php);
+        if (!ok) break;
+#ifdef PACE_TIMING
+        const long long cw1 = clock64();
+#endif
+        tc_fence_after();  // P was written with tcgen05.st
+#ifdef PACE_TIMING
+        PACE_UCLK(c, 3, i0 + j, cw1 - cw0);
+        PACE_UCLK(c, 11, i0 + j, clock64() - cw1);
         PACE_UTRACE(c, 9, i0 + j);
+        const long long ck0 = clock64();
+#endif
         const uint32_t v_lo = v_lo0 + (uint32_t)sp * (STAGE >> 4);
-        const uint32_t tO = tmem + 128 + (uint32_t)w * 128, tP = tmem + 384 + (uint32_t)w * 32;
+        const uint32_t tO = tmem + kTmemO + (uint32_t)w * 128, tP = tmem + (uint32_t)bp * kChunk;
         umma_bf16_ts(tO, tP, pack64(v_lo, DESC_HI), IDESC_PV, j < 2 ? 0u : 1u);
 #pragma unroll
         for (int k = 1; k < 4; ++k)  // 16 keys per instruction
           umma_bf16_ts(tO, tP + k * 8, pack64(v_lo + k * (2048 >> 4), DESC_HI), IDESC_PV, 1u);
         umma_commit(&c.empty_bar[sp]);  // K and V of this stage have been consumed
         umma_commit(&c.o_full[w]);
+#ifdef PACE_TIMING
+        PACE_UCLK(c, 2, i0 + j, clock64() - ck0);
+#endif
         PACE_UTRACE(c, 10, i0 + j);
+        if (++sp == c.n_stages) sp = 0;
+        if (++bp == 3) {
+          bp = 0;
+          php ^= 1;
+        }
+        if (j + 3 < n) {
+          ok = next_qk(i0 + j + 3);
+          if (!ok) break;
+        }
       }
-      __syncwarp();
-      if (++sp == c.n_stages) sp = 0;
-      if (j + 2 < n) {
-        ok = next_qk(i0 + j + 2, w);
-        if (!ok) break;
-      }
+      i0 += n;
     }
-    i0 += n;
+    // nothing may still be writing tensor memory when it is handed back
+    umma_commit(c.drain);
+    for (int k = 0; k < (1 << 20) && !mbar_try_wait(c.drain, 0); ++k) __nanosleep(64);
   }
-  // nothing may still be writing tensor memory when it is handed back
-  if (lane == 0) umma_commit(c.drain);
   __syncwarp();
-  for (int k = 0; k < (1 << 20) && !mbar_try_wait(c.drain, 0); ++k) __nanosleep(64);
 }
 
 // merge of a unit's partials by its last arriver (all softmax threads; every partial is in the workspace)
@@ -280,13 +326,11 @@ __device__ __forceinline__ void umma_merge(const MmaParams& p, const ResMeta& rm
 // ---- the softmax warps: thread (group w, row r) owns query row r for the chunks dealt to group w ----
 template <int D>
 __device__ __forceinline__ void umma_softmax(const MmaParams& p, const UmmaCtx& c, uint32_t tmem, int tid) {
-  constexpr int MR = kUmmaRows, REC = MR * (D + 2), QHALF = MR * 128;
+  constexpr int MR = kUmmaRows, REC = MR * (D + 2);
   const int wg = tid >> 7, row = tid & 127, lane = tid & 31, G = p.G;
   const uint32_t t_lane = tmem + ((uint32_t)(row & ~31) << 16);  // this warp's 32 TMEM lanes
-  const uint32_t tS = t_lane + (uint32_t)wg * kChunk;
-  const uint32_t tOa = t_lane + 128, tOb = t_lane + 256, tO = wg ? tOb : tOa;
+  const uint32_t tO = t_lane + kTmemO + (uint32_t)wg * 128, tOo = t_lane + kTmemO + (uint32_t)(wg ^ 1) * 128;
   const float scale = p.scale_log2;
-  const uint32_t tP = t_lane + 384 + (uint32_t)wg * 32;  // this group's P tile: 64 keys as 32 columns of bf16 pairs
   int cnt = 0;  // chunks this group has worked on (the phase of its barriers)
   int n_pub = 0, n_xch = 0;
   auto group_sync = [&]() -> bool {  // all softmax threads meet (bounded, unlike bar.sync)
@@ -297,7 +341,7 @@ __device__ __forceinline__ void umma_softmax(const MmaParams& p, const UmmaCtx& 
   };
 
   for (int i0 = 0; i0 < c.n_my;) {
-    // ---- new unit part: its record, this thread's share of the Q tile (swizzled A operand) ----
+    // ---- new unit part: its record, this thread's share of the Q tile (A operand in tensor memory) ----
     if (!umma_wait(&c.full_bar[i0 % c.n_stages], (i0 / c.n_stages) & 1, c.abort)) return;
     ResMeta fin;
     int n_part, kvs, lim;
@@ -324,15 +368,22 @@ __device__ __forceinline__ void umma_softmax(const MmaParams& p, const UmmaCtx& 
       const uint4* src = reinterpret_cast<const uint4*>(p.q + (size_t)fin.b * p.q_sb + (size_t)(fin.h * G + g) * p.q_sh +
                                                         (size_t)sq * p.q_ss);
       out_row = p.out + (size_t)fin.b * p.o_sb + (size_t)(fin.h * G + g) * p.o_sh + (size_t)sq * p.o_ss;
-      unsigned char* qrow = c.qsw + row * 128;
+      // 64 head-dim elements (32 columns of bf16 pairs) per thread: group A the first 64, group B the
+      // next 64 of a 128-wide head; a 64-wide head is group A's alone
+      if (D == 128 || wg == 0) {
+        uint32_t qv[32];
 #pragma unroll
-      for (int k = 0; k < D / 16; ++k) {
-        const int cc = wg * (D / 16) + k;
-        const uint4 v = live ? __ldg(src + cc) : make_uint4(0, 0, 0, 0);
-        *reinterpret_cast<uint4*>(qrow + (cc >> 3) * QHALF + (((cc & 7) ^ (row & 7)) << 4)) = v;
+        for (int k = 0; k < 8; ++k) {
+          const uint4 v = live ? __ldg(src + (D == 128 ? wg * 8 : 0) + k) : make_uint4(0, 0, 0, 0);
+          qv[4 * k] = v.x;
+          qv[4 * k + 1] = v.y;
+          qv[4 * k + 2] = v.z;
+          qv[4 * k + 3] = v.w;
+        }
+        tmem_st32(t_lane + kTmemQ + (D == 128 ? wg * 32 : 0), qv);
+        tmem_wait_st();
       }
-      fence_proxy_async();  // generic-proxy writes before the tensor core's async-proxy reads
-      tc_fence_before();    // (and this thread's reads of O for the previous part are done)
+      tc_fence_before();  // (this thread's reads of O for the previous part are done as well)
       __syncwarp();
       if (lane == 0) mbar_arrive(c.q_ready);
     }
@@ -340,37 +391,47 @@ __device__ __forceinline__ void umma_softmax(const MmaParams& p, const UmmaCtx& 
     const bool warp_live = (row & ~31) < fin.live;  // a warp of padding rows only keeps the barriers in step
     float m_used = -INFINITY, l = 0.f;
 
-    for (int j = wg; j < n_part; j += 2) {
-      const int i = i0 + j, s = i % c.n_stages;
+    const int j_first = (i0 ^ wg) & 1;  // this group takes the chunks whose index in the CTA's range has its parity
+    for (int j = j_first; j < n_part; j += 2) {
+      const int i = i0 + j, s = i % c.n_stages, b = i % 3;
+      const uint32_t tS = t_lane + (uint32_t)b * kChunk;
       if (!umma_wait(&c.full_bar[s], (i / c.n_stages) & 1, c.abort)) return;
       const int rows = c.metas[s].rows, tok0 = c.metas[s].tok0;
       if (tid == 0) PACE_UTRACE(c, 4, i);
-      if (!umma_wait(&c.s_full[wg], cnt & 1, c.abort)) return;
+      if (!umma_wait(&c.s_full[b], (i / 3) & 1, c.abort)) return;
       tc_fence_after();
       if (tid == 0) PACE_UTRACE(c, 5, i);
-      uint32_t pk[32];
       if (warp_live) {
-        // ---- scores of this chunk: TMEM -> registers ----
-        uint32_t sr[2][32];
-        tmem_ld32(tS, sr[0]);
-        tmem_ld32(tS + 32, sr[1]);
-        tmem_wait_ld();
+        // Two passes over the scores, 32 columns in registers at a time (tensor memory is cheap to
+        // read twice; 64 scores plus 32 packed results per thread is what spills): the first pass
+        // finds the row maximum, the second turns each half into P and writes it over columns the
+        // pass has already consumed (S columns [0, 32) -> P columns [0, 16), [32, 64) -> [16, 32)).
         const int lo = max(0, kvs - tok0), hi = min(rows, lim - tok0);  // visible keys of the chunk: [lo, hi)
-        if (!__all_sync(0xffffffffu, lo <= 0 && hi >= kChunk)) {
+        const bool all_visible = __all_sync(0xffffffffu, lo <= 0 && hi >= kChunk);
+        float mx;
+        {
+          float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-          for (int k = 0; k < 64; ++k)
-            if (k < lo || k >= hi) sr[k >> 5][k & 31] = 0xff800000u;  // -inf
+          for (int hf = 0; hf < 2; ++hf) {
+            uint32_t sr[32];
+            tmem_ld32(tS + hf * 32, sr);
+            tmem_wait_ld();
+            if (!all_visible) {
+#pragma unroll
+              for (int k = 0; k < 32; ++k)
+                if (hf * 32 + k < lo || hf * 32 + k >= hi) sr[k] = 0xff800000u;  // -inf
+            }
+#pragma unroll
+            for (int k = 0; k < 32; ++k) mx4[k & 3] = fmaxf(mx4[k & 3], __uint_as_float(sr[k]));
+          }
+          mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale;  // scale > 0
         }
-        float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-#pragma unroll
-        for (int k = 0; k < 64; ++k) mx4[k & 3] = fmaxf(mx4[k & 3], __uint_as_float(sr[k >> 5][k & 31]));
-        const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale;  // scale > 0
         // ---- running maximum; O is rescaled only when some row of the warp moved by more than 2^8 ----
         const bool grow = mx > m_used + kLazyRescale;
         if (__any_sync(0xffffffffu, grow)) {
           const float m_new = grow ? mx : m_used;
           const float alpha = grow ? ((m_used == -INFINITY) ? 0.f : fast_exp2(m_used - m_new)) : 1.f;
-          if (j >= 2) {  // O holds the sum of the group's earlier chunks of this part
+          if (j > j_first) {  // O holds the sum of the group's earlier chunks of this part
             if (!umma_wait(&c.o_full[wg], (cnt - 1) & 1, c.abort)) return;
             tc_fence_after();
 #pragma unroll
@@ -391,30 +452,38 @@ __device__ __forceinline__ void umma_softmax(const MmaParams& p, const UmmaCtx& 
         const float ne = (m_used == -INFINITY) ? 0.f : -m_used;
         float l4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-        for (int k = 0; k < 32; ++k) {
-          const float p0 = fast_exp2(fmaf(__uint_as_float(sr[k >> 4][(2 * k) & 31]), scale, ne));
-          const float p1 = fast_exp2(fmaf(__uint_as_float(sr[k >> 4][(2 * k + 1) & 31]), scale, ne));
-          l4[k & 3] += p0 + p1;
-          pk[k] = f2_to_bf2(p0, p1);
+        for (int hf = 0; hf < 2; ++hf) {
+          uint32_t sr[32];
+          tmem_ld32(tS + hf * 32, sr);
+          tmem_wait_ld();
+          if (!all_visible) {
+#pragma unroll
+            for (int k = 0; k < 32; ++k)
+              if (hf * 32 + k < lo || hf * 32 + k >= hi) sr[k] = 0xff800000u;
+          }
+          uint32_t pk[16];
+#pragma unroll
+          for (int k = 0; k < 16; ++k) {
+            const float p0 = fast_exp2(fmaf(__uint_as_float(sr[2 * k]), scale, ne));
+            const float p1 = fast_exp2(fmaf(__uint_as_float(sr[2 * k + 1]), scale, ne));
+            l4[k & 3] += p0 + p1;
+            pk[k] = f2_to_bf2(p0, p1);
+          }
+          tmem_st16(tS + hf * 16, pk);
         }
         l += (l4[0] + l4[1]) + (l4[2] + l4[3]);
-      }
-      if (tid == 0) PACE_UTRACE(c, 6, i);
-      // the P tile (tensor memory) was the A operand of this group's previous PV
-      if (cnt >= 1 && !umma_wait(&c.o_full[wg], (cnt - 1) & 1, c.abort)) return;
-      if (warp_live) {
-        tmem_st32(tP, pk);
         tmem_wait_st();
       }
+      if (tid == 0) PACE_UTRACE(c, 6, i);
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&c.p_full[wg]);
+      if (lane == 0) mbar_arrive(&c.p_full[b]);
       if (tid == 0) PACE_UTRACE(c, 7, i);
       ++cnt;
     }
 
     // ================= end of a unit part: the two groups' accumulators meet =================
-    const bool has_mine = n_part > wg;  // (a part of one chunk leaves group B empty-handed)
+    const bool has_mine = j_first < n_part, has_other = (j_first ^ 1) < n_part;  // (a part of one chunk leaves a group empty-handed)
     if (has_mine && !umma_wait(&c.o_full[wg], (cnt - 1) & 1, c.abort)) return;
     c.xch_m[wg * MR + row] = m_used;
     c.xch_l[wg * MR + row] = l;
@@ -424,27 +493,33 @@ __device__ __forceinline__ void umma_softmax(const MmaParams& p, const UmmaCtx& 
     ++n_xch;
     tc_fence_after();
     const float m_o = c.xch_m[(wg ^ 1) * MR + row], l_o = c.xch_l[(wg ^ 1) * MR + row];
-    const float mA = wg ? m_o : m_used, mB = wg ? m_used : m_o, lA = wg ? l_o : l, lB = wg ? l : l_o;
-    const float M = fmaxf(mA, mB);
-    const float fA = (mA == -INFINITY) ? 0.f : fast_exp2(mA - M), fB = (mB == -INFINITY) ? 0.f : fast_exp2(mB - M);
-    const float den = lA * fA + lB * fB;
-    const bool has_b = n_part > 1;
+    const float M = fmaxf(m_used, m_o);
+    const float f_m = (m_used == -INFINITY) ? 0.f : fast_exp2(m_used - M);
+    const float f_o = (m_o == -INFINITY) ? 0.f : fast_exp2(m_o - M);
+    const float den = l * f_m + l_o * f_o;
     // group A takes the lower half of the head dimension, group B the upper half
     float* rec = p.parts + ((size_t)c.cta * 2 + (fin.mode == 2 ? 1 : 0)) * REC;
     if (warp_live) {
       const float inv = den > 0.f ? 1.0f / den : 0.f;
-      const float sA = fin.mode == 0 ? fA * inv : fA, sB = fin.mode == 0 ? fB * inv : fB;
+      const float s_m = fin.mode == 0 ? f_m * inv : f_m, s_o = fin.mode == 0 ? f_o * inv : f_o;
 #pragma unroll
       for (int d0 = wg * (D / 2); d0 < (wg + 1) * (D / 2); d0 += 32) {
-        uint32_t oa[32], ob[32];
-        tmem_ld32(tOa + d0, oa);
-        if (has_b) tmem_ld32(tOb + d0, ob);
-        tmem_wait_ld();
         float v[32];
 #pragma unroll
-        for (int k = 0; k < 32; ++k) {
-          v[k] = __uint_as_float(oa[k]) * sA;
-          if (has_b) v[k] = fmaf(__uint_as_float(ob[k]), sB, v[k]);
+        for (int k = 0; k < 32; ++k) v[k] = 0.f;
+        if (has_mine) {
+          uint32_t om[32];
+          tmem_ld32(tO + d0, om);
+          tmem_wait_ld();
+#pragma unroll
+          for (int k = 0; k < 32; ++k) v[k] = __uint_as_float(om[k]) * s_m;
+        }
+        if (has_other) {
+          uint32_t oo[32];
+          tmem_ld32(tOo + d0, oo);
+          tmem_wait_ld();
+#pragma unroll
+          for (int k = 0; k < 32; ++k) v[k] = fmaf(__uint_as_float(oo[k]), s_o, v[k]);
         }
         if (live) {
           if (fin.mode == 0) {

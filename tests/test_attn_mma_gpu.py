@@ -81,6 +81,11 @@ CASES = [
     (1, 8, 2, 64, 700, [601], 130),                         # prefill, D = 64
     (1, 8, 2, 128, 40000, [20000], 9),                      # long context: unit split over many CTAs
     (2, 32, 8, 128, 9000, [8190, 4097], 9),                 # page_tokens 94 > 64: sub-page chunks
+    # 128-row tiles (tcgen05 variant): unit parts of one and two chunks, a last tile of 24 live rows
+    (1, 32, 8, 128, 300, [70], 70),
+    (2, 16, 16, 64, 1500, [1400, 129], 128),                # MHA, D = 64, exactly one full tile per head
+    (1, 8, 2, 128, 20000, [16000], 64),                     # two tiles over a long cache: units cut across many CTAs
+    (3, 32, 8, 128, 700, [640, 65, 300], 65),               # 260 rows: three tiles, lengths around chunk boundaries
 ]
 
 
@@ -120,6 +125,48 @@ def test_ragged_query_counts_and_left_padding():
     want = _oracle(q, ks, vs, left_pad=pads, q_lens=q_lens)
     for b in range(B):
         _check(out[b, :, : q_lens[b]], want[b])
+    mgr.pool.check_status()
+
+
+def test_large_tiles_ragged_counts_and_left_padding():
+    """Ragged query counts and left pads on 128-row tiles (the tcgen05 variant's masking paths)."""
+    from pace_b200.llm.cache import KVCacheManager, KVCacheType
+    from pace_b200.ops import MultiHeadAttention
+    g = torch.Generator().manual_seed(78)
+    B, Hq, Hkv, D, S = 3, 16, 4, 128, 48                      # 192 rows per kv head
+    lens, q_lens, pads = [300, 64, 140], [48, 17, 1], [0, 11, 70]
+    ks = [torch.randn(Hkv, L, D, generator=g).bfloat16().to(DEV) for L in lens]
+    vs = [torch.randn(Hkv, L, D, generator=g).bfloat16().to(DEV) for L in lens]
+    q = torch.randn(B, S, Hq, D, generator=g).bfloat16().to(DEV).transpose(1, 2)
+    mgr = KVCacheManager(Cfg(1), 320, KVCacheType.BMC)
+    K, V = _fill(mgr, 0, ks, vs)
+    out = MultiHeadAttention()(q, K, V, kv_start=torch.tensor(pads, dtype=torch.int32, device=DEV),
+                               q_lens=torch.tensor(q_lens, dtype=torch.int32, device=DEV))
+    want = _oracle(q, ks, vs, left_pad=pads, q_lens=q_lens)
+    for b in range(B):
+        _check(out[b, :, : q_lens[b]], want[b])
+    mgr.pool.check_status()
+
+
+@pytest.mark.parametrize("grid", [1, 5, 37])
+def test_prefill_tiles_under_other_partitions(monkeypatch, grid):
+    """The same prefill chunk with the chunk stream cut for 1, 5 and 37 CTAs (cut units, partial
+    merges across CTAs) on 128-row tiles."""
+    from pace_b200.llm.cache import KVCacheManager, KVCacheType
+    from pace_b200.ops import MultiHeadAttention
+    monkeypatch.setenv("PACE_DECODE_GRID", str(grid))
+    g = torch.Generator().manual_seed(grid)
+    B, Hq, Hkv, D, S = 2, 16, 4, 128, 96
+    lens = [777, 96]
+    ks = [torch.randn(Hkv, L, D, generator=g).bfloat16().to(DEV) for L in lens]
+    vs = [torch.randn(Hkv, L, D, generator=g).bfloat16().to(DEV) for L in lens]
+    q = torch.randn(B, S, Hq, D, generator=g).bfloat16().to(DEV).transpose(1, 2)
+    mgr = KVCacheManager(Cfg(1), 800, KVCacheType.BMC)
+    K, V = _fill(mgr, 0, ks, vs)
+    out = MultiHeadAttention()(q, K, V)
+    want = _oracle(q, ks, vs)
+    for b in range(B):
+        _check(out[b], want[b])
     mgr.pool.check_status()
 
 
