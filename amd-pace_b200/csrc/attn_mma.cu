@@ -34,6 +34,8 @@ namespace {
 constexpr int kWarps = 8;
 constexpr int kCThreads = kWarps * 32;
 constexpr int kThreadsM = kCThreads + 64;  // + producer warp + epilogue warp
+constexpr int kThreadsU = kCThreads + 96;  // tcgen05 variant: + producer warp + two MMA issuer warps
+__host__ __device__ constexpr int threads_of(bool umma) { return umma ? kThreadsU : kThreadsM; }
 constexpr int kChunk = 64;
 constexpr int kMaxStagesM = 8;
 constexpr int kMaxItems = 1024;
@@ -132,7 +134,7 @@ __host__ __device__ inline SmemPlan plan_smem(int D, int MT, int NS, int n_stage
   s.res_slot_bytes = (live_max * (D + 2) * 4 + 64 + 15) / 16 * 16;
   s.res = take(umma ? 16 : s.n_res * s.res_slot_bytes, 16);
   s.metas = take(kMaxStagesM * (int)sizeof(MetaM), 64);
-  s.bars = take((2 * kMaxStagesM + 1 + 4 + 12) * 8, 8);
+  s.bars = take((2 * kMaxStagesM + 1 + 4 + 16) * 8, 8);
   s.misc = take(8 * 4, 4);
   s.per_b = take(batch * 4 * 4, 4);
   s.prefix = take((n_items + 1) * 4, 4);
@@ -258,9 +260,10 @@ __device__ __forceinline__ void publish_part(const MmaParams& p, const ResMeta& 
 }
 
 template <int D, int MT, int NS, bool UMMA = false>
-__global__ void __launch_bounds__(kThreadsM, 1)
+__global__ void __launch_bounds__(threads_of(UMMA), 1)
     attn_mma_kernel(const MmaParams p, const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV) {
   static_assert(MT * NS == kWarps, "eight consumer warps");
+  constexpr int NTHR = threads_of(UMMA);
   static_assert(!UMMA || (MT == 8 && NS == 1), "the tcgen05 variant works on whole 128-row tiles");
   // How the NS warps of a row tile share the key stream.  Decode (MT == 1): each chunk's keys are cut
   // into NS slices, every warp works on every chunk.  Verify tiles (MT, NS >= 2): whole chunks are dealt
@@ -295,7 +298,7 @@ __global__ void __launch_bounds__(kThreadsM, 1)
   uint64_t* q_empty = empty_bar + kMaxStagesM;
   uint64_t* res_full = q_empty + 1;   // [2]
   uint64_t* res_empty = res_full + 2; // [2]
-  uint64_t* umma_bars = res_empty + 2; // [12], tcgen05 variant only
+  uint64_t* umma_bars = res_empty + 2; // [16], tcgen05 variant only
   int* misc = reinterpret_cast<int*>(smem + sp.misc);
   int* sb_slot = reinterpret_cast<int*>(smem + sp.per_b);
   int* sb_len = sb_slot + p.batch;
@@ -325,34 +328,34 @@ __global__ void __launch_bounds__(kThreadsM, 1)
   // kernel in front of it on the stream drains; griddepcontrol.wait then holds until that kernel has
   // completed and its writes (the appended rows, the lengths) are visible. ----
   // one barrier per thread of the last warp (its lanes have no sequences to look up in small batches)
-  if (tid >= kThreadsM - 32) {
-    const int k = tid - (kThreadsM - 32);
+  if (tid >= NTHR - 32) {
+    const int k = tid - (NTHR - 32);
     if (k < n_stages) mbar_init(&full_bar[k], 1);
     else if (k < 2 * n_stages) mbar_init(&empty_bar[k - n_stages], UMMA ? 1 : kWarps);
     else if (k == 2 * n_stages) mbar_init(q_empty, kWarps);
     else if (k < 2 * n_stages + 3) mbar_init(&res_full[k - 2 * n_stages - 1], kWarps);
     else if (k < 2 * n_stages + 5) mbar_init(&res_empty[k - 2 * n_stages - 3], 1);
     if (UMMA && k == 31) {
-      // s_full[3], p_full[3] (one arrival per warp of the group), o_full[2], q_ready and xch (one
-      // arrival per softmax warp), drain, pub (every softmax thread)
-      for (int j = 0; j < 12; ++j)
+      // s_full[3], p_full[3] (one arrival per warp of the group), o_full[2], q_ready, drain[2], pub
+      // (every softmax thread), xch (one arrival per softmax warp, like q_ready), p_free[3]
+      for (int j = 0; j < 16; ++j)
         mbar_init(&umma_bars[j],
-                  (j >= 3 && j < 6) ? 4 : (j == 8 || j == 11) ? 8 : (j == 10 ? kUmmaSoftmaxThreads : 1));
+                  (j >= 3 && j < 6) ? 4 : (j == 8 || j == 12) ? 8 : (j == 11 ? kUmmaSoftmaxThreads : 1));
       misc[4] = 0;  // abort flag
     }
     fence_mbar_init();
   }
   for (int s = 0; s < n_stages; ++s) {
     uint4* z = reinterpret_cast<uint4*>(ring + (size_t)s * STAGE + KVB);
-    for (int i = tid; i < KVB / 16; i += kThreadsM) z[i] = make_uint4(0, 0, 0, 0);
+    for (int i = tid; i < KVB / 16; i += NTHR) z[i] = make_uint4(0, 0, 0, 0);
   }
   asm volatile("griddepcontrol.wait;" ::: "memory");
   // ---- prologue, part 2: per-sequence lengths -> chunk prefix -> this CTA's range ----
-  int my_slot[(kMaxItems + kThreadsM - 1) / kThreadsM];
-  int my_len[(kMaxItems + kThreadsM - 1) / kThreadsM];
+  int my_slot[(kMaxItems + NTHR - 1) / NTHR];
+  int my_len[(kMaxItems + NTHR - 1) / NTHR];
 #pragma unroll
-  for (int r = 0; r < (kMaxItems + kThreadsM - 1) / kThreadsM; ++r) {
-    const int b = tid + r * kThreadsM;
+  for (int r = 0; r < (kMaxItems + NTHR - 1) / NTHR; ++r) {
+    const int b = tid + r * NTHR;
     my_slot[r] = -1;
     my_len[r] = 0;
     if (b < p.batch) {
@@ -375,8 +378,8 @@ __global__ void __launch_bounds__(kThreadsM, 1)
   if (tid == 0) PACE_TRACE(3, 1);
   if (tid == 0) PACE_TRACE(3, 2);
 #pragma unroll
-  for (int r = 0; r < (kMaxItems + kThreadsM - 1) / kThreadsM; ++r) {
-    const int b = tid + r * kThreadsM;
+  for (int r = 0; r < (kMaxItems + NTHR - 1) / NTHR; ++r) {
+    const int b = tid + r * NTHR;
     if (b < p.batch) {
       sb_slot[b] = my_slot[r];
       sb_len[b] = my_len[r];
@@ -386,7 +389,7 @@ __global__ void __launch_bounds__(kThreadsM, 1)
   __syncthreads();
   if (tid == 0) PACE_TRACE(3, 3);
   int saw_empty = 0;
-  for (int it = tid; it < n_items; it += kThreadsM) {
+  for (int it = tid; it < n_items; it += NTHR) {
     const int b = p.n_qt == 1 ? it : it / p.n_qt, qt = it - b * p.n_qt;
     int n = 0;
     if (sb_slot[b] >= 0) {
@@ -440,7 +443,7 @@ __global__ void __launch_bounds__(kThreadsM, 1)
     if (prefix[it + 1] != prefix[it]) continue;
     const int b = it / p.n_qt, qt = it - b * p.n_qt;
     const int R = sb_S[b] * G;
-    for (int o = tid; o < MR * D; o += kThreadsM) {
+    for (int o = tid; o < MR * D; o += NTHR) {
       const int r = qt * MR + o / D, d = o % D;
       if (r < R) {
         const int s = r / G, g = r - s * G;
@@ -585,7 +588,7 @@ __global__ void __launch_bounds__(kThreadsM, 1)
   }
 
   if constexpr (UMMA) {
-    // ============== tcgen05 variant: softmax warps 0..7 (two groups), MMA issuer warp 9 ==============
+    // ========= tcgen05 variant: softmax warps 0..7 (two groups), MMA issuer warps 9 (QK) and 10 (PV) =========
     UmmaCtx uc;
     uc.ring = ring;
     uc.metas = metas;
@@ -596,8 +599,9 @@ __global__ void __launch_bounds__(kThreadsM, 1)
     uc.o_full = umma_bars + 6;
     uc.q_ready = umma_bars + 8;
     uc.drain = umma_bars + 9;
-    uc.pub = umma_bars + 10;
-    uc.xch = umma_bars + 11;
+    uc.pub = umma_bars + 11;
+    uc.xch = umma_bars + 12;
+    uc.p_free = umma_bars + 13;
     uc.xch_m = mg_o;
     uc.xch_l = mg_o + 2 * kUmmaRows;
     uc.tmem_slot = reinterpret_cast<uint32_t*>(misc + 5);
@@ -1069,7 +1073,7 @@ int launch_mma(MmaParams& p, const CUtensorMap& tmK, const CUtensorMap& tmV, int
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)grid);
-  cfg.blockDim = dim3(kThreadsM);
+  cfg.blockDim = dim3(threads_of(UMMA));
   cfg.dynamicSmemBytes = smem_bytes;
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];

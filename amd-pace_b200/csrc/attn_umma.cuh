@@ -43,7 +43,8 @@ struct UmmaCtx {
   uint64_t* p_full;       // [3] per score buffer: P is in place (and O has been rescaled); one arrival per warp of the group
   uint64_t* o_full;       // [2] per group: PV of a chunk has been accumulated
   uint64_t* q_ready;      // the Q tile of a unit part is in shared memory (one arrival per softmax warp)
-  uint64_t* drain;        // every MMA this CTA issued has completed
+  uint64_t* p_free;       // [3] per score buffer: the PV that read P from it has completed
+  uint64_t* drain;        // [2] every MMA an issuer warp issued has completed
   uint64_t* pub;          // meeting point of the 256 softmax threads while a cut unit is published
   uint64_t* xch;          // the two groups have posted their (max, sum) of a part (one arrival per warp)
   float* xch_m;           // [2][128]
@@ -161,120 +162,135 @@ __device__ __forceinline__ bool umma_wait(uint64_t* bar, uint32_t parity, volati
 }
 
 
-// ---- the MMA issuer: one warp waits, lane 0 issues ----
+// ---- the two MMA issuers: one lane of warp 9 issues every QK, one lane of warp 10 every PV ----
 // Chunk i of this CTA's range (counted over the whole range, not per unit part) uses score buffer
-// i % 3 and belongs to softmax group i & 1.  Within a unit part of n chunks the issue order is
-//   QK(0), QK(1), QK(2), then for every j: wait P(j) -> PV(j) -> QK(j + 3)
-// so the scores of a group's next chunk are in tensor memory before the group has finished its
-// current one.  QK(j + 3) overwrites the buffer PV(j) reads its P from: the tensor pipe executes the
-// MMAs of this thread in issue order, which is all the protection that reuse needs.
+// i % 3 and belongs to softmax group i & 1.  One issuing thread's dependent instruction stream
+// (barrier probes, descriptor arithmetic, a dozen tcgen05.mma per chunk) was what paced the whole
+// pipeline, hence two of them:
+//   QK issuer:  wait K/V of chunk i, wait until PV(i - 3) has left score buffer i % 3, issue QK(i)
+//   PV issuer:  wait P(i), issue PV(i), release the ring stage, the group's O and the score buffer
+// so scores are computed up to three chunks ahead of the softmax warps.  Only one lane runs each
+// loop: votes or shuffles that keep 32 lanes in agreement would only add latency.
+constexpr uint32_t kDescHi = (1024u >> 4) | (1u << 14) | (2u << 29);  // SBO 1024 B, version 1, 128-byte swizzle
+
+__device__ __forceinline__ bool issuer_wait(const UmmaCtx& c, uint64_t* bar, uint32_t parity) {
+  for (int k = 0; k < (1 << 20); ++k) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((k & 15) == 15 && *c.abort) break;
+  }
+  *c.abort = 1;
+  return false;
+}
+
 template <int D>
-__device__ __forceinline__ void umma_issuer(const UmmaCtx& c, uint32_t tmem, int lane) {
+__device__ __forceinline__ void umma_issue_qk(const UmmaCtx& c, uint32_t tmem, int lane) {
   constexpr int KVB = kChunk * D * 2, HALF_B = kChunk * 128, STAGE = 2 * KVB;
-  constexpr uint32_t IDESC_QK = umma_idesc(kChunk, false), IDESC_PV = umma_idesc(D, true);
+  constexpr uint32_t IDESC_QK = umma_idesc(kChunk, false);
   // Descriptors differ from one instruction to the next only in the start-address field (units of
-  // 16 bytes): everything else is folded into constants, because the scalar instructions between two
-  // tcgen05.mma of the one issuing thread are what limits the issue rate.
-  constexpr uint32_t DESC_HI = (1024u >> 4) | (1u << 14) | (2u << 29);  // SBO 1024 B, version 1, 128-byte swizzle
-  const uint32_t k_lo0 = (smem_u32(c.ring) >> 4) | (1u << 16);          // K-major: LBO unused (1)
-  const uint32_t v_lo0 = ((smem_u32(c.ring) + KVB) >> 4) | ((uint32_t)(HALF_B >> 4) << 16);  // MN-major: LBO = next 64 columns
+  // 16 bytes): everything else is folded into constants.
+  const uint32_t k_lo0 = (smem_u32(c.ring) >> 4) | (1u << 16);  // K-major: LBO unused (1)
   const uint32_t tQ = tmem + kTmemQ;
-  // Only lane 0 runs the loop: what paces this warp is the latency of its own dependent instruction
-  // stream (barrier probes, descriptor arithmetic, the MMA issues), and votes or shuffles that keep
-  // 32 lanes in agreement would only add to it.
   if (lane == 0) {
-    int sq = 0, phq = 0;  // ring stage and phase of the next chunk whose QK is issued (QKs go out in chunk order)
-    int bq = 0;           // score buffer of that chunk
-    int sp = 0, bp = 0, php = 0;  // ring stage / score buffer / barrier phase of the next chunk whose PV is issued
-    int part = 0, i0 = 0;
-    bool ok = true;
-    auto wait1 = [&](uint64_t* bar, uint32_t parity) -> bool {
-      for (int k = 0; k < (1 << 20); ++k) {
-        if (mbar_try_wait(bar, parity)) return true;
-        if ((k & 15) == 15 && *c.abort) break;
+    int s = 0, ph = 0, b = 0, phb = 1;  // ring stage / its phase, score buffer / phase of its previous use
+    int part = 0, left = 0;             // chunks left in the current unit part
+    for (int i = 0; i < c.n_my; ++i) {
+      if (!issuer_wait(c, &c.full_bar[s], ph)) break;
+      if (left == 0) {  // first chunk of a unit part: its Q tile
+        left = c.metas[s].pad;
+        if (left < 1 || !issuer_wait(c, c.q_ready, part & 1)) {
+          *c.abort = 1;
+          break;
+        }
+        ++part;
       }
-      *c.abort = 1;
-      return false;
-    };
-    auto next_qk = [&](int i) -> bool {
-      if (!wait1(&c.full_bar[sq], phq)) return false;
+      --left;
+      if (i >= 3 && !issuer_wait(c, &c.p_free[b], phb)) break;
+      tc_fence_after();  // Q was written with tcgen05.st; PV(i - 3) has read its P
 #ifdef PACE_TIMING
       const long long ck0 = clock64();
 #endif
-      const uint32_t k_lo = k_lo0 + (uint32_t)sq * (STAGE >> 4);
-      const uint32_t tS = tmem + (uint32_t)bq * kChunk;
+      const uint32_t k_lo = k_lo0 + (uint32_t)s * (STAGE >> 4);
+      const uint32_t tS = tmem + (uint32_t)b * kChunk;
 #pragma unroll
       for (int kk = 0; kk < D / 16; ++kk)
-        umma_bf16_ts(tS, tQ + kk * 8, pack64(k_lo + (kk >> 2) * (HALF_B >> 4) + (kk & 3) * 2, DESC_HI), IDESC_QK,
+        umma_bf16_ts(tS, tQ + kk * 8, pack64(k_lo + (kk >> 2) * (HALF_B >> 4) + (kk & 3) * 2, kDescHi), IDESC_QK,
                      kk ? 1u : 0u);
-      umma_commit(&c.s_full[bq]);
+      umma_commit(&c.s_full[b]);
 #ifdef PACE_TIMING
       PACE_UCLK(c, 1, i, clock64() - ck0);
 #endif
       PACE_UTRACE(c, 8, i);
-      if (++sq == c.n_stages) {
-        sq = 0;
-        phq ^= 1;
+      if (++s == c.n_stages) {
+        s = 0;
+        ph ^= 1;
       }
-      if (++bq == 3) bq = 0;
-      return true;
-    };
-    while (i0 < c.n_my && ok) {
-      ok = wait1(&c.full_bar[sq], phq) && wait1(c.q_ready, part & 1);
-      if (!ok) break;
-      ++part;
-      const int n = c.metas[sq].pad;  // chunks of this part
-      if (n < 1) {
-        *c.abort = 1;
-        break;
+      if (++b == 3) {
+        b = 0;
+        phb ^= 1;
       }
-      tc_fence_after();  // the Q tile was written with tcgen05.st by the softmax threads
-      ok = next_qk(i0) && (n < 2 || next_qk(i0 + 1)) && (n < 3 || next_qk(i0 + 2));
-      if (!ok) break;
-      for (int j = 0; j < n; ++j) {
-        const int w = (i0 + j) & 1;
-#ifdef PACE_TIMING
-        const long long cw0 = clock64();
-#endif
-        ok = wait1(&c.p_full[bp], php);
-        if (!ok) break;
-#ifdef PACE_TIMING
-        const long long cw1 = clock64();
-#endif
-        tc_fence_after();  // P was written with tcgen05.st
-#ifdef PACE_TIMING
-        PACE_UCLK(c, 3, i0 + j, cw1 - cw0);
-        PACE_UCLK(c, 11, i0 + j, clock64() - cw1);
-        PACE_UTRACE(c, 9, i0 + j);
-        const long long ck0 = clock64();
-#endif
-        const uint32_t v_lo = v_lo0 + (uint32_t)sp * (STAGE >> 4);
-        const uint32_t tO = tmem + kTmemO + (uint32_t)w * 128, tP = tmem + (uint32_t)bp * kChunk;
-        umma_bf16_ts(tO, tP, pack64(v_lo, DESC_HI), IDESC_PV, j < 2 ? 0u : 1u);
-#pragma unroll
-        for (int k = 1; k < 4; ++k)  // 16 keys per instruction
-          umma_bf16_ts(tO, tP + k * 8, pack64(v_lo + k * (2048 >> 4), DESC_HI), IDESC_PV, 1u);
-        umma_commit(&c.empty_bar[sp]);  // K and V of this stage have been consumed
-        umma_commit(&c.o_full[w]);
-#ifdef PACE_TIMING
-        PACE_UCLK(c, 2, i0 + j, clock64() - ck0);
-#endif
-        PACE_UTRACE(c, 10, i0 + j);
-        if (++sp == c.n_stages) sp = 0;
-        if (++bp == 3) {
-          bp = 0;
-          php ^= 1;
-        }
-        if (j + 3 < n) {
-          ok = next_qk(i0 + j + 3);
-          if (!ok) break;
-        }
-      }
-      i0 += n;
     }
     // nothing may still be writing tensor memory when it is handed back
-    umma_commit(c.drain);
-    for (int k = 0; k < (1 << 20) && !mbar_try_wait(c.drain, 0); ++k) __nanosleep(64);
+    umma_commit(&c.drain[0]);
+    for (int k = 0; k < (1 << 20) && !mbar_try_wait(&c.drain[0], 0); ++k) __nanosleep(64);
+  }
+  __syncwarp();
+}
+
+template <int D>
+__device__ __forceinline__ void umma_issue_pv(const UmmaCtx& c, uint32_t tmem, int lane) {
+  constexpr int KVB = kChunk * D * 2, HALF_B = kChunk * 128, STAGE = 2 * KVB;
+  constexpr uint32_t IDESC_PV = umma_idesc(D, true);
+  const uint32_t v_lo0 = ((smem_u32(c.ring) + KVB) >> 4) | ((uint32_t)(HALF_B >> 4) << 16);  // MN-major: LBO = next 64 columns
+  if (lane == 0) {
+    int s = 0, ph = 0, b = 0, phb = 0;
+    int left = 0, j = 0;  // chunks left in / done of the current unit part
+    for (int i = 0; i < c.n_my; ++i) {
+      if (left == 0) {  // first chunk of a unit part: how many chunks it has
+        if (!issuer_wait(c, &c.full_bar[s], ph)) break;
+        left = c.metas[s].pad;
+        j = 0;
+        if (left < 1) {
+          *c.abort = 1;
+          break;
+        }
+      }
+      --left;
+#ifdef PACE_TIMING
+      const long long cw0 = clock64();
+#endif
+      if (!issuer_wait(c, &c.p_full[b], phb)) break;
+      tc_fence_after();  // P was written with tcgen05.st
+#ifdef PACE_TIMING
+      PACE_UCLK(c, 3, i, clock64() - cw0);
+      PACE_UTRACE(c, 9, i);
+      const long long ck0 = clock64();
+#endif
+      const int w = i & 1;
+      const uint32_t v_lo = v_lo0 + (uint32_t)s * (STAGE >> 4);
+      const uint32_t tO = tmem + kTmemO + (uint32_t)w * 128, tP = tmem + (uint32_t)b * kChunk;
+      umma_bf16_ts(tO, tP, pack64(v_lo, kDescHi), IDESC_PV, j < 2 ? 0u : 1u);
+#pragma unroll
+      for (int k = 1; k < 4; ++k)  // 16 keys per instruction
+        umma_bf16_ts(tO, tP + k * 8, pack64(v_lo + k * (2048 >> 4), kDescHi), IDESC_PV, 1u);
+      umma_commit(&c.p_free[b]);     // the score buffer may take QK(i + 3)
+      umma_commit(&c.empty_bar[s]);  // K and V of this stage have been consumed
+      umma_commit(&c.o_full[w]);
+#ifdef PACE_TIMING
+      PACE_UCLK(c, 2, i, clock64() - ck0);
+#endif
+      PACE_UTRACE(c, 10, i);
+      ++j;
+      if (++s == c.n_stages) {
+        s = 0;
+        ph ^= 1;
+      }
+      if (++b == 3) {
+        b = 0;
+        phb ^= 1;
+      }
+    }
+    umma_commit(&c.drain[1]);
+    for (int k = 0; k < (1 << 20) && !mbar_try_wait(&c.drain[1], 0); ++k) __nanosleep(64);
   }
   __syncwarp();
 }
@@ -563,32 +579,33 @@ __device__ __forceinline__ void umma_softmax(const MmaParams& p, const UmmaCtx& 
   }
 }
 
-// Entry of warps 0..7 and 9 of a CTA that has work: warp 9 owns the tensor memory and issues the
-// MMAs, warps 0..7 are the two softmax groups.  Every wait inside is bounded and every path ends at
+// Entry of warps 0..7, 9 and 10 of a CTA that has work: warp 9 owns the tensor memory and issues
+// the QK MMAs, warp 10 the PV MMAs, warps 0..7 are the two softmax groups.  Every wait inside is bounded and every path ends at
 // the barrier in front of the deallocation: a CTA never exits holding tensor memory.
 template <int D>
 __device__ __forceinline__ void umma_consumer(const MmaParams& p, const UmmaCtx& c, int tid) {
   const int warp = tid >> 5, lane = tid & 31;
-  const bool issuer = warp == 9;
-  if (issuer) {
+  const bool owner = warp == 9;
+  if (owner) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(c.tmem_slot)),
                  "r"(kTmemCols)
                  : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
   tc_fence_before();
-  asm volatile("bar.sync 3, 288;" ::: "memory");
+  asm volatile("bar.sync 3, 320;" ::: "memory");
   tc_fence_after();
   const uint32_t tmem = *reinterpret_cast<volatile uint32_t*>(c.tmem_slot);
-  if (issuer) umma_issuer<D>(c, tmem, lane);
+  if (warp == 9) umma_issue_qk<D>(c, tmem, lane);
+  else if (warp == 10) umma_issue_pv<D>(c, tmem, lane);
   else umma_softmax<D>(p, c, tmem, tid);
   if (lane == 0 && *c.abort) raise_status(p.kv.status, PACE_DEV_WAIT_TIMEOUT);
 #ifdef PACE_TIMING
   if (tid == 0) { unsigned long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_)); c.stamps[5] = t_; }
 #endif
   tc_fence_before();
-  asm volatile("bar.sync 3, 288;" ::: "memory");
-  if (issuer) {
+  asm volatile("bar.sync 3, 320;" ::: "memory");
+  if (owner) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols) : "memory");
   }
