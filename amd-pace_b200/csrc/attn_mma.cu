@@ -127,14 +127,14 @@ __host__ __device__ inline SmemPlan plan_smem(int D, int MT, int NS, int n_stage
     return o;
   };
   s.ring = take(n_stages * 2 * kChunk * D * 2, 1024);
-  s.qbuf = take(umma ? 16 : MR * QS, 128);
+  s.qbuf = umma ? take(MR * D * 2, 1024) : take(MR * QS, 128);
   s.mg_stride = D + 8;  // floats; the pad spreads the rows of a fragment over the banks
   s.mg = take(umma ? 4 * MR * 4 : (NS > 1 ? NS * live_max * (s.mg_stride + 2) * 4 : 16), 16);
   s.n_res = live_max <= 64 ? 2 : 1;
   s.res_slot_bytes = (live_max * (D + 2) * 4 + 64 + 15) / 16 * 16;
   s.res = take(umma ? 16 : s.n_res * s.res_slot_bytes, 16);
   s.metas = take(kMaxStagesM * (int)sizeof(MetaM), 64);
-  s.bars = take((2 * kMaxStagesM + 1 + 4 + 16) * 8, 8);
+  s.bars = take((2 * kMaxStagesM + 1 + 4 + 20) * 8, 8);
   s.misc = take(8 * 4, 4);
   s.per_b = take(batch * 4 * 4, 4);
   s.prefix = take((n_items + 1) * 4, 4);
@@ -298,7 +298,7 @@ __global__ void __launch_bounds__(threads_of(UMMA), 1)
   uint64_t* q_empty = empty_bar + kMaxStagesM;
   uint64_t* res_full = q_empty + 1;   // [2]
   uint64_t* res_empty = res_full + 2; // [2]
-  uint64_t* umma_bars = res_empty + 2; // [16], tcgen05 variant only
+  uint64_t* umma_bars = res_empty + 2; // [20], tcgen05 variant only
   int* misc = reinterpret_cast<int*>(smem + sp.misc);
   int* sb_slot = reinterpret_cast<int*>(smem + sp.per_b);
   int* sb_len = sb_slot + p.batch;
@@ -336,17 +336,20 @@ __global__ void __launch_bounds__(threads_of(UMMA), 1)
     else if (k < 2 * n_stages + 3) mbar_init(&res_full[k - 2 * n_stages - 1], kWarps);
     else if (k < 2 * n_stages + 5) mbar_init(&res_empty[k - 2 * n_stages - 3], 1);
     if (UMMA && k == 31) {
-      // s_full[3], p_full[3] (one arrival per warp of the group), o_full[2], q_ready, drain[2], pub
-      // (every softmax thread), xch (one arrival per softmax warp, like q_ready), p_free[3]
-      for (int j = 0; j < 16; ++j)
+      // s_full[4], p_full[4] (one arrival per warp of the group), o_full[2], q_ready, drain[2], pub
+      // (every softmax thread), xch (one arrival per softmax warp, like q_ready), p_free[4]
+      for (int j = 0; j < 19; ++j)
         mbar_init(&umma_bars[j],
-                  (j >= 3 && j < 6) ? 4 : (j == 8 || j == 12) ? 8 : (j == 11 ? kUmmaSoftmaxThreads : 1));
+                  (j >= 4 && j < 8) ? 4 : (j == 10 || j == 14) ? 8 : (j == 13 ? kUmmaSoftmaxThreads : 1));
       misc[4] = 0;  // abort flag
     }
     fence_mbar_init();
   }
   for (int s = 0; s < n_stages; ++s) {
-    uint4* z = reinterpret_cast<uint4*>(ring + (size_t)s * STAGE + KVB);
+    // (tcgen05 variant: the ring is [K column block 0 of every stage][K column block 1 ...][V of every
+    // stage], so that the K rows of two consecutive stages are contiguous and one MMA can span both)
+    uint4* z = reinterpret_cast<uint4*>(UMMA ? ring + (size_t)n_stages * KVB + (size_t)s * KVB
+                                             : ring + (size_t)s * STAGE + KVB);
     for (int i = tid; i < KVB / 16; i += NTHR) z[i] = make_uint4(0, 0, 0, 0);
   }
   asm volatile("griddepcontrol.wait;" ::: "memory");
@@ -484,7 +487,10 @@ __global__ void __launch_bounds__(threads_of(UMMA), 1)
     const CUtensorMap* tm = is_v ? &tmV : &tmK;
     const int c3 = is_v ? p.c3_v : p.c3_k;
     const int c0 = hf * 64;
-    const uint32_t lane_off = (uint32_t)(is_v ? KVB : 0) + hf * HALF_B + (uint32_t)pi * P * 128;
+    const uint32_t lane_off =
+        UMMA ? (is_v ? (uint32_t)n_stages * KVB + hf * HALF_B : (uint32_t)hf * n_stages * HALF_B) + (uint32_t)pi * P * 128
+             : (uint32_t)(is_v ? KVB : 0) + hf * HALF_B + (uint32_t)pi * P * 128;
+    const uint32_t stage_step = UMMA ? (is_v ? KVB : HALF_B) : STAGE;  // bytes from one stage's tile to the next
     PageWindow pw;
     const int win_step = whole_pages ? (32 / p.pages_per_chunk) * p.pages_per_chunk : 32;
     const uint32_t box_bytes = (uint32_t)p.box_rows * 128u * 2u * HALVES;  // K and V boxes of one page
@@ -547,7 +553,7 @@ __global__ void __launch_bounds__(threads_of(UMMA), 1)
         const int pg = pw.get(lp + pi, lp, lane);
         if (lane == 0 && i == 0) PACE_TRACE(3, 10);
         if (copier && pi < n_pages_c) {
-          if (pg >= 0) tma_load_4d(ring + (size_t)s * STAGE + lane_off, tm, c0, row0, pg * Hkv + c2h, c3, &full_bar[s]);
+          if (pg >= 0) tma_load_4d(ring + (size_t)s * stage_step + lane_off, tm, c0, row0, pg * Hkv + c2h, c3, &full_bar[s]);
           else raise_status(p.kv.status, PACE_DEV_BAD_INDEX);  // the consumers' bounded wait on this stage gives up
         }
         if (first && !UMMA) {  // (the tcgen05 variant's softmax warps write the Q tile themselves, swizzled)
@@ -595,13 +601,14 @@ __global__ void __launch_bounds__(threads_of(UMMA), 1)
     uc.full_bar = full_bar;
     uc.empty_bar = empty_bar;
     uc.s_full = umma_bars;
-    uc.p_full = umma_bars + 3;
-    uc.o_full = umma_bars + 6;
-    uc.q_ready = umma_bars + 8;
-    uc.drain = umma_bars + 9;
-    uc.pub = umma_bars + 11;
-    uc.xch = umma_bars + 12;
-    uc.p_free = umma_bars + 13;
+    uc.p_full = umma_bars + 4;
+    uc.o_full = umma_bars + 8;
+    uc.q_ready = umma_bars + 10;
+    uc.drain = umma_bars + 11;
+    uc.pub = umma_bars + 13;
+    uc.xch = umma_bars + 14;
+    uc.p_free = umma_bars + 15;
+    uc.qsw = qbuf;
     uc.xch_m = mg_o;
     uc.xch_l = mg_o + 2 * kUmmaRows;
     uc.tmem_slot = reinterpret_cast<uint32_t*>(misc + 5);

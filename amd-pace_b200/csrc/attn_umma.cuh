@@ -7,13 +7,12 @@
 // The chunks of a CTA's range are dealt alternately to two softmax warpgroups (A: even, B: odd).
 // Each group has its own running (max, sum) and O accumulator, so the two never wait for one another
 // while a unit part streams; the two accumulators are merged when the part ends.  Tensor memory:
-//     columns [0, 64) [64, 128) [128, 192)    three score buffers, 128 x 64 fp32; chunk i uses i % 3
-//     columns [192, 320) / [320, 448)         O_A / O_B, 128 x D fp32
-//     columns [448, 448 + D / 2)              the Q tile, 128 x D bf16 (two per column)
+//     columns [0, 256)               four score buffers, 128 x 64 fp32; chunk i uses buffer i % 4
+//     columns [256, 384) / [384, 512) O_A / O_B, 128 x D fp32
 // A softmax thread owns one query row (TMEM lane == row): tcgen05.ld the row of S, online softmax in
-// registers, P written over the first 32 columns of the same score buffer as packed bf16 pairs.  Both
-// MMAs take their A operand (Q, P) from tensor memory, so shared memory carries only the K and V
-// stream (an MMA with both operands in shared memory is bound by its bandwidth).  O is rescaled in TMEM
+// registers, P written over the first 32 columns of the same score buffer as packed bf16 pairs; the
+// second MMA takes it from there as its A operand.  Q sits in shared memory (K-major, 128-byte
+// swizzle) next to the K/V ring.  O is rescaled in TMEM
 // only when a row's running maximum grows by more than 2^8 (the result is exact either way:
 // numerator and denominator share whatever maximum was used).
 //
@@ -26,8 +25,8 @@ namespace {
 constexpr int kUmmaRows = 128;          // query rows per tile (UMMA M)
 constexpr int kUmmaSoftmaxThreads = 256;  // two warpgroups
 constexpr int kTmemCols = 512;          // the whole tensor memory of the SM:
-constexpr uint32_t kTmemO = 192;        //   [0, 192) three score buffers, [192, 448) O of group A and B,
-constexpr uint32_t kTmemQ = 448;        //   [448, 512) the Q tile
+constexpr uint32_t kTmemO = 256;        //   [0, 256) four score buffers, [256, 512) O of group A and B
+constexpr int kScoreBufs = 4;
 constexpr float kLazyRescale = 8.0f;    // log2 units
 #ifndef PACE_SOFTMAX_BACKOFF_NS
 #define PACE_SOFTMAX_BACKOFF_NS 100
@@ -37,13 +36,14 @@ constexpr unsigned kSoftmaxBackoffNs = PACE_SOFTMAX_BACKOFF_NS;  // a waiting so
 struct UmmaCtx {
   unsigned char* ring;    // [n_stages][K | V] as the TMA boxes land
   const MetaM* metas;
+  unsigned char* qsw;     // Q tile, K-major 128-byte-swizzled: [D/64][128 rows][128 B]
   uint64_t* full_bar;
   uint64_t* empty_bar;
-  uint64_t* s_full;       // [3] per score buffer: QK^T of a chunk has landed in TMEM
-  uint64_t* p_full;       // [3] per score buffer: P is in place (and O has been rescaled); one arrival per warp of the group
+  uint64_t* s_full;       // [4] per score buffer: QK^T of a chunk has landed in TMEM
+  uint64_t* p_full;       // [4] per score buffer: P is in place (and O has been rescaled); one arrival per warp of the group
   uint64_t* o_full;       // [2] per group: PV of a chunk has been accumulated
   uint64_t* q_ready;      // the Q tile of a unit part is in shared memory (one arrival per softmax warp)
-  uint64_t* p_free;       // [3] per score buffer: the PV that read P from it has completed
+  uint64_t* p_free;       // [4] per score buffer: the PV that read P from it has completed
   uint64_t* drain;        // [2] every MMA an issuer warp issued has completed
   uint64_t* pub;          // meeting point of the 256 softmax threads while a cut unit is published
   uint64_t* xch;          // the two groups have posted their (max, sum) of a part (one arrival per warp)
@@ -134,6 +134,14 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32
       "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
       : "memory");
 }
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr));
+}
 __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
   asm volatile(
       "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
@@ -164,12 +172,12 @@ __device__ __forceinline__ bool umma_wait(uint64_t* bar, uint32_t parity, volati
 
 // ---- the two MMA issuers: one lane of warp 9 issues every QK, one lane of warp 10 every PV ----
 // Chunk i of this CTA's range (counted over the whole range, not per unit part) uses score buffer
-// i % 3 and belongs to softmax group i & 1.  One issuing thread's dependent instruction stream
+// i % 4 and belongs to softmax group i & 1.  One issuing thread's dependent instruction stream
 // (barrier probes, descriptor arithmetic, a dozen tcgen05.mma per chunk) was what paced the whole
 // pipeline, hence two of them:
-//   QK issuer:  wait K/V of chunk i, wait until PV(i - 3) has left score buffer i % 3, issue QK(i)
+//   QK issuer:  wait K/V of chunk i, wait until PV(i - 4) has left score buffer i % 4, issue QK(i)
 //   PV issuer:  wait P(i), issue PV(i), release the ring stage, the group's O and the score buffer
-// so scores are computed up to three chunks ahead of the softmax warps.  Only one lane runs each
+// so scores are computed up to four chunks ahead of the softmax warps.  Only one lane runs each
 // loop: votes or shuffles that keep 32 lanes in agreement would only add latency.
 constexpr uint32_t kDescHi = (1024u >> 4) | (1u << 14) | (2u << 29);  // SBO 1024 B, version 1, 128-byte swizzle
 
@@ -184,16 +192,22 @@ __device__ __forceinline__ bool issuer_wait(const UmmaCtx& c, uint64_t* bar, uin
 
 template <int D>
 __device__ __forceinline__ void umma_issue_qk(const UmmaCtx& c, uint32_t tmem, int lane) {
-  constexpr int KVB = kChunk * D * 2, HALF_B = kChunk * 128, STAGE = 2 * KVB;
-  constexpr uint32_t IDESC_QK = umma_idesc(kChunk, false);
+  constexpr int HALF_B = kChunk * 128;
+  constexpr uint32_t IDESC_QK1 = umma_idesc(kChunk, false), IDESC_QK2 = umma_idesc(2 * kChunk, false);
+  constexpr int QHALF = kUmmaRows * 128;
+  // Ring layout: [K column block 0 of every stage][K column block 1 ...][V of every stage].  The K rows
+  // of stages s and s + 1 are contiguous, so one set of MMAs with N = 128 computes the scores of two
+  // chunks into two adjacent score buffers whenever neither the ring nor the buffers wrap in between
+  // (half the instructions per key: the issue rate of this thread is what bounds the kernel).
   // Descriptors differ from one instruction to the next only in the start-address field (units of
   // 16 bytes): everything else is folded into constants.
   const uint32_t k_lo0 = (smem_u32(c.ring) >> 4) | (1u << 16);  // K-major: LBO unused (1)
-  const uint32_t tQ = tmem + kTmemQ;
+  const uint32_t k_half = (uint32_t)c.n_stages * (HALF_B >> 4);  // from one 64-column block of K to the next
+  const uint32_t q_lo = (smem_u32(c.qsw) >> 4) | (1u << 16);
   if (lane == 0) {
     int s = 0, ph = 0, b = 0, phb = 1;  // ring stage / its phase, score buffer / phase of its previous use
     int part = 0, left = 0;             // chunks left in the current unit part
-    for (int i = 0; i < c.n_my; ++i) {
+    for (int i = 0; i < c.n_my;) {
       if (!issuer_wait(c, &c.full_bar[s], ph)) break;
       if (left == 0) {  // first chunk of a unit part: its Q tile
         left = c.metas[s].pad;
@@ -203,28 +217,37 @@ __device__ __forceinline__ void umma_issue_qk(const UmmaCtx& c, uint32_t tmem, i
         }
         ++part;
       }
-      --left;
-      if (i >= 3 && !issuer_wait(c, &c.p_free[b], phb)) break;
-      tc_fence_after();  // Q was written with tcgen05.st; PV(i - 3) has read its P
+      const bool two = left >= 2 && s + 1 < c.n_stages && b + 1 < kScoreBufs;
+      if (two && !issuer_wait(c, &c.full_bar[s + 1], ph)) break;
+      if (i >= kScoreBufs && !issuer_wait(c, &c.p_free[b], phb)) break;
+      if (two && i + 1 >= kScoreBufs && !issuer_wait(c, &c.p_free[b + 1], phb)) break;
+      tc_fence_after();  // the PVs that read P from these buffers are done
 #ifdef PACE_TIMING
       const long long ck0 = clock64();
 #endif
-      const uint32_t k_lo = k_lo0 + (uint32_t)s * (STAGE >> 4);
+      const uint32_t k_lo = k_lo0 + (uint32_t)s * (HALF_B >> 4);
       const uint32_t tS = tmem + (uint32_t)b * kChunk;
+      const uint32_t idesc = two ? IDESC_QK2 : IDESC_QK1;
 #pragma unroll
       for (int kk = 0; kk < D / 16; ++kk)
-        umma_bf16_ts(tS, tQ + kk * 8, pack64(k_lo + (kk >> 2) * (HALF_B >> 4) + (kk & 3) * 2, kDescHi), IDESC_QK,
-                     kk ? 1u : 0u);
+        umma_bf16(tS, pack64(q_lo + (kk >> 2) * (QHALF >> 4) + (kk & 3) * 2, kDescHi),
+                  pack64(k_lo + (kk >> 2) * k_half + (kk & 3) * 2, kDescHi), idesc, kk ? 1u : 0u);
       umma_commit(&c.s_full[b]);
+      if (two) umma_commit(&c.s_full[b + 1]);
 #ifdef PACE_TIMING
       PACE_UCLK(c, 1, i, clock64() - ck0);
 #endif
       PACE_UTRACE(c, 8, i);
-      if (++s == c.n_stages) {
+      const int n = two ? 2 : 1;
+      i += n;
+      left -= n;
+      s += n;
+      if (s >= c.n_stages) {
         s = 0;
         ph ^= 1;
       }
-      if (++b == 3) {
+      b += n;
+      if (b >= kScoreBufs) {
         b = 0;
         phb ^= 1;
       }
@@ -238,9 +261,10 @@ __device__ __forceinline__ void umma_issue_qk(const UmmaCtx& c, uint32_t tmem, i
 
 template <int D>
 __device__ __forceinline__ void umma_issue_pv(const UmmaCtx& c, uint32_t tmem, int lane) {
-  constexpr int KVB = kChunk * D * 2, HALF_B = kChunk * 128, STAGE = 2 * KVB;
+  constexpr int KVB = kChunk * D * 2, HALF_B = kChunk * 128;
   constexpr uint32_t IDESC_PV = umma_idesc(D, true);
-  const uint32_t v_lo0 = ((smem_u32(c.ring) + KVB) >> 4) | ((uint32_t)(HALF_B >> 4) << 16);  // MN-major: LBO = next 64 columns
+  // V of stage s sits behind the K blocks of all stages; MN-major: LBO = next 64 columns
+  const uint32_t v_lo0 = ((smem_u32(c.ring) + (uint32_t)c.n_stages * KVB) >> 4) | ((uint32_t)(HALF_B >> 4) << 16);
   if (lane == 0) {
     int s = 0, ph = 0, b = 0, phb = 0;
     int left = 0, j = 0;  // chunks left in / done of the current unit part
@@ -266,13 +290,13 @@ __device__ __forceinline__ void umma_issue_pv(const UmmaCtx& c, uint32_t tmem, i
       const long long ck0 = clock64();
 #endif
       const int w = i & 1;
-      const uint32_t v_lo = v_lo0 + (uint32_t)s * (STAGE >> 4);
+      const uint32_t v_lo = v_lo0 + (uint32_t)s * (KVB >> 4);
       const uint32_t tO = tmem + kTmemO + (uint32_t)w * 128, tP = tmem + (uint32_t)b * kChunk;
       umma_bf16_ts(tO, tP, pack64(v_lo, kDescHi), IDESC_PV, j < 2 ? 0u : 1u);
 #pragma unroll
       for (int k = 1; k < 4; ++k)  // 16 keys per instruction
         umma_bf16_ts(tO, tP + k * 8, pack64(v_lo + k * (2048 >> 4), kDescHi), IDESC_PV, 1u);
-      umma_commit(&c.p_free[b]);     // the score buffer may take QK(i + 3)
+      umma_commit(&c.p_free[b]);     // the score buffer may take QK(i + 4)
       umma_commit(&c.empty_bar[s]);  // K and V of this stage have been consumed
       umma_commit(&c.o_full[w]);
 #ifdef PACE_TIMING
@@ -284,7 +308,7 @@ __device__ __forceinline__ void umma_issue_pv(const UmmaCtx& c, uint32_t tmem, i
         s = 0;
         ph ^= 1;
       }
-      if (++b == 3) {
+      if (++b == kScoreBufs) {
         b = 0;
         phb ^= 1;
       }
@@ -357,16 +381,17 @@ __device__ __forceinline__ void umma_softmax(const MmaParams& p, const UmmaCtx& 
   };
 
   for (int i0 = 0; i0 < c.n_my;) {
-    // ---- new unit part: its record, this thread's share of the Q tile (A operand in tensor memory) ----
+    // ---- new unit part: its record, this thread's share of the Q tile ----
     if (!umma_wait(&c.full_bar[i0 % c.n_stages], (i0 / c.n_stages) & 1, c.abort)) return;
     ResMeta fin;
-    int n_part, kvs, lim;
+    int n_part, kvs, lim, tok0_part;
     bool live;
     __nv_bfloat16* out_row;
     {
       const MetaM* meta = &c.metas[i0 % c.n_stages];
       const int R = meta->R, r_lo = meta->r_lo, kv_len = meta->kv_len, S = meta->S;
       kvs = meta->kvs;
+      tok0_part = meta->tok0;
       n_part = meta->pad;
       fin.b = meta->b;
       fin.h = meta->h;
@@ -384,22 +409,16 @@ __device__ __forceinline__ void umma_softmax(const MmaParams& p, const UmmaCtx& 
       const uint4* src = reinterpret_cast<const uint4*>(p.q + (size_t)fin.b * p.q_sb + (size_t)(fin.h * G + g) * p.q_sh +
                                                         (size_t)sq * p.q_ss);
       out_row = p.out + (size_t)fin.b * p.o_sb + (size_t)(fin.h * G + g) * p.o_sh + (size_t)sq * p.o_ss;
-      // 64 head-dim elements (32 columns of bf16 pairs) per thread: group A the first 64, group B the
-      // next 64 of a 128-wide head; a 64-wide head is group A's alone
-      if (D == 128 || wg == 0) {
-        uint32_t qv[32];
+      // each group writes half of the row's 16-byte pieces, at their swizzled places
+      unsigned char* qrow = c.qsw + row * 128;
 #pragma unroll
-        for (int k = 0; k < 8; ++k) {
-          const uint4 v = live ? __ldg(src + (D == 128 ? wg * 8 : 0) + k) : make_uint4(0, 0, 0, 0);
-          qv[4 * k] = v.x;
-          qv[4 * k + 1] = v.y;
-          qv[4 * k + 2] = v.z;
-          qv[4 * k + 3] = v.w;
-        }
-        tmem_st32(t_lane + kTmemQ + (D == 128 ? wg * 32 : 0), qv);
-        tmem_wait_st();
+      for (int k = 0; k < D / 16; ++k) {
+        const int cc = wg * (D / 16) + k;
+        const uint4 v = live ? __ldg(src + cc) : make_uint4(0, 0, 0, 0);
+        *reinterpret_cast<uint4*>(qrow + (cc >> 3) * (MR * 128) + (((cc & 7) ^ (row & 7)) << 4)) = v;
       }
-      tc_fence_before();  // (this thread's reads of O for the previous part are done as well)
+      fence_proxy_async();  // generic-proxy writes before the tensor core's async-proxy reads
+      tc_fence_before();    // (this thread's reads of O for the previous part are done as well)
       __syncwarp();
       if (lane == 0) mbar_arrive(c.q_ready);
     }
@@ -408,40 +427,44 @@ __device__ __forceinline__ void umma_softmax(const MmaParams& p, const UmmaCtx& 
     float m_used = -INFINITY, l = 0.f;
 
     const int j_first = (i0 ^ wg) & 1;  // this group takes the chunks whose index in the CTA's range has its parity
+    // With whole pages per chunk every chunk of a part starts chunk_tokens after the one before and
+    // the row's own limit already bounds what it holds: nothing of the chunk's record is needed, and
+    // neither is a wait for its K/V to land.
+    const bool uniform_chunks = p.pages_per_chunk > 0;
     for (int j = j_first; j < n_part; j += 2) {
-      const int i = i0 + j, s = i % c.n_stages, b = i % 3;
+      const int i = i0 + j, b = i & (kScoreBufs - 1);
       const uint32_t tS = t_lane + (uint32_t)b * kChunk;
-      if (!umma_wait(&c.full_bar[s], (i / c.n_stages) & 1, c.abort)) return;
-      const int rows = c.metas[s].rows, tok0 = c.metas[s].tok0;
+      int rows = p.chunk_tokens, tok0 = tok0_part + j * p.chunk_tokens;
+      if (!uniform_chunks) {
+        const int s = i % c.n_stages;
+        if (!umma_wait(&c.full_bar[s], (i / c.n_stages) & 1, c.abort)) return;
+        rows = c.metas[s].rows;
+        tok0 = c.metas[s].tok0;
+      }
       if (tid == 0) PACE_UTRACE(c, 4, i);
-      if (!umma_wait(&c.s_full[b], (i / 3) & 1, c.abort)) return;
+      if (!umma_wait(&c.s_full[b], (i / kScoreBufs) & 1, c.abort)) return;
       tc_fence_after();
       if (tid == 0) PACE_UTRACE(c, 5, i);
+#ifdef PACE_UMMA_NO_SOFTMAX
+      if (false) {
+#else
       if (warp_live) {
-        // Two passes over the scores, 32 columns in registers at a time (tensor memory is cheap to
-        // read twice; 64 scores plus 32 packed results per thread is what spills): the first pass
-        // finds the row maximum, the second turns each half into P and writes it over columns the
-        // pass has already consumed (S columns [0, 32) -> P columns [0, 16), [32, 64) -> [16, 32)).
+#endif
+        // ---- the row's 64 scores: TMEM -> registers ----
+        uint32_t sr[2][32];
+        tmem_ld32(tS, sr[0]);
+        tmem_ld32(tS + 32, sr[1]);
+        tmem_wait_ld();
         const int lo = max(0, kvs - tok0), hi = min(rows, lim - tok0);  // visible keys of the chunk: [lo, hi)
-        const bool all_visible = __all_sync(0xffffffffu, lo <= 0 && hi >= kChunk);
-        float mx;
-        {
-          float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+        if (!__all_sync(0xffffffffu, lo <= 0 && hi >= kChunk)) {
 #pragma unroll
-          for (int hf = 0; hf < 2; ++hf) {
-            uint32_t sr[32];
-            tmem_ld32(tS + hf * 32, sr);
-            tmem_wait_ld();
-            if (!all_visible) {
-#pragma unroll
-              for (int k = 0; k < 32; ++k)
-                if (hf * 32 + k < lo || hf * 32 + k >= hi) sr[k] = 0xff800000u;  // -inf
-            }
-#pragma unroll
-            for (int k = 0; k < 32; ++k) mx4[k & 3] = fmaxf(mx4[k & 3], __uint_as_float(sr[k]));
-          }
-          mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale;  // scale > 0
+          for (int k = 0; k < 64; ++k)
+            if (k < lo || k >= hi) sr[k >> 5][k & 31] = 0xff800000u;  // -inf
         }
+        float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+        for (int k = 0; k < 64; ++k) mx4[k & 3] = fmaxf(mx4[k & 3], __uint_as_float(sr[k >> 5][k & 31]));
+        const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale;  // scale > 0
         // ---- running maximum; O is rescaled only when some row of the warp moved by more than 2^8 ----
         const bool grow = mx > m_used + kLazyRescale;
         if (__any_sync(0xffffffffu, grow)) {
@@ -451,37 +474,29 @@ __device__ __forceinline__ void umma_softmax(const MmaParams& p, const UmmaCtx& 
             if (!umma_wait(&c.o_full[wg], (cnt - 1) & 1, c.abort)) return;
             tc_fence_after();
 #pragma unroll
-            for (int d0 = 0; d0 < D; d0 += 32) {
-              uint32_t ov[32];
-              tmem_ld32(tO + d0, ov);
+            for (int d0 = 0; d0 < D; d0 += 16) {
+              uint32_t ov[16];
+              tmem_ld16(tO + d0, ov);
               tmem_wait_ld();
 #pragma unroll
-              for (int k = 0; k < 32; ++k) ov[k] = __float_as_uint(__uint_as_float(ov[k]) * alpha);
-              tmem_st32(tO + d0, ov);
+              for (int k = 0; k < 16; ++k) ov[k] = __float_as_uint(__uint_as_float(ov[k]) * alpha);
+              tmem_st16(tO + d0, ov);
             }
             tmem_wait_st();
           }
           l *= alpha;
           m_used = m_new;
         }
-        // ---- P = 2^(s * scale - m), row sum, bf16 pairs ----
+        // ---- P = 2^(s * scale - m), row sum, bf16 pairs written over the scores ----
         const float ne = (m_used == -INFINITY) ? 0.f : -m_used;
         float l4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
         for (int hf = 0; hf < 2; ++hf) {
-          uint32_t sr[32];
-          tmem_ld32(tS + hf * 32, sr);
-          tmem_wait_ld();
-          if (!all_visible) {
-#pragma unroll
-            for (int k = 0; k < 32; ++k)
-              if (hf * 32 + k < lo || hf * 32 + k >= hi) sr[k] = 0xff800000u;
-          }
           uint32_t pk[16];
 #pragma unroll
           for (int k = 0; k < 16; ++k) {
-            const float p0 = fast_exp2(fmaf(__uint_as_float(sr[2 * k]), scale, ne));
-            const float p1 = fast_exp2(fmaf(__uint_as_float(sr[2 * k + 1]), scale, ne));
+            const float p0 = fast_exp2(fmaf(__uint_as_float(sr[hf][2 * k]), scale, ne));
+            const float p1 = fast_exp2(fmaf(__uint_as_float(sr[hf][2 * k + 1]), scale, ne));
             l4[k & 3] += p0 + p1;
             pk[k] = f2_to_bf2(p0, p1);
           }
