@@ -1049,12 +1049,13 @@ bool pdl_enabled() {
 }
 
 // Fewest query rows (tokens x grouped heads) for which a tile goes to the tcgen05 variant; 0 = never.
-// Below 65 rows half of a 128-row tile or more is padding and the mma.sync kernel's smaller tiles win
-// (measured on PARD verify, 36 rows).  PACE_UMMA_MIN_ROWS overrides it (A/B measurements).
+// At 33 rows and more (PARD verify: 9 tokens x 4 grouped heads = 36) a 128-row tile, three quarters of
+// it padding, already beats the mma.sync kernel's 64-row tiles: the MMAs cost the softmax warps
+// nothing.  PACE_UMMA_MIN_ROWS overrides the threshold (A/B measurements).
 int umma_min_rows() {
   static const int v = [] {
     const char* e = getenv("PACE_UMMA_MIN_ROWS");
-    return e ? atoi(e) : 65;
+    return e ? atoi(e) : 33;
   }();
   return v;
 }
