@@ -192,6 +192,30 @@ __global__ void reserve_kernel(pace_kv_pool_t p, int layer, const int32_t* __res
   }
 }
 
+// The last block of an append grid to finish advances the per-layer lengths (a ticket counter in
+// the pool tells which block that is, and is left at zero for the next launch).
+__device__ __forceinline__ void advance_lengths_in_last_block(const pace_kv_pool_t& p, int layer,
+                                                              const int32_t* __restrict__ seq_ids, int batch, int n_new,
+                                                              const int32_t* __restrict__ n_per) {
+  __shared__ int is_last;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    const int ticket = atomicAdd(&p.counters[kCounterTicket], 1);
+    is_last = (ticket == (int)gridDim.x - 1);
+  }
+  __syncthreads();
+  if (is_last) {
+    for (int b = threadIdx.x; b < batch; b += blockDim.x) {
+      const int slot = seq_ids[b];
+      if (slot < 0 || slot >= p.max_seqs) continue;
+      const int n = n_per ? min(n_per[b], n_new) : n_new;
+      if (n > 0) p.seq_len[(size_t)layer * p.max_seqs + slot] += n;
+    }
+    if (threadIdx.x == 0) p.counters[kCounterTicket] = 0;
+  }
+}
+
 // One warp per (sequence, new token, kv head): lanes [0, D/8) move the K row,
 // lanes [16, 16 + D/8) the V row, 16 bytes per lane.  The last block to finish
 // advances the per-layer lengths.
@@ -238,28 +262,112 @@ __global__ void __launch_bounds__(256)
       *d = __ldg(s);
     }
   }
-  // ---- last block advances the lengths ----
-  __shared__ int is_last;
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    __threadfence();
-    const int ticket = atomicAdd(&p.counters[kCounterTicket], 1);
-    is_last = (ticket == (int)gridDim.x - 1);
-  }
-  __syncthreads();
-  if (is_last) {
-    for (int b = threadIdx.x; b < batch; b += blockDim.x) {
-      const int slot = seq_ids[b];
-      if (slot < 0 || slot >= p.max_seqs) continue;
-      const int n = n_per ? min(n_per[b], n_new) : n_new;
-      if (n > 0) p.seq_len[(size_t)layer * p.max_seqs + slot] += n;
-    }
-    if (threadIdx.x == 0) p.counters[kCounterTicket] = 0;
-  }
+  advance_lengths_in_last_block(p, layer, seq_ids, batch, n_new, n_per);
   // Launched as a programmatic dependent, the append overlaps the attention kernel in front of it.
   // It must not COMPLETE before that kernel does: the attention kernel behind the append orders
   // itself after the append only, and shares its workspace with the one in front.
   asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
+// RoPE + append: one half-warp per (sequence, new token, head) row of the projection outputs.  Query
+// rows are rotated into q_out, key rows rotated into their cache slot, value rows copied into theirs.
+// A lane handles eight (x1, x2) pairs: two 16-byte loads, eight fp32 cos and sin values.  The
+// arithmetic reproduces elementwise bf16 ops: cos and sin rounded to bf16 first, then every product
+// and every sum rounded to bf16 (pace/ops/rotary_embedding.py:398-441).
+struct RopeParams {
+  const __nv_bfloat16 *q, *k, *v;
+  __nv_bfloat16* q_out;
+  int64_t q_sb, q_st, q_sh, k_sb, k_st, k_sh, v_sb, v_st, v_sh, o_sb, o_st, o_sh, row_sb;
+  const int32_t* table_row;
+  const float *cos_t, *sin_t;
+  int table_rows, rotary_dim, gptj, n_q_heads;
+};
+
+__device__ __forceinline__ float bf16_round(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
+
+__global__ void __launch_bounds__(256)
+    append_rope_kernel(pace_kv_pool_t p, int layer, const int32_t* __restrict__ seq_ids, int batch, int n_new,
+                       const int32_t* __restrict__ n_per, RopeParams r) {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  const int g = threadIdx.x & 15;
+  const int P = p.page_tokens, D = p.head_dim, R = r.rotary_dim, Hkv = p.n_kv_heads, Hq = r.n_q_heads;
+  const int heads = Hq + 2 * Hkv;
+  const long long total = (long long)batch * n_new * heads;
+  const long long stride = (long long)gridDim.x * (blockDim.x >> 4);
+  const size_t region = (size_t)Hkv * P * D * (size_t)p.n_pages;
+  __nv_bfloat16* kbase = reinterpret_cast<__nv_bfloat16*>(p.pages) + ((size_t)layer * 2) * region;
+  __nv_bfloat16* vbase = kbase + region;
+  const int32_t* lens = p.seq_len + (size_t)layer * p.max_seqs;
+
+  for (long long w = (long long)blockIdx.x * (blockDim.x >> 4) + (threadIdx.x >> 4); w < total; w += stride) {
+    const int hh = (int)(w % heads);
+    const int t = (int)((w / heads) % n_new);
+    const int b = (int)(w / ((long long)heads * n_new));
+    const int slot = seq_ids[b];
+    if (slot < 0 || slot >= p.max_seqs) continue;  // reported by reserve
+    const int n = n_per ? min(n_per[b], n_new) : n_new;
+    if (t >= n) continue;
+    const __nv_bfloat16* src;
+    __nv_bfloat16* dst;
+    const bool is_q = hh < Hq, is_v = hh >= Hq + Hkv;
+    if (is_q) {
+      src = r.q + (size_t)b * r.q_sb + (size_t)t * r.q_st + (size_t)hh * r.q_sh;
+      dst = r.q_out + (size_t)b * r.o_sb + (size_t)t * r.o_st + (size_t)hh * r.o_sh;
+    } else {
+      const int h = is_v ? hh - Hq - Hkv : hh - Hq;
+      src = is_v ? r.v + (size_t)b * r.v_sb + (size_t)t * r.v_st + (size_t)h * r.v_sh
+                 : r.k + (size_t)b * r.k_sb + (size_t)t * r.k_st + (size_t)h * r.k_sh;
+      const int pos = lens[slot] + t;
+      const int lp = pos / P;
+      int page = -1;
+      if (lp < p.max_pages_per_seq) page = p.block_table[(size_t)slot * p.max_pages_per_seq + lp];
+      if (page < 0 || page >= p.n_pages) {
+        if (g == 0) raise_status(p.status, PACE_DEV_BAD_INDEX);
+        continue;
+      }
+      dst = (is_v ? vbase : kbase) + (((size_t)page * Hkv + h) * P + (pos - lp * P)) * (size_t)D;
+    }
+    int row = is_v ? -1 : r.table_row[(size_t)b * r.row_sb + t];
+    if (!is_v && (row < 0 || row >= r.table_rows)) {
+      if (g == 0) raise_status(p.status, PACE_DEV_BAD_INDEX);
+      row = -1;
+    }
+    const int rot = row >= 0 ? R : 0;  // elements [0, rot) are rotated, the rest copied
+    for (int blk = g; blk < rot / 16; blk += 16) {
+      const int offA = r.gptj ? 16 * blk : 8 * blk, offB = r.gptj ? 16 * blk + 8 : R / 2 + 8 * blk;
+      const uint4 a4 = __ldg(reinterpret_cast<const uint4*>(src + offA));
+      const uint4 b4 = __ldg(reinterpret_cast<const uint4*>(src + offB));
+      const float4* cp = reinterpret_cast<const float4*>(r.cos_t + (size_t)row * (R / 2) + 8 * blk);
+      const float4* sp = reinterpret_cast<const float4*>(r.sin_t + (size_t)row * (R / 2) + 8 * blk);
+      const float4 c0 = __ldg(cp), c1 = __ldg(cp + 1), s0 = __ldg(sp), s1 = __ldg(sp + 1);
+      const float cs[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+      const float sn[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+      __nv_bfloat16 xa[8], xb[8], oa[8], ob[8];
+      *reinterpret_cast<uint4*>(xa) = a4;
+      *reinterpret_cast<uint4*>(xb) = b4;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        // NeoX: pair j is (A[j], B[j]); GPT-J: pair j is elements (2j, 2j + 1) of the 16 loaded
+        const float x1 = __bfloat162float(r.gptj ? (j < 4 ? xa[2 * j] : xb[2 * j - 8]) : xa[j]);
+        const float x2 = __bfloat162float(r.gptj ? (j < 4 ? xa[2 * j + 1] : xb[2 * j - 7]) : xb[j]);
+        const float c = bf16_round(cs[j]), s = bf16_round(sn[j]);
+        const __nv_bfloat16 o1 = __float2bfloat16_rn(bf16_round(x1 * c) - bf16_round(x2 * s));
+        const __nv_bfloat16 o2 = __float2bfloat16_rn(bf16_round(x2 * c) + bf16_round(x1 * s));
+        if (r.gptj) {
+          if (j < 4) { oa[2 * j] = o1; oa[2 * j + 1] = o2; } else { ob[2 * j - 8] = o1; ob[2 * j - 7] = o2; }
+        } else {
+          oa[j] = o1;
+          ob[j] = o2;
+        }
+      }
+      *reinterpret_cast<uint4*>(dst + offA) = *reinterpret_cast<const uint4*>(oa);
+      *reinterpret_cast<uint4*>(dst + offB) = *reinterpret_cast<const uint4*>(ob);
+    }
+    for (int c = rot / 8 + g; c < D / 8; c += 16)  // pass-through elements, value rows, unrotated tokens
+      reinterpret_cast<uint4*>(dst)[c] = __ldg(reinterpret_cast<const uint4*>(src) + c);
+  }
+  advance_lengths_in_last_block(p, layer, seq_ids, batch, n_new, n_per);
+  asm volatile("griddepcontrol.wait;" ::: "memory");  // (see append_kernel)
 }
 
 __global__ void truncate_kernel(pace_kv_pool_t p, int layer_begin, int layer_end, const int32_t* __restrict__ seq_ids,
@@ -549,6 +657,56 @@ int pace_kv_append(const pace_kv_pool_t* p, int32_t layer, const int32_t* seq_id
                                    (const __nv_bfloat16*)k_new, (const __nv_bfloat16*)v_new, (int64_t)sb, (int64_t)sh,
                                    (int64_t)st));
   PACE_LAUNCH_CHECK("append_kernel");
+  return PACE_OK;
+}
+
+int pace_kv_append_rope(const pace_kv_pool_t* p, int32_t layer, const int32_t* seq_ids, int32_t batch, int32_t n_new,
+                        const int32_t* n_per, const pace_rope_args_t* a, void* stream) {
+  if (!pool_ok(p) || !seq_ids || !a || batch < 0 || batch > p->max_seqs || n_new < 0 || layer < 0 ||
+      layer >= p->n_layers)
+    return PACE_ERR_INVALID;
+  if (batch == 0 || n_new == 0) return PACE_OK;
+  if (!a->q || !a->k || !a->v || !a->q_out || !a->table_row || !a->cos_table || !a->sin_table) return PACE_ERR_INVALID;
+  if (a->n_q_heads < 1 || a->table_rows < 1 || a->rotary_dim < 16 || a->rotary_dim > p->head_dim || (a->rotary_dim & 15))
+    return PACE_ERR_INVALID;
+  // 16-byte vector moves: bases and strides must keep rows 16-byte aligned
+  const uintptr_t bases = (uintptr_t)a->q | (uintptr_t)a->k | (uintptr_t)a->v | (uintptr_t)a->q_out |
+                          (uintptr_t)a->cos_table | (uintptr_t)a->sin_table;
+  const int64_t strides = a->q_stride_b | a->q_stride_t | a->q_stride_h | a->k_stride_b | a->k_stride_t | a->k_stride_h |
+                          a->v_stride_b | a->v_stride_t | a->v_stride_h | a->o_stride_b | a->o_stride_t | a->o_stride_h;
+  if ((bases & 15) || (strides & 7)) return PACE_ERR_INVALID;
+  RopeParams r;
+  r.q = (const __nv_bfloat16*)a->q;
+  r.k = (const __nv_bfloat16*)a->k;
+  r.v = (const __nv_bfloat16*)a->v;
+  r.q_out = (__nv_bfloat16*)a->q_out;
+  r.q_sb = a->q_stride_b; r.q_st = a->q_stride_t; r.q_sh = a->q_stride_h;
+  r.k_sb = a->k_stride_b; r.k_st = a->k_stride_t; r.k_sh = a->k_stride_h;
+  r.v_sb = a->v_stride_b; r.v_st = a->v_stride_t; r.v_sh = a->v_stride_h;
+  r.o_sb = a->o_stride_b; r.o_st = a->o_stride_t; r.o_sh = a->o_stride_h;
+  r.row_sb = a->row_stride_b;
+  r.table_row = a->table_row;
+  r.cos_t = a->cos_table;
+  r.sin_t = a->sin_table;
+  r.table_rows = a->table_rows;
+  r.rotary_dim = a->rotary_dim;
+  r.gptj = a->gptj_pairs ? 1 : 0;
+  r.n_q_heads = a->n_q_heads;
+  const long long rows = (long long)batch * n_new * (a->n_q_heads + 2 * p->n_kv_heads);
+  long long blocks = (rows + 15) / 16;  // 16 half-warps per block
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)blocks);
+  cfg.blockDim = dim3(256);
+  cfg.dynamicSmemBytes = 0;
+  cfg.stream = (cudaStream_t)stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = g_pdl_append ? 1 : 0;
+  PACE_CUDA_TRY(cudaLaunchKernelEx(&cfg, append_rope_kernel, *p, (int)layer, seq_ids, (int)batch, (int)n_new, n_per, r));
+  PACE_LAUNCH_CHECK("append_rope_kernel");
   return PACE_OK;
 }
 

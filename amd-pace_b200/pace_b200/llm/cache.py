@@ -378,6 +378,87 @@ class KVCacheBase(ABC):
         return attn_mask
 
     # -- append ------------------------------------------------------------------
+    def _begin_append(self, B: int, H: int, n: int, D: int, device, n_new_per_seq):
+        """Host accounting and page reservation shared by the two append entry points.  Returns the
+        pool, the manager, the device pointer of the ragged counts (or None), the stream pointer and
+        the tensor that keeps those counts alive."""
+        mgr = self.manager
+        mgr._ensure_pool(B, H, D, device)
+        pool = self.pool
+        if (H, D) != (pool.n_kv_heads, pool.head_dim) or B != len(mgr.slots):
+            raise ValueError(f"update_cache got [B={B},H={H},D={D}], the cache holds "
+                             f"[B={len(mgr.slots)},H={pool.n_kv_heads},D={pool.head_dim}]")
+        if not self._lens:
+            self._lens = [0] * B
+        counts = [n] * B if n_new_per_seq is None else [int(x) for x in n_new_per_seq]
+        if len(counts) != B or any(c < 0 or c > n for c in counts):
+            raise ValueError("n_new_per_seq must hold B counts in [0, n]")
+        n_dev = None
+        if n_new_per_seq is not None:
+            n_dev = torch.tensor(counts, dtype=torch.int32, device=pool.device)
+        static = mgr.static_launch
+        grow = self._host_account(counts, dry_run=mgr.capturing)
+        sp = _stream_ptr(pool.device)
+        nptr = n_dev.data_ptr() if n_dev is not None else None
+        with torch.cuda.device(pool.device):
+            # after a beam gather pages may be shared: the first layer's reserve un-shares (copies on
+            # write) whatever this append is about to write into, for all layers at once.  Under a
+            # CUDA graph the launch sequence is frozen, so the first layer always reserves.
+            need_reserve = (self.layer == 0) if static else (grow or (pool.shared_pages and self.layer == 0))
+            if need_reserve:
+                _C.check(_C.lib.pace_kv_reserve(pool.ref, self.layer, mgr.slots_dev.data_ptr(), B, n, nptr, sp),
+                         "pace_kv_reserve")
+        return pool, mgr, nptr, sp, n_dev
+
+    def update_cache_rope(self, query: torch.Tensor, key: torch.Tensor, value: torch.Tensor, table_row: torch.Tensor,
+                          rope, n_new_per_seq: Optional[Sequence[int]] = None,
+                          query_out: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, PagedKV, PagedKV]:
+        """RoPE and append in one kernel: the three calls between the projections and the attention
+        op of a decoder layer (reference pace/llm/models/llama.py:130-165: view as heads, rotate q and
+        k, ``update_cache``).  ``query`` / ``key`` / ``value`` are the projection outputs viewed as
+        ``[B, n, heads, D]`` (no transpose), ``table_row`` the int32 ``[B, n]`` rows of the rotary
+        tables (``RotaryEmbedding.table_rows(position_ids)``), ``rope`` a
+        ``pace_b200.ops.RotaryEmbedding``.  Returns the rotated queries as ``[B, Hq, n, D]`` (a view
+        of ``query_out``, by default written over ``query``) and the cache handles."""
+        if self.concat_dim is None:
+            self.concat_dim = 2
+        elif self.concat_dim != 2:
+            raise AssertionError("concat_dim should be the same for all updates")
+        if query.device.type != "cuda":
+            raise RuntimeError("pace_b200 caches take CUDA tensors (there is no CPU path)")
+        for name, x in (("query", query), ("key", key), ("value", value)):
+            if x.dtype != torch.bfloat16 or x.dim() != 4:
+                raise TypeError(f"{name} must be a bf16 [B, n, heads, D] tensor")
+            if x.stride(3) != 1 or any(s % 8 for s in x.stride()[:3]) or x.data_ptr() % 16:
+                raise ValueError(f"{name}: head_dim must be contiguous and every row 16-byte aligned")
+        B, n, Hq, D = query.shape
+        H = key.shape[2]
+        if key.shape != value.shape or key.shape[:2] != (B, n) or key.shape[3] != D:
+            raise ValueError("key and value must be [B, n, kv_heads, D] like the query")
+        out = query if query_out is None else query_out
+        if out.shape != query.shape or out.dtype != torch.bfloat16 or out.stride(3) != 1 or out.data_ptr() % 16 \
+                or any(s % 8 for s in out.stride()[:3]):
+            raise ValueError("query_out must be a bf16 [B, n, Hq, D] tensor with 16-byte aligned rows")
+        if table_row.shape != (B, n) or table_row.dtype != torch.int32 or table_row.stride(1) != 1:
+            raise ValueError("table_row must be an int32 [B, n] tensor")
+        self._ndim = 4
+        pool, mgr, nptr, sp, n_dev = self._begin_append(B, H, n, D, query.device, n_new_per_seq)
+        a = _C.RopeArgs()
+        a.q, (a.q_stride_b, a.q_stride_t, a.q_stride_h) = query.data_ptr(), query.stride()[:3]
+        a.k, (a.k_stride_b, a.k_stride_t, a.k_stride_h) = key.data_ptr(), key.stride()[:3]
+        a.v, (a.v_stride_b, a.v_stride_t, a.v_stride_h) = value.data_ptr(), value.stride()[:3]
+        a.q_out, (a.o_stride_b, a.o_stride_t, a.o_stride_h) = out.data_ptr(), out.stride()[:3]
+        a.table_row, a.row_stride_b = table_row.data_ptr(), table_row.stride(0)
+        cos, sin = rope.device_tables(pool.device)
+        a.cos_table, a.sin_table, a.table_rows = cos.data_ptr(), sin.data_ptr(), cos.shape[0]
+        a.rotary_dim, a.gptj_pairs, a.n_q_heads = rope.rotary_dim, 0 if rope.is_neox_style else 1, Hq
+        with torch.cuda.device(pool.device):
+            _C.check(_C.lib.pace_kv_append_rope(pool.ref, self.layer, mgr.slots_dev.data_ptr(), B, n, nptr,
+                                                _C.byref(a), sp), "pace_kv_append_rope")
+        if self.key is None:
+            self.key, self.value = PagedKV(self, "k"), PagedKV(self, "v")
+        return out.transpose(1, 2), self.key, self.value
+
     def update_cache(self, key_states: torch.Tensor, value_states: torch.Tensor, concat_dim: int,
                      n_new_per_seq: Optional[Sequence[int]] = None) -> Tuple[PagedKV, PagedKV]:
         """Append ``[B, H, n, D]`` new keys/values (cache.py:268-326 / 370-400)."""
@@ -399,36 +480,12 @@ class KVCacheBase(ABC):
         else:
             raise ValueError("expected [B, H, n, D] with concat_dim=2 (or [B, n, D] with concat_dim=1)")
         B, H, n, D = key_states.shape
-        mgr = self.manager
-        mgr._ensure_pool(B, H, D, key_states.device)
-        pool = self.pool
-        if (H, D) != (pool.n_kv_heads, pool.head_dim) or B != len(mgr.slots):
-            raise ValueError(f"update_cache got [B={B},H={H},D={D}], the cache holds "
-                             f"[B={len(mgr.slots)},H={pool.n_kv_heads},D={pool.head_dim}]")
         if key_states.stride(3) != 1 or value_states.stride(3) != 1 or key_states.stride() != value_states.stride():
             key_states, value_states = key_states.contiguous(), value_states.contiguous()
         if any(s % 8 for s in key_states.stride()[:3]) or key_states.data_ptr() % 16 or value_states.data_ptr() % 16:
             key_states, value_states = key_states.contiguous().clone(), value_states.contiguous().clone()
-        if not self._lens:
-            self._lens = [0] * B
-        counts = [n] * B if n_new_per_seq is None else [int(x) for x in n_new_per_seq]
-        if len(counts) != B or any(c < 0 or c > n for c in counts):
-            raise ValueError("n_new_per_seq must hold B counts in [0, n]")
-        n_dev = None
-        if n_new_per_seq is not None:
-            n_dev = torch.tensor(counts, dtype=torch.int32, device=pool.device)
-        static = mgr.static_launch
-        grow = self._host_account(counts, dry_run=mgr.capturing)
-        sp = _stream_ptr(pool.device)
-        nptr = n_dev.data_ptr() if n_dev is not None else None
+        pool, mgr, nptr, sp, n_dev = self._begin_append(B, H, n, D, key_states.device, n_new_per_seq)
         with torch.cuda.device(pool.device):
-            # after a beam gather pages may be shared: the first layer's reserve un-shares (copies on
-            # write) whatever this append is about to write into, for all layers at once.  Under a
-            # CUDA graph the launch sequence is frozen, so the first layer always reserves.
-            need_reserve = (self.layer == 0) if static else (grow or (pool.shared_pages and self.layer == 0))
-            if need_reserve:
-                _C.check(_C.lib.pace_kv_reserve(pool.ref, self.layer, mgr.slots_dev.data_ptr(), B, n, nptr, sp),
-                         "pace_kv_reserve")
             sb, sh, st, _ = key_states.stride()
             _C.check(_C.lib.pace_kv_append(pool.ref, self.layer, mgr.slots_dev.data_ptr(), B, n, nptr,
                                            key_states.data_ptr(), value_states.data_ptr(), sb, sh, st, sp),

@@ -9,11 +9,13 @@ Differences that come from the path being on the GPU:
   * no ``repeat_kv``: the cache holds the KV heads, the attention kernels are GQA-native;
   * no 4-D additive mask: causality and left padding reach the kernels as per-sequence integers
     (``kv_start`` = padded positions, the causal tail follows from the cached lengths);
-  * projections, norms, RoPE and the MLP are stock torch CUDA ops (they are not part of the path);
+  * RoPE is fused into the append kernel (``update_cache_rope``); projections, norms and the MLP
+    are stock torch CUDA ops (they are not part of the path);
   * ``forward_tokens`` takes only the NEW tokens and allows ragged counts per sequence, which
     batched speculative decoding needs; ``forward`` is the reference signature on top of it.
 """
 import math
+import os
 from typing import List, Optional, Sequence
 
 import torch
@@ -22,7 +24,7 @@ from torch import nn
 
 from pace_b200.llm.cache import KVCacheBase, KVCacheManager
 from pace_b200.llm.outputs import ModelOutput
-from pace_b200.ops import MultiHeadAttention
+from pace_b200.ops import MultiHeadAttention, RotaryEmbedding
 
 
 class _FusedLinear(nn.Module):
@@ -56,29 +58,16 @@ class LlamaMLP(nn.Module):
         return self.down_proj(self.up_proj.linear(x) * F.silu(self.gate_proj.linear(x)))
 
 
-class RotaryEmbedding(nn.Module):
-    """Default RoPE: fp32 cos/sin table indexed by position, applied NeoX-style in the activations'
-    dtype (reference pace/ops/rotary_embedding.py:60-110, 396-441)."""
+class FusedRope:
+    """What a decoder layer needs to rotate and append in one kernel: the operator (tables) and the
+    table row of every new token."""
 
-    def __init__(self, rotary_dim: int, max_position_embeddings: int, theta: float):
-        super().__init__()
-        inv_freq = 1.0 / (theta ** (torch.arange(0, rotary_dim, 2, dtype=torch.float) / rotary_dim))
-        freqs = torch.einsum("i,j -> ij", torch.arange(max_position_embeddings, dtype=torch.float), inv_freq)
-        self.register_buffer("cos_cache", freqs.cos(), persistent=False)
-        self.register_buffer("sin_cache", freqs.sin(), persistent=False)
+    def __init__(self, op: RotaryEmbedding, table_row: torch.Tensor):
+        self.op, self.table_row = op, table_row
 
-    def forward(self, x: torch.Tensor, position_ids: torch.Tensor):
-        idx = position_ids.flatten()
-        cos = self.cos_cache.index_select(0, idx).unflatten(0, position_ids.shape).to(x.dtype).unsqueeze(1)
-        sin = self.sin_cache.index_select(0, idx).unflatten(0, position_ids.shape).to(x.dtype).unsqueeze(1)
 
-        def apply(query, key):
-            def rot(t):
-                t1, t2 = torch.chunk(t, 2, dim=-1)
-                return torch.cat((t1 * cos - t2 * sin, t2 * cos + t1 * sin), dim=-1)
-            return rot(query), rot(key)
-
-        return apply
+# PACE_FUSED_ROPE=0 keeps RoPE as separate elementwise ops in front of the append (A/B checks)
+FUSED_ROPE = os.environ.get("PACE_FUSED_ROPE", "1") != "0"
 
 
 class LlamaAttention(nn.Module):
@@ -97,12 +86,16 @@ class LlamaAttention(nn.Module):
     def forward(self, hidden_states, position_embeddings, kv_cache: KVCacheBase, kv_start=None, n_new=None,
                 q_lens=None):
         bsz, q_len, _ = hidden_states.size()
-        q = self.q_proj(hidden_states).view(bsz, q_len, self.num_heads, self.head_dim).transpose(1, 2)
-        k = self.k_proj(hidden_states).view(bsz, q_len, self.num_key_value_heads, self.head_dim).transpose(1, 2)
-        v = self.v_proj(hidden_states).view(bsz, q_len, self.num_key_value_heads, self.head_dim).transpose(1, 2)
-        q, k = position_embeddings(query=q, key=k)
-        # the hot path: append, then attend over the cache (llama.py:155-165)
-        key_h, value_h = kv_cache.update_cache(k, v, concat_dim=2, n_new_per_seq=n_new)
+        q = self.q_proj(hidden_states).view(bsz, q_len, self.num_heads, self.head_dim)
+        k = self.k_proj(hidden_states).view(bsz, q_len, self.num_key_value_heads, self.head_dim)
+        v = self.v_proj(hidden_states).view(bsz, q_len, self.num_key_value_heads, self.head_dim)
+        # the hot path: rotate, append, then attend over the cache (llama.py:146-165)
+        if isinstance(position_embeddings, FusedRope):
+            q, key_h, value_h = kv_cache.update_cache_rope(q, k, v, position_embeddings.table_row,
+                                                           position_embeddings.op, n_new_per_seq=n_new)
+        else:
+            q, k = position_embeddings(query=q.transpose(1, 2), key=k.transpose(1, 2))
+            key_h, value_h = kv_cache.update_cache(k, v.transpose(1, 2), concat_dim=2, n_new_per_seq=n_new)
         out = self.attention(q, key_h, value_h, attention_mask=None, kv_start=kv_start, q_lens=q_lens)
         out = out.transpose(1, 2).reshape(bsz, q_len, -1)
         return self.o_proj(out)
@@ -127,14 +120,18 @@ class LlamaModel(nn.Module):
         super().__init__()
         self.embed_tokens = nn.Embedding(config.vocab_size, config.hidden_size, getattr(config, "pad_token_id", None))
         self.layers = nn.ModuleList([LlamaDecoderLayer(config) for _ in range(config.num_hidden_layers)])
-        self.rotary_emb = RotaryEmbedding(config.hidden_size // config.num_attention_heads,
+        self.rotary_emb = RotaryEmbedding(getattr(config, "rope_scaling", None),
+                                          config.hidden_size // config.num_attention_heads,
                                           config.max_position_embeddings, config.rope_theta)
         self.norm = RMSNorm(config.hidden_size, config.rms_norm_eps)
 
     def forward_tokens(self, new_ids: torch.Tensor, kv_cache: KVCacheManager, position_ids: torch.Tensor,
                        kv_start: Optional[torch.Tensor] = None, n_new: Optional[Sequence[int]] = None):
         hidden = self.embed_tokens(new_ids)
-        rope = self.rotary_emb(hidden, position_ids)
+        if FUSED_ROPE and hidden.dtype == torch.bfloat16:
+            rope = FusedRope(self.rotary_emb, self.rotary_emb.table_rows(position_ids))
+        else:
+            rope = self.rotary_emb(hidden, position_ids)
         q_lens = None
         if n_new is not None:
             q_lens = torch.tensor(list(n_new), dtype=torch.int32, device=new_ids.device)

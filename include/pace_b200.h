@@ -104,6 +104,42 @@ int pace_kv_append(const pace_kv_pool_t* pool, int32_t layer, const int32_t* seq
                    int32_t n_new, const int32_t* n_new_per_seq, const void* k_new, const void* v_new,
                    int64_t stride_b, int64_t stride_h, int64_t stride_t, void* stream);
 
+/* ---- RoPE + append in one pass -----------------------------------------------
+ * Reference: the step in front of the append in every decoder layer,
+ * pace/llm/models/llama.py:130-165: q/k/v are viewed as heads, RotaryEmbedding's
+ * callable rotates q and k (pace/ops/rotary_embedding.py:375-441: table rows picked
+ * by position id, cast to the activations' dtype, NeoX halves or GPT-J pairs, every
+ * product and sum rounded to that dtype), then update_cache stores k and v.
+ *
+ * pace_kv_append_rope reads the projection outputs once, writes the rotated queries
+ * to q_out (which may be q itself) and the rotated keys and the values straight into
+ * the slots [seq_len, seq_len + n) of the paged cache, then advances seq_len[layer]
+ * as pace_kv_append does (pace_kv_reserve must have run).  All tensors are bf16
+ * addressed as [batch][token][head][head_dim] through element strides (head_dim
+ * contiguous, 16-byte aligned rows): the untransposed output of a fused or split
+ * QKV projection needs no copy.  cos/sin are the operator's fp32 tables
+ * [table_rows][rotary_dim / 2]; table_row[b * row_stride_b + t] names the row of
+ * token t of sequence b (the position id, already shifted for longrope).
+ * rotary_dim <= head_dim, a multiple of 16; elements beyond it pass through.
+ * A row index outside the table raises PACE_DEV_BAD_INDEX and leaves that token
+ * unrotated. */
+typedef struct {
+  const void* q;        int64_t q_stride_b, q_stride_t, q_stride_h;
+  const void* k;        int64_t k_stride_b, k_stride_t, k_stride_h;
+  const void* v;        int64_t v_stride_b, v_stride_t, v_stride_h;
+  void* q_out;          int64_t o_stride_b, o_stride_t, o_stride_h;
+  const int32_t* table_row; /* device */
+  int64_t row_stride_b;
+  const float* cos_table;   /* device, fp32 [table_rows][rotary_dim / 2] */
+  const float* sin_table;
+  int32_t table_rows;
+  int32_t rotary_dim;
+  int32_t gptj_pairs;       /* 0: NeoX halves (d, d + rotary_dim / 2); 1: GPT-J pairs (2d, 2d + 1) */
+  int32_t n_q_heads;
+} pace_rope_args_t;
+int pace_kv_append_rope(const pace_kv_pool_t* pool, int32_t layer, const int32_t* seq_ids, int32_t batch,
+                        int32_t n_new, const int32_t* n_new_per_seq, const pace_rope_args_t* rope, void* stream);
+
 /* ---- rollback -------------------------------------------------------------
  * Reference: BMCKVCache.remove_cache (cache.py:224-240): seq_len -= n, pages kept,
  * data untouched.  Over-removal leaves the length alone and raises

@@ -173,3 +173,37 @@ def test_pard_rules():
     assert P.rollback_lengths(8, 8) == (0, 7)      # nothing rejected: target keeps the unverified draft row
     assert P.rollback_lengths(8, 1) == (8, 7)
     assert P.rollback_lengths(8, 5) == (4, 7)
+
+
+# ---------------------------------------------------------------------------------------------
+# RoPE (the step in front of the append): oracle/rope_ref.py against the reference operator's outputs
+# ---------------------------------------------------------------------------------------------
+def _rope_cases():
+    import torch
+    return torch.load(os.path.join(os.path.dirname(__file__), "golden", "rope_cases.pt"))
+
+
+def test_rope_tables_match_reference_for_every_rope_type():
+    import torch
+    from oracle import rope_ref
+    cases = _rope_cases()
+    assert set(cases) >= {"default", "linear", "dynamic", "llama3", "longrope"}
+    for name, c in cases.items():
+        cos, sin, rd, kind, window = rope_ref.build_tables(c["rope_scaling"], c["head_dim"],
+                                                           c["max_position_embeddings"], c["rope_theta"],
+                                                           c["partial_rotary_factor"], **c["kwargs"])
+        assert rd == c["rotary_dim"] and cos.shape[0] == c["cache_rows"], name
+        assert torch.equal(cos, c["cos_cache"]) and torch.equal(sin, c["sin_cache"]), name
+
+
+def test_rope_application_is_bit_exact_against_reference():
+    import torch
+    from oracle import rope_ref
+    for name, c in _rope_cases().items():
+        cos_t, sin_t, rd, kind, window = rope_ref.build_tables(c["rope_scaling"], c["head_dim"],
+                                                               c["max_position_embeddings"], c["rope_theta"],
+                                                               c["partial_rotary_factor"], **c["kwargs"])
+        for tag, a in c["applied"].items():
+            q, k = rope_ref.rotate(c["q"], c["k"], a["position_ids"], cos_t, sin_t, rd, kind, window,
+                                   neox=tag.endswith("neox"))
+            assert torch.equal(q, a["q_rot"]) and torch.equal(k, a["k_rot"]), (name, tag)
