@@ -20,7 +20,8 @@ void set_cuda_error(cudaError_t e, const char* where) {
 namespace {
 
 constexpr int kCounterFree = 0;    // number of free pages
-constexpr int kCounterTicket = 1;  // append kernel: blocks finished
+constexpr int kCounterTicket = 8;  // + layer: append kernels of that layer, blocks finished (appends to
+                                   // different layers may overlap on the GPU, each needs its own count)
 constexpr int kCounterShared = 2;  // set by a beam gather: pages may have more than one owner
 
 __host__ __device__ inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
@@ -43,7 +44,7 @@ MetaLayout meta_layout(const pace_kv_pool_t* g) {
   m.seq_pages = take(S);
   m.page_ref = take(NP);
   m.free_stack = take(NP);
-  m.counters = take(8);
+  m.counters = take(kCounterTicket + L);
   m.status = take(4);
   m.table_tmp = take(S * (MP + 4) + L * S);
   m.total = off;
@@ -91,7 +92,7 @@ __global__ void reset_kernel(pace_kv_pool_t p) {
     p.page_ref[i] = 0;
     p.free_stack[i] = p.n_pages - 1 - (int)i;  // page 0 is handed out first
   }
-  if (tid < 8) p.counters[tid] = (tid == kCounterFree) ? p.n_pages : 0;
+  for (size_t i = tid; i < (size_t)(kCounterTicket + p.n_layers); i += nth) p.counters[i] = (i == kCounterFree) ? p.n_pages : 0;
   if (tid < 4) p.status[tid] = 0;
 }
 
@@ -201,7 +202,7 @@ __device__ __forceinline__ void advance_lengths_in_last_block(const pace_kv_pool
   __syncthreads();
   if (threadIdx.x == 0) {
     __threadfence();
-    const int ticket = atomicAdd(&p.counters[kCounterTicket], 1);
+    const int ticket = atomicAdd(&p.counters[kCounterTicket + layer], 1);
     is_last = (ticket == (int)gridDim.x - 1);
   }
   __syncthreads();
@@ -212,7 +213,7 @@ __device__ __forceinline__ void advance_lengths_in_last_block(const pace_kv_pool
       const int n = n_per ? min(n_per[b], n_new) : n_new;
       if (n > 0) p.seq_len[(size_t)layer * p.max_seqs + slot] += n;
     }
-    if (threadIdx.x == 0) p.counters[kCounterTicket] = 0;
+    if (threadIdx.x == 0) p.counters[kCounterTicket + layer] = 0;
   }
 }
 
@@ -269,11 +270,12 @@ __global__ void __launch_bounds__(256)
   asm volatile("griddepcontrol.wait;" ::: "memory");
 }
 
-// RoPE + append: one half-warp per (sequence, new token, head) row of the projection outputs.  Query
-// rows are rotated into q_out, key rows rotated into their cache slot, value rows copied into theirs.
-// A lane handles eight (x1, x2) pairs: two 16-byte loads, eight fp32 cos and sin values.  The
-// arithmetic reproduces elementwise bf16 ops: cos and sin rounded to bf16 first, then every product
-// and every sum rounded to bf16 (pace/ops/rotary_embedding.py:398-441).
+// RoPE + append: eight lanes per (sequence, new token, group of kRopeHeads heads) of the projection
+// outputs.  Query rows are rotated into q_out, key rows rotated into their cache slot, value rows
+// copied into theirs.  A lane owns eight (x1, x2) pairs of every row of its group: it loads their
+// fp32 cos and sin values once per token and then, per head, two 16-byte vectors in and two out.
+// The arithmetic reproduces elementwise bf16 ops: cos and sin rounded to bf16 first, then every
+// product and every sum rounded to bf16 (pace/ops/rotary_embedding.py:398-441).
 struct RopeParams {
   const __nv_bfloat16 *q, *k, *v;
   __nv_bfloat16* q_out;
@@ -282,89 +284,148 @@ struct RopeParams {
   const float *cos_t, *sin_t;
   int table_rows, rotary_dim, gptj, n_q_heads;
 };
+constexpr int kRopeHeads = 6;  // heads per work item: 32 + 2 x 8 heads make eight items per token
 
 __device__ __forceinline__ float bf16_round(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
 
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, 3)
     append_rope_kernel(pace_kv_pool_t p, int layer, const int32_t* __restrict__ seq_ids, int batch, int n_new,
                        const int32_t* __restrict__ n_per, RopeParams r) {
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-  const int g = threadIdx.x & 15;
+  const int g = threadIdx.x & 7;
   const int P = p.page_tokens, D = p.head_dim, R = r.rotary_dim, Hkv = p.n_kv_heads, Hq = r.n_q_heads;
   const int heads = Hq + 2 * Hkv;
-  const long long total = (long long)batch * n_new * heads;
-  const long long stride = (long long)gridDim.x * (blockDim.x >> 4);
+  const int groups = (heads + kRopeHeads - 1) / kRopeHeads;
+  const long long total = (long long)batch * n_new * groups;
+  const long long stride = (long long)gridDim.x * (blockDim.x >> 3);
   const size_t region = (size_t)Hkv * P * D * (size_t)p.n_pages;
   __nv_bfloat16* kbase = reinterpret_cast<__nv_bfloat16*>(p.pages) + ((size_t)layer * 2) * region;
   __nv_bfloat16* vbase = kbase + region;
   const int32_t* lens = p.seq_len + (size_t)layer * p.max_seqs;
 
-  for (long long w = (long long)blockIdx.x * (blockDim.x >> 4) + (threadIdx.x >> 4); w < total; w += stride) {
-    const int hh = (int)(w % heads);
-    const int t = (int)((w / heads) % n_new);
-    const int b = (int)(w / ((long long)heads * n_new));
+  for (long long w = (long long)blockIdx.x * (blockDim.x >> 3) + (threadIdx.x >> 3); w < total; w += stride) {
+    const int hg = (int)(w % groups);
+    const int t = (int)((w / groups) % n_new);
+    const int b = (int)(w / ((long long)groups * n_new));
     const int slot = seq_ids[b];
     if (slot < 0 || slot >= p.max_seqs) continue;  // reported by reserve
     const int n = n_per ? min(n_per[b], n_new) : n_new;
     if (t >= n) continue;
-    const __nv_bfloat16* src;
-    __nv_bfloat16* dst;
-    const bool is_q = hh < Hq, is_v = hh >= Hq + Hkv;
-    if (is_q) {
-      src = r.q + (size_t)b * r.q_sb + (size_t)t * r.q_st + (size_t)hh * r.q_sh;
-      dst = r.q_out + (size_t)b * r.o_sb + (size_t)t * r.o_st + (size_t)hh * r.o_sh;
-    } else {
-      const int h = is_v ? hh - Hq - Hkv : hh - Hq;
-      src = is_v ? r.v + (size_t)b * r.v_sb + (size_t)t * r.v_st + (size_t)h * r.v_sh
-                 : r.k + (size_t)b * r.k_sb + (size_t)t * r.k_st + (size_t)h * r.k_sh;
-      const int pos = lens[slot] + t;
-      const int lp = pos / P;
-      int page = -1;
-      if (lp < p.max_pages_per_seq) page = p.block_table[(size_t)slot * p.max_pages_per_seq + lp];
-      if (page < 0 || page >= p.n_pages) {
-        if (g == 0) raise_status(p.status, PACE_DEV_BAD_INDEX);
-        continue;
-      }
-      dst = (is_v ? vbase : kbase) + (((size_t)page * Hkv + h) * P + (pos - lp * P)) * (size_t)D;
+    // the token's cache row (key and value heads of this group go there)
+    const int pos = lens[slot] + t;
+    const int lp = pos / P;
+    int page = -1;
+    if (lp < p.max_pages_per_seq) page = p.block_table[(size_t)slot * p.max_pages_per_seq + lp];
+    const bool page_ok = page >= 0 && page < p.n_pages;
+    int row = r.table_row[(size_t)b * r.row_sb + t];
+    if (row < 0 || row >= r.table_rows) {
+      if (g == 0 && hg == 0) raise_status(p.status, PACE_DEV_BAD_INDEX);
+      row = -1;  // the token passes through unrotated
     }
-    int row = is_v ? -1 : r.table_row[(size_t)b * r.row_sb + t];
-    if (!is_v && (row < 0 || row >= r.table_rows)) {
-      if (g == 0) raise_status(p.status, PACE_DEV_BAD_INDEX);
-      row = -1;
-    }
-    const int rot = row >= 0 ? R : 0;  // elements [0, rot) are rotated, the rest copied
-    for (int blk = g; blk < rot / 16; blk += 16) {
-      const int offA = r.gptj ? 16 * blk : 8 * blk, offB = r.gptj ? 16 * blk + 8 : R / 2 + 8 * blk;
-      const uint4 a4 = __ldg(reinterpret_cast<const uint4*>(src + offA));
-      const uint4 b4 = __ldg(reinterpret_cast<const uint4*>(src + offB));
-      const float4* cp = reinterpret_cast<const float4*>(r.cos_t + (size_t)row * (R / 2) + 8 * blk);
-      const float4* sp = reinterpret_cast<const float4*>(r.sin_t + (size_t)row * (R / 2) + 8 * blk);
+    // this lane's eight cos / sin values (rotation block g)
+    float cs[8], sn[8];
+    const bool turns = row >= 0 && g < R / 16;
+    if (turns) {
+      const float4* cp = reinterpret_cast<const float4*>(r.cos_t + (size_t)row * (R / 2) + 8 * g);
+      const float4* sp = reinterpret_cast<const float4*>(r.sin_t + (size_t)row * (R / 2) + 8 * g);
       const float4 c0 = __ldg(cp), c1 = __ldg(cp + 1), s0 = __ldg(sp), s1 = __ldg(sp + 1);
-      const float cs[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
-      const float sn[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
-      __nv_bfloat16 xa[8], xb[8], oa[8], ob[8];
-      *reinterpret_cast<uint4*>(xa) = a4;
-      *reinterpret_cast<uint4*>(xb) = b4;
+      cs[0] = c0.x; cs[1] = c0.y; cs[2] = c0.z; cs[3] = c0.w; cs[4] = c1.x; cs[5] = c1.y; cs[6] = c1.z; cs[7] = c1.w;
+      sn[0] = s0.x; sn[1] = s0.y; sn[2] = s0.z; sn[3] = s0.w; sn[4] = s1.x; sn[5] = s1.y; sn[6] = s1.z; sn[7] = s1.w;
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
-        // NeoX: pair j is (A[j], B[j]); GPT-J: pair j is elements (2j, 2j + 1) of the 16 loaded
-        const float x1 = __bfloat162float(r.gptj ? (j < 4 ? xa[2 * j] : xb[2 * j - 8]) : xa[j]);
-        const float x2 = __bfloat162float(r.gptj ? (j < 4 ? xa[2 * j + 1] : xb[2 * j - 7]) : xb[j]);
-        const float c = bf16_round(cs[j]), s = bf16_round(sn[j]);
-        const __nv_bfloat16 o1 = __float2bfloat16_rn(bf16_round(x1 * c) - bf16_round(x2 * s));
-        const __nv_bfloat16 o2 = __float2bfloat16_rn(bf16_round(x2 * c) + bf16_round(x1 * s));
-        if (r.gptj) {
-          if (j < 4) { oa[2 * j] = o1; oa[2 * j + 1] = o2; } else { ob[2 * j - 8] = o1; ob[2 * j - 7] = o2; }
+        cs[j] = bf16_round(cs[j]);
+        sn[j] = bf16_round(sn[j]);
+      }
+    }
+    const int offA = r.gptj ? 16 * g : 8 * g, offB = r.gptj ? 16 * g + 8 : R / 2 + 8 * g;
+    const int rot = row >= 0 ? R : 0;  // elements [0, rot) are rotated, the rest copied
+    const int h_end = min(heads, (hg + 1) * kRopeHeads);
+    // Heads go three at a time: all loads of a batch are issued before its first store.  (q_out may be
+    // q itself, so the compiler has to keep every load behind the stores in front of it; batching by
+    // hand is what puts several rows in flight per lane.)
+    constexpr int HB = 3;
+    for (int h0 = hg * kRopeHeads; h0 < h_end; h0 += HB) {
+      const __nv_bfloat16* src[HB];
+      __nv_bfloat16* dst[HB];
+      bool live[HB], is_v[HB];
+      uint4 va[HB], vb[HB];
+#pragma unroll
+      for (int u = 0; u < HB; ++u) {
+        const int hh = h0 + u;
+        live[u] = hh < h_end;
+        is_v[u] = hh >= Hq + Hkv;
+        src[u] = nullptr;
+        dst[u] = nullptr;
+        if (!live[u]) continue;
+        if (hh < Hq) {
+          src[u] = r.q + (size_t)b * r.q_sb + (size_t)t * r.q_st + (size_t)hh * r.q_sh;
+          dst[u] = r.q_out + (size_t)b * r.o_sb + (size_t)t * r.o_st + (size_t)hh * r.o_sh;
         } else {
-          oa[j] = o1;
-          ob[j] = o2;
+          const int h = is_v[u] ? hh - Hq - Hkv : hh - Hq;
+          src[u] = is_v[u] ? r.v + (size_t)b * r.v_sb + (size_t)t * r.v_st + (size_t)h * r.v_sh
+                           : r.k + (size_t)b * r.k_sb + (size_t)t * r.k_st + (size_t)h * r.k_sh;
+          if (!page_ok) {
+            if (g == 0) raise_status(p.status, PACE_DEV_BAD_INDEX);
+            live[u] = false;
+            continue;
+          }
+          dst[u] = (is_v[u] ? vbase : kbase) + (((size_t)page * Hkv + h) * P + (pos - lp * P)) * (size_t)D;
+        }
+        if (turns && !is_v[u]) {
+          va[u] = __ldg(reinterpret_cast<const uint4*>(src[u] + offA));
+          vb[u] = __ldg(reinterpret_cast<const uint4*>(src[u] + offB));
+        } else if (D == 128 || g < D / 16) {  // a row that is only copied: this lane's two vectors of it
+          va[u] = __ldg(reinterpret_cast<const uint4*>(src[u]) + g);
+          vb[u] = __ldg(reinterpret_cast<const uint4*>(src[u]) + g + D / 16);
         }
       }
-      *reinterpret_cast<uint4*>(dst + offA) = *reinterpret_cast<const uint4*>(oa);
-      *reinterpret_cast<uint4*>(dst + offB) = *reinterpret_cast<const uint4*>(ob);
+#pragma unroll
+      for (int u = 0; u < HB; ++u) {
+        if (!live[u]) continue;
+        const bool rotated = turns && !is_v[u];
+        if (rotated) {
+          __nv_bfloat16 xa[8], xb[8], oa[8], ob[8];
+          *reinterpret_cast<uint4*>(xa) = va[u];
+          *reinterpret_cast<uint4*>(xb) = vb[u];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            // NeoX: pair j is (A[j], B[j]); GPT-J: pair j is elements (2j, 2j + 1) of the 16 loaded
+            const float x1 = __bfloat162float(r.gptj ? (j < 4 ? xa[2 * j] : xb[2 * j - 8]) : xa[j]);
+            const float x2 = __bfloat162float(r.gptj ? (j < 4 ? xa[2 * j + 1] : xb[2 * j - 7]) : xb[j]);
+            // two values per conversion instruction (conversions run at a fraction of the FMA rate)
+            const float2 pc = __bfloat1622float2(__floats2bfloat162_rn(x1 * cs[j], x2 * cs[j]));
+            const float2 ps = __bfloat1622float2(__floats2bfloat162_rn(x2 * sn[j], x1 * sn[j]));
+            const __nv_bfloat162 o12 = __floats2bfloat162_rn(pc.x - ps.x, pc.y + ps.y);
+            if (r.gptj) {
+              if (j < 4) { oa[2 * j] = o12.x; oa[2 * j + 1] = o12.y; } else { ob[2 * j - 8] = o12.x; ob[2 * j - 7] = o12.y; }
+            } else {
+              oa[j] = o12.x;
+              ob[j] = o12.y;
+            }
+          }
+          *reinterpret_cast<uint4*>(dst[u] + offA) = *reinterpret_cast<const uint4*>(oa);
+          *reinterpret_cast<uint4*>(dst[u] + offB) = *reinterpret_cast<const uint4*>(ob);
+          // elements beyond the rotated part
+          for (int c = R / 8 + g; c < D / 8; c += 8)
+            reinterpret_cast<uint4*>(dst[u])[c] = __ldg(reinterpret_cast<const uint4*>(src[u]) + c);
+        } else if (turns || row < 0 || is_v[u]) {
+          const bool whole = is_v[u] || row < 0;  // value rows and unrotated tokens are copied whole
+          if (whole) {
+            if (D == 128 || g < D / 16) {
+              reinterpret_cast<uint4*>(dst[u])[g] = va[u];
+              reinterpret_cast<uint4*>(dst[u])[g + D / 16] = vb[u];
+            }
+          } else {
+            for (int c = R / 8 + g; c < D / 8; c += 8)
+              reinterpret_cast<uint4*>(dst[u])[c] = __ldg(reinterpret_cast<const uint4*>(src[u]) + c);
+          }
+        } else {
+          // a lane without a rotation block (rotary_dim < 128) of a rotated row: its share of the tail
+          for (int c = R / 8 + g; c < D / 8; c += 8)
+            reinterpret_cast<uint4*>(dst[u])[c] = __ldg(reinterpret_cast<const uint4*>(src[u]) + c);
+        }
+      }
     }
-    for (int c = rot / 8 + g; c < D / 8; c += 16)  // pass-through elements, value rows, unrotated tokens
-      reinterpret_cast<uint4*>(dst)[c] = __ldg(reinterpret_cast<const uint4*>(src) + c);
   }
   advance_lengths_in_last_block(p, layer, seq_ids, batch, n_new, n_per);
   asm volatile("griddepcontrol.wait;" ::: "memory");  // (see append_kernel)
@@ -692,8 +753,10 @@ int pace_kv_append_rope(const pace_kv_pool_t* p, int32_t layer, const int32_t* s
   r.rotary_dim = a->rotary_dim;
   r.gptj = a->gptj_pairs ? 1 : 0;
   r.n_q_heads = a->n_q_heads;
-  const long long rows = (long long)batch * n_new * (a->n_q_heads + 2 * p->n_kv_heads);
-  long long blocks = (rows + 15) / 16;  // 16 half-warps per block
+  if (a->rotary_dim > 128) return PACE_ERR_UNSUPPORTED;  // eight lanes x 16 elements cover a row's rotated part
+  const int groups = (a->n_q_heads + 2 * p->n_kv_heads + kRopeHeads - 1) / kRopeHeads;
+  const long long items = (long long)batch * n_new * groups;
+  long long blocks = (items + 31) / 32;  // 32 eight-lane groups per block
   if (blocks > 148 * 8) blocks = 148 * 8;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)blocks);

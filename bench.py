@@ -367,6 +367,69 @@ def run_aux(args):
     print(json.dumps(line), flush=True)
 
 
+def run_rope(args):
+    """Side measurement of the fused RoPE + append kernel against the unfused sequence it replaces
+    (table lookup + elementwise rotation as torch ops, then the plain append), on the decode shape
+    (batch 32, 1 token: launch-bound) and on 2048 new tokens per sequence (batch 8: long enough for the
+    GPU, not the host, to set the pace), 32/8 heads of 128.  Layers are visited round-robin.  Prints
+    one JSON line."""
+    from pace_b200.llm.cache import KVCacheManager, KVCacheType
+    from pace_b200.ops import RotaryEmbedding
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    L = min(args.layers, 8)
+    Hq, Hkv, D = CFG["hq"], CFG["hkv"], args.head_dim
+    rope = RotaryEmbedding({"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                            "original_max_position_embeddings": 8192}, D, 131072, 500000.0).to(dev)
+
+    class Cfg:
+        num_hidden_layers = L
+
+    out = {"workload": "rope_append", "head_dim": D, "layers": L}
+    g = torch.Generator(device=dev).manual_seed(11)
+    for tag, B, n, past in (("decode_b32_n1", 32, 1, 512), ("prefill_b8_n2048", 8, 2048, 0)):
+        reps = 10
+        qkv = torch.randn(B, n, (Hq + 2 * Hkv) * D, device=dev, generator=g, dtype=torch.float32).bfloat16()
+        q = qkv[..., : Hq * D].view(B, n, Hq, D)
+        k = qkv[..., Hq * D: (Hq + Hkv) * D].view(B, n, Hkv, D)
+        v = qkv[..., (Hq + Hkv) * D:].view(B, n, Hkv, D)
+        pos = (torch.arange(n, device=dev) + past).expand(B, n)
+        rows = rope.table_rows(pos)
+        q_out = torch.empty(B, n, Hq, D, dtype=torch.bfloat16, device=dev)
+        times = {}
+        for mode in ("fused", "unfused"):
+            mgr = KVCacheManager(Cfg(), past + n * (reps + 4) + 64, KVCacheType.BMC)
+            if past:
+                old = torch.zeros(B, Hkv, past, D, dtype=torch.bfloat16, device=dev)
+                for l in range(L):
+                    mgr[l].update_cache(old, old, concat_dim=2)
+
+            def step():
+                for l in range(L):
+                    if mode == "fused":
+                        mgr[l].update_cache_rope(q, k, v, rows, rope, query_out=q_out)
+                    else:
+                        qr, kr = rope(q, pos)(query=q.transpose(1, 2), key=k.transpose(1, 2))
+                        mgr[l].update_cache(kr, v.transpose(1, 2), concat_dim=2)
+            for _ in range(3):
+                step()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(reps):
+                step()
+            e1.record()
+            torch.cuda.synchronize()
+            mgr.pool.check_status()
+            times[mode] = e0.elapsed_time(e1) * 1e3 / (reps * L)
+            mgr.release()
+        alg = B * n * (Hq + 2 * Hkv) * D * 2 * 2 + B * n * rope.rotary_dim * 4
+        out[tag] = {"us_fused": times["fused"], "us_unfused_torch_rope_plus_append": times["unfused"],
+                    "alg_bytes": alg, "fused_gbs": alg / times["fused"] / 1e3,
+                    "note": "host-launched, one call per layer (launch overhead included on both sides)"}
+    print(json.dumps(out), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -376,7 +439,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--layers", type=int, default=CFG["n_layers"],
                     help="profiling aid: fewer layers = less device memory; the bench line is only valid at 32")
-    ap.add_argument("--workload", default="decode", choices=["decode", "verify", "prefill"],
+    ap.add_argument("--workload", default="decode", choices=["decode", "verify", "prefill", "rope_append"],
                     help="decode = the bench line; verify / prefill = side measurements of the multi-token kernels")
     ap.add_argument("--past", type=int, default=3584, help="prefill side measurement: tokens cached before the chunk")
     ap.add_argument("--head-dim", type=int, default=128, choices=[64, 128])
@@ -388,6 +451,10 @@ def main():
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if args.impl == "reference":
         run_reference(args, rank)
+        return
+    if args.workload == "rope_append":
+        if rank == 0:
+            run_rope(args)
         return
     if args.workload != "decode":
         if rank == 0:

@@ -46,7 +46,7 @@ extern "C" {
  *   seq_pages    int32 [max_seqs]   pages a slot owns; capacity = seq_pages*page_tokens
  *   page_ref     int32 [n_pages]    reference counts (beam gather shares pages)
  *   free_stack   int32 [n_pages]    free physical pages; counters[0] = number free
- *   counters     int32 [8]          [0] free pages, [1..] kernel tickets
+ *   counters     int32 [8 + n_layers] [0] free pages, [2] pages shared after a gather, [8 + layer] append ticket
  *   status       int32 [4]          [0] sticky PACE_DEV_* bits
  *   table_tmp    int32 [max_seqs][max_pages_per_seq + 1]   scratch of pace_kv_gather
  *

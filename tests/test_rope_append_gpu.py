@@ -105,3 +105,26 @@ def test_fused_rope_error_surface():
     assert torch.equal(out[0, :, 1], q1[0, 1])
     with pytest.raises(_C.PaceError):
         mgr.pool.check_status()
+
+
+def test_back_to_back_appends_to_different_layers_keep_their_lengths():
+    """Appends to different layers launched with nothing in between may overlap on the GPU
+    (programmatic dependent launch); every layer must still advance its own lengths exactly once."""
+    from pace_b200.llm.cache import KVCacheManager, KVCacheType
+    from pace_b200.ops import RotaryEmbedding
+    L, B, Hq, Hkv, D = 8, 32, 32, 8, 128
+    rope = RotaryEmbedding(None, D, 4096, 10000.0)
+    mgr = KVCacheManager(Cfg(L), 600, KVCacheType.BMC)
+    q = torch.randn(B, 1, Hq, D, device=DEV).bfloat16()
+    k = torch.randn(B, 1, Hkv, D, device=DEV).bfloat16()
+    for step in range(40):
+        rows = torch.full((B, 1), step, dtype=torch.int32, device=DEV)
+        for l in range(L):
+            if step % 2:
+                mgr[l].update_cache_rope(q, k, k, rows, rope, query_out=torch.empty_like(q))
+            else:
+                mgr[l].update_cache(k.transpose(1, 2), k.transpose(1, 2), concat_dim=2)
+    torch.cuda.synchronize()
+    mgr.pool.check_status()
+    lens = mgr.pool.seq_len().cpu()
+    assert bool((lens[:L, :B] == 40).all()), lens[:L, :B]
