@@ -466,6 +466,71 @@ def run_rope(args):
     print(json.dumps(out), flush=True)
 
 
+def run_device_loop(args):
+    """Side measurement of the whole decode step of a Llama-3.1-8B-shaped model (random weights,
+    `--layers` of its 32 layers; projections/MLP/LM head are cuBLAS through torch, the KV path is this
+    library): tokens/s of the host-driven loop (one Python step per token, a host synchronisation for
+    the argmax) against the device-resident loop (one CUDA graph per token).  Batch 32, 512-token
+    prompt, 64 new tokens.  Prints one JSON line."""
+    from pace_b200.llm.cache import KVCacheManager, KVCacheType
+    from pace_b200.llm.device_loop import GreedyDeviceLoop
+    from pace_b200.llm.models.llama import LlamaForCausalLM
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+
+    class Cfg:
+        hidden_size, intermediate_size, num_hidden_layers = 4096, 14336, min(args.layers, 32)
+        num_attention_heads, num_key_value_heads, vocab_size = 32, 8, 128256
+        max_position_embeddings, rope_theta, rms_norm_eps, pad_token_id = 8192, 500000.0, 1e-5, 0
+        rope_scaling = {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                        "original_max_position_embeddings": 8192}
+
+    cfg = Cfg()
+    with torch.device(dev):
+        model = LlamaForCausalLM(cfg).to(torch.bfloat16)
+    g = torch.Generator(device=dev).manual_seed(5)
+    with torch.no_grad():
+        for p_ in model.parameters():
+            if p_.dim() >= 2:
+                p_.normal_(0.0, 0.02, generator=g)
+    model.eval()
+    B, P0, N = CFG["batch"], CFG["prompt"], 64
+    prompts = torch.randint(1, cfg.vocab_size, (B, P0), device=dev, generator=g)
+    res = {}
+    for mode in ("host_loop", "device_loop"):
+        mgr = KVCacheManager(cfg, P0 + N + 8, KVCacheType.BMC)
+        with torch.inference_mode():
+            done = 0
+            while done < P0:                       # chunked prefill keeps the activations small
+                n = min(128, P0 - done)
+                pos = (torch.arange(n, device=dev) + done).expand(B, n)
+                hidden = model.model.forward_tokens(prompts[:, done: done + n], mgr, pos)
+                done += n
+            nxt = model.lm_head(hidden[:, -1:]).float().argmax(dim=-1).reshape(B)
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            if mode == "host_loop":
+                pos = torch.full((B, 1), P0, device=dev)
+                for _ in range(N):
+                    hidden = model.model.forward_tokens(nxt.reshape(B, 1), mgr, pos)
+                    nxt = model.lm_head(hidden)[:, -1].float().argmax(dim=-1)
+                    _ = nxt.tolist()               # the reference's loop hands the tokens to Python every step
+                    pos = pos + 1
+            else:
+                loop = GreedyDeviceLoop(model, mgr, nxt, torch.full((B,), P0, device=dev), max_new_tokens=N)
+                t0 = time.perf_counter()           # graph capture is set-up, not decoding
+                loop.run(poll_every=32)
+            torch.cuda.synchronize()
+            dt = time.perf_counter() - t0
+        mgr.pool.check_status()
+        steps = N if mode == "host_loop" else N - 1
+        res[mode] = {"ms_per_token_step": dt * 1e3 / steps, "tokens_per_s": B * steps / dt}
+        mgr.release()
+    res.update({"workload": "device_loop", "model": f"llama-3.1-8b shape, {cfg.num_hidden_layers} layers, random weights",
+                "batch": B, "prompt": P0, "new_tokens": N})
+    print(json.dumps(res), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -475,7 +540,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--layers", type=int, default=CFG["n_layers"],
                     help="profiling aid: fewer layers = less device memory; the bench line is only valid at 32")
-    ap.add_argument("--workload", default="decode", choices=["decode", "verify", "prefill", "rope_append"],
+    ap.add_argument("--workload", default="decode", choices=["decode", "verify", "prefill", "rope_append", "device_loop"],
                     help="decode = the bench line; verify / prefill = side measurements of the multi-token kernels")
     ap.add_argument("--past", type=int, default=3584, help="prefill side measurement: tokens cached before the chunk")
     ap.add_argument("--head-dim", type=int, default=128, choices=[64, 128])
@@ -488,9 +553,9 @@ def main():
     if args.impl == "reference":
         run_reference(args, rank)
         return
-    if args.workload == "rope_append":
+    if args.workload in ("rope_append", "device_loop"):
         if rank == 0:
-            run_rope(args)
+            (run_rope if args.workload == "rope_append" else run_device_loop)(args)
         return
     if args.workload != "decode":
         if rank == 0:
