@@ -328,8 +328,11 @@ def run_ours(args, rank, world, local_rank):
     if os.path.exists(traffic_file):
         try:
             t = json.load(open(traffic_file))
-            # DRAM bytes of a captured launch scale with the cached tokens it streams
-            line["roofline"]["traffic"] = t["dram_bytes_per_launch"] * (B * lens_now) / t["tokens_per_launch"]
+            # DRAM bytes of the captured launch scale with the page rows a launch streams (whole
+            # pages leave DRAM: a sequence of n tokens reads ceil(n / page) pages)
+            P_ = mgr.pool.page_tokens
+            rows_now = B * ((lens_now + P_ - 1) // P_) * P_
+            line["roofline"]["traffic"] = t["dram_bytes_per_launch"] * rows_now / t["page_rows_per_launch"]
         except Exception:
             pass
     print(json.dumps(line), flush=True)
