@@ -60,8 +60,10 @@ struct UmmaCtx {
 };
 #ifdef PACE_TIMING
 #define PACE_UTRACE(c, k, i) do { if ((c).cta == 7 && (i) < 64) (c).trace[(k) * 64 + (i)] = (unsigned long long)clock64(); } while (0)
+#define PACE_USTAMP(c, k) do { unsigned long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_)); (c).stamps[k] = t_; } while (0)
 #define PACE_UCLK(c, k, i, v) do { if ((c).cta == 7 && (i) < 64) (c).trace[(k) * 64 + (i)] = (unsigned long long)(v); } while (0)
 #else
+#define PACE_USTAMP(c, k) do {} while (0)
 #define PACE_UCLK(c, k, i, v) do {} while (0)
 #define PACE_UTRACE(c, k, i) do {} while (0)
 #endif
@@ -319,47 +321,70 @@ __device__ __forceinline__ void umma_issue_pv(const UmmaCtx& c, uint32_t tmem, i
   __syncwarp();
 }
 
-// merge of a unit's partials by its last arriver (all softmax threads; every partial is in the workspace)
+// Merge of a unit's partials by its last arriver (all softmax threads; every partial is in the
+// workspace).  A thread owns four adjacent output elements at a time and keeps the loads of two such
+// groups times four partials in flight: the loop is bound by L2 latency, not by arithmetic.
 template <int D>
 __device__ __forceinline__ void umma_merge(const MmaParams& p, const ResMeta& rm, int t) {
-  constexpr int MR = kUmmaRows, REC = MR * (D + 2);
-  const int G = p.G;
-  for (int oi = t * 2; oi < rm.live * D; oi += kUmmaSoftmaxThreads * 2) {
-    const int row = oi / D, d = oi - row * D;
-    float M = -INFINITY, n0 = 0.f, n1 = 0.f, den = 0.f;
-    for (int c0 = 0; c0 < rm.parts; c0 += 4) {
-      float mc[4], dc[4];
-      float2 nn[4];
+  constexpr int MR = kUmmaRows, REC = MR * (D + 2), V4 = D / 4, U = 2;
+  const int G = p.G, total = rm.live * V4;
+  for (int e0 = t; e0 < total; e0 += kUmmaSoftmaxThreads * U) {
+    int row[U], col[U];
+    float M[U], den[U];
+    float4 num[U];
 #pragma unroll
-      for (int k = 0; k < 4; ++k) {
-        const int c = c0 + k;
-        mc[k] = -INFINITY;
-        dc[k] = 0.f;
-        nn[k] = make_float2(0.f, 0.f);
-        if (c < rm.parts) {
-          const float* r = p.parts + ((size_t)(rm.first_cta + c) * 2 + (c == 0 ? rm.first_slot : 0)) * REC;
-          mc[k] = __ldcg(r + MR * D + row);
-          dc[k] = __ldcg(r + MR * D + MR + row);
-          nn[k] = __ldcg(reinterpret_cast<const float2*>(r + oi));
-        }
-      }
-#pragma unroll
-      for (int k = 0; k < 4; ++k) {
-        const float Mn = fmaxf(M, mc[k]);
-        if (Mn != -INFINITY) {
-          const float a = (M == -INFINITY) ? 0.f : fast_exp2(M - Mn);
-          const float f = (mc[k] == -INFINITY) ? 0.f : fast_exp2(mc[k] - Mn);
-          n0 = n0 * a + nn[k].x * f;
-          n1 = n1 * a + nn[k].y * f;
-          den = den * a + dc[k] * f;
-          M = Mn;
-        }
-      }
+    for (int u = 0; u < U; ++u) {
+      const int e = min(e0 + u * kUmmaSoftmaxThreads, total - 1);  // (a clamped duplicate is not stored)
+      row[u] = e / V4;
+      col[u] = (e - row[u] * V4) * 4;
+      M[u] = -INFINITY;
+      den[u] = 0.f;
+      num[u] = make_float4(0.f, 0.f, 0.f, 0.f);
     }
-    const float inv = den > 0.f ? 1.0f / den : 0.f;
-    const int rr = rm.r_lo + row, sq = rr / G, g = rr - sq * G;
-    *reinterpret_cast<uint32_t*>(p.out + (size_t)rm.b * p.o_sb + (size_t)(rm.h * G + g) * p.o_sh + (size_t)sq * p.o_ss +
-                                 d) = f2_to_bf2(n0 * inv, n1 * inv);
+    for (int c0 = 0; c0 < rm.parts; c0 += 4) {
+      float mc[U][4], dc[U][4];
+      float4 nn[U][4];
+#pragma unroll
+      for (int u = 0; u < U; ++u)
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const int c = c0 + k;
+          mc[u][k] = -INFINITY;
+          dc[u][k] = 0.f;
+          nn[u][k] = make_float4(0.f, 0.f, 0.f, 0.f);
+          if (c < rm.parts) {
+            const float* r = p.parts + ((size_t)(rm.first_cta + c) * 2 + (c == 0 ? rm.first_slot : 0)) * REC;
+            mc[u][k] = __ldcg(r + MR * D + row[u]);
+            dc[u][k] = __ldcg(r + MR * D + MR + row[u]);
+            nn[u][k] = __ldcg(reinterpret_cast<const float4*>(r + row[u] * D + col[u]));
+          }
+        }
+#pragma unroll
+      for (int u = 0; u < U; ++u)
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const float Mn = fmaxf(M[u], mc[u][k]);
+          if (Mn != -INFINITY) {
+            const float a = (M[u] == -INFINITY) ? 0.f : fast_exp2(M[u] - Mn);
+            const float f = (mc[u][k] == -INFINITY) ? 0.f : fast_exp2(mc[u][k] - Mn);
+            num[u].x = num[u].x * a + nn[u][k].x * f;
+            num[u].y = num[u].y * a + nn[u][k].y * f;
+            num[u].z = num[u].z * a + nn[u][k].z * f;
+            num[u].w = num[u].w * a + nn[u][k].w * f;
+            den[u] = den[u] * a + dc[u][k] * f;
+            M[u] = Mn;
+          }
+        }
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      if (e0 + u * kUmmaSoftmaxThreads >= total) continue;
+      const float inv = den[u] > 0.f ? 1.0f / den[u] : 0.f;
+      const int rr = rm.r_lo + row[u], sq = rr / G, g = rr - sq * G;
+      *reinterpret_cast<uint2*>(p.out + (size_t)rm.b * p.o_sb + (size_t)(rm.h * G + g) * p.o_sh + (size_t)sq * p.o_ss +
+                                col[u]) =
+          make_uint2(f2_to_bf2(num[u].x * inv, num[u].y * inv), f2_to_bf2(num[u].z * inv, num[u].w * inv));
+    }
   }
 }
 
@@ -375,7 +400,9 @@ __device__ __forceinline__ void umma_softmax(const MmaParams& p, const UmmaCtx& 
   int n_pub = 0, n_xch = 0;
   auto group_sync = [&]() -> bool {  // all softmax threads meet (bounded, unlike bar.sync)
     mbar_arrive(c.pub);
-    const bool ok = umma_wait(c.pub, n_pub & 1, c.abort);
+    bool ok = false;
+    for (int k = 0; k < 4096 && !ok; ++k) ok = mbar_try_wait(c.pub, n_pub & 1);  // everyone is about to arrive
+    ok = __all_sync(0xffffffffu, ok) || umma_wait(c.pub, n_pub & 1, c.abort);
     ++n_pub;
     return ok;
   };
@@ -383,6 +410,7 @@ __device__ __forceinline__ void umma_softmax(const MmaParams& p, const UmmaCtx& 
   for (int i0 = 0; i0 < c.n_my;) {
     // ---- new unit part: its record, this thread's share of the Q tile ----
     if (!umma_wait(&c.full_bar[i0 % c.n_stages], (i0 / c.n_stages) & 1, c.abort)) return;
+    if (tid == 0 && i0 == 0) PACE_USTAMP(c, 2);
     ResMeta fin;
     int n_part, kvs, lim, tok0_part;
     bool live;
@@ -514,6 +542,7 @@ __device__ __forceinline__ void umma_softmax(const MmaParams& p, const UmmaCtx& 
     }
 
     // ================= end of a unit part: the two groups' accumulators meet =================
+    if (tid == 0) PACE_USTAMP(c, 3);
     const bool has_mine = j_first < n_part, has_other = (j_first ^ 1) < n_part;  // (a part of one chunk leaves a group empty-handed)
     if (has_mine && !umma_wait(&c.o_full[wg], (cnt - 1) & 1, c.abort)) return;
     c.xch_m[wg * MR + row] = m_used;
@@ -570,6 +599,7 @@ __device__ __forceinline__ void umma_softmax(const MmaParams& p, const UmmaCtx& 
     }
     tc_fence_before();
     i0 += n_part;
+    if (tid == 0) PACE_USTAMP(c, 4);
     if (fin.mode == 0) continue;
     // cut unit: the fp32 partial is in the workspace; arrival count, merge by the last arriver
     if (live && wg == 0) {
@@ -578,19 +608,21 @@ __device__ __forceinline__ void umma_softmax(const MmaParams& p, const UmmaCtx& 
     }
     __threadfence();
     if (!group_sync()) return;
+    int* const flag = c.flag + (n_pub & 2 ? 1 : 0);  // two slots in turn: no third meeting to protect a rewrite
     if (tid == 0) {
       const int old = atomicAdd(&p.unit_count[fin.unit], 1);
       const int is_last = (old == fin.parts - 1);
       if (is_last) p.unit_count[fin.unit] = 0;  // ready for the next launch
-      *c.flag = is_last;
+      *flag = is_last;
     }
     if (!group_sync()) return;
-    const int is_last = *c.flag;
-    if (!group_sync()) return;  // the flag is rewritten by the next cut unit
+    const int is_last = *flag;
+    if (tid == 0) PACE_USTAMP(c, 6);
     if (is_last) {
       __threadfence();
       umma_merge<D>(p, fin, tid);
     }
+    if (tid == 0) PACE_USTAMP(c, 7);
   }
 }
 
