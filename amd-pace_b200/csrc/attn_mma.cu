@@ -312,6 +312,8 @@ __global__ void __launch_bounds__(threads_of(UMMA), 1)
   // touches nothing this kernel reads or writes) may start as soon as every CTA is past this point
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 #ifdef PACE_TIMING
+  // (measurement builds only: the stamps land behind the partial records, so the caller must pass a
+  // workspace some 64 KB larger than pace_attn_workspace_bytes asks for)
   unsigned long long* stamps = reinterpret_cast<unsigned long long*>(p.parts + (size_t)gridDim.x * 2 * REC) + blockIdx.x * 8;
 #define PACE_STAMP(i) do { unsigned long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_)); stamps[i] = t_; } while (0)
   unsigned long long* trace = reinterpret_cast<unsigned long long*>(p.parts + (size_t)gridDim.x * 2 * REC) + gridDim.x * 8;

@@ -1,4 +1,5 @@
-"""Wave-admission serving loop over one shared KV pool (one model instance on one GPU).
+"""Serving loops over one shared KV pool (one model instance on one GPU): wave admission and
+continuous batching.
 
 The reference serves static batches: the router collects requests for a time window and the server
 runs ``generate`` on the padded batch (pace/server/router.py:112-191, server.py:74-100); continuous
@@ -112,4 +113,137 @@ class WaveServer:
             stats.output_tokens += n * max_new
             stats.prefill_s += t1 - t0
             stats.decode_s += t2 - t1
+        return outputs, stats
+
+
+# ---------------------------------------------------------------------------------------------------
+# Continuous batching
+# ---------------------------------------------------------------------------------------------------
+@dataclass
+class _Running:
+    request: int
+    prompt: torch.Tensor
+    max_new: int
+    fed: int = 0                      # prompt tokens already in the cache
+    out: List[int] = field(default_factory=list)
+    next_token: Optional[int] = None  # generated, not yet fed back
+
+
+@dataclass
+class BatchStats:
+    steps: int = 0
+    prompt_tokens: int = 0
+    output_tokens: int = 0
+    seconds: float = 0.0
+    max_running: int = 0
+    padded_tokens: int = 0            # rows the padded [slots, width] batches carried in total
+
+
+class ContinuousBatcher:
+    """Iteration-level scheduling over a fixed set of cache slots (the reference names continuous
+    batching as future work, docs/LLM.md:24-25; its router batches statically,
+    pace/server/router.py:112-191).
+
+    Every step feeds each running sequence what it needs next - up to ``prefill_chunk`` prompt tokens
+    or its one newest generated token - through one ragged forward pass; a sequence that finishes
+    gives its pages back at once (``KVCacheManager.recycle``) and the next waiting request takes its
+    slot in the same step, provided the pool has the pages for its prompt and its ``max_new`` tokens.
+    What makes this cheap on this cache: ragged appends and ragged attention are single launches,
+    and admitting or retiring a sequence moves no K/V bytes, only block-table rows.
+    """
+
+    def __init__(self, model, pool_tokens: int, max_batch: int, max_seq_len: int, prefill_chunk: int = 256,
+                 cache_type: KVCacheType = KVCacheType.BMC):
+        self.model = model
+        cfg = model.config
+        self.device = next(model.parameters()).device
+        self.page_tokens = physical_page_tokens(None)
+        self.prefill_chunk = prefill_chunk
+        self.max_batch = max_batch
+        head_dim = cfg.hidden_size // cfg.num_attention_heads
+        n_pages = max(1, pool_tokens // self.page_tokens)
+        max_pages = (max_seq_len + 2 * self.page_tokens) // self.page_tokens + 2
+        self.pool = KVPool(cfg.num_hidden_layers, cfg.num_key_value_heads, head_dim, self.page_tokens, n_pages,
+                           max_seqs=max_batch, max_pages_per_seq=max_pages, device=self.device)
+        self.manager = KVCacheManager(cfg, max_seq_len, cache_type, pool=self.pool)
+        self.slots: List[Optional[_Running]] = [None] * max_batch
+        self.reserved_pages = 0        # pages promised to running sequences (prompt + max_new each)
+
+    def _pages_for(self, n_tokens: int) -> int:
+        return (n_tokens + self.page_tokens - 1) // self.page_tokens + 1
+
+    def _admit(self, waiting: List[_Running]) -> None:
+        total = self.pool.n_pages
+        for b in range(self.max_batch):
+            if not waiting:
+                return
+            if self.slots[b] is not None:
+                continue
+            need = self._pages_for(len(waiting[0].prompt) + waiting[0].max_new)
+            if need > total:
+                raise RuntimeError(f"request of {len(waiting[0].prompt)} tokens does not fit the KV pool")
+            if self.reserved_pages + need > total:
+                return                  # first come, first served: nobody overtakes the head of the queue
+            self.reserved_pages += need
+            self.slots[b] = waiting.pop(0)
+
+    @torch.inference_mode()
+    def run(self, prompts: List[torch.Tensor], max_new: int, pad_id: int = 0):
+        """Serves every prompt (1-D token tensors) greedily for ``max_new`` tokens.  Returns the generated
+        tokens per request and the statistics."""
+        stats = BatchStats()
+        outputs: List[Optional[List[int]]] = [None] * len(prompts)
+        waiting = [_Running(i, p, max_new) for i, p in enumerate(prompts)]
+        B = self.max_batch
+        torch.cuda.synchronize(self.device)
+        t0 = time.perf_counter()
+        # the manager's batch is every slot, from the first pass on
+        while waiting or any(s is not None for s in self.slots):
+            self._admit(waiting)
+            counts = [0] * B
+            for b, s in enumerate(self.slots):
+                if s is None:
+                    continue
+                counts[b] = min(self.prefill_chunk, len(s.prompt) - s.fed) if s.fed < len(s.prompt) else 1
+            width = max(counts)
+            if width == 0:
+                raise RuntimeError("nothing admitted and nothing running")
+            new = torch.full((B, width), pad_id, dtype=torch.long)
+            for b, s in enumerate(self.slots):
+                if s is None:
+                    continue
+                if s.fed < len(s.prompt):
+                    new[b, : counts[b]] = s.prompt[s.fed: s.fed + counts[b]]
+                else:
+                    new[b, 0] = s.next_token
+            logits = self.model.forward_ragged(new.to(self.device), counts, self.manager).logits
+            last = torch.tensor([max(c - 1, 0) for c in counts], device=self.device)
+            picked = logits[torch.arange(B, device=self.device), last].float().argmax(dim=-1).tolist()
+            done = []
+            for b, s in enumerate(self.slots):
+                if s is None:
+                    continue
+                if s.fed < len(s.prompt):
+                    s.fed += counts[b]
+                    stats.prompt_tokens += counts[b]
+                    if s.fed < len(s.prompt):
+                        continue        # still prefilling: this pass's logits are not sampled
+                s.next_token = picked[b]
+                s.out.append(picked[b])
+                stats.output_tokens += 1
+                if len(s.out) >= s.max_new:
+                    done.append(b)
+            if done:
+                self.manager.recycle(done)
+                for b in done:
+                    s = self.slots[b]
+                    outputs[s.request] = s.out
+                    self.reserved_pages -= self._pages_for(len(s.prompt) + s.max_new)
+                    self.slots[b] = None
+            stats.steps += 1
+            stats.padded_tokens += B * width
+            stats.max_running = max(stats.max_running, sum(s is not None for s in self.slots) + len(done))
+        torch.cuda.synchronize(self.device)
+        stats.seconds = time.perf_counter() - t0
+        self.pool.check_status()
         return outputs, stats

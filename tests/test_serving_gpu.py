@@ -48,3 +48,31 @@ def test_request_larger_than_the_pool_is_refused():
     server = WaveServer(_model(), pool_tokens=64 * 3, max_batch=2, max_seq_len=600)
     with pytest.raises(RuntimeError, match="does not fit the KV pool"):
         server.run([torch.randint(1, 97, (400,))], 4)
+
+
+def test_continuous_batching_serves_every_request_and_returns_every_page():
+    """Requests join and leave a fixed set of slots step by step; what each one generates starts with
+    the token a run of that request alone produces, and the pool ends as full as it began."""
+    from pace_b200.llm.serving import ContinuousBatcher, WaveServer
+    model = _model()
+    g = torch.Generator().manual_seed(9)
+    lens = [300, 37, 129, 64, 511, 5, 200, 90, 33]
+    prompts = [torch.randint(1, 97, (n,), generator=g) for n in lens]
+    new = 7
+    cb = ContinuousBatcher(model, pool_tokens=64 * 16, max_batch=4, max_seq_len=600, prefill_chunk=128)
+    free0 = cb.pool.query()[1]
+    outs, stats = cb.run(prompts, new)
+    assert all(o is not None and len(o) == new for o in outs)
+    assert stats.prompt_tokens == sum(lens) and stats.output_tokens == new * len(prompts)
+    assert 2 <= stats.max_running <= 4
+    bits, free1 = cb.pool.query()
+    assert bits == 0 and free1 == free0 and cb.pool.host_free_pages == free0 and cb.reserved_pages == 0
+    assert all(n == 0 for n in cb.manager[0].seq_lens)
+    big = WaveServer(model, pool_tokens=64 * 64, max_batch=1, max_seq_len=600, prefill_chunk=512)
+    agree = sum(int(big.run([p], new)[0][0][0] == outs[i][0]) for i, p in enumerate(prompts))
+    assert agree >= len(prompts) - 1
+    # a second run on the same batcher reuses the recycled slots and pages
+    outs2, _ = cb.run(prompts[:3], new)
+    assert [o[0] for o in outs2] == [o[0] for o in outs[:3]]
+    with pytest.raises(RuntimeError, match="does not fit the KV pool"):
+        cb.run([torch.randint(1, 97, (590,))], 600)
