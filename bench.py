@@ -534,6 +534,55 @@ def run_device_loop(args):
     print(json.dumps(res), flush=True)
 
 
+def run_serving(args):
+    """Side measurement of the two serving loops over one paged pool on a Llama-3.1-8B-shaped model
+    (`--layers` of its layers, default 8 here; random weights): 48 requests with prompt lengths drawn
+    log-uniformly from 64..4096 tokens (seeded), 32 new tokens each, 16 cache slots, a pool of 24576
+    tokens.  Wave admission (a wave is admitted, runs to the end, is released) against continuous
+    batching (a finished request's slot and pages go to the next one at once).  Prints one JSON line."""
+    import math
+    from pace_b200.llm.models.llama import LlamaForCausalLM
+    from pace_b200.llm.serving import ContinuousBatcher, WaveServer
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+
+    class Cfg:
+        hidden_size, intermediate_size, num_hidden_layers = 4096, 14336, min(args.layers, 8)
+        num_attention_heads, num_key_value_heads, vocab_size = 32, 8, 128256
+        max_position_embeddings, rope_theta, rms_norm_eps, pad_token_id = 8192, 500000.0, 1e-5, 0
+        rope_scaling = None
+
+    cfg = Cfg()
+    with torch.device(dev):
+        model = LlamaForCausalLM(cfg).to(torch.bfloat16)
+    g = torch.Generator(device=dev).manual_seed(6)
+    with torch.no_grad():
+        for p_ in model.parameters():
+            if p_.dim() >= 2:
+                p_.normal_(0.0, 0.02, generator=g)
+    model.eval()
+    gc = torch.Generator().manual_seed(7)
+    lens = [int(math.exp(math.log(64) + float(torch.rand(1, generator=gc)) * math.log(4096 / 64))) for _ in range(48)]
+    prompts = [torch.randint(1, cfg.vocab_size, (n,), generator=gc) for n in lens]
+    new = 32
+    res = {"workload": "serving", "model": f"llama-3.1-8b shape, {cfg.num_hidden_layers} layers, random weights",
+           "requests": len(prompts), "prompt_tokens": sum(lens), "new_tokens_each": new, "slots": 16,
+           "pool_tokens": 24576}
+    for name, cls in (("wave", WaveServer), ("continuous", ContinuousBatcher)):
+        srv = cls(model, pool_tokens=24576, max_batch=16, max_seq_len=4096 + new + 64, prefill_chunk=512)
+        srv.run(prompts[:4], 4)                      # warm-up (allocator, cuBLAS handles)
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        outs, st = srv.run(prompts, new)
+        torch.cuda.synchronize()
+        dt = time.perf_counter() - t0
+        assert all(len(o) == new for o in outs)
+        res[name] = {"seconds": dt, "total_tokens_per_s": (sum(lens) + new * len(prompts)) / dt,
+                     "output_tokens_per_s": new * len(prompts) / dt,
+                     "steps_or_waves": getattr(st, "steps", None) or getattr(st, "waves", None)}
+    print(json.dumps(res), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -543,7 +592,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--layers", type=int, default=CFG["n_layers"],
                     help="profiling aid: fewer layers = less device memory; the bench line is only valid at 32")
-    ap.add_argument("--workload", default="decode", choices=["decode", "verify", "prefill", "rope_append", "device_loop"],
+    ap.add_argument("--workload", default="decode", choices=["decode", "verify", "prefill", "rope_append", "device_loop", "serving"],
                     help="decode = the bench line; verify / prefill = side measurements of the multi-token kernels")
     ap.add_argument("--past", type=int, default=3584, help="prefill side measurement: tokens cached before the chunk")
     ap.add_argument("--head-dim", type=int, default=128, choices=[64, 128])
@@ -556,9 +605,9 @@ def main():
     if args.impl == "reference":
         run_reference(args, rank)
         return
-    if args.workload in ("rope_append", "device_loop"):
+    if args.workload in ("rope_append", "device_loop", "serving"):
         if rank == 0:
-            (run_rope if args.workload == "rope_append" else run_device_loop)(args)
+            {"rope_append": run_rope, "device_loop": run_device_loop, "serving": run_serving}[args.workload](args)
         return
     if args.workload != "decode":
         if rank == 0:
