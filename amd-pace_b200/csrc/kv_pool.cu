@@ -338,7 +338,7 @@ __global__ void __launch_bounds__(256, 3)
       }
     }
     const int offA = r.gptj ? 16 * g : 8 * g, offB = r.gptj ? 16 * g + 8 : R / 2 + 8 * g;
-    const int rot = row >= 0 ? R : 0;  // elements [0, rot) are rotated, the rest copied
+
     const int h_end = min(heads, (hg + 1) * kRopeHeads);
     // Heads go three at a time: all loads of a batch are issued before its first store.  (q_out may be
     // q itself, so the compiler has to keep every load behind the stores in front of it; batching by
