@@ -1,7 +1,7 @@
 """Imports the reference's own Python modules, unmodified, from its source tree.
 
 TEST INFRASTRUCTURE ONLY, and only usable where the reference tree exists
-(it is located through $PACE_REF_ROOT, default /root/reference).  Used by
+(it is located through $PACE_REF_ROOT, with a built-in default).  Used by
 tests/golden/make_golden.py to produce the committed golden vectors and by the
 CPU tests that re-check the oracle against the live reference when it is there.
 

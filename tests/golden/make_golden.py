@@ -1,6 +1,6 @@
 """Generates the golden vectors under tests/golden/ by RUNNING THE REFERENCE.
 
-Run where the reference source tree is present (default /root/reference, or
+Run where the reference source tree is present (it is found through
 $PACE_REF_ROOT):
 
     python tests/golden/make_golden.py
