@@ -286,8 +286,6 @@ struct RopeParams {
 };
 constexpr int kRopeHeads = 6;  // heads per work item: 32 + 2 x 8 heads make eight items per token
 
-__device__ __forceinline__ float bf16_round(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
-
 __global__ void __launch_bounds__(256, 3)
     append_rope_kernel(pace_kv_pool_t p, int layer, const int32_t* __restrict__ seq_ids, int batch, int n_new,
                        const int32_t* __restrict__ n_per, RopeParams r) {
@@ -322,19 +320,29 @@ __global__ void __launch_bounds__(256, 3)
       if (g == 0 && hg == 0) raise_status(p.status, PACE_DEV_BAD_INDEX);
       row = -1;  // the token passes through unrotated
     }
-    // this lane's eight cos / sin values (rotation block g)
-    float cs[8], sn[8];
+    // This lane's eight cos / sin values (rotation block g), rounded to bf16 and paired the way the
+    // packed arithmetic below wants them: NeoX (c[2j], c[2j+1]), GPT-J (c[j], c[j]).  bf16x2
+    // multiplies, adds and subtracts round every result to bf16 exactly like the elementwise ops.
+    __nv_bfloat162 c2[8], s2[8];
     const bool turns = row >= 0 && g < R / 16;
     if (turns) {
       const float4* cp = reinterpret_cast<const float4*>(r.cos_t + (size_t)row * (R / 2) + 8 * g);
       const float4* sp = reinterpret_cast<const float4*>(r.sin_t + (size_t)row * (R / 2) + 8 * g);
       const float4 c0 = __ldg(cp), c1 = __ldg(cp + 1), s0 = __ldg(sp), s1 = __ldg(sp + 1);
-      cs[0] = c0.x; cs[1] = c0.y; cs[2] = c0.z; cs[3] = c0.w; cs[4] = c1.x; cs[5] = c1.y; cs[6] = c1.z; cs[7] = c1.w;
-      sn[0] = s0.x; sn[1] = s0.y; sn[2] = s0.z; sn[3] = s0.w; sn[4] = s1.x; sn[5] = s1.y; sn[6] = s1.z; sn[7] = s1.w;
+      const float cs[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+      const float sn[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+      if (r.gptj) {
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        cs[j] = bf16_round(cs[j]);
-        sn[j] = bf16_round(sn[j]);
+        for (int j = 0; j < 8; ++j) {
+          c2[j] = __floats2bfloat162_rn(cs[j], cs[j]);
+          s2[j] = __floats2bfloat162_rn(sn[j], sn[j]);
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          c2[j] = __floats2bfloat162_rn(cs[2 * j], cs[2 * j + 1]);
+          s2[j] = __floats2bfloat162_rn(sn[2 * j], sn[2 * j + 1]);
+        }
       }
     }
     const int offA = r.gptj ? 16 * g : 8 * g, offB = r.gptj ? 16 * g + 8 : R / 2 + 8 * g;
@@ -384,23 +392,27 @@ __global__ void __launch_bounds__(256, 3)
         if (!live[u]) continue;
         const bool rotated = turns && !is_v[u];
         if (rotated) {
-          __nv_bfloat16 xa[8], xb[8], oa[8], ob[8];
+          __nv_bfloat162 xa[4], xb[4], oa[4], ob[4];
           *reinterpret_cast<uint4*>(xa) = va[u];
           *reinterpret_cast<uint4*>(xb) = vb[u];
+          if (r.gptj) {
+            // a register holds one pair (x1, x2): (x1 c, x2 c) + (-(x2 s), x1 s); the sign flip is exact
 #pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            // NeoX: pair j is (A[j], B[j]); GPT-J: pair j is elements (2j, 2j + 1) of the 16 loaded
-            const float x1 = __bfloat162float(r.gptj ? (j < 4 ? xa[2 * j] : xb[2 * j - 8]) : xa[j]);
-            const float x2 = __bfloat162float(r.gptj ? (j < 4 ? xa[2 * j + 1] : xb[2 * j - 7]) : xb[j]);
-            // two values per conversion instruction (conversions run at a fraction of the FMA rate)
-            const float2 pc = __bfloat1622float2(__floats2bfloat162_rn(x1 * cs[j], x2 * cs[j]));
-            const float2 ps = __bfloat1622float2(__floats2bfloat162_rn(x2 * sn[j], x1 * sn[j]));
-            const __nv_bfloat162 o12 = __floats2bfloat162_rn(pc.x - ps.x, pc.y + ps.y);
-            if (r.gptj) {
-              if (j < 4) { oa[2 * j] = o12.x; oa[2 * j + 1] = o12.y; } else { ob[2 * j - 8] = o12.x; ob[2 * j - 7] = o12.y; }
-            } else {
-              oa[j] = o12.x;
-              ob[j] = o12.y;
+            for (int j = 0; j < 8; ++j) {
+              const __nv_bfloat162 x = j < 4 ? xa[j] : xb[j - 4];
+              const __nv_bfloat162 t = __hmul2_rn(x, c2[j]);
+              __nv_bfloat162 w = __hmul2_rn(__lowhigh2highlow(x), s2[j]);   // (x2 s, x1 s)
+              uint32_t bits = *reinterpret_cast<uint32_t*>(&w) ^ 0x00008000u;
+              w = *reinterpret_cast<__nv_bfloat162*>(&bits);
+              const __nv_bfloat162 o = __hadd2_rn(t, w);
+              if (j < 4) oa[j] = o; else ob[j - 4] = o;
+            }
+          } else {
+            // register j of the first half holds x1 of pairs 2j, 2j + 1, of the second half their x2
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              oa[j] = __hsub2_rn(__hmul2_rn(xa[j], c2[j]), __hmul2_rn(xb[j], s2[j]));
+              ob[j] = __hadd2_rn(__hmul2_rn(xb[j], c2[j]), __hmul2_rn(xa[j], s2[j]));
             }
           }
           *reinterpret_cast<uint4*>(dst[u] + offA) = *reinterpret_cast<const uint4*>(oa);
