@@ -348,6 +348,12 @@ __global__ void __launch_bounds__(256, 3)
     const int offA = r.gptj ? 16 * g : 8 * g, offB = r.gptj ? 16 * g + 8 : R / 2 + 8 * g;
 
     const int h_end = min(heads, (hg + 1) * kRopeHeads);
+    // the token's rows: everything but the head offset
+    const __nv_bfloat16* const q_tok = r.q + (size_t)b * r.q_sb + (size_t)t * r.q_st;
+    const __nv_bfloat16* const k_tok = r.k + (size_t)b * r.k_sb + (size_t)t * r.k_st;
+    const __nv_bfloat16* const v_tok = r.v + (size_t)b * r.v_sb + (size_t)t * r.v_st;
+    __nv_bfloat16* const o_tok = r.q_out + (size_t)b * r.o_sb + (size_t)t * r.o_st;
+    const size_t cache_tok = ((size_t)page * Hkv * P + (pos - lp * P)) * (size_t)D;
     // Heads go three at a time: all loads of a batch are issued before its first store.  (q_out may be
     // q itself, so the compiler has to keep every load behind the stores in front of it; batching by
     // hand is what puts several rows in flight per lane.)
@@ -366,18 +372,17 @@ __global__ void __launch_bounds__(256, 3)
         dst[u] = nullptr;
         if (!live[u]) continue;
         if (hh < Hq) {
-          src[u] = r.q + (size_t)b * r.q_sb + (size_t)t * r.q_st + (size_t)hh * r.q_sh;
-          dst[u] = r.q_out + (size_t)b * r.o_sb + (size_t)t * r.o_st + (size_t)hh * r.o_sh;
+          src[u] = q_tok + (size_t)hh * r.q_sh;
+          dst[u] = o_tok + (size_t)hh * r.o_sh;
         } else {
           const int h = is_v[u] ? hh - Hq - Hkv : hh - Hq;
-          src[u] = is_v[u] ? r.v + (size_t)b * r.v_sb + (size_t)t * r.v_st + (size_t)h * r.v_sh
-                           : r.k + (size_t)b * r.k_sb + (size_t)t * r.k_st + (size_t)h * r.k_sh;
+          src[u] = is_v[u] ? v_tok + (size_t)h * r.v_sh : k_tok + (size_t)h * r.k_sh;
           if (!page_ok) {
             if (g == 0) raise_status(p.status, PACE_DEV_BAD_INDEX);
             live[u] = false;
             continue;
           }
-          dst[u] = (is_v[u] ? vbase : kbase) + (((size_t)page * Hkv + h) * P + (pos - lp * P)) * (size_t)D;
+          dst[u] = (is_v[u] ? vbase : kbase) + cache_tok + (size_t)h * P * D;
         }
         if (turns && !is_v[u]) {
           va[u] = __ldg(reinterpret_cast<const uint4*>(src[u] + offA));
