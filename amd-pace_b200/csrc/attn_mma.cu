@@ -337,6 +337,7 @@ __global__ void __launch_bounds__(threads_of(UMMA), 1)
     else if (k == 2 * n_stages) mbar_init(q_empty, kWarps);
     else if (k < 2 * n_stages + 3) mbar_init(&res_full[k - 2 * n_stages - 1], kWarps);
     else if (k < 2 * n_stages + 5) mbar_init(&res_empty[k - 2 * n_stages - 3], 1);
+    if (k == 30) misc[2] = 0;  // longest unit, in chunks (a maximum over the items, taken below)
     if (UMMA && k == 31) {
       // s_full[4], p_full[4] (one arrival per warp of the group), o_full[2], q_ready, drain[2], pub
       // (every softmax thread), xch (one arrival per softmax warp, like q_ready), p_free[4]
@@ -408,6 +409,7 @@ __global__ void __launch_bounds__(threads_of(UMMA), 1)
     }
     prefix[it + 1] = n;
     saw_empty |= (n == 0);
+    if (n > 0) atomicMax(&misc[2], n / Hkv);
   }
   const int any_empty = __syncthreads_or(saw_empty);
   if (tid == 0) PACE_TRACE(3, 4);
@@ -440,7 +442,20 @@ __global__ void __launch_bounds__(threads_of(UMMA), 1)
     return small ? (int)(((unsigned)(x + 1) * (unsigned)NC + (unsigned)T - 1u) / (unsigned)T) - 1
                  : (int)(((x + 1) * NC + T - 1) / T) - 1;
   };
-  const long long x0 = cta < NC ? range_begin(cta) : 0, x1 = cta < NC ? range_begin(cta + 1) : 0;
+  long long x0 = cta < NC ? range_begin(cta) : 0, x1 = cta < NC ? range_begin(cta + 1) : 0;
+  // When there are no more units than CTAs and the longest unit is not much longer than an equal share
+  // of the chunks, every CTA takes one whole unit instead: a little more streaming for the busiest CTA,
+  // but no unit is cut, so nothing is published to and merged from the workspace.
+  const int n_units = n_items * Hkv;
+  if (n_units <= (int)gridDim.x && (long long)misc[2] * gridDim.x * 10 <= T * 13) {
+    x0 = x1 = 0;
+    if (cta < n_units) {
+      const int it = cta / Hkv, h = cta - it * Hkv;
+      const int nch = (prefix[it + 1] - prefix[it]) / Hkv;
+      x0 = (long long)prefix[it] + (long long)h * nch;
+      x1 = x0 + nch;
+    }
+  }
 
   // query rows that see no key at all (nothing cached) get zeros
   for (int u = cta; any_empty && u < n_items * Hkv; u += gridDim.x) {
