@@ -740,18 +740,18 @@ __global__ void __launch_bounds__(threads_of(UMMA), 1)
       for (int n = 0; n < ON; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
     }
 
-#ifdef PACE_SKIP_MATH
-    if (false) {
-#else
     // The chunk's keys are dealt to the NS warps of a row tile in equal slices of whole 8-key tiles:
     // a short chunk (a page of 33..63 tokens, a sequence's last chunk) keeps every warp busy instead of
     // filling the first slices only.  Row tiles made of padding rows only sit the chunk out.
     int tw = TW;
     if (SL > 1 && NT > 1 && rows < kChunk) tw = min(TW, (((rows + SL - 1) / SL) + 7) & ~7);
     const int tw0 = (ns % SL) * tw;
+#ifdef PACE_SKIP_MATH
+    const bool mine = false;  // (measurement builds: the ring alone, no arithmetic)
+#else
     const bool mine = (i % DG) == (ns / SL);
-    if (mine && tw0 < rows && mt * 16 < fin.live) {
 #endif
+    if (mine && tw0 < rows && mt * 16 < fin.live) {
       const uint32_t kb = smem_u32(st), vb = kb + KVB;
       // ---- S = Q K^T ----
       // (the k-steps of a tile go to CH independent accumulators: a chain of dependent MMAs is the
