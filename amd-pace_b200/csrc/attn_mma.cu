@@ -39,7 +39,6 @@ __host__ __device__ constexpr int threads_of(bool umma) { return umma ? kThreads
 constexpr int kChunk = 64;
 constexpr int kMaxStagesM = 8;
 constexpr int kMaxItems = 1024;
-constexpr int kWholeUnitsMax = 4;  // most whole units a CTA takes before the chunk-balanced partition is preferred
 
 struct MetaM {  // one 64-byte record per ring stage, written by the producer
   int rows, tok0, flags, kvs;
@@ -451,14 +450,14 @@ __global__ void __launch_bounds__(threads_of(UMMA), 1)
                  : (int)(((x + 1) * NC + T - 1) / T) - 1;
   };
   long long x0 = cta < NC ? range_begin(cta) : 0, x1 = cta < NC ? range_begin(cta + 1) : 0;
-  // When giving every CTA a few WHOLE units keeps the busiest CTA within 1.2x of an equal share of the
+  // When giving every CTA the same number of WHOLE units keeps the busiest CTA within 1.2x of an equal share of the
   // chunks, do that instead: a little more streaming for the busiest CTA (and some SMs idle), but no unit
   // is cut, so nothing is published to and merged from the workspace and no CTA waits for a last
   // arriver.  (Batch 32 x 8 KV heads on 148 SMs: 128 CTAs take two units each; measured 22.5 us against
   // 23.5 us for the chunk-balanced partition.  PARD verify, 128 units: 24.9 us against 34.0 us.)
   const int n_units = n_items * Hkv;
   const int per_cta = (n_units + (int)gridDim.x - 1) / (int)gridDim.x;  // whole units per CTA
-  if (per_cta <= kWholeUnitsMax && (long long)per_cta * misc[2] * gridDim.x * 10 <= T * 12) {
+  if ((long long)per_cta * misc[2] * gridDim.x * 10 <= T * 12) {
     x0 = x1 = 0;
     const int u0 = cta * per_cta, u1 = min(n_units, u0 + per_cta);
     if (u0 < n_units) {
