@@ -2,6 +2,7 @@
 // decode kernel.
 #include <cstdlib>
 #include <cstring>
+#include <mutex>
 
 #include "common.cuh"
 
@@ -10,6 +11,46 @@ int decode_cuda_cores(const pace_attn_args_t* a, void* stream);
 int run_mma_paged(const pace_attn_args_t* a, int causal, cudaStream_t stream);
 uint64_t decode_workspace_bytes(int batch, int n_q_heads, int n_kv_heads, int head_dim);
 uint64_t mma_workspace_bytes(int n_q_heads, int n_kv_heads, int head_dim, int q_len);
+}  // namespace pace
+
+namespace pace {
+namespace {
+struct StreamNote {
+  cudaStream_t stream;
+  int device;
+  bool uses_workspace;
+};
+std::mutex g_note_mu;
+StreamNote g_notes[64];
+int g_n_notes = 0, g_next_note = 0;
+}  // namespace
+
+void note_attention_launch(cudaStream_t stream, bool uses_workspace) {
+  int dev = 0;
+  cudaGetDevice(&dev);
+  std::lock_guard<std::mutex> lk(g_note_mu);
+  for (int i = 0; i < g_n_notes; ++i)
+    if (g_notes[i].stream == stream && g_notes[i].device == dev) {
+      g_notes[i].uses_workspace = uses_workspace;
+      return;
+    }
+  // a full table recycles its oldest entry; a stream that lost its note counts as "uses the workspace"
+  StreamNote& n = g_notes[g_next_note];
+  g_next_note = (g_next_note + 1) % 64;
+  if (g_n_notes < 64) ++g_n_notes;
+  n.stream = stream;
+  n.device = dev;
+  n.uses_workspace = uses_workspace;
+}
+
+bool front_attention_uses_workspace(cudaStream_t stream) {
+  int dev = 0;
+  cudaGetDevice(&dev);
+  std::lock_guard<std::mutex> lk(g_note_mu);
+  for (int i = 0; i < g_n_notes; ++i)
+    if (g_notes[i].stream == stream && g_notes[i].device == dev) return g_notes[i].uses_workspace;
+  return true;
+}
 }  // namespace pace
 
 using namespace pace;

@@ -31,11 +31,10 @@
 namespace pace {
 namespace {
 
-constexpr int kWarps = 8;
-constexpr int kCThreads = kWarps * 32;
-constexpr int kThreadsM = kCThreads + 64;  // + producer warp + epilogue warp
-constexpr int kThreadsU = kCThreads + 96;  // tcgen05 variant: + producer warp + two MMA issuer warps
-__host__ __device__ constexpr int threads_of(bool umma) { return umma ? kThreadsU : kThreadsM; }
+// Threads of a CTA with nw consumer warps: + producer warp + epilogue warp (tcgen05 variant: + producer
+// warp + two MMA issuer warps).  Eight consumer warps and one CTA per SM, or - decode only - four and
+// two CTAs per SM, so that CTAs of the next launch on the stream move in beside CTAs of this one.
+__host__ __device__ constexpr int threads_of(bool umma, int nw = 8) { return nw * 32 + (umma ? 96 : 64); }
 constexpr int kChunk = 64;
 constexpr int kMaxStagesM = 8;
 constexpr int kMaxItems = 1024;
@@ -58,6 +57,7 @@ struct MmaParams {
   const int32_t* kv_start;
   const int32_t* q_lens;
   int batch, q_len, G, n_qt, causal;
+  int whole_units;  // never cut a unit across CTAs (no workspace traffic)
   float scale_log2;
   float* parts;
   int32_t* unit_count;
@@ -75,7 +75,8 @@ __device__ __forceinline__ int chunks_of_m(const MmaParams& p, int len) {
   return full * p.chunks_per_page + (rem + kChunk - 1) / kChunk;
 }
 
-__device__ __forceinline__ void csync() { asm volatile("bar.sync 1, %0;" ::"n"(kCThreads) : "memory"); }
+template <int CTHR>
+__device__ __forceinline__ void csync() { asm volatile("bar.sync 1, %0;" ::"n"(CTHR) : "memory"); }
 
 __device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
@@ -127,20 +128,25 @@ __host__ __device__ inline SmemPlan plan_smem(int D, int MT, int NS, int n_stage
     return o;
   };
   s.ring = take(n_stages * 2 * kChunk * D * 2, 1024);
-  s.qbuf = umma ? take(MR * D * 2, 1024) : take(MR * QS, 128);
+  // (mma.sync kernels: only the live rows are ever written; a fragment load of the padding rows of the
+  // last 8-row group and beyond reads whatever follows in shared memory, which no live row depends on)
+  const int q_rows = MR < ((live_max + 7) & ~7) ? MR : ((live_max + 7) & ~7);
+  s.qbuf = umma ? take(MR * D * 2, 1024) : take(q_rows * QS, 128);
   s.mg_stride = D + 8;  // floats; the pad spreads the rows of a fragment over the banks
   s.mg = take(umma ? 4 * MR * 4 : (NS > 1 ? NS * live_max * (s.mg_stride + 2) * 4 : 16), 16);
   s.n_res = live_max <= 64 ? 2 : 1;
   s.res_slot_bytes = (live_max * (D + 2) * 4 + 64 + 15) / 16 * 16;
   s.res = take(umma ? 16 : s.n_res * s.res_slot_bytes, 16);
-  s.metas = take(kMaxStagesM * (int)sizeof(MetaM), 64);
-  s.bars = take((2 * kMaxStagesM + 1 + 4 + 20) * 8, 8);
+  s.metas = take(n_stages * (int)sizeof(MetaM), 64);
+  s.bars = take((2 * kMaxStagesM + 1 + 4 + (umma ? 20 : 0)) * 8, 8);
   s.misc = take(8 * 4, 4);
   s.per_b = take(batch * 4 * 4, 4);
   s.prefix = take((n_items + 1) * 4, 4);
   s.total = (off + 15) / 16 * 16;
   return s;
 }
+
+constexpr int kHalfSmemBudget = 113 * 1024;  // two CTAs per SM: 228 KB less the 1 KB the system keeps per CTA
 
 struct ResMeta {  // trails each result slot
   int b, h, r_lo, live, mode, parts, first_cta, first_slot, unit, last_part, pad[6];
@@ -162,7 +168,7 @@ __device__ __forceinline__ void publish_part(const MmaParams& p, const ResMeta& 
   constexpr int REC = MR * (D + 2);
   const int G = p.G, live = rm.live;
   auto group_sync = [&]() {
-    if (WARP) __syncwarp(); else csync();
+    if (WARP) __syncwarp(); else csync<NTHR>();
   };
   if (rm.mode == 0) {
     for (int oi = t * 2; oi < live * D; oi += NTHR * 2) {
@@ -186,9 +192,9 @@ __device__ __forceinline__ void publish_part(const MmaParams& p, const ResMeta& 
       *flag = (seen == rm.parts - 1);
       if (seen == rm.parts - 1) p.unit_count[rm.unit] = 0;  // ready for the next launch
     }
-    csync();
+    csync<NTHR>();
     if (*flag) own = cta - rm.first_cta;
-    csync();  // flag is rewritten below
+    csync<NTHR>();  // flag is rewritten below
   }
   float* rec = p.parts + ((size_t)cta * 2 + (rm.mode == 2 ? 1 : 0)) * REC;
   if (own < 0) {
@@ -210,7 +216,7 @@ __device__ __forceinline__ void publish_part(const MmaParams& p, const ResMeta& 
   if (WARP) {
     is_last = __shfl_sync(0xffffffffu, is_last, 0);
   } else {
-    csync();
+    csync<NTHR>();
     is_last = *flag;
   }
   if (!is_last) return;
@@ -260,22 +266,26 @@ __device__ __forceinline__ void publish_part(const MmaParams& p, const ResMeta& 
 }
 
 template <int D, int MT, int NS, bool UMMA = false>
-__global__ void __launch_bounds__(threads_of(UMMA), 1)
+__global__ void __launch_bounds__(threads_of(UMMA, MT * NS), MT * NS == 4 ? 2 : 1)
     attn_mma_kernel(const MmaParams p, const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV) {
-  static_assert(MT * NS == kWarps, "eight consumer warps");
-  constexpr int NTHR = threads_of(UMMA);
+  constexpr int NW = MT * NS;      // consumer warps
+  constexpr int CTHR = NW * 32;
+  static_assert(NW == 8 || (NW == 4 && MT == 1 && !UMMA), "eight consumer warps, or four in the two-per-SM decode form");
+  constexpr int NTHR = threads_of(UMMA, NW);
   static_assert(!UMMA || (MT == 8 && NS == 1), "the tcgen05 variant works on whole 128-row tiles");
   // How the NS warps of a row tile share the key stream: DG groups of SL warps; chunk i goes to group
   // i % DG, whose warps cut its keys into SL slices.  Verify tiles (MT, NS >= 2): DG = NS, whole chunks
   // are dealt round-robin to the warps, so NS chunks are in flight in the tensor pipe at a time and a
-  // warp's MMA chains have 8 independent tiles to overlap.  Decode (MT == 1): two groups of four warps,
-  // 16 keys per warp - one group works on chunk i while the other already has chunk i + 1 (measured on
-  // batch 32, 600 cached tokens: 22.6 us with one group of eight slices, 21.5 us with two groups, 22.6 us
-  // with four, 24.5 us with whole chunks per warp).
+  // warp's MMA chains have 8 independent tiles to overlap.  Decode (MT == 1) with eight warps: two groups
+  // of four warps, 16 keys per warp - one group works on chunk i while the other already has chunk i + 1
+  // (measured on batch 32, 600 cached tokens: 22.6 us with one group of eight slices, 21.5 us with two
+  // groups, 22.6 us with four, 24.5 us with whole chunks per warp).  Decode with four warps (two CTAs per
+  // SM, each with its own producer warp and a three-stage ring): one group, 16 keys per warp; the two
+  // CTAs of an SM are the two groups, and they drift apart instead of marching in step - 19.3 us.
 #ifndef PACE_DECODE_DEAL
 #define PACE_DECODE_DEAL 2
 #endif
-  constexpr int DG = (MT >= 2 && NS >= 2) ? NS : (MT == 1 ? PACE_DECODE_DEAL : 1);
+  constexpr int DG = (MT >= 2 && NS >= 2) ? NS : (MT == 1 ? (NS == 4 ? 1 : PACE_DECODE_DEAL) : 1);
   constexpr int SL = NS / DG;
   constexpr int TW = kChunk / SL;  // keys of a chunk one warp works on
   constexpr int NT = TW / 8;                              // score n-tiles per warp
@@ -315,9 +325,6 @@ __global__ void __launch_bounds__(threads_of(UMMA), 1)
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int Hkv = p.kv.n_kv_heads, P = p.kv.page_tokens, G = p.G;
-  // a kernel launched as a programmatic dependent of this one (the next layer's K/V append, which
-  // touches nothing this kernel reads or writes) may start as soon as every CTA is past this point
-  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 #ifdef PACE_TIMING
   // (measurement builds only: the stamps land behind the partial records, so the caller must pass a
   // workspace some 64 KB larger than pace_attn_workspace_bytes asks for)
@@ -340,9 +347,9 @@ __global__ void __launch_bounds__(threads_of(UMMA), 1)
   if (tid >= NTHR - 32) {
     const int k = tid - (NTHR - 32);
     if (k < n_stages) mbar_init(&full_bar[k], 1);
-    else if (k < 2 * n_stages) mbar_init(&empty_bar[k - n_stages], UMMA ? 1 : kWarps);
-    else if (k == 2 * n_stages) mbar_init(q_empty, kWarps);
-    else if (k < 2 * n_stages + 3) mbar_init(&res_full[k - 2 * n_stages - 1], kWarps);
+    else if (k < 2 * n_stages) mbar_init(&empty_bar[k - n_stages], UMMA ? 1 : NW);
+    else if (k == 2 * n_stages) mbar_init(q_empty, NW);
+    else if (k < 2 * n_stages + 3) mbar_init(&res_full[k - 2 * n_stages - 1], NW);
     else if (k < 2 * n_stages + 5) mbar_init(&res_empty[k - 2 * n_stages - 3], 1);
     if (k == 30) misc[2] = 0;  // longest unit, in chunks (a maximum over the items, taken below)
     if (UMMA && k == 31) {
@@ -363,6 +370,12 @@ __global__ void __launch_bounds__(threads_of(UMMA), 1)
     for (int i = tid; i < KVB / 16; i += NTHR) z[i] = make_uint4(0, 0, 0, 0);
   }
   asm volatile("griddepcontrol.wait;" ::: "memory");
+  // A kernel launched as a programmatic dependent of this one (the next layer's K/V append, which
+  // touches nothing this kernel reads or writes) may start once every CTA is past this point.  The
+  // trigger comes after the wait on purpose: a dependent that starts then knows that the kernel in
+  // front of this one has completed, which is what keeps two launches that use the workspace apart
+  // (see the appends' trailing wait).
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   // ---- prologue, part 2: per-sequence lengths -> chunk prefix -> this CTA's range ----
   int my_slot[(kMaxItems + NTHR - 1) / NTHR];
   int my_len[(kMaxItems + NTHR - 1) / NTHR];
@@ -450,14 +463,17 @@ __global__ void __launch_bounds__(threads_of(UMMA), 1)
                  : (int)(((x + 1) * NC + T - 1) / T) - 1;
   };
   long long x0 = cta < NC ? range_begin(cta) : 0, x1 = cta < NC ? range_begin(cta + 1) : 0;
-  // When giving every CTA the same number of WHOLE units keeps the busiest CTA within 1.2x of an equal share of the
+  // When giving every CTA the same number of WHOLE units keeps the busiest CTA within 1.3x of an equal share of the
   // chunks, do that instead: a little more streaming for the busiest CTA (and some SMs idle), but no unit
   // is cut, so nothing is published to and merged from the workspace and no CTA waits for a last
-  // arriver.  (Batch 32 x 8 KV heads on 148 SMs: 128 CTAs take two units each; measured 22.5 us against
-  // 23.5 us for the chunk-balanced partition.  PARD verify, 128 units: 24.9 us against 34.0 us.)
+  // arriver.  (Batch 32 x 8 KV heads: on 148 eight-warp CTAs, two units each, measured 22.5 us against
+  // 23.5 us for the chunk-balanced partition; on 296 four-warp CTAs, one unit each and 1.24x the equal
+  // share, 19.1 us against 19.6 us.  PARD verify, 128 units: 24.9 us against 34.0 us.)
   const int n_units = n_items * Hkv;
   const int per_cta = (n_units + (int)gridDim.x - 1) / (int)gridDim.x;  // whole units per CTA
-  if ((long long)per_cta * misc[2] * gridDim.x * 10 <= T * 12) {
+  // p.whole_units: the caller asked for this form whatever the balance; such a launch never touches
+  // the workspace.
+  if (p.whole_units || (long long)per_cta * misc[2] * gridDim.x * 10 <= T * 13) {
     x0 = x1 = 0;
     const int u0 = cta * per_cta, u1 = min(n_units, u0 + per_cta);
     if (u0 < n_units) {
@@ -487,7 +503,7 @@ __global__ void __launch_bounds__(threads_of(UMMA), 1)
   if (tid == 0) PACE_STAMP(1);
   if (tid == 0) PACE_TRACE(3, 6);
 
-  if (warp == kWarps) {
+  if (warp == NW) {
     // ================================ producer ================================
     // One warp feeds the ring.  Everything costly (table walks, divisions, the partition
     // arithmetic, the 48-byte part record) happens once per unit part; one iteration of the
@@ -653,7 +669,7 @@ __global__ void __launch_bounds__(threads_of(UMMA), 1)
     return;
   }
 
-  if (warp == kWarps + 1) {
+  if (warp == NW + 1) {
     // ================================ epilogue warp ================================
     // Takes each finished unit part from shared memory to global memory: the output rows, or an
     // fp32 partial plus the arrival count (and the merge, when this CTA arrives last).  The global
@@ -905,7 +921,7 @@ __global__ void __launch_bounds__(threads_of(UMMA), 1)
       bool ok_res = true;
       if (NS > 1) {
         // the NS token slices of each row meet in shared memory
-        csync();  // every thread is done reading the merge buffer for the previous part
+        csync<CTHR>();  // every thread is done reading the merge buffer for the previous part
         float* wo = mg_o + (size_t)ns * p.live_max * sp.mg_stride;
         if (row0 < live) {
 #pragma unroll
@@ -926,8 +942,8 @@ __global__ void __launch_bounds__(threads_of(UMMA), 1)
           }
         }
         if (n_parts_done >= sp.n_res) ok_res = mbar_wait(&res_empty[rs], ((n_parts_done / sp.n_res) - 1) & 1);
-        csync();
-        for (int oi = tid; oi < live * D; oi += kCThreads) {
+        csync<CTHR>();
+        for (int oi = tid; oi < live * D; oi += CTHR) {
           const int row = oi / D, d = oi - row * D;
           float M = -INFINITY;
 #pragma unroll
@@ -981,8 +997,8 @@ __global__ void __launch_bounds__(threads_of(UMMA), 1)
       if (fin.last_part) {
         // nothing is left to stream: all eight warps take the result out (the epilogue warp only
         // wakes up to leave), which keeps the kernel's tail short
-        csync();
-        publish_part<D, MR, kCThreads, false>(p, fin, rnum, rM, rden, tid, cta, misc);
+        csync<CTHR>();
+        publish_part<D, MR, CTHR, false>(p, fin, rnum, rM, rden, tid, cta, misc);
         if (tid == 0) PACE_STAMP(5);
       }
     }
@@ -1076,6 +1092,12 @@ bool pdl_enabled() {
   return on;
 }
 
+// PACE_DECODE_HALF=0 keeps decode on eight-warp CTAs, one per SM (A/B measurements)
+bool decode_half_enabled() {
+  const char* e = getenv("PACE_DECODE_HALF");
+  return !(e && e[0] == '0');
+}
+
 // Fewest query rows (tokens x grouped heads) for which a tile goes to the tcgen05 variant; 0 = never.
 // At 33 rows and more (PARD verify: 9 tokens x 4 grouped heads = 36) a 128-row tile, three quarters of
 // it padding, already beats the mma.sync kernel's 64-row tiles: the MMAs cost the softmax warps
@@ -1091,9 +1113,11 @@ int umma_min_rows() {
 template <int D, int MT, int NS, bool UMMA = false>
 int launch_mma(MmaParams& p, const CUtensorMap& tmK, const CUtensorMap& tmV, int grid, cudaStream_t stream) {
   constexpr int MR = 16 * MT;
+  constexpr int NW = MT * NS;
   const int n_items = p.batch * p.n_qt;
   p.live_max = p.G * p.q_len < MR ? p.G * p.q_len : MR;
-  const int budget = 226 * 1024;
+  // two CTAs per SM (four consumer warps): 228 KB of shared memory less 1 KB the system keeps per CTA
+  const int budget = NW == 4 ? kHalfSmemBudget : 226 * 1024;
   int ns = kMaxStagesM;
   while (ns >= 2 && plan_smem(D, MT, NS, ns, p.live_max, p.batch, n_items, UMMA).total > budget) --ns;
   if (ns < 2) return PACE_ERR_UNSUPPORTED;
@@ -1105,11 +1129,13 @@ int launch_mma(MmaParams& p, const CUtensorMap& tmK, const CUtensorMap& tmV, int
   if (dev >= 16 || !configured[dev]) {
     PACE_CUDA_TRY(cudaFuncSetAttribute(attn_mma_kernel<D, MT, NS, UMMA>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        budget));
+    PACE_CUDA_TRY(cudaFuncSetAttribute(attn_mma_kernel<D, MT, NS, UMMA>,
+                                       cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
     if (dev < 16) configured[dev] = true;
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)grid);
-  cfg.blockDim = dim3(threads_of(UMMA));
+  cfg.blockDim = dim3(threads_of(UMMA, NW));
   cfg.dynamicSmemBytes = smem_bytes;
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
@@ -1119,6 +1145,7 @@ int launch_mma(MmaParams& p, const CUtensorMap& tmK, const CUtensorMap& tmV, int
   cfg.numAttrs = pdl_enabled() ? 1 : 0;
   PACE_CUDA_TRY(cudaLaunchKernelEx(&cfg, attn_mma_kernel<D, MT, NS, UMMA>, p, tmK, tmV));
   PACE_LAUNCH_CHECK("attn_mma_kernel");
+  note_attention_launch(stream, /*uses_workspace=*/!p.whole_units);
   return PACE_OK;
 }
 
@@ -1128,7 +1155,8 @@ uint64_t mma_workspace_bytes(int n_q_heads, int n_kv_heads, int head_dim, int q_
   const int G = n_q_heads / (n_kv_heads > 0 ? n_kv_heads : 1);
   const int M = G * q_len;
   const int MT = (umma_min_rows() > 0 && M >= umma_min_rows()) ? 8 : M <= 16 ? 1 : M <= 32 ? 2 : M <= 64 ? 4 : 8;
-  return kWorkspaceCounterBytes + (uint64_t)sm_count_m() * 2 * (16 * MT) * (head_dim + 2) * sizeof(float) + 256;
+  const int ctas = (MT == 1 ? 2 : 1) * sm_count_m();  // decode runs two four-warp CTAs per SM
+  return kWorkspaceCounterBytes + (uint64_t)ctas * 2 * (16 * MT) * (head_dim + 2) * sizeof(float) + 256;
 }
 
 // One launch per slice of the batch small enough for the shared-memory prefix array.
@@ -1136,7 +1164,7 @@ int run_mma(const KVView& kv, const CUtensorMap& tmK, const CUtensorMap& tmV, in
             int n_q_heads, int q_len, const void* q, int64_t q_sb, int64_t q_sh, int64_t q_ss, void* out, int64_t o_sb,
             int64_t o_sh, int64_t o_ss, const int32_t* kv_start, const int32_t* q_lens, int causal, float scale,
             const void* mask, int mask_fp32, int mask_rows, int64_t mask_sb, void* workspace, uint64_t workspace_bytes,
-            cudaStream_t stream) {
+            uint32_t flags, cudaStream_t stream) {
   const int D = kv.head_dim, Hkv = kv.n_kv_heads;
   if (batch <= 0 || q_len <= 0) return PACE_OK;
   if (n_q_heads % Hkv) return PACE_ERR_INVALID;
@@ -1151,12 +1179,20 @@ int run_mma(const KVView& kv, const CUtensorMap& tmK, const CUtensorMap& tmV, in
   const int MT = umma ? 8 : M <= 16 ? 1 : M <= 32 ? 2 : M <= 64 ? 4 : 8;
   const int MR = 16 * MT;
   int grid = sm_count_m();
+  auto workspace_for = [&](int ctas) { return kWorkspaceCounterBytes + (uint64_t)ctas * 2 * MR * (D + 2) * sizeof(float); };
+  // Decode: CTAs of four consumer warps, two per SM, when the workspace has room for their partial
+  // records (the fixed scratch of pace_attn_decode_static has not).
+  // ... and three ring stages fit beside the per-sequence arrays (they do up to a batch of about 80).
+  const int live = G * q_len < MR ? G * q_len : MR;
+  const int slice = batch < kMaxItems ? batch : kMaxItems;
+  const bool half = MT == 1 && decode_half_enabled() && workspace_bytes >= workspace_for(2 * grid) &&
+                    plan_smem(D, 1, 4, 3, live, slice, slice, false).total <= kHalfSmemBudget;
+  if (half) grid *= 2;
   if (const char* g = getenv("PACE_DECODE_GRID")) {  // test hook: other partitions of the same work
     const int v = atoi(g);
     if (v > 0 && v < grid) grid = v;
   }
-  if (workspace_bytes < kWorkspaceCounterBytes + (uint64_t)grid * 2 * MR * (D + 2) * sizeof(float))
-    return PACE_ERR_INVALID;
+  if (workspace_bytes < workspace_for(grid)) return PACE_ERR_INVALID;
 
   MmaParams p;
   p.kv = kv;
@@ -1172,6 +1208,7 @@ int run_mma(const KVView& kv, const CUtensorMap& tmK, const CUtensorMap& tmV, in
   p.G = G;
   p.n_qt = (M + MR - 1) / MR;
   p.causal = causal;
+  p.whole_units = (flags & PACE_ATTN_WHOLE_UNITS) ? 1 : 0;
   p.scale_log2 = (scale > 0.f ? scale : 1.0f / sqrtf((float)D)) * kLog2e;
   p.unit_count = reinterpret_cast<int32_t*>(workspace);
   p.parts = reinterpret_cast<float*>(static_cast<char*>(workspace) + kWorkspaceCounterBytes);
@@ -1214,11 +1251,16 @@ int run_mma(const KVView& kv, const CUtensorMap& tmK, const CUtensorMap& tmV, in
       if (D == 128) rc = launch_mma<128, 8, 1, true>(p, tmK, tmV, grid, stream);
       if (D == 64) rc = launch_mma<64, 8, 1, true>(p, tmK, tmV, grid, stream);
     } else {
-      PACE_MMA_CASE(128, 1, 8)
+      if (half) {
+        if (D == 128) rc = launch_mma<128, 1, 4>(p, tmK, tmV, grid, stream);
+        if (D == 64) rc = launch_mma<64, 1, 4>(p, tmK, tmV, grid, stream);
+      } else {
+        PACE_MMA_CASE(128, 1, 8)
+        PACE_MMA_CASE(64, 1, 8)
+      }
       PACE_MMA_CASE(128, 2, 4)
       PACE_MMA_CASE(128, 4, 2)
       PACE_MMA_CASE(128, 8, 1)
-      PACE_MMA_CASE(64, 1, 8)
       PACE_MMA_CASE(64, 2, 4)
       PACE_MMA_CASE(64, 4, 2)
       PACE_MMA_CASE(64, 8, 1)
@@ -1238,7 +1280,7 @@ int run_mma_paged(const pace_attn_args_t* a, int causal, cudaStream_t stream) {
   const KVView kv = make_view(a->pool, a->layer, a->seq_ids);
   return run_mma(kv, tm, tm, a->layer * 2, a->layer * 2 + 1, a->batch, a->n_q_heads, a->q_len, a->q, a->q_stride_b,
                  a->q_stride_h, a->q_stride_s, a->out, a->o_stride_b, a->o_stride_h, a->o_stride_s, a->kv_start,
-                 a->q_lens, causal, a->scale, nullptr, 0, 1, 0, a->workspace, a->workspace_bytes, stream);
+                 a->q_lens, causal, a->scale, nullptr, 0, 1, 0, a->workspace, a->workspace_bytes, a->flags, stream);
 }
 
 }  // namespace pace
@@ -1343,5 +1385,5 @@ extern "C" int pace_attention_dense(const void* q, const void* k, const void* v,
   if (rc != PACE_OK) return rc;
   return run_mma(kv, tmK, tmV, 0, 0, B, N, S, q, (int64_t)N * S * H, (int64_t)S * H, H, out, (int64_t)N * S * H,
                  (int64_t)S * H, H, nullptr, nullptr, /*causal=*/0, 0.f, mask, mask_is_fp32, mask_rows,
-                 (int64_t)mask_rows * L, workspace, workspace_bytes, (cudaStream_t)stream);
+                 (int64_t)mask_rows * L, workspace, workspace_bytes, 0u, (cudaStream_t)stream);
 }

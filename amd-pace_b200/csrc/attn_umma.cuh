@@ -220,9 +220,17 @@ __device__ __forceinline__ void umma_issue_qk(const UmmaCtx& c, uint32_t tmem, i
         ++part;
       }
       const bool two = left >= 2 && s + 1 < c.n_stages && b + 1 < kScoreBufs;
-      if (two && !issuer_wait(c, &c.full_bar[s + 1], ph)) break;
-      if (i >= kScoreBufs && !issuer_wait(c, &c.p_free[b], phb)) break;
-      if (two && i + 1 >= kScoreBufs && !issuer_wait(c, &c.p_free[b + 1], phb)) break;
+      {
+        // up to three more barriers stand between this thread and the issue: probe them together (the
+        // probes' latencies overlap) and wait one by one only for those that have not completed yet
+        const bool w1 = two, w2 = i >= kScoreBufs, w3 = two && i + 1 >= kScoreBufs;
+        const bool r1 = !w1 || mbar_test_wait(&c.full_bar[s + 1], ph);
+        const bool r2 = !w2 || mbar_test_wait(&c.p_free[b], phb);
+        const bool r3 = !w3 || mbar_test_wait(&c.p_free[b + 1], phb);
+        if (!r1 && !issuer_wait(c, &c.full_bar[s + 1], ph)) break;
+        if (!r2 && !issuer_wait(c, &c.p_free[b], phb)) break;
+        if (!r3 && !issuer_wait(c, &c.p_free[b + 1], phb)) break;
+      }
       tc_fence_after();  // the PVs that read P from these buffers are done
 #ifdef PACE_TIMING
       const long long ck0 = clock64();

@@ -14,6 +14,13 @@ namespace pace {
 // ---------------------------------------------------------------------------
 void set_cuda_error(cudaError_t e, const char* where);
 
+// What the newest tensor-core attention launch on a stream does with its workspace (host-side note,
+// kept per stream).  Those launches let the K/V append behind them start early; the append asks here
+// whether it has to hold its own completion until that launch has completed (see append_kernel).
+// A stream nobody noted counts as "uses the workspace".
+void note_attention_launch(cudaStream_t stream, bool uses_workspace);
+bool front_attention_uses_workspace(cudaStream_t stream);
+
 #define PACE_CUDA_TRY(expr)                         \
   do {                                              \
     cudaError_t _e = (expr);                        \
@@ -181,6 +188,18 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
       "selp.u32 %0, 1, 0, p;\n\t}"
       : "=r"(ok)
       : "r"(smem_u32(bar)), "r"(parity), "r"((uint32_t)PACE_WAIT_HINT_NS)
+      : "memory");
+  return ok != 0;
+}
+// One non-blocking probe.
+__device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
       : "memory");
   return ok != 0;
 }

@@ -223,9 +223,11 @@ __device__ __forceinline__ void advance_lengths_in_last_block(const pace_kv_pool
 __global__ void __launch_bounds__(256)
     append_kernel(pace_kv_pool_t p, int layer, const int32_t* __restrict__ seq_ids, int batch, int n_new,
                   const int32_t* __restrict__ n_per, const __nv_bfloat16* __restrict__ k_new,
-                  const __nv_bfloat16* __restrict__ v_new, int64_t sb, int64_t sh, int64_t st) {
+                  const __nv_bfloat16* __restrict__ v_new, int64_t sb, int64_t sh, int64_t st, int drain) {
   // the attention kernel behind this append may set up while the append runs
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  // (The new rows are read with L2 loads, __ldcg: launched as a programmatic dependent this kernel does
+  // not start with the cache maintenance of a kernel boundary behind it.)
   const int lane = threadIdx.x & 31;
   const int warps_per_block = blockDim.x >> 5;
   const long long total = (long long)batch * n_new * p.n_kv_heads;
@@ -260,14 +262,16 @@ __global__ void __launch_bounds__(256)
     if (l16 < vec_per_row) {
       const uint4* s = reinterpret_cast<const uint4*>((half ? v_new : k_new) + src) + l16;
       uint4* d = reinterpret_cast<uint4*>((half ? vbase : kbase) + dst) + l16;
-      *d = __ldg(s);
+      *d = __ldcg(s);
     }
   }
   advance_lengths_in_last_block(p, layer, seq_ids, batch, n_new, n_per);
   // Launched as a programmatic dependent, the append overlaps the attention kernel in front of it.
-  // It must not COMPLETE before that kernel does: the attention kernel behind the append orders
-  // itself after the append only, and shares its workspace with the one in front.
-  asm volatile("griddepcontrol.wait;" ::: "memory");
+  // drain: it must not COMPLETE before that kernel does - the attention kernel behind the append
+  // orders itself after the append only, and shares its workspace with the one in front.  The host
+  // clears drain when the attention launch in front never touches the workspace: the launch behind
+  // the append then learns of that launch's completion without the detour through this kernel's exit.
+  if (drain) asm volatile("griddepcontrol.wait;" ::: "memory");
 }
 
 // RoPE + append: eight lanes per (sequence, new token, group of kRopeHeads heads) of the projection
@@ -288,7 +292,7 @@ constexpr int kRopeHeads = 6;  // heads per work item: 32 + 2 x 8 heads make eig
 
 __global__ void __launch_bounds__(256, 3)
     append_rope_kernel(pace_kv_pool_t p, int layer, const int32_t* __restrict__ seq_ids, int batch, int n_new,
-                       const int32_t* __restrict__ n_per, RopeParams r) {
+                       const int32_t* __restrict__ n_per, RopeParams r, int drain) {
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const int g = threadIdx.x & 7;
   const int P = p.page_tokens, D = p.head_dim, R = r.rotary_dim, Hkv = p.n_kv_heads, Hq = r.n_q_heads;
@@ -385,11 +389,11 @@ __global__ void __launch_bounds__(256, 3)
           dst[u] = (is_v[u] ? vbase : kbase) + cache_tok + (size_t)h * P * D;
         }
         if (turns && !is_v[u]) {
-          va[u] = __ldg(reinterpret_cast<const uint4*>(src[u] + offA));
-          vb[u] = __ldg(reinterpret_cast<const uint4*>(src[u] + offB));
+          va[u] = __ldcg(reinterpret_cast<const uint4*>(src[u] + offA));
+          vb[u] = __ldcg(reinterpret_cast<const uint4*>(src[u] + offB));
         } else if (D == 128 || g < D / 16) {  // a row that is only copied: this lane's two vectors of it
-          va[u] = __ldg(reinterpret_cast<const uint4*>(src[u]) + g);
-          vb[u] = __ldg(reinterpret_cast<const uint4*>(src[u]) + g + D / 16);
+          va[u] = __ldcg(reinterpret_cast<const uint4*>(src[u]) + g);
+          vb[u] = __ldcg(reinterpret_cast<const uint4*>(src[u]) + g + D / 16);
         }
       }
 #pragma unroll
@@ -424,7 +428,7 @@ __global__ void __launch_bounds__(256, 3)
           *reinterpret_cast<uint4*>(dst[u] + offB) = *reinterpret_cast<const uint4*>(ob);
           // elements beyond the rotated part
           for (int c = R / 8 + g; c < D / 8; c += 8)
-            reinterpret_cast<uint4*>(dst[u])[c] = __ldg(reinterpret_cast<const uint4*>(src[u]) + c);
+            reinterpret_cast<uint4*>(dst[u])[c] = __ldcg(reinterpret_cast<const uint4*>(src[u]) + c);
         } else if (turns || row < 0 || is_v[u]) {
           const bool whole = is_v[u] || row < 0;  // value rows and unrotated tokens are copied whole
           if (whole) {
@@ -434,18 +438,18 @@ __global__ void __launch_bounds__(256, 3)
             }
           } else {
             for (int c = R / 8 + g; c < D / 8; c += 8)
-              reinterpret_cast<uint4*>(dst[u])[c] = __ldg(reinterpret_cast<const uint4*>(src[u]) + c);
+              reinterpret_cast<uint4*>(dst[u])[c] = __ldcg(reinterpret_cast<const uint4*>(src[u]) + c);
           }
         } else {
           // a lane without a rotation block (rotary_dim < 128) of a rotated row: its share of the tail
           for (int c = R / 8 + g; c < D / 8; c += 8)
-            reinterpret_cast<uint4*>(dst[u])[c] = __ldg(reinterpret_cast<const uint4*>(src[u]) + c);
+            reinterpret_cast<uint4*>(dst[u])[c] = __ldcg(reinterpret_cast<const uint4*>(src[u]) + c);
         }
       }
     }
   }
   advance_lengths_in_last_block(p, layer, seq_ids, batch, n_new, n_per);
-  asm volatile("griddepcontrol.wait;" ::: "memory");  // (see append_kernel)
+  if (drain) asm volatile("griddepcontrol.wait;" ::: "memory");  // (see append_kernel)
 }
 
 __global__ void truncate_kernel(pace_kv_pool_t p, int layer_begin, int layer_end, const int32_t* __restrict__ seq_ids,
@@ -733,7 +737,7 @@ int pace_kv_append(const pace_kv_pool_t* p, int32_t layer, const int32_t* seq_id
   cfg.numAttrs = g_pdl_append ? 1 : 0;
   PACE_CUDA_TRY(cudaLaunchKernelEx(&cfg, append_kernel, *p, (int)layer, seq_ids, (int)batch, (int)n_new, n_per,
                                    (const __nv_bfloat16*)k_new, (const __nv_bfloat16*)v_new, (int64_t)sb, (int64_t)sh,
-                                   (int64_t)st));
+                                   (int64_t)st, front_attention_uses_workspace((cudaStream_t)stream) ? 1 : 0));
   PACE_LAUNCH_CHECK("append_kernel");
   return PACE_OK;
 }
@@ -785,7 +789,8 @@ int pace_kv_append_rope(const pace_kv_pool_t* p, int32_t layer, const int32_t* s
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = g_pdl_append ? 1 : 0;
-  PACE_CUDA_TRY(cudaLaunchKernelEx(&cfg, append_rope_kernel, *p, (int)layer, seq_ids, (int)batch, (int)n_new, n_per, r));
+  PACE_CUDA_TRY(cudaLaunchKernelEx(&cfg, append_rope_kernel, *p, (int)layer, seq_ids, (int)batch, (int)n_new, n_per, r,
+                                   front_attention_uses_workspace((cudaStream_t)stream) ? 1 : 0));
   PACE_LAUNCH_CHECK("append_rope_kernel");
   return PACE_OK;
 }

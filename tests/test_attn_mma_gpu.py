@@ -195,6 +195,91 @@ def test_decode_kernels_agree_with_oracle(monkeypatch, impl, B, Hq, Hkv, D, max_
     mgr.pool.check_status()
 
 
+@pytest.mark.parametrize("lens", [[128, 1024, 577, 300], [40 + 17 * i for i in range(48)]])
+def test_decode_whole_units_flag_on_ragged_lengths(monkeypatch, lens):
+    """PACE_ATTN_WHOLE_UNITS only changes the schedule: forced on a ragged batch (where the host
+    would not set it) the result is the oracle's."""
+    from pace_b200.llm.cache import KVCacheManager, KVCacheType
+    from pace_b200.ops import MultiHeadAttention
+    from pace_b200.ops.backends import b200
+    monkeypatch.setattr(b200, "even_lengths", lambda *a, **k: True)
+    B, Hq, Hkv, D = len(lens), 32, 8, 128
+    g = torch.Generator().manual_seed(B)
+    ks = [torch.randn(Hkv, L, D, generator=g).bfloat16().to(DEV) for L in lens]
+    vs = [torch.randn(Hkv, L, D, generator=g).bfloat16().to(DEV) for L in lens]
+    q = torch.randn(B, Hq, 1, D, generator=g).bfloat16().to(DEV)
+    mgr = KVCacheManager(Cfg(1), max(lens) + 1, KVCacheType.BMC)
+    K, V = _fill(mgr, 0, ks, vs)
+    out = MultiHeadAttention()(q, K, V)
+    want = _oracle(q, ks, vs)
+    for b in range(B):
+        _check(out[b], want[b])
+    mgr.pool.check_status()
+
+
+def test_decode_eight_warp_ctas(monkeypatch):
+    """PACE_DECODE_HALF=0: decode on eight-warp thread blocks, one per SM (the form used when the
+    workspace or the shared memory has no room for two four-warp blocks per SM)."""
+    from pace_b200.llm.cache import KVCacheManager, KVCacheType
+    from pace_b200.ops import MultiHeadAttention
+    monkeypatch.setenv("PACE_DECODE_HALF", "0")
+    lens = [513 + 3 * i for i in range(32)]
+    B, Hq, Hkv, D = len(lens), 32, 8, 128
+    g = torch.Generator().manual_seed(77)
+    ks = [torch.randn(Hkv, L, D, generator=g).bfloat16().to(DEV) for L in lens]
+    vs = [torch.randn(Hkv, L, D, generator=g).bfloat16().to(DEV) for L in lens]
+    q = torch.randn(B, Hq, 1, D, generator=g).bfloat16().to(DEV)
+    mgr = KVCacheManager(Cfg(1), 768, KVCacheType.BMC)
+    K, V = _fill(mgr, 0, ks, vs)
+    out = MultiHeadAttention()(q, K, V)
+    want = _oracle(q, ks, vs)
+    for b in range(B):
+        _check(out[b], want[b])
+    mgr.pool.check_status()
+
+
+def test_layers_alternating_whole_units_and_cut_units(monkeypatch):
+    """[append, decode attention] for layer after layer with nothing between the launches, every
+    other attention launch told to keep units whole: the append behind such a launch does not wait
+    for it, the one behind a launch that may use the workspace does.  Every layer's output over
+    several steps is the oracle's."""
+    from pace_b200.llm.cache import KVCacheManager, KVCacheType
+    from pace_b200.ops import MultiHeadAttention
+    from pace_b200.ops.backends import b200
+    L, B, Hq, Hkv, D, steps = 6, 8, 32, 8, 128, 5
+    lens = [300 + 40 * b for b in range(B)]
+    g = torch.Generator().manual_seed(5)
+    ks = [[torch.randn(Hkv, n, D, generator=g).bfloat16().to(DEV) for n in lens] for _ in range(L)]
+    vs = [[torch.randn(Hkv, n, D, generator=g).bfloat16().to(DEV) for n in lens] for _ in range(L)]
+    mgr = KVCacheManager(Cfg(L), max(lens) + steps + 1, KVCacheType.BMC)
+    for l in range(L):
+        _fill(mgr, l, ks[l], vs[l])
+    new = torch.randn(steps, L, B, 2 * Hkv + Hq, 1, D, generator=g).bfloat16().to(DEV)
+    outs = torch.empty(steps, L, B, Hq, 1, D, dtype=torch.bfloat16, device=DEV)
+    mha = MultiHeadAttention()
+    flip = {"n": 0}
+
+    def every_other(*a, **k):
+        flip["n"] += 1
+        return flip["n"] % 2 == 1
+
+    monkeypatch.setattr(b200, "even_lengths", every_other)
+    for t in range(steps):
+        for l in range(L):
+            K, V = mgr[l].update_cache(new[t, l, :, :Hkv], new[t, l, :, Hkv:2 * Hkv], concat_dim=2)
+            mha(new[t, l, :, 2 * Hkv:], K, V, out=outs[t, l])
+    torch.cuda.synchronize()
+    mgr.pool.check_status()
+    for l in (0, 3, 5):
+        kk = [torch.cat([ks[l][b]] + [new[t, l, b, :Hkv, 0][:, None] for t in range(steps)], dim=1) for b in range(B)]
+        vv = [torch.cat([vs[l][b]] + [new[t, l, b, Hkv:2 * Hkv, 0][:, None] for t in range(steps)], dim=1) for b in range(B)]
+        for t in (0, steps - 1):
+            n_t = [lens[b] + t + 1 for b in range(B)]
+            want = _oracle(new[t, l, :, 2 * Hkv:], [kk[b][:, :n_t[b]] for b in range(B)], [vv[b][:, :n_t[b]] for b in range(B)])
+            for b in range(B):
+                _check(outs[t, l, b], want[b])
+
+
 # ---- the dense form: the reference custom op's operands (reference tests/ops/test_sdpa.py:79-127) ----
 @pytest.mark.parametrize("B,N,S,H,L", [(1, 1, 1, 64, 1), (2, 16, 1, 128, 512), (2, 16, 128, 64, 512),
                                        (1, 32, 128, 128, 2048), (3, 4, 7, 128, 33), (32, 1, 1, 64, 512)])
