@@ -369,6 +369,18 @@ __global__ void __launch_bounds__(threads_of(UMMA, MT * NS), MT * NS == 4 ? 2 : 
                                              : ring + (size_t)s * STAGE + KVB);
     for (int i = tid; i < KVB / 16; i += NTHR) z[i] = make_uint4(0, 0, 0, 0);
   }
+  // Short prologue (decode told to keep units whole, PACE_ATTN_WHOLE_UNITS): the CTA's units are known
+  // from its index alone, so the producer warp needs nobody else - it looks up its own few sequences
+  // and starts streaming while the general prologue below would still be counting every sequence's
+  // chunks behind three CTA-wide barriers (about 2 us of a 19 us launch).  The consumers learn where
+  // the CTA's work ends from the chunk records.
+  const int n_units_all = n_items * Hkv;
+  const int per_cta_w = (n_units_all + (int)gridDim.x - 1) / (int)gridDim.x;  // whole units per CTA
+  const bool fast = !UMMA && MT == 1 && p.whole_units && p.n_qt == 1 && (per_cta_w + Hkv - 1) / Hkv + 1 <= 32;
+  if (fast) {
+    fence_proxy_async();  // generic-proxy zero fill before async-proxy (TMA) writes to the same bytes
+    __syncthreads();      // barriers initialised, V slots zeroed: nothing here depends on an earlier kernel
+  }
   asm volatile("griddepcontrol.wait;" ::: "memory");
   // A kernel launched as a programmatic dependent of this one (the next layer's K/V append, which
   // touches nothing this kernel reads or writes) may start once every CTA is past this point.  The
@@ -376,6 +388,93 @@ __global__ void __launch_bounds__(threads_of(UMMA, MT * NS), MT * NS == 4 ? 2 : 
   // front of this one has completed, which is what keeps two launches that use the workspace apart
   // (see the appends' trailing wait).
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  const int cta = blockIdx.x;
+  long long T = 0, x0 = 0, x1 = 0;
+  int NC = 1, n_my = 0;
+  bool small = true;
+  // range boundaries floor(T * c / NC); 32-bit arithmetic whenever it cannot overflow
+  auto range_begin = [&](int c) -> long long {
+    return small ? (long long)((unsigned)T * (unsigned)c / (unsigned)NC) : T * c / NC;
+  };
+  auto cta_of = [&](long long x) -> int {  // the CTA whose range holds chunk x
+    return small ? (int)(((unsigned)(x + 1) * (unsigned)NC + (unsigned)T - 1u) / (unsigned)T) - 1
+                 : (int)(((x + 1) * NC + T - 1) / T) - 1;
+  };
+  PageWindow pw;
+  int pw_slot = -1;  // short prologue: the sequence whose first block-table window is already loaded
+  int fast_it0 = 0, fast_it1 = -1;
+  if (fast) {
+    const int u0 = cta * per_cta_w, u1 = min(n_units_all, u0 + per_cta_w);
+    if (u0 >= n_units_all) return;  // (known from the CTA index: every thread leaves)
+    n_my = INT_MAX;                 // consumers run until the record of the CTA's last chunk
+    if (warp == NW) {
+      const int it0 = u0 / Hkv, it1 = (u1 - 1) / Hkv;
+      fast_it0 = it0;
+      fast_it1 = it1;
+      const int b = it0 + lane;  // one lane per sequence this CTA touches
+      int n = 0, slot = -1;
+      if (b <= it1) {
+        slot = view_slot(p.kv, b);
+        const int len = slot >= 0 ? view_len(p.kv, slot) : 0;
+        const int S = p.q_lens ? min(p.q_lens[b], p.q_len) : p.q_len;
+        sb_slot[b] = slot;
+        sb_len[b] = len;
+        sb_kvs[b] = p.kv_start ? p.kv_start[b] : 0;
+        sb_S[b] = S;
+        if (slot >= 0 && S > 0) {
+          const int s_hi = min(S - 1, (MR - 1) / G);
+          const int hi = p.causal ? len - S + s_hi + 1 : len;
+          n = chunks_of_m(p, min(hi, len)) * Hkv;
+        }
+      }
+      // the first sequence's block-table window: its load is in flight while the lengths arrive
+      const int slot0 = __shfl_sync(0xffffffffu, slot, 0);
+      if (slot0 >= 0) {
+        const int step0 = p.pages_per_chunk > 0 ? (32 / p.pages_per_chunk) * p.pages_per_chunk : 32;
+        pw.start(p.kv, slot0, 0, step0, lane);
+        pw_slot = slot0;
+      }
+      int v = n;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int t = __shfl_up_sync(0xffffffffu, v, o);
+        if (lane >= o) v += t;
+      }
+      // chunk coordinates local to this CTA: the first sequence it touches starts at 0
+      if (b <= it1) prefix[b + 1] = v;
+      if (lane == 0) prefix[it0] = 0;
+      __syncwarp();
+      const int h0 = u0 - it0 * Hkv, h1 = (u1 - 1) - it1 * Hkv;
+      x0 = (long long)prefix[it0] + (long long)h0 * ((prefix[it0 + 1] - prefix[it0]) / Hkv);
+      x1 = (long long)prefix[it1] + (long long)(h1 + 1) * ((prefix[it1 + 1] - prefix[it1]) / Hkv);
+      // query rows that see no key at all (nothing cached) get zeros
+      for (int u = u0; u < u1; ++u) {
+        const int it = u / Hkv, h = u - it * Hkv;
+        if (prefix[it + 1] != prefix[it]) continue;
+        const int R = sb_S[it] * G;
+        for (int o = lane; o < MR * D; o += 32) {
+          const int r = o / D, d = o % D;
+          if (r < R) {
+            const int sq = r / G, g = r - sq * G;
+            p.out[(size_t)it * p.o_sb + (size_t)(h * G + g) * p.o_sh + (size_t)sq * p.o_ss + d] = __float2bfloat16(0.f);
+          }
+        }
+      }
+      n_my = (int)(x1 - x0);
+      if (n_my <= 0) {
+        // nothing to stream: a record that says so for the consumers, a result slot that says so for
+        // the epilogue warp
+        if (lane == 0) {
+          metas[0].flags = 8;
+          mbar_arrive(&full_bar[0]);
+          float* rden0 = reinterpret_cast<float*>(res) + p.live_max * D + p.live_max;
+          reinterpret_cast<ResMeta*>(rden0 + p.live_max)->last_part = 1;
+          for (int k = 0; k < NW; ++k) mbar_arrive(&res_full[0]);
+        }
+        return;
+      }
+    }
+  } else {
   // ---- prologue, part 2: per-sequence lengths -> chunk prefix -> this CTA's range ----
   int my_slot[(kMaxItems + NTHR - 1) / NTHR];
   int my_len[(kMaxItems + NTHR - 1) / NTHR];
@@ -450,19 +549,11 @@ __global__ void __launch_bounds__(threads_of(UMMA, MT * NS), MT * NS == 4 ? 2 : 
   }
   __syncthreads();
   if (tid == 0) PACE_TRACE(3, 5);
-  const long long T = prefix[n_items];
-  const int NC = (long long)gridDim.x < T ? (int)gridDim.x : (int)T;
-  const int cta = blockIdx.x;
-  // range boundaries floor(T * c / NC); 32-bit arithmetic whenever it cannot overflow
-  const bool small = (T + 1) * (NC + 1) < (1LL << 31);
-  auto range_begin = [&](int c) -> long long {
-    return small ? (long long)((unsigned)T * (unsigned)c / (unsigned)NC) : T * c / NC;
-  };
-  auto cta_of = [&](long long x) -> int {  // the CTA whose range holds chunk x
-    return small ? (int)(((unsigned)(x + 1) * (unsigned)NC + (unsigned)T - 1u) / (unsigned)T) - 1
-                 : (int)(((x + 1) * NC + T - 1) / T) - 1;
-  };
-  long long x0 = cta < NC ? range_begin(cta) : 0, x1 = cta < NC ? range_begin(cta + 1) : 0;
+  T = prefix[n_items];
+  NC = (long long)gridDim.x < T ? (int)gridDim.x : (int)T;
+  small = (T + 1) * (NC + 1) < (1LL << 31);
+  x0 = cta < NC ? range_begin(cta) : 0;
+  x1 = cta < NC ? range_begin(cta + 1) : 0;
   // When giving every CTA the same number of WHOLE units keeps the busiest CTA within 1.3x of an equal share of the
   // chunks, do that instead: a little more streaming for the busiest CTA (and some SMs idle), but no unit
   // is cut, so nothing is published to and merged from the workspace and no CTA waits for a last
@@ -499,7 +590,8 @@ __global__ void __launch_bounds__(threads_of(UMMA, MT * NS), MT * NS == 4 ? 2 : 
     }
   }
   if (x1 <= x0) return;
-  const int n_my = (int)(x1 - x0);
+  n_my = (int)(x1 - x0);
+  }  // general prologue
   if (tid == 0) PACE_STAMP(1);
   if (tid == 0) PACE_TRACE(3, 6);
 
@@ -511,6 +603,11 @@ __global__ void __launch_bounds__(threads_of(UMMA, MT * NS), MT * NS == 4 ? 2 : 
     // stream is what paces the whole pipeline.
     // the item holding chunk x0: the last one whose prefix is <= x0; 32 candidates per ballot
     int it = 0;
+    if (fast) {
+      const int k = fast_it0 + lane;
+      const unsigned m = __ballot_sync(0xffffffffu, k <= fast_it1 && (long long)prefix[k] <= x0);
+      it = fast_it0 + 31 - __clz(m);  // (lane 0 always votes: prefix[it0] = 0)
+    } else
     for (int base = 0; base < n_items; base += 32) {
       const int k = base + lane;
       const unsigned m = __ballot_sync(0xffffffffu, k < n_items && (long long)prefix[k] <= x0);
@@ -535,7 +632,6 @@ __global__ void __launch_bounds__(threads_of(UMMA, MT * NS), MT * NS == 4 ? 2 : 
         UMMA ? (is_v ? (uint32_t)n_stages * KVB + hf * HALF_B : (uint32_t)hf * n_stages * HALF_B) + (uint32_t)pi * P * 128
              : (uint32_t)(is_v ? KVB : 0) + hf * HALF_B + (uint32_t)pi * P * 128;
     const uint32_t stage_step = UMMA ? (is_v ? KVB : HALF_B) : STAGE;  // bytes from one stage's tile to the next
-    PageWindow pw;
     const int win_step = whole_pages ? (32 / p.pages_per_chunk) * p.pages_per_chunk : 32;
     const uint32_t box_bytes = (uint32_t)p.box_rows * 128u * 2u * HALVES;  // K and V boxes of one page
     const int CT = p.chunk_tokens;
@@ -559,7 +655,9 @@ __global__ void __launch_bounds__(threads_of(UMMA, MT * NS), MT * NS == 4 ? 2 : 
         lp = j / p.chunks_per_page;
         row0 = (j - lp * p.chunks_per_page) * kChunk;
       }
-      pw.start(p.kv, slot, lp, win_step, lane);  // loads in flight while the arithmetic below runs
+      const bool loaded = pw_slot == slot && lp == 0;  // (short prologue: the first window may be here already)
+      pw_slot = -1;
+      if (!loaded) pw.start(p.kv, slot, lp, win_step, lane);  // loads in flight while the arithmetic below runs
       if (lane == 0 && i == 0) PACE_TRACE(3, 8);
       int mode = 0, parts = 1, first_cta = cta, first_slot = 0;
       {
@@ -620,6 +718,7 @@ __global__ void __launch_bounds__(threads_of(UMMA, MT * NS), MT * NS == 4 ? 2 : 
       if (!ok) break;
       ++part_idx;
       j = 0;
+      if (i >= n_my) break;
       if (++h == Hkv) {
         h = 0;
         ++it;
@@ -717,6 +816,7 @@ __global__ void __launch_bounds__(threads_of(UMMA, MT * NS), MT * NS == 4 ? 2 : 
     const unsigned char* st = ring + (size_t)s * STAGE;
     const MetaM* meta = &metas[s];
     const int rows = meta->rows, tok0 = meta->tok0, flags = meta->flags, kvs = meta->kvs;
+    if (flags & 8) return;  // (short prologue: the producer found nothing to stream)
     if (tid == 0 && i == 0) PACE_STAMP(3);
     if (tid == 0) PACE_TRACE(1, i);
     if (tid == 0 && i == n_my - 1) PACE_STAMP(4);
@@ -1002,6 +1102,7 @@ __global__ void __launch_bounds__(threads_of(UMMA, MT * NS), MT * NS == 4 ? 2 : 
         if (tid == 0) PACE_STAMP(5);
       }
     }
+    if (flags & 4) break;  // the CTA's last chunk (the short prologue gives the consumers no count)
   }
 }
 
