@@ -344,6 +344,11 @@ __global__ void __launch_bounds__(threads_of(UMMA, MT * NS), MT * NS == 4 ? 2 : 
   // kernel in front of it on the stream drains; griddepcontrol.wait then holds until that kernel has
   // completed and its writes (the appended rows, the lengths) are visible. ----
   // one barrier per thread of the last warp (its lanes have no sequences to look up in small batches)
+  if (tid == NW * 32) {
+    // the producer's first tiled copy would otherwise wait for its 128-byte descriptor to arrive
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmK)) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmV)) : "memory");
+  }
   if (tid >= NTHR - 32) {
     const int k = tid - (NTHR - 32);
     if (k < n_stages) mbar_init(&full_bar[k], 1);
@@ -403,19 +408,76 @@ __global__ void __launch_bounds__(threads_of(UMMA, MT * NS), MT * NS == 4 ? 2 : 
   PageWindow pw;
   int pw_slot = -1;  // short prologue: the sequence whose first block-table window is already loaded
   int fast_it0 = 0, fast_it1 = -1;
+  int n_spec = 0;  // short prologue: ring stages whose copies went out before the length was known
+  const uint32_t page_box_bytes = (uint32_t)p.box_rows * 128u * 2u * HALVES;  // K and V boxes of one page
+  int q_spec = 0;  // ... and whether the unit's query rows went out with them
   if (fast) {
     const int u0 = cta * per_cta_w, u1 = min(n_units_all, u0 + per_cta_w);
     if (u0 >= n_units_all) return;  // (known from the CTA index: every thread leaves)
     n_my = INT_MAX;                 // consumers run until the record of the CTA's last chunk
+    // A CTA with a single unit of one-page chunks: the copies of the unit's first pages and of its query
+    // rows leave before its length is known - a first page that is in the table holds keys unless the
+    // sequence is empty, and pages that turn out to lie beyond the length are received and dropped by
+    // the producer.  The epilogue warp, idle until the first unit is done, issues them while the
+    // producer warp works out the unit's chunks: one warp's couple of microseconds of dependent scalar
+    // work then runs beside the DRAM latency of the first copies, not in front of it.
+    const bool spec_ok = u1 - u0 == 1 && p.pages_per_chunk == 1 && p.kv.block_table && !p.q_lens;
+    if (warp == NW + 1 && spec_ok) {
+      const int b0 = u0 / Hkv, h0s = u0 - b0 * Hkv;
+      const int slot0 = view_slot(p.kv, b0);
+      const int want = min(n_stages, 4);
+      int n = 0, qs = 0;
+      if (slot0 >= 0) {
+        int pg = -1;
+        if (lane < want && lane < p.kv.max_pages_per_seq) {
+          pg = __ldg(p.kv.block_table + (size_t)slot0 * p.kv.max_pages_per_seq + lane);
+          if (pg >= p.kv.n_pages) pg = -1;
+        }
+        const unsigned have = __ballot_sync(0xffffffffu, pg >= 0);
+        n = __ffs(~have) - 1;  // leading pages that are in the table
+        const int is_v = lane & 1, hf = (lane >> 1) % HALVES;
+        for (int c = 0; c < n; ++c) {
+          const int pgc = __shfl_sync(0xffffffffu, pg, c);
+          if (lane < 2 * HALVES)
+            tma_load_4d(ring + (size_t)c * STAGE + (is_v ? KVB : 0) + hf * HALF_B, is_v ? &tmV : &tmK, hf * 64, 0,
+                        pgc * Hkv + h0s, is_v ? p.c3_v : p.c3_k, &full_bar[c]);
+        }
+        if (n > 0) {
+          const int q_rows = min(MR, p.q_len * G);
+          for (int r = lane; r < q_rows; r += 32) {
+            const int sq = r / G, g = r - sq * G;
+            bulk_g2s(qbuf + r * QS, p.q + (size_t)b0 * p.q_sb + (size_t)(h0s * G + g) * p.q_sh + (size_t)sq * p.q_ss,
+                     D * 2u, &full_bar[0]);
+          }
+          qs = 1;
+        }
+      }
+      if (lane == 0) {
+        misc[3] = n;
+        misc[7] = qs;
+      }
+      __syncwarp();
+      asm volatile("bar.arrive 2, 64;" ::: "memory");  // the producer picks the two numbers up behind this
+    }
     if (warp == NW) {
       const int it0 = u0 / Hkv, it1 = (u1 - 1) / Hkv;
       fast_it0 = it0;
       fast_it1 = it1;
       const int b = it0 + lane;  // one lane per sequence this CTA touches
-      int n = 0, slot = -1;
+      int n = 0, slot = -1, len = 0;
       if (b <= it1) {
         slot = view_slot(p.kv, b);
-        const int len = slot >= 0 ? view_len(p.kv, slot) : 0;
+        if (slot >= 0) len = view_len(p.kv, slot);
+      }
+      // the first sequence's block-table window: its loads go out right behind the loads of the
+      // lengths, before anything waits for either
+      const int slot0 = __shfl_sync(0xffffffffu, slot, 0);
+      if (slot0 >= 0) {
+        const int step0 = p.pages_per_chunk > 0 ? (32 / p.pages_per_chunk) * p.pages_per_chunk : 32;
+        pw.start(p.kv, slot0, 0, step0, lane);
+        pw_slot = slot0;
+      }
+      if (b <= it1) {
         const int S = p.q_lens ? min(p.q_lens[b], p.q_len) : p.q_len;
         sb_slot[b] = slot;
         sb_len[b] = len;
@@ -426,13 +488,6 @@ __global__ void __launch_bounds__(threads_of(UMMA, MT * NS), MT * NS == 4 ? 2 : 
           const int hi = p.causal ? len - S + s_hi + 1 : len;
           n = chunks_of_m(p, min(hi, len)) * Hkv;
         }
-      }
-      // the first sequence's block-table window: its load is in flight while the lengths arrive
-      const int slot0 = __shfl_sync(0xffffffffu, slot, 0);
-      if (slot0 >= 0) {
-        const int step0 = p.pages_per_chunk > 0 ? (32 / p.pages_per_chunk) * p.pages_per_chunk : 32;
-        pw.start(p.kv, slot0, 0, step0, lane);
-        pw_slot = slot0;
       }
       int v = n;
 #pragma unroll
@@ -461,12 +516,24 @@ __global__ void __launch_bounds__(threads_of(UMMA, MT * NS), MT * NS == 4 ? 2 : 
         }
       }
       n_my = (int)(x1 - x0);
+      if (spec_ok) {
+        asm volatile("bar.sync 2, 64;" ::: "memory");
+        n_spec = misc[3];
+        q_spec = misc[7];
+      }
       if (n_my <= 0) {
         // nothing to stream: a record that says so for the consumers, a result slot that says so for
         // the epilogue warp
         if (lane == 0) {
           metas[0].flags = 8;
-          mbar_arrive(&full_bar[0]);
+          if (n_spec > 0) {  // (the record travels with the first speculative copy; the others are received here)
+            for (int k = 0; k < n_spec; ++k)
+              mbar_arrive_expect_tx(&full_bar[k],
+                                    page_box_bytes + ((k == 0 && q_spec) ? (uint32_t)min(MR, p.q_len * G) * D * 2u : 0u));
+            for (int k = 0; k < n_spec; ++k) mbar_wait(&full_bar[k], 0);
+          } else {
+            mbar_arrive(&full_bar[0]);
+          }
           float* rden0 = reinterpret_cast<float*>(res) + p.live_max * D + p.live_max;
           reinterpret_cast<ResMeta*>(rden0 + p.live_max)->last_part = 1;
           for (int k = 0; k < NW; ++k) mbar_arrive(&res_full[0]);
@@ -633,7 +700,7 @@ __global__ void __launch_bounds__(threads_of(UMMA, MT * NS), MT * NS == 4 ? 2 : 
              : (uint32_t)(is_v ? KVB : 0) + hf * HALF_B + (uint32_t)pi * P * 128;
     const uint32_t stage_step = UMMA ? (is_v ? KVB : HALF_B) : STAGE;  // bytes from one stage's tile to the next
     const int win_step = whole_pages ? (32 / p.pages_per_chunk) * p.pages_per_chunk : 32;
-    const uint32_t box_bytes = (uint32_t)p.box_rows * 128u * 2u * HALVES;  // K and V boxes of one page
+    const uint32_t box_bytes = page_box_bytes;
     const int CT = p.chunk_tokens;
     int i = 0, s = 0, ph = 0, part_idx = 0;
     bool ok = true;
@@ -694,11 +761,13 @@ __global__ void __launch_bounds__(threads_of(UMMA, MT * NS), MT * NS == 4 ? 2 : 
         __syncwarp();
         const int pg = pw.get(lp + pi, lp, lane);
         if (lane == 0 && i == 0) PACE_TRACE(3, 10);
-        if (copier && pi < n_pages_c) {
+        if (i < n_spec) {
+          // (short prologue: this chunk's copy is on its way already - same sequence, head and page)
+        } else if (copier && pi < n_pages_c) {
           if (pg >= 0) tma_load_4d(ring + (size_t)s * stage_step + lane_off, tm, c0, row0, pg * Hkv + c2h, c3, &full_bar[s]);
           else raise_status(p.kv.status, PACE_DEV_BAD_INDEX);  // the consumers' bounded wait on this stage gives up
         }
-        if (first && !UMMA) {  // (the tcgen05 variant's softmax warps write the Q tile themselves, swizzled)
+        if (first && !UMMA && !(q_spec && i == 0)) {  // (the tcgen05 variant's softmax warps write the Q tile themselves, swizzled)
           for (int r = lane; r < q_rows; r += 32) {
             const int rr = r_lo + r, sq = rr / G, g = rr - sq * G;
             const __nv_bfloat16* src = p.q + (size_t)b * p.q_sb + (size_t)(h * G + g) * p.q_sh + (size_t)sq * p.q_ss;
@@ -732,6 +801,11 @@ __global__ void __launch_bounds__(threads_of(UMMA, MT * NS), MT * NS == 4 ? 2 : 
       // let copies already in flight land before the CTA's shared memory is released
       const int from = i > n_stages ? i - n_stages : 0;
       for (int k = from; k < i; ++k) mbar_wait(&full_bar[k % n_stages], (k / n_stages) & 1);
+    }
+    if (lane == 0 && i < n_spec) {
+      // speculative copies of pages beyond the unit's length: nobody consumes them, receive them here
+      for (int k = i; k < n_spec; ++k) mbar_arrive_expect_tx(&full_bar[k], page_box_bytes);
+      for (int k = i; k < n_spec; ++k) mbar_wait(&full_bar[k], 0);
     }
     return;
   }

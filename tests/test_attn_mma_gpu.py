@@ -217,6 +217,38 @@ def test_decode_whole_units_flag_on_ragged_lengths(monkeypatch, lens):
     mgr.pool.check_status()
 
 
+def test_decode_early_copies_short_and_empty_sequences(monkeypatch):
+    """Whole-unit decode on 64-token pages sends the copies of a unit's first pages before it knows the
+    length: sequences of less than that many pages (copies received and dropped), of exactly a page,
+    and sequences rolled back to nothing (zeros out) all give the oracle's rows."""
+    from pace_b200.llm.cache import KVCacheManager, KVCacheType
+    from pace_b200.ops import MultiHeadAttention
+    from pace_b200.ops.backends import b200
+    monkeypatch.setattr(b200, "even_lengths", lambda *a, **k: True)
+    lens = [1, 63, 64, 65, 128, 129, 191, 192, 300, 2]
+    B, Hq, Hkv, D = len(lens), 32, 8, 128
+    g = torch.Generator().manual_seed(11)
+    ks = [torch.randn(Hkv, L, D, generator=g).bfloat16().to(DEV) for L in lens]
+    vs = [torch.randn(Hkv, L, D, generator=g).bfloat16().to(DEV) for L in lens]
+    q = torch.randn(B, Hq, 1, D, generator=g).bfloat16().to(DEV)
+    mgr = KVCacheManager(Cfg(1), 4096, KVCacheType.BMC)
+    K, V = _fill(mgr, 0, ks, vs)
+    assert mgr.pool.page_tokens == 64
+    mha = MultiHeadAttention()
+    out = mha(q, K, V)
+    want = _oracle(q, ks, vs)
+    for b in range(B):
+        _check(out[b], want[b])
+    # roll two sequences back to nothing: their rows come out as zeros, the others are unchanged
+    mgr.remove_cache([1, 0, 0, 0, 0, 0, 0, 0, 0, 2])
+    out2 = mha(q, K, V)
+    torch.cuda.synchronize()
+    assert torch.count_nonzero(out2[0]) == 0 and torch.count_nonzero(out2[9]) == 0
+    for b in range(1, 9):
+        assert torch.equal(out2[b], out[b])
+    mgr.pool.check_status()
+
+
 def test_decode_eight_warp_ctas(monkeypatch):
     """PACE_DECODE_HALF=0: decode on eight-warp thread blocks, one per SM (the form used when the
     workspace or the shared memory has no room for two four-warp blocks per SM)."""
