@@ -430,7 +430,7 @@ __global__ void __launch_bounds__(threads_of(UMMA, MT * NS), MT * NS == 4 ? 2 : 
       if (slot0 >= 0) {
         int pg = -1;
         if (lane < want && lane < p.kv.max_pages_per_seq) {
-          pg = __ldg(p.kv.block_table + (size_t)slot0 * p.kv.max_pages_per_seq + lane);
+          pg = __ldcg(p.kv.block_table + (size_t)slot0 * p.kv.max_pages_per_seq + lane);
           if (pg >= p.kv.n_pages) pg = -1;
         }
         const unsigned have = __ballot_sync(0xffffffffu, pg >= 0);
