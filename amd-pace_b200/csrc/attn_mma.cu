@@ -281,11 +281,16 @@ __global__ void __launch_bounds__(threads_of(UMMA, MT * NS), MT * NS == 4 ? 2 : 
   // (measured on batch 32, 600 cached tokens: 22.6 us with one group of eight slices, 21.5 us with two
   // groups, 22.6 us with four, 24.5 us with whole chunks per warp).  Decode with four warps (two CTAs per
   // SM, each with its own producer warp and a three-stage ring): one group, 16 keys per warp; the two
-  // CTAs of an SM are the two groups, and they drift apart instead of marching in step - 19.3 us.
+  // CTAs of an SM are the two groups, and they drift apart instead of marching in step - 19.3 us
+  // (PACE_DECODE_DEAL_HALF=2, two groups of two warps with 32 keys each, holds two of the three ring
+  // stages at a time: 19.1 us where one group takes 18.0 us).
 #ifndef PACE_DECODE_DEAL
 #define PACE_DECODE_DEAL 2
 #endif
-  constexpr int DG = (MT >= 2 && NS >= 2) ? NS : (MT == 1 ? (NS == 4 ? 1 : PACE_DECODE_DEAL) : 1);
+#ifndef PACE_DECODE_DEAL_HALF
+#define PACE_DECODE_DEAL_HALF 1
+#endif
+  constexpr int DG = (MT >= 2 && NS >= 2) ? NS : (MT == 1 ? (NS == 4 ? PACE_DECODE_DEAL_HALF : PACE_DECODE_DEAL) : 1);
   constexpr int SL = NS / DG;
   constexpr int TW = kChunk / SL;  // keys of a chunk one warp works on
   constexpr int NT = TW / 8;                              // score n-tiles per warp
@@ -893,7 +898,7 @@ __global__ void __launch_bounds__(threads_of(UMMA, MT * NS), MT * NS == 4 ? 2 : 
     if (flags & 8) return;  // (short prologue: the producer found nothing to stream)
     if (tid == 0 && i == 0) PACE_STAMP(3);
     if (tid == 0) PACE_TRACE(1, i);
-    if (tid == 0 && i == n_my - 1) PACE_STAMP(4);
+    if (tid == 0 && (flags & 4)) PACE_STAMP(4);
 
     if (flags & 1) {
       // ---- new unit part: Q fragments to registers, per-row visibility limits ----
