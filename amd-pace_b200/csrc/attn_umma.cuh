@@ -24,6 +24,9 @@ namespace {
 
 constexpr int kUmmaRows = 128;          // query rows per tile (UMMA M)
 constexpr int kUmmaSoftmaxThreads = 256;  // two warpgroups
+// Warps 0-7: softmax; 8: producer; 9: QK issuer; 10: PV issuer.  (Issuers on warps 10 and 11, away from
+// the schedulers of the softmax warps that hold a verify tile's live rows, measured the same.)
+constexpr int kUmmaQkWarp = 9, kUmmaPvWarp = 10;
 constexpr int kTmemCols = 512;          // the whole tensor memory of the SM:
 constexpr uint32_t kTmemO = 256;        //   [0, 256) four score buffers, [256, 512) O of group A and B
 constexpr int kScoreBufs = 4;
@@ -219,17 +222,17 @@ __device__ __forceinline__ void umma_issue_qk(const UmmaCtx& c, uint32_t tmem, i
         }
         ++part;
       }
-      const bool two = left >= 2 && s + 1 < c.n_stages && b + 1 < kScoreBufs;
+      // Two chunks with one set of MMAs only when the second one costs no waiting: its K has landed and
+      // its score buffer is free already (probes, not waits: holding the first chunk back for the second
+      // lengthens the time a ring stage stays occupied, which is what bounds short streams like verify).
+      bool two = left >= 2 && s + 1 < c.n_stages && b + 1 < kScoreBufs;
       {
-        // up to three more barriers stand between this thread and the issue: probe them together (the
-        // probes' latencies overlap) and wait one by one only for those that have not completed yet
-        const bool w1 = two, w2 = i >= kScoreBufs, w3 = two && i + 1 >= kScoreBufs;
-        const bool r1 = !w1 || mbar_test_wait(&c.full_bar[s + 1], ph);
+        const bool w2 = i >= kScoreBufs;
+        const bool r1 = !two || mbar_test_wait(&c.full_bar[s + 1], ph);
         const bool r2 = !w2 || mbar_test_wait(&c.p_free[b], phb);
-        const bool r3 = !w3 || mbar_test_wait(&c.p_free[b + 1], phb);
-        if (!r1 && !issuer_wait(c, &c.full_bar[s + 1], ph)) break;
+        const bool r3 = !(two && i + 1 >= kScoreBufs) || mbar_test_wait(&c.p_free[b + 1], phb);
+        two = two && r1 && r3;
         if (!r2 && !issuer_wait(c, &c.p_free[b], phb)) break;
-        if (!r3 && !issuer_wait(c, &c.p_free[b + 1], phb)) break;
       }
       tc_fence_after();  // the PVs that read P from these buffers are done
 #ifdef PACE_TIMING
@@ -492,10 +495,13 @@ __device__ __forceinline__ void umma_softmax(const MmaParams& p, const UmmaCtx& 
         tmem_ld32(tS + 32, sr[1]);
         tmem_wait_ld();
         const int lo = max(0, kvs - tok0), hi = min(rows, lim - tok0);  // visible keys of the chunk: [lo, hi)
-        if (!__all_sync(0xffffffffu, lo <= 0 && hi >= kChunk)) {
+        // (Rows of padding need no mask: their Q is zero, their scores are finite and nothing of them
+        // is ever stored - a warp of a few live rows would otherwise mask on every chunk.)
+        if (!__all_sync(0xffffffffu, !live || (lo <= 0 && hi >= kChunk))) {
+          const unsigned span = hi > lo ? (unsigned)(hi - lo) : 0u;
 #pragma unroll
           for (int k = 0; k < 64; ++k)
-            if (k < lo || k >= hi) sr[k >> 5][k & 31] = 0xff800000u;  // -inf
+            if ((unsigned)(k - lo) >= span) sr[k >> 5][k & 31] = 0xff800000u;  // -inf
         }
         float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
@@ -640,7 +646,7 @@ __device__ __forceinline__ void umma_softmax(const MmaParams& p, const UmmaCtx& 
 template <int D>
 __device__ __forceinline__ void umma_consumer(const MmaParams& p, const UmmaCtx& c, int tid) {
   const int warp = tid >> 5, lane = tid & 31;
-  const bool owner = warp == 9;
+  const bool owner = warp == kUmmaQkWarp;
   if (owner) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(c.tmem_slot)),
                  "r"(kTmemCols)
@@ -651,8 +657,8 @@ __device__ __forceinline__ void umma_consumer(const MmaParams& p, const UmmaCtx&
   asm volatile("bar.sync 3, 320;" ::: "memory");
   tc_fence_after();
   const uint32_t tmem = *reinterpret_cast<volatile uint32_t*>(c.tmem_slot);
-  if (warp == 9) umma_issue_qk<D>(c, tmem, lane);
-  else if (warp == 10) umma_issue_pv<D>(c, tmem, lane);
+  if (warp == kUmmaQkWarp) umma_issue_qk<D>(c, tmem, lane);
+  else if (warp == kUmmaPvWarp) umma_issue_pv<D>(c, tmem, lane);
   else umma_softmax<D>(p, c, tmem, tid);
   if (lane == 0 && *c.abort) raise_status(p.kv.status, PACE_DEV_WAIT_TIMEOUT);
 #ifdef PACE_TIMING
