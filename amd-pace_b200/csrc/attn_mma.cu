@@ -133,7 +133,7 @@ __host__ __device__ inline SmemPlan plan_smem(int D, int MT, int NS, int n_stage
   const int q_rows = MR < ((live_max + 7) & ~7) ? MR : ((live_max + 7) & ~7);
   s.qbuf = umma ? take(MR * D * 2, 1024) : take(q_rows * QS, 128);
   s.mg_stride = D + 8;  // floats; the pad spreads the rows of a fragment over the banks
-  s.mg = take(umma ? 4 * MR * 4 : (NS > 1 ? NS * live_max * (s.mg_stride + 2) * 4 : 16), 16);
+  s.mg = take(umma ? 16 : (NS > 1 ? NS * live_max * (s.mg_stride + 2) * 4 : 16), 16);
   s.n_res = live_max <= 64 ? 2 : 1;
   s.res_slot_bytes = (live_max * (D + 2) * 4 + 64 + 15) / 16 * 16;
   s.res = take(umma ? 16 : s.n_res * s.res_slot_bytes, 16);
@@ -831,8 +831,6 @@ __global__ void __launch_bounds__(threads_of(UMMA, MT * NS), MT * NS == 4 ? 2 : 
     uc.xch = umma_bars + 14;
     uc.p_free = umma_bars + 15;
     uc.qsw = qbuf;
-    uc.xch_m = mg_o;
-    uc.xch_l = mg_o + 2 * kUmmaRows;
     uc.tmem_slot = reinterpret_cast<uint32_t*>(misc + 5);
     uc.flag = misc + 6;
     uc.abort = misc + 4;
@@ -1297,7 +1295,7 @@ int launch_mma(MmaParams& p, const CUtensorMap& tmK, const CUtensorMap& tmV, int
   const int n_items = p.batch * p.n_qt;
   p.live_max = p.G * p.q_len < MR ? p.G * p.q_len : MR;
   // two CTAs per SM (four consumer warps): 228 KB of shared memory less 1 KB the system keeps per CTA
-  const int budget = NW == 4 ? kHalfSmemBudget : 226 * 1024;
+  const int budget = NW == 4 ? kHalfSmemBudget : 227 * 1024;  // (227 KB: the most one CTA may ask for)
   int ns = kMaxStagesM;
   while (ns >= 2 && plan_smem(D, MT, NS, ns, p.live_max, p.batch, n_items, UMMA).total > budget) --ns;
   if (ns < 2) return PACE_ERR_UNSUPPORTED;

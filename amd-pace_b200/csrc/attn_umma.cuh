@@ -50,8 +50,6 @@ struct UmmaCtx {
   uint64_t* drain;        // [2] every MMA an issuer warp issued has completed
   uint64_t* pub;          // meeting point of the 256 softmax threads while a cut unit is published
   uint64_t* xch;          // the two groups have posted their (max, sum) of a part (one arrival per warp)
-  float* xch_m;           // [2][128]
-  float* xch_l;           // [2][128]
   uint32_t* tmem_slot;    // where tcgen05.alloc wrote the base address
   int* flag;              // "this CTA arrived last" broadcast
   volatile int* abort;
@@ -154,6 +152,12 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16
       "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
       "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
       : "memory");
+}
+__device__ __forceinline__ void tmem_ld2(uint32_t taddr, uint32_t& r0, uint32_t& r1) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x2.b32 {%0, %1}, [%2];" : "=r"(r0), "=r"(r1) : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_st2(uint32_t taddr, uint32_t r0, uint32_t r1) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x2.b32 [%0], {%1, %2};" ::"r"(taddr), "r"(r0), "r"(r1) : "memory");
 }
 __device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
@@ -559,14 +563,32 @@ __device__ __forceinline__ void umma_softmax(const MmaParams& p, const UmmaCtx& 
     if (tid == 0) PACE_USTAMP(c, 3);
     const bool has_mine = j_first < n_part, has_other = (j_first ^ 1) < n_part;  // (a part of one chunk leaves a group empty-handed)
     if (has_mine && !umma_wait(&c.o_full[wg], (cnt - 1) & 1, c.abort)) return;
-    c.xch_m[wg * MR + row] = m_used;
-    c.xch_l[wg * MR + row] = l;
+    // Each row's (reference maximum, sum) crosses to the other group through tensor memory: columns 32
+    // and 33 of the score buffer of the group's own last chunk, which hold nothing any more (P, packed
+    // bf16, sits in columns 0..31 and its PV MMA has completed; the next QK into the buffer waits for the
+    // next part's Q).  Both groups' warp w own the same 32 TMEM lanes, so no shared memory is needed -
+    // the 2 KB it took are what a sixth ring stage was short of.
+    const int j_last_mine = ((n_part - 1) & 1) == j_first ? n_part - 1 : n_part - 2;
+    const int j_last_other = ((n_part - 1) & 1) == j_first ? n_part - 2 : n_part - 1;
+    if (has_mine) {
+      tmem_st2(t_lane + (uint32_t)((i0 + j_last_mine) & (kScoreBufs - 1)) * kChunk + 32, __float_as_uint(m_used),
+               __float_as_uint(l));
+      tmem_wait_st();
+    }
+    tc_fence_before();
     __syncwarp();
     if (lane == 0) mbar_arrive(c.xch);
     if (!umma_wait(c.xch, n_xch & 1, c.abort)) return;
     ++n_xch;
     tc_fence_after();
-    const float m_o = c.xch_m[(wg ^ 1) * MR + row], l_o = c.xch_l[(wg ^ 1) * MR + row];
+    float m_o = -INFINITY, l_o = 0.f;
+    if (has_other) {
+      uint32_t xm, xl;
+      tmem_ld2(t_lane + (uint32_t)((i0 + j_last_other) & (kScoreBufs - 1)) * kChunk + 32, xm, xl);
+      tmem_wait_ld();
+      m_o = __uint_as_float(xm);
+      l_o = __uint_as_float(xl);
+    }
     const float M = fmaxf(m_used, m_o);
     const float f_m = (m_used == -INFINITY) ? 0.f : fast_exp2(m_used - M);
     const float f_o = (m_o == -INFINITY) ? 0.f : fast_exp2(m_o - M);
