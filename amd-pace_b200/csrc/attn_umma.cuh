@@ -217,7 +217,14 @@ __device__ __forceinline__ void umma_issue_qk(const UmmaCtx& c, uint32_t tmem, i
     int s = 0, ph = 0, b = 0, phb = 1;  // ring stage / its phase, score buffer / phase of its previous use
     int part = 0, left = 0;             // chunks left in the current unit part
     for (int i = 0; i < c.n_my;) {
+#ifdef PACE_TIMING
+      const long long cq0 = clock64();
+#endif
       if (!issuer_wait(c, &c.full_bar[s], ph)) break;
+#ifdef PACE_TIMING
+      PACE_UCLK(c, 12, i, clock64() - cq0);
+      const long long cq1 = clock64();
+#endif
       if (left == 0) {  // first chunk of a unit part: its Q tile
         left = c.metas[s].pad;
         if (left < 1 || !issuer_wait(c, c.q_ready, part & 1)) {
@@ -240,6 +247,7 @@ __device__ __forceinline__ void umma_issue_qk(const UmmaCtx& c, uint32_t tmem, i
       }
       tc_fence_after();  // the PVs that read P from these buffers are done
 #ifdef PACE_TIMING
+      PACE_UCLK(c, 13, i, clock64() - cq1);
       const long long ck0 = clock64();
 #endif
       const uint32_t k_lo = k_lo0 + (uint32_t)s * (HALF_B >> 4);
