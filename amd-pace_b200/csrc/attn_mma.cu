@@ -109,6 +109,24 @@ __device__ __forceinline__ void tma_load_4d(void* smem_dst, const CUtensorMap* t
       : "memory");
 }
 
+// The same copy with an L2 eviction policy: decode and verify (one query tile per sequence and KV head)
+// stream every K/V byte once per launch, and marked
+// evict-first the stream leaves the small things every launch starts with (block table, lengths, query
+// rows) in L2 instead of pushing them out.
+__device__ __forceinline__ void tma_load_4d_hint(void* smem_dst, const CUtensorMap* tm, int c0, int c1, int c2, int c3,
+                                                 uint64_t* bar, uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%3, "
+      "%4, %5, %6}], [%2], %7;" ::"r"(smem_u32(smem_dst)),
+      "l"(tm), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "l"(policy)
+      : "memory");
+}
+__device__ __forceinline__ uint64_t l2_evict_first_policy() {
+  uint64_t pol;
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
+  return pol;
+}
+
 // Shared-memory carve-up, computed identically on host and device.
 struct SmemPlan {
   int ring, metas, qbuf, mg, res, bars, misc, per_b, prefix, total;
@@ -444,8 +462,8 @@ __global__ void __launch_bounds__(threads_of(UMMA, MT * NS), MT * NS == 4 ? 2 : 
         for (int c = 0; c < n; ++c) {
           const int pgc = __shfl_sync(0xffffffffu, pg, c);
           if (lane < 2 * HALVES)
-            tma_load_4d(ring + (size_t)c * STAGE + (is_v ? KVB : 0) + hf * HALF_B, is_v ? &tmV : &tmK, hf * 64, 0,
-                        pgc * Hkv + h0s, is_v ? p.c3_v : p.c3_k, &full_bar[c]);
+            tma_load_4d_hint(ring + (size_t)c * STAGE + (is_v ? KVB : 0) + hf * HALF_B, is_v ? &tmV : &tmK, hf * 64, 0,
+                             pgc * Hkv + h0s, is_v ? p.c3_v : p.c3_k, &full_bar[c], l2_evict_first_policy());
         }
         if (n > 0) {
           const int q_rows = min(MR, p.q_len * G);
@@ -706,6 +724,7 @@ __global__ void __launch_bounds__(threads_of(UMMA, MT * NS), MT * NS == 4 ? 2 : 
     const uint32_t stage_step = UMMA ? (is_v ? KVB : HALF_B) : STAGE;  // bytes from one stage's tile to the next
     const int win_step = whole_pages ? (32 / p.pages_per_chunk) * p.pages_per_chunk : 32;
     const uint32_t box_bytes = page_box_bytes;
+    const uint64_t stream_policy = l2_evict_first_policy();
     const int CT = p.chunk_tokens;
     int i = 0, s = 0, ph = 0, part_idx = 0;
     bool ok = true;
@@ -769,7 +788,10 @@ __global__ void __launch_bounds__(threads_of(UMMA, MT * NS), MT * NS == 4 ? 2 : 
         if (i < n_spec) {
           // (short prologue: this chunk's copy is on its way already - same sequence, head and page)
         } else if (copier && pi < n_pages_c) {
-          if (pg >= 0) tma_load_4d(ring + (size_t)s * stage_step + lane_off, tm, c0, row0, pg * Hkv + c2h, c3, &full_bar[s]);
+          if (pg >= 0) {
+            if (p.n_qt == 1) tma_load_4d_hint(ring + (size_t)s * stage_step + lane_off, tm, c0, row0, pg * Hkv + c2h, c3, &full_bar[s], stream_policy);
+            else tma_load_4d(ring + (size_t)s * stage_step + lane_off, tm, c0, row0, pg * Hkv + c2h, c3, &full_bar[s]);
+          }
           else raise_status(p.kv.status, PACE_DEV_BAD_INDEX);  // the consumers' bounded wait on this stage gives up
         }
         if (first && !UMMA && !(q_spec && i == 0)) {  // (the tcgen05 variant's softmax warps write the Q tile themselves, swizzled)
