@@ -99,6 +99,12 @@ __device__ __forceinline__ void mma1688(float (&c)[4], uint32_t a0, uint32_t a1,
                : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
                : "r"(a0), "r"(a1), "r"(b0));
 }
+// 8x8 b16 matrix held in fragment layout (thread: row lane / 4, columns 2 * (lane % 4) + {0, 1}) -> its transpose
+__device__ __forceinline__ uint32_t movmatrix_t(uint32_t a) {
+  uint32_t d;
+  asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(d) : "r"(a));
+  return d;
+}
 // tiled TMA load of one box, completion on an mbarrier (no multicast)
 __device__ __forceinline__ void tma_load_4d(void* smem_dst, const CUtensorMap* tm, int c0, int c1, int c2, int c3,
                                             uint64_t* bar) {
@@ -305,6 +311,9 @@ __global__ void __launch_bounds__(threads_of(UMMA, MT * NS), MT * NS == 4 ? 2 : 
 #ifndef PACE_DECODE_DEAL
 #define PACE_DECODE_DEAL 2
 #endif
+#ifndef PACE_DECODE_TRANSPOSED
+#define PACE_DECODE_TRANSPOSED 1
+#endif
 #ifndef PACE_DECODE_DEAL_HALF
 #define PACE_DECODE_DEAL_HALF 1
 #endif
@@ -355,9 +364,11 @@ __global__ void __launch_bounds__(threads_of(UMMA, MT * NS), MT * NS == 4 ? 2 : 
 #define PACE_STAMP(i) do { unsigned long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_)); stamps[i] = t_; } while (0)
   unsigned long long* trace = reinterpret_cast<unsigned long long*>(p.parts + (size_t)gridDim.x * 2 * REC) + gridDim.x * 8;
 #define PACE_TRACE(k, i) do { if (blockIdx.x == 7 && (i) < 64) { unsigned long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_)); trace[(k) * 64 + (i)] = t_; } } while (0)
+#define PACE_CLK(k, i) do { if (blockIdx.x == 7 && tid == 0 && (i) < 64) trace[(k) * 64 + (i)] = (unsigned long long)clock64(); } while (0)
   if (tid == 0) PACE_STAMP(0);
 #else
 #define PACE_TRACE(k, i) do {} while (0)
+#define PACE_CLK(k, i) do {} while (0)
 #define PACE_STAMP(i) do {} while (0)
 #endif
 
@@ -899,6 +910,13 @@ __global__ void __launch_bounds__(threads_of(UMMA, MT * NS), MT * NS == 4 ? 2 : 
   int lim0 = INT_MAX, lim1 = INT_MAX;  // first key NOT visible to my two rows
   int srow0 = 0, srow1 = 0, bcur = 0;  // query token of my two rows (additive-mask lookup)
   int n_parts_done = 0;
+  // Decode tiles of at most 8 live rows (grouped heads x tokens) are computed transposed: S^T = K Q^T and
+  // O^T = V^T P^T, keys and head dimensions on the 16-row side of m16n8k16 and the query rows on its 8-column
+  // side.  Half the MMAs of the 16-row tile for the same keys (mma.sync runs at one m16n8k16 per 16 cycles
+  // and scheduler here, and the consumers' chunk time is mostly those), half the accumulator registers.
+  // Same variables, other meaning: qa[k][0..1] is the B fragment of Q^T, o[t] the tile of 16 head
+  // dimensions x 8 query rows, m0/l0 and m1/l1 belong to query rows 2 * qc and 2 * qc + 1.
+  bool tr = false;
   ResMeta fin;  // the current unit part, read from the part record of its first chunk
   fin.last_part = 0;
 #pragma unroll
@@ -922,18 +940,30 @@ __global__ void __launch_bounds__(threads_of(UMMA, MT * NS), MT * NS == 4 ? 2 : 
 
     if (flags & 1) {
       // ---- new unit part: Q fragments to registers, per-row visibility limits ----
+      const int R = meta->R, r_lo = meta->r_lo, kv_len = meta->kv_len, S = meta->S;
+      tr = MT == 1 && PACE_DECODE_TRANSPOSED && R - r_lo <= 8 && !p.mask;
       const uint32_t qb = smem_u32(qbuf) + (uint32_t)(mt * 16) * QS;
+      if (tr) {
+        // B fragments of Q^T (16 head dimensions x 8 query rows): thread holds row qr, dimensions 2 qc + {0, 1} (+ 8)
+        const unsigned char* qrow = qbuf + qr * QS + qc * 4;
 #pragma unroll
-      for (int k = 0; k < KS; ++k) {
-        const int mi = lane >> 3;
-        const int row = (mi & 1) * 8 + (lane & 7);
-        const int cch = k * 2 + (mi >> 1);
-        ldsm_x4(qb + row * QS + cch * 16, qa[k][0], qa[k][1], qa[k][2], qa[k][3]);
+        for (int k = 0; k < KS; ++k) {
+          qa[k][0] = *reinterpret_cast<const uint32_t*>(qrow + k * 32);
+          qa[k][1] = *reinterpret_cast<const uint32_t*>(qrow + k * 32 + 16);
+        }
+      } else {
+#pragma unroll
+        for (int k = 0; k < KS; ++k) {
+          const int mi = lane >> 3;
+          const int row = (mi & 1) * 8 + (lane & 7);
+          const int cch = k * 2 + (mi >> 1);
+          ldsm_x4(qb + row * QS + cch * 16, qa[k][0], qa[k][1], qa[k][2], qa[k][3]);
+        }
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(q_empty);
-      const int R = meta->R, r_lo = meta->r_lo, kv_len = meta->kv_len, S = meta->S;
-      const int r0 = r_lo + mt * 16 + qr, r1 = r0 + 8;
+      // (transposed: my two query rows are 2 qc and 2 qc + 1, the columns of my accumulators)
+      const int r0 = tr ? r_lo + 2 * qc : r_lo + mt * 16 + qr, r1 = tr ? r0 + 1 : r0 + 8;
       srow0 = r0 / G;
       srow1 = r1 / G;
       lim0 = (r0 < R) ? (p.causal ? kv_len - S + srow0 + 1 : kv_len) : INT_MAX;
@@ -967,6 +997,75 @@ __global__ void __launch_bounds__(threads_of(UMMA, MT * NS), MT * NS == 4 ? 2 : 
 #endif
     if (mine && tw0 < rows && mt * 16 < fin.live) {
       const uint32_t kb = smem_u32(st), vb = kb + KVB;
+      PACE_CLK(4, i);
+      if (tr) {
+        // ---- S^T = K Q^T: my 16 keys x 8 query rows, two accumulators over the k-steps ----
+        const int mi = lane >> 3;
+        float sa[4] = {0.f, 0.f, 0.f, 0.f}, sb[4] = {0.f, 0.f, 0.f, 0.f};
+        {
+          const int row = tw0 + (mi & 1) * 8 + (lane & 7);
+#pragma unroll
+          for (int k = 0; k < KS; ++k) {
+            const int cg = k * 2 + (mi >> 1);
+            uint32_t a[4];
+            ldsm_x4(kb + (cg >> 3) * HALF_B + row * 128 + (((cg & 7) ^ (row & 7)) << 4), a[0], a[1], a[2], a[3]);
+            mma16816((k & 1) ? sb : sa, a, qa[k][0], qa[k][1]);
+          }
+        }
+        PACE_CLK(5, i);
+        // sc[0], sc[1]: key qr, query rows 2 qc and 2 qc + 1; sc[2], sc[3]: key qr + 8
+        float sc[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) sc[e] = (sa[e] + sb[e]) * p.scale_log2;
+        {
+          // keys outside my slice of the chunk, outside the chunk, left padding, beyond the row's limit
+          const int kk0 = tw0 + qr, kk1 = kk0 + 8;
+          const int t0 = tok0 + kk0, t1 = tok0 + kk1;
+          const bool in0 = qr < tw && kk0 < rows && t0 >= kvs, in1 = qr + 8 < tw && kk1 < rows && t1 >= kvs;
+          if (!(in0 && t0 < lim0)) sc[0] = -INFINITY;
+          if (!(in0 && t0 < lim1)) sc[1] = -INFINITY;
+          if (!(in1 && t1 < lim0)) sc[2] = -INFINITY;
+          if (!(in1 && t1 < lim1)) sc[3] = -INFINITY;
+        }
+        // ---- online softmax down the key side: my two keys, then the 8 lanes that share my query rows ----
+        float mx0 = fmaxf(sc[0], sc[2]), mx1 = fmaxf(sc[1], sc[3]);
+#pragma unroll
+        for (int o_ = 4; o_ < 32; o_ <<= 1) {
+          mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, o_));
+          mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, o_));
+        }
+        const float n0 = fmaxf(m0, mx0), n1 = fmaxf(m1, mx1);
+        const float a0 = (m0 == -INFINITY) ? 0.f : fast_exp2(m0 - n0);
+        const float a1 = (m1 == -INFINITY) ? 0.f : fast_exp2(m1 - n1);
+        const float e0 = (n0 == -INFINITY) ? 0.f : n0, e1 = (n1 == -INFINITY) ? 0.f : n1;
+        m0 = n0;
+        m1 = n1;
+        const float p00 = fast_exp2(sc[0] - e0), p01 = fast_exp2(sc[1] - e1);
+        const float p10 = fast_exp2(sc[2] - e0), p11 = fast_exp2(sc[3] - e1);
+        l0 = l0 * a0 + p00 + p10;  // (this thread's keys only: summed over the lanes at the end of the part)
+        l1 = l1 * a1 + p01 + p11;
+#pragma unroll
+        for (int t = 0; t < D / 16; ++t) {
+          o[t][0] *= a0;
+          o[t][1] *= a1;
+          o[t][2] *= a0;
+          o[t][3] *= a1;
+        }
+        // P (keys x query rows) -> B fragments of P^T: one 8x8 transpose per 8 keys
+        const uint32_t pb0 = movmatrix_t(f2_to_bf2(p00, p01)), pb1 = movmatrix_t(f2_to_bf2(p10, p11));
+        PACE_CLK(6, i);
+        // ---- O^T += V^T P^T: tiles of 16 head dimensions x 8 query rows ----
+        {
+          const int row = tw0 + (mi >> 1) * 8 + (lane & 7);
+#pragma unroll
+          for (int t = 0; t < D / 16; ++t) {
+            const int cg = t * 2 + (mi & 1);
+            uint32_t a[4];
+            ldsm_x4_t(vb + (cg >> 3) * HALF_B + row * 128 + (((cg & 7) ^ (row & 7)) << 4), a[0], a[1], a[2], a[3]);
+            mma16816(o[t], a, pb0, pb1);
+          }
+        }
+      } else {
       // ---- S = Q K^T ----
       // (the k-steps of a tile go to CH independent accumulators: a chain of dependent MMAs is the
       // longest latency in the loop)
@@ -998,6 +1097,7 @@ __global__ void __launch_bounds__(threads_of(UMMA, MT * NS), MT * NS == 4 ? 2 : 
           sc[nt][0] = sc[nt][1] = sc[nt][2] = sc[nt][3] = -INFINITY;
         }
       }
+      PACE_CLK(5, i);
       // ---- scale, additive mask, visibility ----
       const int t_base = tok0 + tw0 + 2 * qc;  // key index of sc[0][0]
       const bool need_mask = (tw0 + tw > rows) || (tok0 + tw0 < kvs) || (tok0 + tw0 + tw > min(lim0, lim1));
@@ -1067,6 +1167,7 @@ __global__ void __launch_bounds__(threads_of(UMMA, MT * NS), MT * NS == 4 ? 2 : 
         pk[nt][0] = f2_to_bf2(p00, p01);
         pk[nt][1] = f2_to_bf2(p10, p11);
       }
+      PACE_CLK(6, i);
       // ---- O += P V ----
       if constexpr (NT == 1) {
 #pragma unroll
@@ -1098,7 +1199,9 @@ __global__ void __launch_bounds__(threads_of(UMMA, MT * NS), MT * NS == 4 ? 2 : 
           }
         }
       }
+      }  // row-major path
     }
+    PACE_CLK(7, i);
     if (flags & 2) fin.last_part = (flags & 4) ? 1 : 0;
     __syncwarp();
     if (lane == 0) mbar_arrive(&empty_bar[s]);
@@ -1107,10 +1210,18 @@ __global__ void __launch_bounds__(threads_of(UMMA, MT * NS), MT * NS == 4 ? 2 : 
     if (flags & 2) {
       // ================= end of a unit part: hand the result to the epilogue warp =================
       float lt0 = l0, lt1 = l1;
-      lt0 += __shfl_xor_sync(0xffffffffu, lt0, 1);
-      lt0 += __shfl_xor_sync(0xffffffffu, lt0, 2);
-      lt1 += __shfl_xor_sync(0xffffffffu, lt1, 1);
-      lt1 += __shfl_xor_sync(0xffffffffu, lt1, 2);
+      if (tr) {  // a query row's keys sit in the 8 lanes with the same qc
+#pragma unroll
+        for (int o_ = 4; o_ < 32; o_ <<= 1) {
+          lt0 += __shfl_xor_sync(0xffffffffu, lt0, o_);
+          lt1 += __shfl_xor_sync(0xffffffffu, lt1, o_);
+        }
+      } else {
+        lt0 += __shfl_xor_sync(0xffffffffu, lt0, 1);
+        lt0 += __shfl_xor_sync(0xffffffffu, lt0, 2);
+        lt1 += __shfl_xor_sync(0xffffffffu, lt1, 1);
+        lt1 += __shfl_xor_sync(0xffffffffu, lt1, 2);
+      }
       const int live = fin.live;
       const int row0 = mt * 16 + qr, row1 = row0 + 8;
       const int rs = n_parts_done % sp.n_res;
@@ -1122,6 +1233,32 @@ __global__ void __launch_bounds__(threads_of(UMMA, MT * NS), MT * NS == 4 ? 2 : 
         // the NS token slices of each row meet in shared memory
         csync<CTHR>();  // every thread is done reading the merge buffer for the previous part
         float* wo = mg_o + (size_t)ns * p.live_max * sp.mg_stride;
+        if (tr) {
+          // transposed accumulators: o[t] = head dimensions 16 t + qr (+ 8) of query rows 2 qc, 2 qc + 1
+          const int ra = 2 * qc, rb = ra + 1;
+          if (ra < live) {
+#pragma unroll
+            for (int t = 0; t < D / 16; ++t) {
+              wo[ra * sp.mg_stride + 16 * t + qr] = o[t][0];
+              wo[ra * sp.mg_stride + 16 * t + qr + 8] = o[t][2];
+            }
+            if (qr == 0) {
+              mg_m[ns * p.live_max + ra] = m0;
+              mg_l[ns * p.live_max + ra] = lt0;
+            }
+          }
+          if (rb < live) {
+#pragma unroll
+            for (int t = 0; t < D / 16; ++t) {
+              wo[rb * sp.mg_stride + 16 * t + qr] = o[t][1];
+              wo[rb * sp.mg_stride + 16 * t + qr + 8] = o[t][3];
+            }
+            if (qr == 0) {
+              mg_m[ns * p.live_max + rb] = m1;
+              mg_l[ns * p.live_max + rb] = lt1;
+            }
+          }
+        } else {
         if (row0 < live) {
 #pragma unroll
           for (int n = 0; n < ON; ++n)
@@ -1140,6 +1277,7 @@ __global__ void __launch_bounds__(threads_of(UMMA, MT * NS), MT * NS == 4 ? 2 : 
             mg_l[ns * p.live_max + row1] = lt1;
           }
         }
+        }  // row-major accumulators
         if (n_parts_done >= sp.n_res) ok_res = mbar_wait(&res_empty[rs], ((n_parts_done / sp.n_res) - 1) & 1);
         csync<CTHR>();
         for (int oi = tid; oi < live * D; oi += CTHR) {
