@@ -1,7 +1,5 @@
 // Entry points shared by the attention kernels: workspace sizing and the choice of
 // decode kernel.
-#include <cstdlib>
-#include <cstring>
 #include <mutex>
 
 #include "common.cuh"
@@ -15,41 +13,49 @@ uint64_t mma_workspace_bytes(int n_q_heads, int n_kv_heads, int head_dim, int q_
 
 namespace pace {
 namespace {
-struct StreamNote {
-  cudaStream_t stream;
-  int device;
-  bool uses_workspace;
-};
 std::mutex g_note_mu;
 StreamNote g_notes[64];
 int g_n_notes = 0, g_next_note = 0;
-}  // namespace
 
-void note_attention_launch(cudaStream_t stream, bool uses_workspace) {
+// the stream's note, made (as "unknown": workspace in use, pool written) when there is none;
+// a full table recycles its oldest entry.  Call with g_note_mu held.
+StreamNote& note_of(cudaStream_t stream) {
   int dev = 0;
   cudaGetDevice(&dev);
-  std::lock_guard<std::mutex> lk(g_note_mu);
   for (int i = 0; i < g_n_notes; ++i)
-    if (g_notes[i].stream == stream && g_notes[i].device == dev) {
-      g_notes[i].uses_workspace = uses_workspace;
-      return;
-    }
-  // a full table recycles its oldest entry; a stream that lost its note counts as "uses the workspace"
+    if (g_notes[i].stream == stream && g_notes[i].device == dev) return g_notes[i];
   StreamNote& n = g_notes[g_next_note];
   g_next_note = (g_next_note + 1) % 64;
   if (g_n_notes < 64) ++g_n_notes;
   n.stream = stream;
   n.device = dev;
+  n.uses_workspace = true;
+  n.pool_written = true;
+  n.pages = nullptr;
+  n.layer = -1;
+  n.q = nullptr;
+  return n;
+}
+}  // namespace
+
+void note_attention_launch(cudaStream_t stream, bool uses_workspace, const void* pages, int layer, const void* q) {
+  std::lock_guard<std::mutex> lk(g_note_mu);
+  StreamNote& n = note_of(stream);
   n.uses_workspace = uses_workspace;
+  n.pool_written = false;
+  n.pages = pages;
+  n.layer = layer;
+  n.q = q;
 }
 
-bool front_attention_uses_workspace(cudaStream_t stream) {
-  int dev = 0;
-  cudaGetDevice(&dev);
+void note_pool_write(cudaStream_t stream) {
   std::lock_guard<std::mutex> lk(g_note_mu);
-  for (int i = 0; i < g_n_notes; ++i)
-    if (g_notes[i].stream == stream && g_notes[i].device == dev) return g_notes[i].uses_workspace;
-  return true;
+  note_of(stream).pool_written = true;
+}
+
+StreamNote stream_note(cudaStream_t stream) {
+  std::lock_guard<std::mutex> lk(g_note_mu);
+  return note_of(stream);
 }
 }  // namespace pace
 
@@ -63,16 +69,15 @@ extern "C" uint64_t pace_attn_workspace_bytes(int32_t batch, int32_t n_q_heads, 
   return a > b ? a : b;
 }
 
-// Decode (one query token).  Two kernels compute it: the CUDA-core kernel streams K/V rows
-// through packed fp32 FMAs and costs G * 2 FMAs per cached byte; the tensor-core kernel packs the
-// G grouped query heads into one 16-row MMA tile.  PACE_DECODE_IMPL=cuda|mma forces one of them.
+// Decode (one query token).  Two kernels compute it: the tensor-core kernel packs the G grouped
+// query heads of a KV head into one mma.sync tile (any G); the CUDA-core kernel streams K/V rows
+// through packed fp32 FMAs at G * 2 FMAs per cached byte, which is the cheaper form for G of 1 or 2
+// (a 16-row tile would be seven eighths padding).  A launch that carries a pending row always takes
+// the tensor-core kernel.
 extern "C" int pace_attn_decode(const pace_attn_args_t* a, void* stream) {
   if (!a || !a->pool || a->q_len != 1) return PACE_ERR_INVALID;
-  const int G = a->pool->n_kv_heads > 0 ? a->n_q_heads / a->pool->n_kv_heads : 0;
-  bool use_mma = G >= 4 && G <= 16;
-  if (const char* e = getenv("PACE_DECODE_IMPL")) {
-    if (!strcmp(e, "cuda")) use_mma = false;
-    if (!strcmp(e, "mma") && G <= 16) use_mma = true;
-  }
-  return use_mma ? run_mma_paged(a, 1, (cudaStream_t)stream) : decode_cuda_cores(a, stream);
+  if (a->pool->n_kv_heads <= 0 || a->n_q_heads <= 0 || a->n_q_heads % a->pool->n_kv_heads) return PACE_ERR_INVALID;
+  const int G = a->n_q_heads / a->pool->n_kv_heads;
+  const bool cuda_cores = G <= 2 && !(a->flags & PACE_ATTN_PENDING_ROW);
+  return cuda_cores ? decode_cuda_cores(a, stream) : run_mma_paged(a, 1, (cudaStream_t)stream);
 }

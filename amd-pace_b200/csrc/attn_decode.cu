@@ -601,7 +601,7 @@ int sm_count() {
 // Shared by the paged and the dense entry points.
 int run_decode(const KVView& kv, int batch, int n_q_heads, const void* q, int64_t q_sb, int64_t q_sh, void* out,
                int64_t o_sb, int64_t o_sh, const int32_t* kv_start, float scale, void* workspace,
-               uint64_t workspace_bytes, cudaStream_t stream) {
+               uint64_t workspace_bytes, int max_ctas, cudaStream_t stream) {
   const int D = kv.head_dim, Hkv = kv.n_kv_heads;
   if (batch <= 0) return PACE_OK;
   if (n_q_heads % Hkv) return PACE_ERR_INVALID;
@@ -609,10 +609,7 @@ int run_decode(const KVView& kv, int batch, int n_q_heads, const void* q, int64_
   if (!q || !out || ((uintptr_t)q & 15) || (q_sb & 7) || (q_sh & 7)) return PACE_ERR_INVALID;
   if (batch > 8192) return PACE_ERR_UNSUPPORTED;  // the prefix array lives in shared memory
   int grid = sm_count();
-  if (const char* g = getenv("PACE_DECODE_GRID")) {  // test hook: other partitions of the same work
-    const int v = atoi(g);
-    if (v > 0 && v < grid) grid = v;
-  }
+  if (max_ctas > 0 && max_ctas < grid) grid = max_ctas;  // the caller's share of the GPU
   const uint64_t rec = (uint64_t)G * (D + 2) * sizeof(float);
   if (!workspace || ((uintptr_t)workspace & 15)) return PACE_ERR_INVALID;
 
@@ -683,6 +680,12 @@ int decode_cuda_cores(const pace_attn_args_t* a, void* stream) {
   if (a->batch > a->pool->max_seqs) return PACE_ERR_INVALID;
   const KVView kv = make_view(a->pool, a->layer, a->seq_ids);
   return run_decode(kv, a->batch, a->n_q_heads, a->q, a->q_stride_b, a->q_stride_h, a->out, a->o_stride_b,
-                    a->o_stride_h, a->kv_start, a->scale, a->workspace, a->workspace_bytes, (cudaStream_t)stream);
+                    a->o_stride_h, a->kv_start, a->scale, a->workspace, a->workspace_bytes, a->max_ctas,
+                    (cudaStream_t)stream);
 }
 }  // namespace pace
+
+extern "C" int pace_attn_decode_cuda_cores(const pace_attn_args_t* a, void* stream) {
+  if (a && (a->flags & PACE_ATTN_PENDING_ROW)) return PACE_ERR_UNSUPPORTED;  // the tensor-core kernels take pending rows
+  return pace::decode_cuda_cores(a, stream);
+}

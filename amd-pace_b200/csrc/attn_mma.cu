@@ -22,7 +22,6 @@
 #include <cuda.h>
 
 #include <climits>
-#include <cstdlib>
 #include <cstring>
 #include <mutex>
 
@@ -65,6 +64,11 @@ struct MmaParams {
   const void* mask;  // additive [B,1,mask_rows,L] or null
   int mask_fp32, mask_rows;
   int64_t mask_sb;
+  // decode with a pending row: key number kv_len of every (sequence, kv head), not in the pool yet
+  const __nv_bfloat16* k_pend;
+  const __nv_bfloat16* v_pend;
+  int64_t pend_sb, pend_sh;
+  int early_kv;  // whole-unit decode: K/V copies may leave ahead of the wait for the kernel in front
 };
 
 __device__ __forceinline__ int chunks_of_m(const MmaParams& p, int len) {
@@ -289,6 +293,33 @@ __device__ __forceinline__ void publish_part(const MmaParams& p, const ResMeta& 
   }
 }
 
+// One warp stores the pending K and V row of (sequence b, kv head h) in their slot of the pool: row
+// number seq_len of the sequence, i.e. the first unused row of its last page (or the first row of the
+// page behind it, which the step's reservation has made sure of).  seq_len is left alone.  Lanes
+// 0..15 move the K row, 16..31 the V row, 16 bytes each.  Returns false on a bad slot or page.
+template <int D>
+__device__ __forceinline__ bool store_pending_row(const MmaParams& p, int b, int h, int lane) {
+  const int slot = view_slot(p.kv, b);
+  if (slot < 0) return false;
+  const int len = view_len(p.kv, slot), P = p.kv.page_tokens;
+  const int lp = len / P;
+  const int pg = view_page(p.kv, slot, lp);
+  if (pg < 0) return false;
+  const int half = lane >> 4, l16 = lane & 15;
+  if (l16 < D / 8) {
+    const __nv_bfloat16* src = (half ? p.v_pend : p.k_pend) + (size_t)b * p.pend_sb + (size_t)h * p.pend_sh;
+    __nv_bfloat16* dst = const_cast<__nv_bfloat16*>(half ? p.kv.v : p.kv.k) + view_row_offset(p.kv, pg, h, len - lp * P);
+    reinterpret_cast<uint4*>(dst)[l16] = __ldcg(reinterpret_cast<const uint4*>(src) + l16);
+  }
+  return true;
+}
+// the row stores above (generic proxy) are performed, then ordered before async-proxy reads (the TMA
+// copy of that page)
+__device__ __forceinline__ void fence_proxy_async_all() {
+  __threadfence();
+  asm volatile("fence.proxy.async;" ::: "memory");
+}
+
 template <int D, int MT, int NS, bool UMMA = false>
 __global__ void __launch_bounds__(threads_of(UMMA, MT * NS), MT * NS == 4 ? 2 : 1)
     attn_mma_kernel(const MmaParams p, const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV) {
@@ -334,6 +365,9 @@ __global__ void __launch_bounds__(threads_of(UMMA, MT * NS), MT * NS == 4 ? 2 : 
   extern __shared__ __align__(1024) unsigned char smem[];
   const int n_stages = p.n_stages;
   const int n_items = p.batch * p.n_qt;
+  // pend: every sequence has one more key than the pool says, whose row this launch first stores in
+  // its slot of the sequence's last page (position seq_len; seq_len itself is left alone)
+  const bool pend = !UMMA && p.k_pend != nullptr;
   const SmemPlan sp = plan_smem(D, MT, NS, n_stages, p.live_max, p.batch, n_items, UMMA);
   unsigned char* ring = smem + sp.ring;  // [n_stages][K | V]
   MetaM* metas = reinterpret_cast<MetaM*>(smem + sp.metas);
@@ -420,13 +454,29 @@ __global__ void __launch_bounds__(threads_of(UMMA, MT * NS), MT * NS == 4 ? 2 : 
     fence_proxy_async();  // generic-proxy zero fill before async-proxy (TMA) writes to the same bytes
     __syncthreads();      // barriers initialised, V slots zeroed: nothing here depends on an earlier kernel
   }
-  asm volatile("griddepcontrol.wait;" ::: "memory");
-  // A kernel launched as a programmatic dependent of this one (the next layer's K/V append, which
-  // touches nothing this kernel reads or writes) may start once every CTA is past this point.  The
-  // trigger comes after the wait on purpose: a dependent that starts then knows that the kernel in
-  // front of this one has completed, which is what keeps two launches that use the workspace apart
-  // (see the appends' trailing wait).
-  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  // Early K/V (whole-unit decode, p.early_kv): the host knows that nothing of the pool this launch
+  // reads - lengths, block table, pages - was written by the kernel in front of it on the stream.
+  // The two warps that issue copies then skip the wait here: they look the unit up and send its
+  // first K/V chunks while the kernel in front is still in its tail, and wait only before the
+  // first thing that does depend on that kernel (the query rows, the pending rows, a write to out).
+  // gdc_open: this thread has not waited for the kernel in front yet.
+  bool gdc_open = fast && p.early_kv && warp >= NW;
+  auto gdc_wait = [&]() {
+    if (gdc_open) {
+      asm volatile("griddepcontrol.wait;" ::: "memory");
+      asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+      gdc_open = false;
+    }
+  };
+  if (!gdc_open) {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    // A kernel launched as a programmatic dependent of this one (the next layer's attention launch, or
+    // its K/V append, which touches nothing this kernel reads or writes) may start once every CTA is
+    // past this point.  The trigger comes after the wait on purpose: a dependent that starts then knows
+    // that the kernel in front of this one has completed, which is what keeps two launches that use the
+    // workspace apart (see the appends' trailing wait) and what lets a dependent trust everything older.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  }
   const int cta = blockIdx.x;
   long long T = 0, x0 = 0, x1 = 0;
   int NC = 1, n_my = 0;
@@ -469,6 +519,13 @@ __global__ void __launch_bounds__(threads_of(UMMA, MT * NS), MT * NS == 4 ? 2 : 
         }
         const unsigned have = __ballot_sync(0xffffffffu, pg >= 0);
         n = __ffs(~have) - 1;  // leading pages that are in the table
+        if (pend) {
+          // (the page that takes the pending row is copied only after the row has been stored: lane 31
+          // fetches the length beside the other lanes' table entries)
+          int len0 = lane == 31 ? view_len(p.kv, slot0) : 0;
+          len0 = __shfl_sync(0xffffffffu, len0, 31);
+          n = min(n, len0 / P);
+        }
         const int is_v = lane & 1, hf = (lane >> 1) % HALVES;
         for (int c = 0; c < n; ++c) {
           const int pgc = __shfl_sync(0xffffffffu, pg, c);
@@ -476,15 +533,7 @@ __global__ void __launch_bounds__(threads_of(UMMA, MT * NS), MT * NS == 4 ? 2 : 
             tma_load_4d_hint(ring + (size_t)c * STAGE + (is_v ? KVB : 0) + hf * HALF_B, is_v ? &tmV : &tmK, hf * 64, 0,
                              pgc * Hkv + h0s, is_v ? p.c3_v : p.c3_k, &full_bar[c], l2_evict_first_policy());
         }
-        if (n > 0) {
-          const int q_rows = min(MR, p.q_len * G);
-          for (int r = lane; r < q_rows; r += 32) {
-            const int sq = r / G, g = r - sq * G;
-            bulk_g2s(qbuf + r * QS, p.q + (size_t)b0 * p.q_sb + (size_t)(h0s * G + g) * p.q_sh + (size_t)sq * p.q_ss,
-                     D * 2u, &full_bar[0]);
-          }
-          qs = 1;
-        }
+        qs = n > 0;
       }
       if (lane == 0) {
         misc[3] = n;
@@ -492,6 +541,28 @@ __global__ void __launch_bounds__(threads_of(UMMA, MT * NS), MT * NS == 4 ? 2 : 
       }
       __syncwarp();
       asm volatile("bar.arrive 2, 64;" ::: "memory");  // the producer picks the two numbers up behind this
+      gdc_wait();  // (early K/V: the page copies above are out; what follows reads the step's own inputs)
+      if (qs) {
+        const int q_rows = min(MR, p.q_len * G);
+        for (int r = lane; r < q_rows; r += 32) {
+          const int sq = r / G, g = r - sq * G;
+          bulk_g2s(qbuf + r * QS, p.q + (size_t)b0 * p.q_sb + (size_t)(h0s * G + g) * p.q_sh + (size_t)sq * p.q_ss,
+                   D * 2u, &full_bar[0]);
+        }
+      }
+    }
+    if (warp == NW + 1) {
+      gdc_wait();
+      if (pend) {
+        // the pending rows of this CTA's units go into the pool now, long before the producer reaches
+        // the chunks that hold them; it picks the all-clear up at named barrier 4
+        bool ok_rows = true;
+        for (int u = u0; u < u1; ++u) ok_rows &= store_pending_row<D>(p, u / Hkv, u - (u / Hkv) * Hkv, lane);
+        if (!ok_rows && lane == 0) raise_status(p.kv.status, PACE_DEV_BAD_INDEX);
+        fence_proxy_async_all();
+        __syncwarp();
+        asm volatile("bar.arrive 4, 64;" ::: "memory");
+      }
     }
     if (warp == NW) {
       const int it0 = u0 / Hkv, it1 = (u1 - 1) / Hkv;
@@ -501,7 +572,7 @@ __global__ void __launch_bounds__(threads_of(UMMA, MT * NS), MT * NS == 4 ? 2 : 
       int n = 0, slot = -1, len = 0;
       if (b <= it1) {
         slot = view_slot(p.kv, b);
-        if (slot >= 0) len = view_len(p.kv, slot);
+        if (slot >= 0) len = view_len(p.kv, slot) + (pend ? 1 : 0);
       }
       // the first sequence's block-table window: its loads go out right behind the loads of the
       // lengths, before anything waits for either
@@ -540,6 +611,7 @@ __global__ void __launch_bounds__(threads_of(UMMA, MT * NS), MT * NS == 4 ? 2 : 
       for (int u = u0; u < u1; ++u) {
         const int it = u / Hkv, h = u - it * Hkv;
         if (prefix[it + 1] != prefix[it]) continue;
+        gdc_wait();  // (early K/V: a write to out)
         const int R = sb_S[it] * G;
         for (int o = lane; o < MR * D; o += 32) {
           const int r = o / D, d = o % D;
@@ -587,7 +659,7 @@ __global__ void __launch_bounds__(threads_of(UMMA, MT * NS), MT * NS == 4 ? 2 : 
     if (b < p.batch) {
       my_slot[r] = view_slot(p.kv, b);
       if (my_slot[r] >= 0) {
-        my_len[r] = view_len(p.kv, my_slot[r]);
+        my_len[r] = view_len(p.kv, my_slot[r]) + (pend ? 1 : 0);
         // the producer will walk this row of the block table a few microseconds from now: start
         // bringing its first lines into L2 (the K/V stream of the previous launch has evicted them)
         if (p.kv.block_table) {
@@ -739,6 +811,24 @@ __global__ void __launch_bounds__(threads_of(UMMA, MT * NS), MT * NS == 4 ? 2 : 
     const int CT = p.chunk_tokens;
     int i = 0, s = 0, ph = 0, part_idx = 0;
     bool ok = true;
+    // Early K/V: the query rows of the first unit part are the first thing this warp touches that the
+    // kernel in front may have written.  Their copies are held back - the part's K/V chunks go out
+    // first - until the warp would block anyway, then it waits for that kernel and sends them.
+    // dq_*: the copies held back.
+    int dq_b = -1, dq_h = 0, dq_r_lo = 0, dq_rows = 0, dq_s = 0;
+    auto send_q_rows = [&](int b, int h, int r_lo, int q_rows, uint64_t* bar) {
+      for (int r = lane; r < q_rows; r += 32) {
+        const int rr = r_lo + r, sq = rr / G, g = rr - sq * G;
+        const __nv_bfloat16* src = p.q + (size_t)b * p.q_sb + (size_t)(h * G + g) * p.q_sh + (size_t)sq * p.q_ss;
+        bulk_g2s(qbuf + r * QS, src, D * 2u, bar);
+      }
+    };
+    auto flush_q = [&]() {
+      gdc_wait();
+      if (dq_b >= 0) send_q_rows(dq_b, dq_h, dq_r_lo, dq_rows, &full_bar[dq_s]);
+      dq_b = -1;
+    };
+    bool rows_stored = false;  // short prologue with a pending row: the epilogue warp's all-clear has been picked up
     while (i < n_my && ok) {
       const int b = p.n_qt == 1 ? it : it / p.n_qt, qt = it - b * p.n_qt;
       const int slot = sb_slot[b];
@@ -775,9 +865,15 @@ __global__ void __launch_bounds__(threads_of(UMMA, MT * NS), MT * NS == 4 ? 2 : 
       const int q_rows = min(MR, R - r_lo);
       const int c2h = h;
       if (lane == 0 && i == 0) PACE_TRACE(3, 9);
-      if (!UMMA && part_idx > 0 && !mbar_wait(q_empty, (part_idx - 1) & 1)) { ok = false; break; }
+      if (!UMMA && part_idx > 0) {
+        flush_q();
+        if (!mbar_wait(q_empty, (part_idx - 1) & 1)) { ok = false; break; }
+      }
       for (bool first = true; j < j_end; ++j, ++i, first = false) {
-        if (i >= n_stages && !mbar_wait(&empty_bar[s], ph ^ 1)) { ok = false; break; }
+        if (i >= n_stages) {
+          if (!UMMA && MT == 1) flush_q();
+          if (!mbar_wait(&empty_bar[s], ph ^ 1)) { ok = false; break; }
+        }
         const int tok0 = whole_pages ? j * CT : lp * P + row0;
         const int rows = whole_pages ? min(CT, len - tok0) : min(min(kChunk, P - row0), len - tok0);
         const int n_pages_c = !whole_pages ? 1 : (rows == CT ? p.pages_per_chunk : (rows + P - 1) / P);
@@ -796,6 +892,19 @@ __global__ void __launch_bounds__(threads_of(UMMA, MT * NS), MT * NS == 4 ? 2 : 
         __syncwarp();
         const int pg = pw.get(lp + pi, lp, lane);
         if (lane == 0 && i == 0) PACE_TRACE(3, 10);
+        if (pend && j == nch - 1) {
+          // The unit's final chunk holds the pending row, which has to be in the pool before the copy
+          // leaves.  Short prologue: the epilogue warp stored this CTA's rows at the start (one
+          // meeting, once).  General prologue: this warp stores the unit's row itself, now.
+          if (fast) {
+            if (!rows_stored) asm volatile("bar.sync 4, 64;" ::: "memory");
+            rows_stored = true;
+          } else {
+            if (!store_pending_row<D>(p, b, h, lane) && lane == 0) raise_status(p.kv.status, PACE_DEV_BAD_INDEX);
+            fence_proxy_async_all();
+            __syncwarp();
+          }
+        }
         if (i < n_spec) {
           // (short prologue: this chunk's copy is on its way already - same sequence, head and page)
         } else if (copier && pi < n_pages_c) {
@@ -806,12 +915,11 @@ __global__ void __launch_bounds__(threads_of(UMMA, MT * NS), MT * NS == 4 ? 2 : 
           else raise_status(p.kv.status, PACE_DEV_BAD_INDEX);  // the consumers' bounded wait on this stage gives up
         }
         if (first && !UMMA && !(q_spec && i == 0)) {  // (the tcgen05 variant's softmax warps write the Q tile themselves, swizzled)
-          for (int r = lane; r < q_rows; r += 32) {
-            const int rr = r_lo + r, sq = rr / G, g = rr - sq * G;
-            const __nv_bfloat16* src = p.q + (size_t)b * p.q_sb + (size_t)(h * G + g) * p.q_sh + (size_t)sq * p.q_ss;
-            bulk_g2s(qbuf + r * QS, src, D * 2u, &full_bar[s]);
+          if (gdc_open) {
+            dq_b = b, dq_h = h, dq_r_lo = r_lo, dq_rows = q_rows, dq_s = s;
+          } else {
+            send_q_rows(b, h, r_lo, q_rows, &full_bar[s]);
           }
-          if (i == 0 && lane == 0) PACE_STAMP(2);
         }
         if (lane == 0) PACE_TRACE(0, i);
         if (whole_pages) {
@@ -823,6 +931,7 @@ __global__ void __launch_bounds__(threads_of(UMMA, MT * NS), MT * NS == 4 ? 2 : 
         if (++s == n_stages) { s = 0; ph ^= 1; }
       }
       if (!ok) break;
+      if (!UMMA && MT == 1) flush_q();
       ++part_idx;
       j = 0;
       if (i >= n_my) break;
@@ -960,6 +1069,10 @@ __global__ void __launch_bounds__(threads_of(UMMA, MT * NS), MT * NS == 4 ? 2 : 
           ldsm_x4(qb + row * QS + cch * 16, qa[k][0], qa[k][1], qa[k][2], qa[k][3]);
         }
       }
+      m0 = m1 = -INFINITY;
+      l0 = l1 = 0.f;
+#pragma unroll
+      for (int n = 0; n < ON; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
       __syncwarp();
       if (lane == 0) mbar_arrive(q_empty);
       // (transposed: my two query rows are 2 qc and 2 qc + 1, the columns of my accumulators)
@@ -978,10 +1091,6 @@ __global__ void __launch_bounds__(threads_of(UMMA, MT * NS), MT * NS == 4 ? 2 : 
       fin.first_cta = meta->first_cta;
       fin.first_slot = meta->first_slot;
       fin.unit = meta->unit;
-      m0 = m1 = -INFINITY;
-      l0 = l1 = 0.f;
-#pragma unroll
-      for (int n = 0; n < ON; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
     }
 
     // The chunk's keys are dealt to the NS warps of a row tile in equal slices of whole 8-key tiles:
@@ -1421,35 +1530,28 @@ int sm_count_m() {
   return n;
 }
 
-// PACE_PDL=0 turns programmatic dependent launches off (A/B measurements)
-bool pdl_enabled() {
-  static const bool on = [] {
-    const char* e = getenv("PACE_PDL");
-    return !(e && e[0] == '0');
-  }();
-  return on;
-}
-
-// PACE_DECODE_HALF=0 keeps decode on eight-warp CTAs, one per SM (A/B measurements)
-bool decode_half_enabled() {
-  const char* e = getenv("PACE_DECODE_HALF");
-  return !(e && e[0] == '0');
-}
-
-// Fewest query rows (tokens x grouped heads) for which a tile goes to the tcgen05 variant; 0 = never.
+// Fewest query rows (tokens x grouped heads) for which a tile goes to the tcgen05 variant.
 // At 33 rows and more (PARD verify: 9 tokens x 4 grouped heads = 36) a 128-row tile, three quarters of
 // it padding, already beats the mma.sync kernel's 64-row tiles: the MMAs cost the softmax warps
-// nothing.  PACE_UMMA_MIN_ROWS overrides the threshold (A/B measurements).
-int umma_min_rows() {
-  static const int v = [] {
-    const char* e = getenv("PACE_UMMA_MIN_ROWS");
-    return e ? atoi(e) : 33;
-  }();
-  return v;
-}
+// nothing.
+constexpr int kUmmaMinRows = 33;
+
+// What run_mma needs beyond the operands of the reference op: the pending row of a decode launch,
+// the caller's limit on thread blocks, and what the stream note records about the launch.
+struct MmaExtra {
+  const void* k_pend = nullptr;
+  const void* v_pend = nullptr;
+  int64_t pend_sb = 0, pend_sh = 0;
+  int max_ctas = 0;            // 0: one thread block per SM (two for the four-warp decode form)
+  bool one_cta_per_sm = false; // decode: keep the eight-warp form
+  bool no_early_kv = false;
+  const void* pages = nullptr; // pool the launch reads (null: the dense form)
+  int layer = -1;
+};
 
 template <int D, int MT, int NS, bool UMMA = false>
-int launch_mma(MmaParams& p, const CUtensorMap& tmK, const CUtensorMap& tmV, int grid, cudaStream_t stream) {
+int launch_mma(MmaParams& p, const CUtensorMap& tmK, const CUtensorMap& tmV, int grid, cudaStream_t stream,
+               const MmaExtra& ex) {
   constexpr int MR = 16 * MT;
   constexpr int NW = MT * NS;
   const int n_items = p.batch * p.n_qt;
@@ -1461,6 +1563,12 @@ int launch_mma(MmaParams& p, const CUtensorMap& tmK, const CUtensorMap& tmV, int
   if (ns < 2) return PACE_ERR_UNSUPPORTED;
   p.n_stages = ns;
   const size_t smem_bytes = plan_smem(D, MT, NS, ns, p.live_max, p.batch, n_items, UMMA).total;
+  // Early K/V streaming: only the short prologue of whole-unit decode has it, and only when this
+  // library's newest launch on the stream was an attention launch (nothing wrote the pool since).
+  p.early_kv = (!UMMA && MT == 1 && p.whole_units && !ex.no_early_kv && ex.pages && !p.q_lens &&
+                !stream_note(stream).pool_written)
+                   ? 1
+                   : 0;
   static bool configured[16] = {};
   int dev = 0;
   PACE_CUDA_TRY(cudaGetDevice(&dev));
@@ -1480,10 +1588,10 @@ int launch_mma(MmaParams& p, const CUtensorMap& tmK, const CUtensorMap& tmV, int
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  cfg.numAttrs = 1;
   PACE_CUDA_TRY(cudaLaunchKernelEx(&cfg, attn_mma_kernel<D, MT, NS, UMMA>, p, tmK, tmV));
   PACE_LAUNCH_CHECK("attn_mma_kernel");
-  note_attention_launch(stream, /*uses_workspace=*/!p.whole_units);
+  note_attention_launch(stream, /*uses_workspace=*/!p.whole_units, ex.pages, ex.layer, p.q);
   return PACE_OK;
 }
 
@@ -1492,7 +1600,7 @@ int launch_mma(MmaParams& p, const CUtensorMap& tmK, const CUtensorMap& tmV, int
 uint64_t mma_workspace_bytes(int n_q_heads, int n_kv_heads, int head_dim, int q_len) {
   const int G = n_q_heads / (n_kv_heads > 0 ? n_kv_heads : 1);
   const int M = G * q_len;
-  const int MT = (umma_min_rows() > 0 && M >= umma_min_rows()) ? 8 : M <= 16 ? 1 : M <= 32 ? 2 : M <= 64 ? 4 : 8;
+  const int MT = M >= kUmmaMinRows ? 8 : M <= 16 ? 1 : M <= 32 ? 2 : M <= 64 ? 4 : 8;
   const int ctas = (MT == 1 ? 2 : 1) * sm_count_m();  // decode runs two four-warp CTAs per SM
   return kWorkspaceCounterBytes + (uint64_t)ctas * 2 * (16 * MT) * (head_dim + 2) * sizeof(float) + 256;
 }
@@ -1502,7 +1610,7 @@ int run_mma(const KVView& kv, const CUtensorMap& tmK, const CUtensorMap& tmV, in
             int n_q_heads, int q_len, const void* q, int64_t q_sb, int64_t q_sh, int64_t q_ss, void* out, int64_t o_sb,
             int64_t o_sh, int64_t o_ss, const int32_t* kv_start, const int32_t* q_lens, int causal, float scale,
             const void* mask, int mask_fp32, int mask_rows, int64_t mask_sb, void* workspace, uint64_t workspace_bytes,
-            uint32_t flags, cudaStream_t stream) {
+            uint32_t flags, cudaStream_t stream, const MmaExtra& ex) {
   const int D = kv.head_dim, Hkv = kv.n_kv_heads;
   if (batch <= 0 || q_len <= 0) return PACE_OK;
   if (n_q_heads % Hkv) return PACE_ERR_INVALID;
@@ -1512,8 +1620,15 @@ int run_mma(const KVView& kv, const CUtensorMap& tmK, const CUtensorMap& tmV, in
   if (!workspace || ((uintptr_t)workspace & 15)) return PACE_ERR_INVALID;
   const int M = G * q_len;
   // 128-row tiles on the 5th-generation tensor cores (no additive mask there; 16-byte output stores)
-  const bool umma = umma_min_rows() > 0 && M >= umma_min_rows() && !mask && !((uintptr_t)out & 15) && !(o_sb & 7) &&
-                    !(o_sh & 7) && !(o_ss & 7);
+  const bool pend = (flags & PACE_ATTN_PENDING_ROW) != 0;
+  if (pend) {
+    // one pending row per sequence: a decode launch over the pool, on the mma.sync kernels
+    if (q_len != 1 || !ex.pages || mask || M >= kUmmaMinRows) return PACE_ERR_UNSUPPORTED;
+    if (!ex.k_pend || !ex.v_pend || ((uintptr_t)ex.k_pend & 15) || ((uintptr_t)ex.v_pend & 15) || (ex.pend_sb & 7) ||
+        (ex.pend_sh & 7))
+      return PACE_ERR_INVALID;
+  }
+  const bool umma = M >= kUmmaMinRows && !mask && !((uintptr_t)out & 15) && !(o_sb & 7) && !(o_sh & 7) && !(o_ss & 7);
   const int MT = umma ? 8 : M <= 16 ? 1 : M <= 32 ? 2 : M <= 64 ? 4 : 8;
   const int MR = 16 * MT;
   int grid = sm_count_m();
@@ -1523,13 +1638,10 @@ int run_mma(const KVView& kv, const CUtensorMap& tmK, const CUtensorMap& tmV, in
   // ... and three ring stages fit beside the per-sequence arrays (they do up to a batch of about 80).
   const int live = G * q_len < MR ? G * q_len : MR;
   const int slice = batch < kMaxItems ? batch : kMaxItems;
-  const bool half = MT == 1 && decode_half_enabled() && workspace_bytes >= workspace_for(2 * grid) &&
+  const bool half = MT == 1 && !ex.one_cta_per_sm && workspace_bytes >= workspace_for(2 * grid) &&
                     plan_smem(D, 1, 4, 3, live, slice, slice, false).total <= kHalfSmemBudget;
   if (half) grid *= 2;
-  if (const char* g = getenv("PACE_DECODE_GRID")) {  // test hook: other partitions of the same work
-    const int v = atoi(g);
-    if (v > 0 && v < grid) grid = v;
-  }
+  if (ex.max_ctas > 0 && ex.max_ctas < grid) grid = ex.max_ctas;  // the caller's share of the GPU
   if (workspace_bytes < workspace_for(grid)) return PACE_ERR_INVALID;
 
   MmaParams p;
@@ -1554,6 +1666,11 @@ int run_mma(const KVView& kv, const CUtensorMap& tmK, const CUtensorMap& tmV, in
   p.mask_fp32 = mask_fp32;
   p.mask_rows = mask_rows;
   p.mask_sb = mask_sb;
+  p.k_pend = pend ? (const __nv_bfloat16*)ex.k_pend : nullptr;
+  p.v_pend = pend ? (const __nv_bfloat16*)ex.v_pend : nullptr;
+  p.pend_sb = ex.pend_sb;
+  p.pend_sh = ex.pend_sh;
+  p.early_kv = 0;
   const int P = kv.page_tokens;
   const int HALVES = D / 64;
   if (P <= kChunk) {
@@ -1582,16 +1699,20 @@ int run_mma(const KVView& kv, const CUtensorMap& tmK, const CUtensorMap& tmV, in
     p.out = (__nv_bfloat16*)out + (size_t)b0 * o_sb;
     p.kv_start = kv_start ? kv_start + b0 : nullptr;
     p.q_lens = q_lens ? q_lens + b0 : nullptr;
+    if (pend) {
+      p.k_pend = (const __nv_bfloat16*)ex.k_pend + (size_t)b0 * ex.pend_sb;
+      p.v_pend = (const __nv_bfloat16*)ex.v_pend + (size_t)b0 * ex.pend_sb;
+    }
     int rc = PACE_ERR_UNSUPPORTED;
 #define PACE_MMA_CASE(DD, MM, NN) \
-  if (D == DD && MT == MM) rc = launch_mma<DD, MM, NN>(p, tmK, tmV, grid, stream);
+  if (D == DD && MT == MM) rc = launch_mma<DD, MM, NN>(p, tmK, tmV, grid, stream, ex);
     if (umma) {
-      if (D == 128) rc = launch_mma<128, 8, 1, true>(p, tmK, tmV, grid, stream);
-      if (D == 64) rc = launch_mma<64, 8, 1, true>(p, tmK, tmV, grid, stream);
+      if (D == 128) rc = launch_mma<128, 8, 1, true>(p, tmK, tmV, grid, stream, ex);
+      if (D == 64) rc = launch_mma<64, 8, 1, true>(p, tmK, tmV, grid, stream, ex);
     } else {
       if (half) {
-        if (D == 128) rc = launch_mma<128, 1, 4>(p, tmK, tmV, grid, stream);
-        if (D == 64) rc = launch_mma<64, 1, 4>(p, tmK, tmV, grid, stream);
+        if (D == 128) rc = launch_mma<128, 1, 4>(p, tmK, tmV, grid, stream, ex);
+        if (D == 64) rc = launch_mma<64, 1, 4>(p, tmK, tmV, grid, stream, ex);
       } else {
         PACE_MMA_CASE(128, 1, 8)
         PACE_MMA_CASE(64, 1, 8)
@@ -1616,9 +1737,21 @@ int run_mma_paged(const pace_attn_args_t* a, int causal, cudaStream_t stream) {
   const int rc = pool_map(a->pool, &tm);
   if (rc != PACE_OK) return rc;
   const KVView kv = make_view(a->pool, a->layer, a->seq_ids);
+  MmaExtra ex;
+  if (a->flags & PACE_ATTN_PENDING_ROW) {
+    ex.k_pend = a->k_pending;
+    ex.v_pend = a->v_pending;
+    ex.pend_sb = a->pending_stride_b;
+    ex.pend_sh = a->pending_stride_h;
+  }
+  ex.max_ctas = a->max_ctas;
+  ex.one_cta_per_sm = (a->flags & PACE_ATTN_ONE_CTA_PER_SM) != 0;
+  ex.no_early_kv = (a->flags & PACE_ATTN_NO_EARLY_KV) != 0;
+  ex.pages = a->pool->pages;
+  ex.layer = a->layer;
   return run_mma(kv, tm, tm, a->layer * 2, a->layer * 2 + 1, a->batch, a->n_q_heads, a->q_len, a->q, a->q_stride_b,
                  a->q_stride_h, a->q_stride_s, a->out, a->o_stride_b, a->o_stride_h, a->o_stride_s, a->kv_start,
-                 a->q_lens, causal, a->scale, nullptr, 0, 1, 0, a->workspace, a->workspace_bytes, a->flags, stream);
+                 a->q_lens, causal, a->scale, nullptr, 0, 1, 0, a->workspace, a->workspace_bytes, a->flags, stream, ex);
 }
 
 }  // namespace pace
@@ -1675,6 +1808,7 @@ extern "C" int pace_attn_decode_static(const pace_attn_args_t* a, void* stream) 
   if (G > 16 || pl->head_dim > 128) return PACE_ERR_UNSUPPORTED;
   if ((uint64_t)a->batch * pl->n_kv_heads * sizeof(int32_t) > kWorkspaceCounterBytes) return PACE_ERR_UNSUPPORTED;
   if (sm_count_m() > kStaticMaxSMs) return PACE_ERR_UNSUPPORTED;
+  if (a->layer < 0 || a->layer >= pl->n_layers || a->batch > pl->max_seqs) return PACE_ERR_INVALID;  // before the array is touched
   if (a->batch == 0) return PACE_OK;
   void* scratch = nullptr;
   const int rc = static_scratch_ptr(&scratch);  // first call on a device: resolves the array's device address
@@ -1689,9 +1823,8 @@ extern "C" int pace_attn_decode_static(const pace_attn_args_t* a, void* stream) 
 extern "C" int pace_attn_verify(const pace_attn_args_t* a, void* stream) {
   return run_mma_paged(a, 1, (cudaStream_t)stream);
 }
-extern "C" int pace_attn_prefill(const pace_attn_args_t* a, void* stream) {
-  return run_mma_paged(a, 1, (cudaStream_t)stream);
-}
+// (an alias: one kernel family serves every query length; the name is what a chunked-prefill caller looks for)
+extern "C" int pace_attn_prefill(const pace_attn_args_t* a, void* stream) { return pace_attn_verify(a, stream); }
 
 extern "C" int pace_attention_dense(const void* q, const void* k, const void* v, const void* mask,
                                     int32_t mask_is_fp32, int32_t mask_rows, void* out, int32_t B, int32_t N,
@@ -1723,5 +1856,5 @@ extern "C" int pace_attention_dense(const void* q, const void* k, const void* v,
   if (rc != PACE_OK) return rc;
   return run_mma(kv, tmK, tmV, 0, 0, B, N, S, q, (int64_t)N * S * H, (int64_t)S * H, H, out, (int64_t)N * S * H,
                  (int64_t)S * H, H, nullptr, nullptr, /*causal=*/0, 0.f, mask, mask_is_fp32, mask_rows,
-                 (int64_t)mask_rows * L, workspace, workspace_bytes, 0u, (cudaStream_t)stream);
+                 (int64_t)mask_rows * L, workspace, workspace_bytes, 0u, (cudaStream_t)stream, MmaExtra());
 }

@@ -14,12 +14,29 @@ namespace pace {
 // ---------------------------------------------------------------------------
 void set_cuda_error(cudaError_t e, const char* where);
 
-// What the newest tensor-core attention launch on a stream does with its workspace (host-side note,
-// kept per stream).  Those launches let the K/V append behind them start early; the append asks here
-// whether it has to hold its own completion until that launch has completed (see append_kernel).
-// A stream nobody noted counts as "uses the workspace".
-void note_attention_launch(cudaStream_t stream, bool uses_workspace);
-bool front_attention_uses_workspace(cudaStream_t stream);
+// What the library's newest launch on a stream was (host-side note, kept per stream and device).
+// Attention launches let the kernel behind them start early (programmatic dependent launch); the
+// note is how a later entry point on the same stream learns what it may overlap with:
+//   * an append asks whether the attention launch in front shares its workspace with the launch
+//     behind the append (then the append holds its own completion until that launch is done), and
+//     whether that launch reads the very layer (or q buffer) the append is about to write (then the
+//     append is launched as an ordinary, fully ordered kernel);
+//   * a decode launch asks whether anything since the newest attention launch wrote pool state; if
+//     not, it may stream K/V ahead of its wait for the kernel in front.
+// A stream nobody noted counts as "uses the workspace, wrote the pool".
+struct StreamNote {
+  cudaStream_t stream;
+  int device;
+  bool uses_workspace;   // newest attention launch: units may be cut, partials meet in the workspace
+  bool pool_written;     // a pool-writing kernel was launched after the newest attention launch
+  const void* pages;     // newest attention launch: pool it reads (pages pointer), layer, q buffer
+  int layer;
+  const void* q;
+};
+void note_attention_launch(cudaStream_t stream, bool uses_workspace, const void* pages, int layer, const void* q);
+void note_pool_write(cudaStream_t stream);
+StreamNote stream_note(cudaStream_t stream);
+inline bool front_attention_uses_workspace(cudaStream_t stream) { return stream_note(stream).uses_workspace; }
 
 #define PACE_CUDA_TRY(expr)                         \
   do {                                              \

@@ -274,6 +274,72 @@ __global__ void __launch_bounds__(256)
   if (drain) asm volatile("griddepcontrol.wait;" ::: "memory");
 }
 
+// The appends of a whole decode step in one launch: one warp per (layer, sequence).  The warp looks
+// the sequence's slot, length and page up once, moves the rows of all KV heads (16 bytes per lane,
+// the loads of up to eight rows in flight together) and then advances that one length itself - no
+// other warp reads or writes it, so the launch needs neither a ticket nor a fence.  Meant for decode
+// steps (a few tokens per sequence); a prefill chunk is better served by one append_kernel per layer.
+// The kernel waits for everything in front of it on the stream before it touches anything (the
+// step's attention launches read the lengths it advances), and nothing behind it starts early.
+__global__ void __launch_bounds__(256)
+    append_layers_kernel(pace_kv_pool_t p, int layer_begin, int layer_end, const int32_t* __restrict__ seq_ids, int batch,
+                         int n_new, const int32_t* __restrict__ n_per, const __nv_bfloat16* __restrict__ k_new,
+                         const __nv_bfloat16* __restrict__ v_new, int64_t sl, int64_t sb, int64_t sh, int64_t st) {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  const int lane = threadIdx.x & 31;
+  const int P = p.page_tokens, D = p.head_dim, H = p.n_kv_heads;
+  const int vec_per_row = D / 8;             // 16-byte vectors in a row: 16 (D = 128) or 8
+  const int rows_per_pass = 32 / vec_per_row;  // rows one pass of the warp moves: 2 or 4
+  const size_t page_elems = (size_t)H * P * D;
+  const size_t region = page_elems * (size_t)p.n_pages;
+  const int w = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (w >= batch * (layer_end - layer_begin)) return;
+  const int b = w % batch, li = w / batch, layer = layer_begin + li;
+  const int slot = seq_ids[b];
+  if (slot < 0 || slot >= p.max_seqs) return;  // reported by reserve
+  const int n = n_per ? min(n_per[b], n_new) : n_new;
+  if (n <= 0) return;
+  int32_t* len_p = p.seq_len + (size_t)layer * p.max_seqs + slot;
+  const int len = *len_p;
+  __nv_bfloat16* kbase = reinterpret_cast<__nv_bfloat16*>(p.pages) + ((size_t)layer * 2) * region;
+  const int r_in = lane / vec_per_row, vec = lane - r_in * vec_per_row;
+  bool bad = false;
+  for (int t = 0; t < n; ++t) {
+    const int pos = len + t, lp = pos / P;
+    int page = -1;
+    if (lp < p.max_pages_per_seq) page = p.block_table[(size_t)slot * p.max_pages_per_seq + lp];
+    if (page < 0 || page >= p.n_pages) {
+      bad = true;
+      continue;
+    }
+    // rows of this token: K of head 0 .. H-1, then V of head 0 .. H-1
+    const size_t tok_src = (size_t)li * sl + (size_t)b * sb + (size_t)t * st;
+    const size_t tok_dst = ((size_t)page * H * P + (pos - lp * P)) * (size_t)D;
+    for (int r0 = 0; r0 < 2 * H; r0 += 4 * rows_per_pass) {
+      uint4 val[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int r = r0 + u * rows_per_pass + r_in;
+        if (r < 2 * H) {
+          const int is_v = r >= H, h = is_v ? r - H : r;
+          val[u] = __ldcg(reinterpret_cast<const uint4*>((is_v ? v_new : k_new) + tok_src + (size_t)h * sh) + vec);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int r = r0 + u * rows_per_pass + r_in;
+        if (r < 2 * H) {
+          const int is_v = r >= H, h = is_v ? r - H : r;
+          reinterpret_cast<uint4*>(kbase + (is_v ? region : 0) + tok_dst + (size_t)h * P * D)[vec] = val[u];
+        }
+      }
+    }
+  }
+  if (bad && lane == 0) raise_status(p.status, PACE_DEV_BAD_INDEX);
+  __syncwarp();
+  if (lane == 0) *len_p = len + n;
+}
+
 // RoPE + append: eight lanes per (sequence, new token, group of kRopeHeads heads) of the projection
 // outputs.  Query rows are rotated into q_out, key rows rotated into their cache slot, value rows
 // copied into theirs.  A lane owns eight (x1, x2) pairs of every row of its group: it loads their
@@ -588,11 +654,16 @@ __global__ void read_dense_kernel(pace_kv_pool_t p, int layer, const int32_t* __
   }
 }
 
-// PACE_PDL=0 turns the programmatic launch of the append kernel off (A/B measurements)
-const bool g_pdl_append = [] {
-  const char* e = getenv("PACE_PDL");
-  return !(e && e[0] == '0');
-}();
+// Whether an append to `layer` of this pool may be launched as a programmatic dependent, i.e. start
+// while this library's newest attention launch on the stream is still running.  Not when that
+// launch reads the same layer of the same pool (its blocks may still be reading the lengths the
+// append advances), and not when the append rewrites the buffer that launch takes its queries from.
+bool append_may_overlap(cudaStream_t stream, const pace_kv_pool_t* p, int layer, const void* rewritten = nullptr) {
+  const StreamNote n = stream_note(stream);
+  if (n.pages == p->pages && (n.layer == layer || p->n_layers == 1)) return false;
+  if (rewritten && n.q == rewritten) return false;
+  return true;
+}
 
 bool pool_ok(const pace_kv_pool_t* p) {
   return geometry_ok(p) && p->pages && p->block_table && p->seq_len && p->seq_pages && p->page_ref &&
@@ -667,6 +738,7 @@ int pace_kv_pool_reset(const pace_kv_pool_t* p, void* stream) {
   if (!pool_ok(p)) return PACE_ERR_INVALID;
   reset_kernel<<<148, 256, 0, (cudaStream_t)stream>>>(*p);
   PACE_LAUNCH_CHECK("reset_kernel");
+  note_pool_write((cudaStream_t)stream);
   return PACE_OK;
 }
 
@@ -694,6 +766,7 @@ int pace_kv_seq_release(const pace_kv_pool_t* p, const int32_t* seq_ids, int32_t
   if (batch == 0) return PACE_OK;
   release_kernel<<<batch < 148 ? batch : 148, 128, 0, (cudaStream_t)stream>>>(*p, seq_ids, batch);
   PACE_LAUNCH_CHECK("release_kernel");
+  note_pool_write((cudaStream_t)stream);
   return PACE_OK;
 }
 
@@ -705,6 +778,7 @@ int pace_kv_reserve(const pace_kv_pool_t* p, int32_t layer, const int32_t* seq_i
   if (batch == 0 || n_new == 0) return PACE_OK;
   reserve_kernel<<<1, 256, 0, (cudaStream_t)stream>>>(*p, layer, seq_ids, batch, n_new, n_per);
   PACE_LAUNCH_CHECK("reserve_kernel");
+  note_pool_write((cudaStream_t)stream);
   return PACE_OK;
 }
 
@@ -734,11 +808,44 @@ int pace_kv_append(const pace_kv_pool_t* p, int32_t layer, const int32_t* seq_id
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = g_pdl_append ? 1 : 0;
+  cfg.numAttrs = append_may_overlap((cudaStream_t)stream, p, layer) ? 1 : 0;
   PACE_CUDA_TRY(cudaLaunchKernelEx(&cfg, append_kernel, *p, (int)layer, seq_ids, (int)batch, (int)n_new, n_per,
                                    (const __nv_bfloat16*)k_new, (const __nv_bfloat16*)v_new, (int64_t)sb, (int64_t)sh,
                                    (int64_t)st, front_attention_uses_workspace((cudaStream_t)stream) ? 1 : 0));
   PACE_LAUNCH_CHECK("append_kernel");
+  note_pool_write((cudaStream_t)stream);
+  return PACE_OK;
+}
+
+int pace_kv_append_layers(const pace_kv_pool_t* p, int32_t layer_begin, int32_t layer_end, const int32_t* seq_ids,
+                          int32_t batch, int32_t n_new, const int32_t* n_per, const void* k_new, const void* v_new,
+                          int64_t sl, int64_t sb, int64_t sh, int64_t st, void* stream) {
+  if (!pool_ok(p) || !seq_ids || batch < 0 || batch > p->max_seqs || n_new < 0 || layer_begin < 0 ||
+      layer_end > p->n_layers || layer_begin > layer_end)
+    return PACE_ERR_INVALID;
+  if (batch == 0 || n_new == 0 || layer_begin == layer_end) return PACE_OK;
+  if (!k_new || !v_new) return PACE_ERR_INVALID;
+  if (((uintptr_t)k_new & 15) || ((uintptr_t)v_new & 15) || (sl & 7) || (sb & 7) || (sh & 7) || (st & 7))
+    return PACE_ERR_INVALID;
+  const long long warps = (long long)batch * (layer_end - layer_begin);
+  if (warps > (1LL << 30)) return PACE_ERR_UNSUPPORTED;
+  // Launched as a programmatic dependent so that the launch itself overlaps the tail of the kernel in
+  // front; the kernel's first instruction waits for that kernel (and everything older) to complete.
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)((warps + 7) / 8));
+  cfg.blockDim = dim3(256);
+  cfg.dynamicSmemBytes = 0;
+  cfg.stream = (cudaStream_t)stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  PACE_CUDA_TRY(cudaLaunchKernelEx(&cfg, append_layers_kernel, *p, (int)layer_begin, (int)layer_end, seq_ids, (int)batch,
+                                   (int)n_new, n_per, (const __nv_bfloat16*)k_new, (const __nv_bfloat16*)v_new,
+                                   (int64_t)sl, (int64_t)sb, (int64_t)sh, (int64_t)st));
+  PACE_LAUNCH_CHECK("append_layers_kernel");
+  note_pool_write((cudaStream_t)stream);
   return PACE_OK;
 }
 
@@ -788,10 +895,11 @@ int pace_kv_append_rope(const pace_kv_pool_t* p, int32_t layer, const int32_t* s
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = g_pdl_append ? 1 : 0;
+  cfg.numAttrs = append_may_overlap((cudaStream_t)stream, p, layer, a->q_out) ? 1 : 0;
   PACE_CUDA_TRY(cudaLaunchKernelEx(&cfg, append_rope_kernel, *p, (int)layer, seq_ids, (int)batch, (int)n_new, n_per, r,
                                    front_attention_uses_workspace((cudaStream_t)stream) ? 1 : 0));
   PACE_LAUNCH_CHECK("append_rope_kernel");
+  note_pool_write((cudaStream_t)stream);
   return PACE_OK;
 }
 
@@ -805,6 +913,7 @@ int pace_kv_truncate(const pace_kv_pool_t* p, int32_t layer_begin, int32_t layer
   truncate_kernel<<<(n + 255) / 256, 256, 0, (cudaStream_t)stream>>>(*p, layer_begin, layer_end, seq_ids, batch,
                                                                     remove_len, remove_per);
   PACE_LAUNCH_CHECK("truncate_kernel");
+  note_pool_write((cudaStream_t)stream);
   return PACE_OK;
 }
 
@@ -814,6 +923,7 @@ int pace_kv_gather(const pace_kv_pool_t* p, const int32_t* seq_ids, const int64_
   if (batch == 0) return PACE_OK;
   gather_kernel<<<1, 256, 0, (cudaStream_t)stream>>>(*p, seq_ids, beam_idx, batch);
   PACE_LAUNCH_CHECK("gather_kernel");
+  note_pool_write((cudaStream_t)stream);
   return PACE_OK;
 }
 

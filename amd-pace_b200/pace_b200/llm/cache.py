@@ -19,7 +19,10 @@ synchronous about them (``len(manager)``, ``ValueError`` on over-removal).
 
 Extensions the reference does not have (its batch shares one length): ragged
 per-sequence appends and rollbacks (``n_new_per_seq=``, list-valued
-``remove_cache``) and a shared long-lived pool (``pool=``).
+``remove_cache``), a shared long-lived pool (``pool=``) and deferred decode appends
+(``defer_appends``): a one-token ``update_cache`` then only stages the new row, the
+attention op reads it from the staging buffer as the newest key, and ``commit()`` stores
+the staged rows of all layers with one kernel after the step's last layer.
 """
 import ctypes as C
 import math
@@ -231,6 +234,14 @@ class KVCacheManager:
         self.static_launch = False   # frozen launch sequence (CUDA graphs): layer 0 always reserves
         self.capturing = False       # launches are being recorded, not executed: leave the mirror alone
         self.skip_reserve = False    # with static_launch: record the step without its page reservation
+        # Deferred decode appends: a one-token update_cache only stages its row (nothing is launched when
+        # the caller already wrote it into the staging buffer), attention takes it as a pending key, and
+        # commit() appends every layer's row in one launch.  Off by default: update_cache then appends
+        # at once, as the reference does.
+        self.defer_appends = False
+        self._stage_k: Optional[torch.Tensor] = None   # [layers, B, H, 1, D] views of the staging buffer
+        self._stage_v: Optional[torch.Tensor] = None
+        self._pending: set = set()                     # layers whose newest row is staged, not yet in the pool
         self.cache_objects: List[KVCacheBase] = [
             self.kv_cache_class(max_seq_length, manager=self, layer=i) for i in range(self.num_layers)
         ]
@@ -258,6 +269,56 @@ class KVCacheManager:
     def __len__(self) -> int:
         return int(self.cache_objects[0].seq_len)
 
+    # -- deferred decode appends ---------------------------------------------------------------
+    def adopt_staging(self, k_all: torch.Tensor, v_all: torch.Tensor) -> None:
+        """Use the caller's buffers as the staging area of deferred appends: bf16 ``[layers, B, H, 1, D]``
+        tensors (views with any uniform strides, D contiguous, rows 16-byte aligned) that hold every
+        layer's new K and V row when the step runs - typically the output buffer of the projections.
+        ``update_cache(k_all[l], v_all[l], 2)`` then stages without launching anything."""
+        for x in (k_all, v_all):
+            if x.dtype != torch.bfloat16 or x.dim() != 5 or x.shape[0] != self.num_layers or x.shape[3] != 1:
+                raise ValueError("staging tensors must be bf16 [layers, B, H, 1, D]")
+            if x.stride(4) != 1 or any(st % 8 for st in x.stride()[:4]) or x.data_ptr() % 16:
+                raise ValueError("staging rows must be contiguous in D and 16-byte aligned")
+        if k_all.shape != v_all.shape or k_all.stride() != v_all.stride():
+            raise ValueError("K and V staging tensors must have the same shape and strides")
+        self.commit()
+        self._stage_k, self._stage_v = k_all, v_all
+
+    def staging(self, layer: int) -> Tuple[torch.Tensor, torch.Tensor]:
+        """Where layer ``layer``'s next K and V row go in deferred mode: ``[B, H, 1, D]`` views."""
+        if self._stage_k is None:
+            pool = self.pool
+            if pool is None or self.slots is None:
+                raise RuntimeError("the staging buffer is sized on the first update_cache")
+            buf = torch.zeros(self.num_layers, 2, len(self.slots), pool.n_kv_heads, 1, pool.head_dim,
+                              dtype=torch.bfloat16, device=pool.device)
+            self._stage_k, self._stage_v = buf[:, 0], buf[:, 1]
+        return self._stage_k[layer], self._stage_v[layer]
+
+    def commit(self) -> None:
+        """Stores every staged row in the pool and advances the device lengths: one kernel per run of
+        consecutive layers (one kernel for a whole decode step).  Called by whatever needs the pool
+        itself up to date (rollback, gather, read-back, a multi-token append or attention call); a
+        step that only decodes calls it once, after its last layer."""
+        if not self._pending:
+            return
+        layers = sorted(self._pending)
+        pool, k_all, v_all = self.pool, self._stage_k, self._stage_v
+        sl, sb, sh, st, _ = k_all.stride()
+        lo = 0
+        with torch.cuda.device(pool.device):
+            while lo < len(layers):
+                hi = lo
+                while hi + 1 < len(layers) and layers[hi + 1] == layers[hi] + 1:
+                    hi += 1
+                a, b = layers[lo], layers[hi] + 1
+                _C.check(_C.lib.pace_kv_append_layers(pool.ref, a, b, self.slots_dev.data_ptr(), len(self.slots), 1,
+                                                      None, k_all[a].data_ptr(), v_all[a].data_ptr(), sl, sb, sh, st,
+                                                      _stream_ptr(pool.device)), "pace_kv_append_layers")
+                lo = hi + 1
+        self._pending.clear()
+
     def __getitem__(self, idx: int) -> "KVCacheBase":
         return self.cache_objects[idx]
 
@@ -268,6 +329,7 @@ class KVCacheManager:
         """Beam gather (cache.py:106-116): ONE index-only kernel for all layers."""
         if self.slots is None:
             return
+        self.commit()
         pool = self.pool
         idx = beam_idx.to(device=pool.device, dtype=torch.int64).contiguous()
         if idx.numel() != len(self.slots):
@@ -289,6 +351,7 @@ class KVCacheManager:
         live = [c for c in self.cache_objects if c.key is not None]
         if not live:
             return
+        self.commit()
         per_seq = live[0]._normalise_remove(remove_len)
         for c in live:
             c._check_remove(per_seq)
@@ -312,6 +375,7 @@ class KVCacheManager:
         idx = sorted(set(int(b) for b in batch_indices))
         if not idx or self.slots is None:
             return
+        self.commit()
         pool = self.pool
         slots = [self.slots[b] for b in idx]
         dev = torch.tensor(slots, dtype=torch.int32, device=pool.device)
@@ -329,6 +393,7 @@ class KVCacheManager:
 
     def release(self) -> None:
         if self.pool is not None and self.slots is not None:
+            self._pending.clear()   # staged rows of sequences that are being dropped
             if not self._owns_pool:
                 self.pool.release_slots(self.slots, self.slots_dev)
             self.slots = None
@@ -358,6 +423,7 @@ class KVCacheBase(ABC):
             manager.pool, manager._owns_pool, manager.slots, manager.slots_dev = None, True, None, None
             manager.static_launch = manager.capturing = manager.skip_reserve = False
             manager.identity_slots = False
+            manager.defer_appends, manager._stage_k, manager._stage_v, manager._pending = False, None, None, set()
             manager.cache_objects = [self]
         self.manager = manager
         self.layer = layer
@@ -468,6 +534,7 @@ class KVCacheBase(ABC):
         if table_row.shape != (B, n) or table_row.dtype != torch.int32 or table_row.stride(1) != 1:
             raise ValueError("table_row must be an int32 [B, n] tensor")
         self._ndim = 4
+        self.manager.commit()
         pool, mgr, nptr, sp, n_dev = self._begin_append(B, H, n, D, query.device, n_new_per_seq)
         a = _C.RopeArgs()
         a.q, (a.q_stride_b, a.q_stride_t, a.q_stride_h) = query.data_ptr(), query.stride()[:3]
@@ -510,12 +577,38 @@ class KVCacheBase(ABC):
             key_states, value_states = key_states.contiguous(), value_states.contiguous()
         if any(s % 8 for s in key_states.stride()[:3]) or key_states.data_ptr() % 16 or value_states.data_ptr() % 16:
             key_states, value_states = key_states.contiguous().clone(), value_states.contiguous().clone()
+        mgr = self.manager
+        if mgr.defer_appends and n == 1 and n_new_per_seq is None and self._ndim == 4:
+            return self._stage_row(key_states, value_states)
+        mgr.commit()
         pool, mgr, nptr, sp, n_dev = self._begin_append(B, H, n, D, key_states.device, n_new_per_seq)
         with torch.cuda.device(pool.device):
             sb, sh, st, _ = key_states.stride()
             _C.check(_C.lib.pace_kv_append(pool.ref, self.layer, mgr.slots_dev.data_ptr(), B, n, nptr,
                                            key_states.data_ptr(), value_states.data_ptr(), sb, sh, st, sp),
                      "pace_kv_append")
+        if self.key is None:
+            self.key, self.value = PagedKV(self, "k"), PagedKV(self, "v")
+        return self.key, self.value
+
+    @property
+    def pending(self) -> bool:
+        """True while this layer's newest row is staged (counted in ``seq_len``, not yet in the pool)."""
+        return self.layer in self.manager._pending
+
+    def _stage_row(self, key_states: torch.Tensor, value_states: torch.Tensor) -> Tuple[PagedKV, PagedKV]:
+        """Deferred form of a one-token append: host accounting and page reservation as usual, the row
+        itself only goes to (or already sits in) the manager's staging buffer."""
+        mgr = self.manager
+        if self.pending:
+            mgr.commit()    # a second token for this layer: the first one has to be in the pool
+        B, H, _, D = key_states.shape
+        self._begin_append(B, H, 1, D, key_states.device, None)
+        ks, vs = mgr.staging(self.layer)
+        for dst, src in ((ks, key_states), (vs, value_states)):
+            if dst.data_ptr() != src.data_ptr() or dst.stride() != src.stride():
+                dst.copy_(src)
+        mgr._pending.add(self.layer)
         if self.key is None:
             self.key, self.value = PagedKV(self, "k"), PagedKV(self, "v")
         return self.key, self.value
@@ -580,6 +673,7 @@ class KVCacheBase(ABC):
         """Forget the last tokens (cache.py:224-240 / 352-368): lengths only, pages kept."""
         if self.key is None:
             return  # silent no-op on an empty cache, as the reference
+        self.manager.commit()
         per_seq = self._normalise_remove(remove_len)
         self._check_remove(per_seq)
         pool, mgr = self.pool, self.manager
@@ -605,6 +699,7 @@ class KVCacheBase(ABC):
     def read_dense(self) -> Tuple[torch.Tensor, torch.Tensor]:
         """Dense ``[B, H, capacity, D]`` K and V, i.e. what the reference's update_cache returns."""
         pool, mgr = self.pool, self.manager
+        mgr.commit()
         B, cap = len(self._lens), self._capacity
         k = torch.empty(B, pool.n_kv_heads, cap, pool.head_dim, dtype=torch.bfloat16, device=pool.device)
         v = torch.empty_like(k)

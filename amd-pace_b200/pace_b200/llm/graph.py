@@ -20,7 +20,9 @@ class StepGraph:
     ``manager`` and attends) and replays it.
 
     ``step_fn`` must use fixed tensors for its inputs and outputs; refill them between
-    replays.  Two eager warm-up steps run first (they append real tokens).
+    replays.  Two eager warm-up steps run first (they append real tokens).  With deferred
+    appends (``manager.defer_appends``) the step ends with ``manager.commit()``: the recorded
+    sequence is then the layers' attention launches back to back and one batched append.
     """
 
     def __init__(self, manager: KVCacheManager, step_fn: Callable[[], object], n_new: int = 1, warmup: int = 2):
@@ -29,6 +31,12 @@ class StepGraph:
         self.stream = torch.cuda.Stream()
         self.replays_with_reserve = 0    # replays that needed the page reservation kernel
         self.graph = torch.cuda.CUDAGraph()
+        inner = step_fn
+
+        def step_fn():
+            out = inner()
+            manager.commit()
+            return out
         manager.static_launch = True
         self.stream.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(self.stream):
@@ -46,7 +54,11 @@ class StepGraph:
             self.graph_no_reserve = torch.cuda.CUDAGraph()
             manager.skip_reserve = True
             with torch.cuda.graph(self.graph_no_reserve, stream=self.stream, pool=self.graph.pool()):
-                step_fn()
+                second = step_fn()
+            if isinstance(self.result, torch.Tensor) and isinstance(second, torch.Tensor) \
+                    and second.data_ptr() != self.result.data_ptr():
+                raise ValueError("StepGraph: step_fn must write its result into a fixed tensor (pass out= to the "
+                                 "attention op); it returned a different buffer on the second recording")
         finally:
             manager.capturing = False
             manager.skip_reserve = False

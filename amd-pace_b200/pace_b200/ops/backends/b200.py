@@ -8,7 +8,6 @@ tensor that is not on a CUDA device is an error.
 """
 import ctypes as C
 import math
-import os
 from typing import Dict, Optional, Tuple
 
 import torch
@@ -52,9 +51,6 @@ def kv_start_from_mask(mask: torch.Tensor) -> Optional[torch.Tensor]:
 
 
 _sm_counts: Dict[int, int] = {}
-# PACE_WHOLE_UNITS_HINT=0: never pass PACE_ATTN_WHOLE_UNITS (A/B measurements; the kernel then decides
-# the partition on the device alone)
-WHOLE_UNITS_HINT = os.environ.get("PACE_WHOLE_UNITS_HINT", "1") != "0"
 
 
 def even_lengths(lens, n_kv_heads: int, head_dim: int, page_tokens: int, device: Optional[torch.device],
@@ -84,7 +80,17 @@ def even_lengths(lens, n_kv_heads: int, head_dim: int, page_tokens: int, device:
 
 def paged_attention(query: torch.Tensor, key: PagedKV, kv_start: Optional[torch.Tensor] = None,
                     q_lens: Optional[torch.Tensor] = None, scale: Optional[float] = None,
-                    out: Optional[torch.Tensor] = None) -> torch.Tensor:
+                    out: Optional[torch.Tensor] = None, max_ctas: int = 0, decode_kernel: Optional[str] = None,
+                    whole_units: Optional[bool] = None, one_cta_per_sm: bool = False,
+                    no_early_kv: bool = False) -> torch.Tensor:
+    """Attention of ``query`` [B, Hq, S, D] over one layer of the paged pool.
+
+    The last five arguments choose among schedules that give the same result (tests walk through
+    them; callers normally leave them alone): ``max_ctas`` limits the thread blocks,
+    ``decode_kernel`` forces ``"cuda"`` (CUDA-core kernel) or ``"mma"`` (tensor-core kernel) for
+    S == 1, ``whole_units`` overrides the host's own test for ``PACE_ATTN_WHOLE_UNITS``,
+    ``one_cta_per_sm`` keeps decode on eight-warp thread blocks, ``no_early_kv`` makes a decode
+    launch wait for the kernel in front of it before it fetches anything."""
     cache = key.cache
     pool, mgr = cache.pool, cache.manager
     if query.device != pool.device:
@@ -99,6 +105,12 @@ def paged_attention(query: torch.Tensor, key: PagedKV, kv_start: Optional[torch.
                          f"(B={len(mgr.slots)}, Hkv={pool.n_kv_heads}, D={pool.head_dim})")
     if query.stride(3) != 1 or any(s % 8 for s in query.stride()[:3]) or query.data_ptr() % 16:
         query = query.contiguous()
+    # a staged row (deferred append) rides along as the newest key of a one-token decode launch on the
+    # tensor-core kernel; anything else needs it in the pool first
+    pending = cache.pending
+    if pending and (S != 1 or Hq // pool.n_kv_heads >= 33 or decode_kernel == "cuda"):
+        mgr.commit()
+        pending = False
     # [B, S, Hq, D] storage so the caller's transpose(1, 2).reshape(B, S, Hq*D) is a view
     if out is None:
         out = torch.empty(B, S, Hq, D, dtype=torch.bfloat16, device=query.device).transpose(1, 2)
@@ -120,11 +132,25 @@ def paged_attention(query: torch.Tensor, key: PagedKV, kv_start: Optional[torch.
     a.scale = float(scale) if scale is not None else 1.0 / math.sqrt(D)
     a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel()
     a.flags = 0
-    if S == 1 and WHOLE_UNITS_HINT and even_lengths(cache._lens, pool.n_kv_heads, D, pool.page_tokens, query.device):
-        a.flags = _C.ATTN_WHOLE_UNITS
+    a.max_ctas = int(max_ctas)
+    if whole_units is None:
+        whole_units = S == 1 and even_lengths(cache._lens, pool.n_kv_heads, D, pool.page_tokens, query.device)
+    if S == 1 and whole_units:
+        a.flags |= _C.ATTN_WHOLE_UNITS
+    if one_cta_per_sm:
+        a.flags |= _C.ATTN_ONE_CTA_PER_SM
+    if no_early_kv:
+        a.flags |= _C.ATTN_NO_EARLY_KV
+    if pending:
+        ks, vs = mgr.staging(cache.layer)
+        a.flags |= _C.ATTN_PENDING_ROW
+        a.k_pending, a.v_pending = ks.data_ptr(), vs.data_ptr()
+        a.pending_stride_b, a.pending_stride_h = ks.stride(0), ks.stride(1)
     stream = torch.cuda.current_stream(query.device).cuda_stream
     with torch.cuda.device(query.device):
-        if S == 1:
+        if S == 1 and decode_kernel == "cuda":
+            _C.check(_C.lib.pace_attn_decode_cuda_cores(C.byref(a), stream), "pace_attn_decode_cuda_cores")
+        elif S == 1 and decode_kernel != "mma":
             _C.check(_C.lib.pace_attn_decode(C.byref(a), stream), "pace_attn_decode")
         elif S <= 64:
             _C.check(_C.lib.pace_attn_verify(C.byref(a), stream), "pace_attn_verify")
@@ -173,13 +199,13 @@ def dense_attention(query: torch.Tensor, key: torch.Tensor, value: torch.Tensor,
 class B200Attention(BackendBase):
     def execute(self, query: torch.Tensor, key, value, attention_mask: Optional[torch.Tensor] = None,
                 kv_start: Optional[torch.Tensor] = None, q_lens: Optional[torch.Tensor] = None,
-                out: Optional[torch.Tensor] = None) -> torch.Tensor:
+                out: Optional[torch.Tensor] = None, **schedule) -> torch.Tensor:
         if isinstance(key, PagedKV):
             if not isinstance(value, PagedKV) or value.cache is not key.cache:
                 raise ValueError("key and value must come from the same update_cache call")
             if kv_start is None and attention_mask is not None:
                 kv_start = kv_start_from_mask(attention_mask)
-            return paged_attention(query, key, kv_start=kv_start, q_lens=q_lens, out=out)
+            return paged_attention(query, key, kv_start=kv_start, q_lens=q_lens, out=out, **schedule)
         return dense_attention(query, key, value, attention_mask)
 
 

@@ -50,8 +50,12 @@ extern "C" {
  *   status       int32 [4]          [0] sticky PACE_DEV_* bits
  *   table_tmp    int32 [max_seqs][max_pages_per_seq + 1]   scratch of pace_kv_gather
  *
- * page_tokens is the reference's `tokens_per_split` (cache.py:177-181) so that
- * capacity = pages * page_tokens reproduces the BMC capacity trace exactly.
+ * page_tokens is the physical page size (the Python host uses 64: one page is one K/V chunk of
+ * the attention kernels).  The reference's capacity (whole `tokens_per_split` segments,
+ * cache.py:177-181, 292-313) is host bookkeeping on top of the pages and does not depend on it;
+ * a page of exactly tokens_per_split tokens makes the two coincide.
+ *
+ * Between calls the pool's memory belongs to the library: only its kernels write it.
  */
 typedef struct pace_kv_pool {
   int32_t n_layers, n_kv_heads, head_dim, page_tokens;
@@ -103,6 +107,27 @@ int pace_kv_reserve(const pace_kv_pool_t* pool, int32_t layer, const int32_t* se
 int pace_kv_append(const pace_kv_pool_t* pool, int32_t layer, const int32_t* seq_ids, int32_t batch,
                    int32_t n_new, const int32_t* n_new_per_seq, const void* k_new, const void* v_new,
                    int64_t stride_b, int64_t stride_h, int64_t stride_t, void* stream);
+/* Ordering of the two append entry points against an attention launch in front of them on the
+ * stream: the library remembers, per stream, the pool and layer its newest attention launch reads.
+ * An append to ANOTHER layer (the decoder-layer pattern attn(l), append(l+1), attn(l+1)) starts
+ * while that launch is still running (programmatic dependent launch) - it touches nothing the
+ * launch reads.  An append to the SAME pool and layer, or a pace_kv_append_rope whose q_out is the
+ * q of that launch, is ordered behind its completion like any other kernel. */
+
+/* One launch for a whole decode step: the rows of layers [layer_begin, layer_end) at once.
+ * Reference: the same BMCKVCache.update_cache (cache.py:268-326), called once per layer per
+ * generated token (llama.py:159); here the per-layer calls of a step collapse into one kernel that
+ * runs after the step's last attention launch, which is possible because the attention entry
+ * points can take the step's new row straight from the caller's buffer (PACE_ATTN_PENDING_ROW).
+ * k_new / v_new are bf16 [layer][batch][n_kv_heads][n_new][head_dim] through element strides
+ * (stride_l first; head_dim contiguous, rows 16-byte aligned); layer `layer_begin` is at offset 0.
+ * Every listed layer's seq_len advances by the same counts.  pace_kv_reserve for the step must have
+ * run (any one layer: pages are shared by all layers).  The kernel is ordered behind everything in
+ * front of it on the stream and in front of everything behind it (no programmatic overlap). */
+int pace_kv_append_layers(const pace_kv_pool_t* pool, int32_t layer_begin, int32_t layer_end,
+                          const int32_t* seq_ids, int32_t batch, int32_t n_new, const int32_t* n_new_per_seq,
+                          const void* k_new, const void* v_new, int64_t stride_l, int64_t stride_b,
+                          int64_t stride_h, int64_t stride_t, void* stream);
 
 /* ---- RoPE + append in one pass -----------------------------------------------
  * Reference: the step in front of the append in every decoder layer,
@@ -192,6 +217,15 @@ typedef struct pace_attn_args {
   void* workspace;          /* device scratch, pace_attn_workspace_bytes(); zero it once after allocation */
   uint64_t workspace_bytes;
   uint32_t flags;           /* PACE_ATTN_* bits, 0 = none */
+  /* PACE_ATTN_PENDING_ROW only: the step's new K and V row of every (sequence, kv head), bf16
+   * [batch][n_kv_heads][head_dim] through element strides (head_dim contiguous, rows 16-byte aligned). */
+  const void* k_pending;
+  const void* v_pending;
+  int64_t pending_stride_b, pending_stride_h;
+  /* At most this many thread blocks (a caller that shares the GPU with work on another stream);
+   * 0 = the kernels' own choice, one per SM or two for the four-warp decode form.  Any value gives
+   * the same result: the kernels cut the work into as many contiguous ranges as there are blocks. */
+  int32_t max_ctas;
 } pace_attn_args_t;
 
 /* Never cut one (sequence, KV head) stream of keys across thread blocks.  The kernels normally decide
@@ -205,11 +239,50 @@ typedef struct pace_attn_args {
  * seq_len per layer, cache.py:184, is enough to tell).  It only changes the schedule, never the result. */
 #define PACE_ATTN_WHOLE_UNITS 1u
 
+/* Decode (q_len == 1) over the cache PLUS one row per sequence that is not in the cache yet: the
+ * launch first stores k_pending / v_pending in the row's slot of the pool - row number seq_len of
+ * the sequence, whose page pace_kv_reserve must have provided - and then attends over keys
+ * [kv_start, seq_len].  seq_len itself is NOT advanced.  The result is what pace_kv_append of that
+ * row followed by a plain decode launch gives.  This takes the per-layer append out of the chain of
+ * a decode step (llama.py:159-165 does update_cache, then attention, in every layer): the rows stay
+ * in the caller's staging buffer, every layer's attention launch follows the previous layer's
+ * directly, and one pace_kv_append_layers after the last layer advances all layers' lengths (it
+ * stores the rows again, which changes nothing).  A row that is never committed is simply a stale
+ * row beyond seq_len, as after a rollback.  Served by the tensor-core kernels for every group size
+ * below 33 query heads per KV head; PACE_ERR_UNSUPPORTED otherwise. */
+#define PACE_ATTN_PENDING_ROW 2u
+
+/* Decode launches normally begin by waiting for the kernel in front of them on the stream
+ * (a programmatic dependent launch: only the set-up overlaps).  When the library knows that its own
+ * newest launch on the stream was an attention launch - so nothing of the pool this launch reads
+ * (lengths, block table, pages) can have been written by the kernel directly in front - a
+ * whole-unit decode launch starts streaming K/V pages at once and waits only before it touches q,
+ * the pending rows and out.  The K/V stream then runs beside the tail of the kernel in front (the
+ * previous layer's attention, or the projection that produces q).  This bit forbids that: set it
+ * if seq_ids, kv_start or the pool were written by a kernel of your own directly in front. */
+#define PACE_ATTN_NO_EARLY_KV 4u
+
+/* Decode: keep the form with eight consumer warps and one thread block per SM (the kernels fall
+ * back to it by themselves when the workspace or shared memory has no room for two blocks per SM). */
+#define PACE_ATTN_ONE_CTA_PER_SM 8u
+
 uint64_t pace_attn_workspace_bytes(int32_t batch, int32_t n_q_heads, int32_t n_kv_heads, int32_t head_dim,
                                    int32_t q_len);
-int pace_attn_decode(const pace_attn_args_t* a, void* stream);  /* q_len == 1, CUDA cores, TMA-streamed cache */
-int pace_attn_verify(const pace_attn_args_t* a, void* stream);  /* short q (PARD verify), tensor-core tiles  */
-int pace_attn_prefill(const pace_attn_args_t* a, void* stream); /* prefill chunks, tensor-core tiles         */
+/* q_len == 1.  The grouped query heads of a KV head are packed into one mma.sync tile (any group
+ * size); groups of 1 or 2 (plain multi-head attention) run on the CUDA-core kernel instead, whose
+ * packed fp32 FMAs cost less than a tile that is seven eighths padding. */
+int pace_attn_decode(const pace_attn_args_t* a, void* stream);
+/* The CUDA-core decode kernel whatever the group size (1, 2, 4 or 8 query heads per KV head;
+ * PACE_ERR_UNSUPPORTED otherwise): 8 lanes per K/V row, packed fp32 FMAs, warp-shuffle online
+ * softmax - the form the reference's head-by-head CPU loop maps to most directly.  pace_attn_decode
+ * picks it only for groups of 1 or 2; pace_attn_verify with q_len = 1 is the tensor-core form. */
+int pace_attn_decode_cuda_cores(const pace_attn_args_t* a, void* stream);
+/* q_len >= 1 query tokens per sequence, causal among themselves (PARD verify: d + 1 tokens; a
+ * prefill chunk: hundreds).  Tiles of 33 and more query rows (tokens x grouped heads) run on the
+ * tcgen05 tensor cores, smaller ones on mma.sync.  pace_attn_prefill is the same entry point under
+ * the name the chunked-prefill caller expects. */
+int pace_attn_verify(const pace_attn_args_t* a, void* stream);
+int pace_attn_prefill(const pace_attn_args_t* a, void* stream);
 
 /* Decode attention without any allocation.  (No counterpart in the reference: its CPU op
  * allocates its score tensor on every call, attention_kernels.cpp:222-226.)
@@ -221,8 +294,10 @@ int pace_attn_prefill(const pace_attn_args_t* a, void* stream); /* prefill chunk
  * the scratch is a fixed device array inside the library (about 3.4 MB per GPU, held until the
  * process exits).  Limits, refused with PACE_ERR_UNSUPPORTED beyond them: at most 16 query heads per
  * KV head, head_dim <= 128, batch * n_kv_heads <= 65536, at most 192 SMs.  The first call on a device
- * resolves the array's address there (make it before any stream capture).  Calls share the array:
- * issue them on one stream, or otherwise keep them from overlapping on the GPU. */
+ * resolves the array's address there (make it before any stream capture) and keeps it for the life
+ * of the process: after a cudaDeviceReset the kept address is stale and the entry point must not be
+ * used again in that process.  Calls share the array: issue them on one stream, or otherwise keep
+ * them from overlapping on the GPU. */
 int pace_attn_decode_static(const pace_attn_args_t* a, void* stream);
 
 /* Dense form with the reference op's exact operands: q [B,N,S,H], k/v [B,Nkv,L,H]

@@ -149,12 +149,11 @@ def test_large_tiles_ragged_counts_and_left_padding():
 
 
 @pytest.mark.parametrize("grid", [1, 5, 37])
-def test_prefill_tiles_under_other_partitions(monkeypatch, grid):
+def test_prefill_tiles_under_other_partitions(grid):
     """The same prefill chunk with the chunk stream cut for 1, 5 and 37 CTAs (cut units, partial
     merges across CTAs) on 128-row tiles."""
     from pace_b200.llm.cache import KVCacheManager, KVCacheType
     from pace_b200.ops import MultiHeadAttention
-    monkeypatch.setenv("PACE_DECODE_GRID", str(grid))
     g = torch.Generator().manual_seed(grid)
     B, Hq, Hkv, D, S = 2, 16, 4, 128, 96
     lens = [777, 96]
@@ -163,7 +162,7 @@ def test_prefill_tiles_under_other_partitions(monkeypatch, grid):
     q = torch.randn(B, S, Hq, D, generator=g).bfloat16().to(DEV).transpose(1, 2)
     mgr = KVCacheManager(Cfg(1), 800, KVCacheType.BMC)
     K, V = _fill(mgr, 0, ks, vs)
-    out = MultiHeadAttention()(q, K, V)
+    out = MultiHeadAttention()(q, K, V, max_ctas=grid)
     want = _oracle(q, ks, vs)
     for b in range(B):
         _check(out[b], want[b])
@@ -178,15 +177,39 @@ def test_prefill_tiles_under_other_partitions(monkeypatch, grid):
     (1, 8, 2, 128, 40000, [33000]),
     (2, 32, 4, 128, 500, [200, 437]),
 ])
-def test_decode_kernels_agree_with_oracle(monkeypatch, impl, B, Hq, Hkv, D, max_len, lens):
+def test_decode_kernels_agree_with_oracle(impl, B, Hq, Hkv, D, max_len, lens):
     from pace_b200.llm.cache import KVCacheManager, KVCacheType
     from pace_b200.ops import MultiHeadAttention
-    monkeypatch.setenv("PACE_DECODE_IMPL", impl)
     g = torch.Generator().manual_seed(B + Hq + D)
     ks = [torch.randn(Hkv, L, D, generator=g).bfloat16().to(DEV) for L in lens]
     vs = [torch.randn(Hkv, L, D, generator=g).bfloat16().to(DEV) for L in lens]
     q = torch.randn(B, Hq, 1, D, generator=g).bfloat16().to(DEV)
     mgr = KVCacheManager(Cfg(1), max_len, KVCacheType.BMC)
+    K, V = _fill(mgr, 0, ks, vs)
+    out = MultiHeadAttention()(q, K, V, decode_kernel=impl)
+    want = _oracle(q, ks, vs)
+    for b in range(B):
+        _check(out[b], want[b])
+    mgr.pool.check_status()
+
+
+@pytest.mark.parametrize("Hq,Hkv,D", [(24, 8, 128), (12, 2, 64), (32, 2, 128), (64, 2, 64), (6, 2, 128)])
+@pytest.mark.parametrize("tps", [False, True])
+def test_decode_group_sizes_without_a_cuda_core_kernel(monkeypatch, Hq, Hkv, D, tps):
+    """Groups of 3, 6, 16 and 32 query heads per KV head (the CUDA-core kernel is built for 1, 2, 4
+    and 8 only): pace_attn_decode sends them to the tensor-core kernels, 17 and more rows as several
+    16-row tiles.  Both page modes."""
+    from pace_b200.llm.cache import KVCacheManager, KVCacheType
+    from pace_b200.ops import MultiHeadAttention
+    if tps:
+        monkeypatch.setenv("PACE_KV_PAGE_TOKENS", "tps")
+    lens = [5, 64, 333, 130]
+    B = len(lens)
+    g = torch.Generator().manual_seed(Hq * 7 + D)
+    ks = [torch.randn(Hkv, L, D, generator=g).bfloat16().to(DEV) for L in lens]
+    vs = [torch.randn(Hkv, L, D, generator=g).bfloat16().to(DEV) for L in lens]
+    q = torch.randn(B, Hq, 1, D, generator=g).bfloat16().to(DEV)
+    mgr = KVCacheManager(Cfg(1), 400, KVCacheType.BMC)
     K, V = _fill(mgr, 0, ks, vs)
     out = MultiHeadAttention()(q, K, V)
     want = _oracle(q, ks, vs)
@@ -196,13 +219,11 @@ def test_decode_kernels_agree_with_oracle(monkeypatch, impl, B, Hq, Hkv, D, max_
 
 
 @pytest.mark.parametrize("lens", [[128, 1024, 577, 300], [40 + 17 * i for i in range(48)]])
-def test_decode_whole_units_flag_on_ragged_lengths(monkeypatch, lens):
+def test_decode_whole_units_flag_on_ragged_lengths(lens):
     """PACE_ATTN_WHOLE_UNITS only changes the schedule: forced on a ragged batch (where the host
     would not set it) the result is the oracle's."""
     from pace_b200.llm.cache import KVCacheManager, KVCacheType
     from pace_b200.ops import MultiHeadAttention
-    from pace_b200.ops.backends import b200
-    monkeypatch.setattr(b200, "even_lengths", lambda *a, **k: True)
     B, Hq, Hkv, D = len(lens), 32, 8, 128
     g = torch.Generator().manual_seed(B)
     ks = [torch.randn(Hkv, L, D, generator=g).bfloat16().to(DEV) for L in lens]
@@ -210,21 +231,19 @@ def test_decode_whole_units_flag_on_ragged_lengths(monkeypatch, lens):
     q = torch.randn(B, Hq, 1, D, generator=g).bfloat16().to(DEV)
     mgr = KVCacheManager(Cfg(1), max(lens) + 1, KVCacheType.BMC)
     K, V = _fill(mgr, 0, ks, vs)
-    out = MultiHeadAttention()(q, K, V)
+    out = MultiHeadAttention()(q, K, V, whole_units=True)
     want = _oracle(q, ks, vs)
     for b in range(B):
         _check(out[b], want[b])
     mgr.pool.check_status()
 
 
-def test_decode_early_copies_short_and_empty_sequences(monkeypatch):
+def test_decode_early_copies_short_and_empty_sequences():
     """Whole-unit decode on 64-token pages sends the copies of a unit's first pages before it knows the
     length: sequences of less than that many pages (copies received and dropped), of exactly a page,
     and sequences rolled back to nothing (zeros out) all give the oracle's rows."""
     from pace_b200.llm.cache import KVCacheManager, KVCacheType
     from pace_b200.ops import MultiHeadAttention
-    from pace_b200.ops.backends import b200
-    monkeypatch.setattr(b200, "even_lengths", lambda *a, **k: True)
     lens = [1, 63, 64, 65, 128, 129, 191, 192, 300, 2]
     B, Hq, Hkv, D = len(lens), 32, 8, 128
     g = torch.Generator().manual_seed(11)
@@ -235,13 +254,13 @@ def test_decode_early_copies_short_and_empty_sequences(monkeypatch):
     K, V = _fill(mgr, 0, ks, vs)
     assert mgr.pool.page_tokens == 64
     mha = MultiHeadAttention()
-    out = mha(q, K, V)
+    out = mha(q, K, V, whole_units=True)
     want = _oracle(q, ks, vs)
     for b in range(B):
         _check(out[b], want[b])
     # roll two sequences back to nothing: their rows come out as zeros, the others are unchanged
     mgr.remove_cache([1, 0, 0, 0, 0, 0, 0, 0, 0, 2])
-    out2 = mha(q, K, V)
+    out2 = mha(q, K, V, whole_units=True)
     torch.cuda.synchronize()
     assert torch.count_nonzero(out2[0]) == 0 and torch.count_nonzero(out2[9]) == 0
     for b in range(1, 9):
@@ -249,12 +268,11 @@ def test_decode_early_copies_short_and_empty_sequences(monkeypatch):
     mgr.pool.check_status()
 
 
-def test_decode_eight_warp_ctas(monkeypatch):
-    """PACE_DECODE_HALF=0: decode on eight-warp thread blocks, one per SM (the form used when the
+def test_decode_eight_warp_ctas():
+    """PACE_ATTN_ONE_CTA_PER_SM: decode on eight-warp thread blocks, one per SM (the form used when the
     workspace or the shared memory has no room for two four-warp blocks per SM)."""
     from pace_b200.llm.cache import KVCacheManager, KVCacheType
     from pace_b200.ops import MultiHeadAttention
-    monkeypatch.setenv("PACE_DECODE_HALF", "0")
     lens = [513 + 3 * i for i in range(32)]
     B, Hq, Hkv, D = len(lens), 32, 8, 128
     g = torch.Generator().manual_seed(77)
@@ -263,7 +281,7 @@ def test_decode_eight_warp_ctas(monkeypatch):
     q = torch.randn(B, Hq, 1, D, generator=g).bfloat16().to(DEV)
     mgr = KVCacheManager(Cfg(1), 768, KVCacheType.BMC)
     K, V = _fill(mgr, 0, ks, vs)
-    out = MultiHeadAttention()(q, K, V)
+    out = MultiHeadAttention()(q, K, V, one_cta_per_sm=True)
     want = _oracle(q, ks, vs)
     for b in range(B):
         _check(out[b], want[b])
