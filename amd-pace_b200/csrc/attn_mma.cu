@@ -69,6 +69,7 @@ struct MmaParams {
   const __nv_bfloat16* v_pend;
   int64_t pend_sb, pend_sh;
   int early_kv;  // whole-unit decode: K/V copies may leave ahead of the wait for the kernel in front
+  int sub_boxes;  // 64-token pages: a unit's partly filled last page is fetched in 16-row boxes (tmS)
 };
 
 __device__ __forceinline__ int chunks_of_m(const MmaParams& p, int len) {
@@ -322,7 +323,8 @@ __device__ __forceinline__ void fence_proxy_async_all() {
 
 template <int D, int MT, int NS, bool UMMA = false>
 __global__ void __launch_bounds__(threads_of(UMMA, MT * NS), MT * NS == 4 ? 2 : 1)
-    attn_mma_kernel(const MmaParams p, const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV) {
+    attn_mma_kernel(const MmaParams p, const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
+                    const __grid_constant__ CUtensorMap tmS) {
   constexpr int NW = MT * NS;      // consumer warps
   constexpr int CTHR = NW * 32;
   static_assert(NW == 8 || (NW == 4 && MT == 1 && !UMMA), "eight consumer warps, or four in the two-per-SM decode form");
@@ -416,6 +418,7 @@ __global__ void __launch_bounds__(threads_of(UMMA, MT * NS), MT * NS == 4 ? 2 : 
     // the producer's first tiled copy would otherwise wait for its 128-byte descriptor to arrive
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmK)) : "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmV)) : "memory");
+    if (p.sub_boxes) asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmS)) : "memory");
   }
   if (tid >= NTHR - 32) {
     const int k = tid - (NTHR - 32);
@@ -535,6 +538,7 @@ __global__ void __launch_bounds__(threads_of(UMMA, MT * NS), MT * NS == 4 ? 2 : 
         }
         qs = n > 0;
       }
+      if (lane == 0) PACE_STAMP(6);
       if (lane == 0) {
         misc[3] = n;
         misc[7] = qs;
@@ -542,6 +546,7 @@ __global__ void __launch_bounds__(threads_of(UMMA, MT * NS), MT * NS == 4 ? 2 : 
       __syncwarp();
       asm volatile("bar.arrive 2, 64;" ::: "memory");  // the producer picks the two numbers up behind this
       gdc_wait();  // (early K/V: the page copies above are out; what follows reads the step's own inputs)
+      if (lane == 0) PACE_STAMP(7);
       if (qs) {
         const int q_rows = min(MR, p.q_len * G);
         for (int r = lane; r < q_rows; r += 32) {
@@ -878,6 +883,13 @@ __global__ void __launch_bounds__(threads_of(UMMA, MT * NS), MT * NS == 4 ? 2 : 
         const int rows = whole_pages ? min(CT, len - tok0) : min(min(kChunk, P - row0), len - tok0);
         const int n_pages_c = !whole_pages ? 1 : (rows == CT ? p.pages_per_chunk : (rows + P - 1) / P);
         const bool last = (j == j_end - 1);
+        // A partly filled page of 64 tokens (a sequence's last one) is fetched in boxes of 16 rows, one
+        // lane each, through a second tensor map: a whole-page box would bring up to 63 rows from DRAM
+        // that nobody reads (one launch of batch 32 at 515 cached tokens reads 13 % more than it needs).
+        // Rows of the stage that no box covers keep what an earlier chunk left there: finite numbers,
+        // masked out of the scores and multiplied by zero weights.
+        const bool sub = !UMMA && MT == 1 && p.sub_boxes && rows <= kChunk - 16 && i >= n_spec;
+        const int n_sub = (rows + 15) >> 4;
         if (lane == 0) {
           MetaM* m = &metas[s];
           *reinterpret_cast<int4*>(m) = make_int4(
@@ -887,10 +899,11 @@ __global__ void __launch_bounds__(threads_of(UMMA, MT * NS), MT * NS == 4 ? 2 : 
             *reinterpret_cast<int4*>(&m->kv_len) = make_int4(kv_len, S, mode, parts);
             *reinterpret_cast<int4*>(&m->first_cta) = make_int4(first_cta, first_slot, it * Hkv + h, j_end - j);
           }
-          mbar_arrive_expect_tx(&full_bar[s], (uint32_t)n_pages_c * box_bytes + ((first && !UMMA) ? (uint32_t)q_rows * D * 2u : 0u));
+          mbar_arrive_expect_tx(&full_bar[s], (sub ? (uint32_t)n_sub * (box_bytes / 4u) : (uint32_t)n_pages_c * box_bytes) +
+                                                  ((first && !UMMA) ? (uint32_t)q_rows * D * 2u : 0u));
         }
         __syncwarp();
-        const int pg = pw.get(lp + pi, lp, lane);
+        const int pg = pw.get(sub ? lp : lp + pi, lp, lane);
         if (lane == 0 && i == 0) PACE_TRACE(3, 10);
         if (pend && j == nch - 1) {
           // The unit's final chunk holds the pending row, which has to be in the pool before the copy
@@ -907,6 +920,15 @@ __global__ void __launch_bounds__(threads_of(UMMA, MT * NS), MT * NS == 4 ? 2 : 
         }
         if (i < n_spec) {
           // (short prologue: this chunk's copy is on its way already - same sequence, head and page)
+        } else if (sub) {
+          // lane = (16-row box, K | V, column block): the same lane order as for pages of a chunk
+          const int bx = lane / (2 * HALVES);
+          if (bx < n_sub) {
+            if (pg >= 0)
+              tma_load_4d_hint(ring + (size_t)s * STAGE + (is_v ? KVB : 0) + hf * HALF_B + bx * 16 * 128, &tmS, c0, bx * 16,
+                               pg * Hkv + c2h, c3, &full_bar[s], stream_policy);
+            else raise_status(p.kv.status, PACE_DEV_BAD_INDEX);
+          }
         } else if (copier && pi < n_pages_c) {
           if (pg >= 0) {
             if (p.n_qt == 1) tma_load_4d_hint(ring + (size_t)s * stage_step + lane_off, tm, c0, row0, pg * Hkv + c2h, c3, &full_bar[s], stream_policy);
@@ -922,6 +944,7 @@ __global__ void __launch_bounds__(threads_of(UMMA, MT * NS), MT * NS == 4 ? 2 : 
           }
         }
         if (lane == 0) PACE_TRACE(0, i);
+        if (lane == 0 && i == n_spec) PACE_STAMP(2);
         if (whole_pages) {
           lp += p.pages_per_chunk;
         } else {
@@ -1495,24 +1518,29 @@ int make_map(CUtensorMap* tm, const void* base, int D, int rows, uint64_t tiles,
 struct PoolMapEntry {
   const void* pages;
   int geom[6];
-  CUtensorMap tm;
+  CUtensorMap tm;      // boxes of one page (or 64 rows of a larger page)
+  CUtensorMap tm_sub;  // boxes of 16 rows
 };
 std::mutex g_map_mu;
 PoolMapEntry g_maps[16];
 int g_n_maps = 0, g_next_map = 0;
 
-int pool_map(const pace_kv_pool_t* pl, CUtensorMap* out) {
+int pool_map(const pace_kv_pool_t* pl, CUtensorMap* out, CUtensorMap* out_sub) {
   const int geom[6] = {pl->n_layers, pl->n_kv_heads, pl->head_dim, pl->page_tokens, pl->n_pages, 0};
   std::lock_guard<std::mutex> lk(g_map_mu);
   for (int i = 0; i < g_n_maps; ++i)
     if (g_maps[i].pages == pl->pages && memcmp(g_maps[i].geom, geom, sizeof(geom)) == 0) {
       *out = g_maps[i].tm;
+      *out_sub = g_maps[i].tm_sub;
       return PACE_OK;
     }
-  CUtensorMap tm;
+  CUtensorMap tm, tm_sub;
   const uint64_t tiles = (uint64_t)pl->n_pages * pl->n_kv_heads;
-  const int rc = make_map(&tm, pl->pages, pl->head_dim, pl->page_tokens, tiles, (uint64_t)pl->n_layers * 2,
-                          tiles * pl->page_tokens * pl->head_dim, pl->page_tokens <= kChunk ? pl->page_tokens : kChunk);
+  int rc = make_map(&tm, pl->pages, pl->head_dim, pl->page_tokens, tiles, (uint64_t)pl->n_layers * 2,
+                    tiles * pl->page_tokens * pl->head_dim, pl->page_tokens <= kChunk ? pl->page_tokens : kChunk);
+  if (rc != PACE_OK) return rc;
+  rc = make_map(&tm_sub, pl->pages, pl->head_dim, pl->page_tokens, tiles, (uint64_t)pl->n_layers * 2,
+                tiles * pl->page_tokens * pl->head_dim, pl->page_tokens < 16 ? pl->page_tokens : 16);
   if (rc != PACE_OK) return rc;
   PoolMapEntry& e = g_maps[g_next_map];
   g_next_map = (g_next_map + 1) % 16;
@@ -1520,7 +1548,9 @@ int pool_map(const pace_kv_pool_t* pl, CUtensorMap* out) {
   e.pages = pl->pages;
   memcpy(e.geom, geom, sizeof(geom));
   e.tm = tm;
+  e.tm_sub = tm_sub;
   *out = tm;
+  *out_sub = tm_sub;
   return PACE_OK;
 }
 
@@ -1547,6 +1577,7 @@ struct MmaExtra {
   bool no_early_kv = false;
   const void* pages = nullptr; // pool the launch reads (null: the dense form)
   int layer = -1;
+  const CUtensorMap* tm_sub = nullptr;  // the pool seen in 16-row boxes (64-token pages only)
 };
 
 template <int D, int MT, int NS, bool UMMA = false>
@@ -1589,7 +1620,8 @@ int launch_mma(MmaParams& p, const CUtensorMap& tmK, const CUtensorMap& tmV, int
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  PACE_CUDA_TRY(cudaLaunchKernelEx(&cfg, attn_mma_kernel<D, MT, NS, UMMA>, p, tmK, tmV));
+  p.sub_boxes = (ex.tm_sub && !UMMA && MT == 1 && p.pages_per_chunk == 1 && p.kv.page_tokens == kChunk) ? 1 : 0;
+  PACE_CUDA_TRY(cudaLaunchKernelEx(&cfg, attn_mma_kernel<D, MT, NS, UMMA>, p, tmK, tmV, ex.tm_sub ? *ex.tm_sub : tmK));
   PACE_LAUNCH_CHECK("attn_mma_kernel");
   note_attention_launch(stream, /*uses_workspace=*/!p.whole_units, ex.pages, ex.layer, p.q);
   return PACE_OK;
@@ -1733,8 +1765,8 @@ int run_mma(const KVView& kv, const CUtensorMap& tmK, const CUtensorMap& tmV, in
 int run_mma_paged(const pace_attn_args_t* a, int causal, cudaStream_t stream) {
   if (!a || !a->pool || a->q_len < 1 || a->layer < 0 || a->layer >= a->pool->n_layers) return PACE_ERR_INVALID;
   if (a->batch > a->pool->max_seqs) return PACE_ERR_INVALID;
-  CUtensorMap tm;
-  const int rc = pool_map(a->pool, &tm);
+  CUtensorMap tm, tm_sub;
+  const int rc = pool_map(a->pool, &tm, &tm_sub);
   if (rc != PACE_OK) return rc;
   const KVView kv = make_view(a->pool, a->layer, a->seq_ids);
   MmaExtra ex;
@@ -1749,6 +1781,7 @@ int run_mma_paged(const pace_attn_args_t* a, int causal, cudaStream_t stream) {
   ex.no_early_kv = (a->flags & PACE_ATTN_NO_EARLY_KV) != 0;
   ex.pages = a->pool->pages;
   ex.layer = a->layer;
+  ex.tm_sub = &tm_sub;
   return run_mma(kv, tm, tm, a->layer * 2, a->layer * 2 + 1, a->batch, a->n_q_heads, a->q_len, a->q, a->q_stride_b,
                  a->q_stride_h, a->q_stride_s, a->out, a->o_stride_b, a->o_stride_h, a->o_stride_s, a->kv_start,
                  a->q_lens, causal, a->scale, nullptr, 0, 1, 0, a->workspace, a->workspace_bytes, a->flags, stream, ex);

@@ -340,6 +340,20 @@ __global__ void __launch_bounds__(256)
   if (lane == 0) *len_p = len + n;
 }
 
+// The same step when its attention launches have already stored the rows (PACE_ATTN_PENDING_ROW):
+// only the lengths are left to advance, one thread per (layer, sequence).
+__global__ void advance_layers_kernel(pace_kv_pool_t p, int layer_begin, int layer_end, const int32_t* __restrict__ seq_ids,
+                                      int batch, int n_new, const int32_t* __restrict__ n_per) {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= batch * (layer_end - layer_begin)) return;
+  const int b = i % batch, layer = layer_begin + i / batch;
+  const int slot = seq_ids[b];
+  if (slot < 0 || slot >= p.max_seqs) return;  // reported by reserve
+  const int n = n_per ? min(n_per[b], n_new) : n_new;
+  if (n > 0) p.seq_len[(size_t)layer * p.max_seqs + slot] += n;
+}
+
 // RoPE + append: eight lanes per (sequence, new token, group of kRopeHeads heads) of the projection
 // outputs.  Query rows are rotated into q_out, key rows rotated into their cache slot, value rows
 // copied into theirs.  A lane owns eight (x1, x2) pairs of every row of its group: it loads their
@@ -824,8 +838,10 @@ int pace_kv_append_layers(const pace_kv_pool_t* p, int32_t layer_begin, int32_t 
       layer_end > p->n_layers || layer_begin > layer_end)
     return PACE_ERR_INVALID;
   if (batch == 0 || n_new == 0 || layer_begin == layer_end) return PACE_OK;
-  if (!k_new || !v_new) return PACE_ERR_INVALID;
-  if (((uintptr_t)k_new & 15) || ((uintptr_t)v_new & 15) || (sl & 7) || (sb & 7) || (sh & 7) || (st & 7))
+  const bool lengths_only = !k_new && !v_new;  // the rows are in the pool already
+  if (!lengths_only && (!k_new || !v_new)) return PACE_ERR_INVALID;
+  if (!lengths_only &&
+      (((uintptr_t)k_new & 15) || ((uintptr_t)v_new & 15) || (sl & 7) || (sb & 7) || (sh & 7) || (st & 7)))
     return PACE_ERR_INVALID;
   const long long warps = (long long)batch * (layer_end - layer_begin);
   if (warps > (1LL << 30)) return PACE_ERR_UNSUPPORTED;
@@ -841,6 +857,14 @@ int pace_kv_append_layers(const pace_kv_pool_t* p, int32_t layer_begin, int32_t 
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
+  if (lengths_only) {
+    cfg.gridDim = dim3((unsigned)((warps + 255) / 256));
+    PACE_CUDA_TRY(cudaLaunchKernelEx(&cfg, advance_layers_kernel, *p, (int)layer_begin, (int)layer_end, seq_ids, (int)batch,
+                                     (int)n_new, n_per));
+    PACE_LAUNCH_CHECK("advance_layers_kernel");
+    note_pool_write((cudaStream_t)stream);
+    return PACE_OK;
+  }
   PACE_CUDA_TRY(cudaLaunchKernelEx(&cfg, append_layers_kernel, *p, (int)layer_begin, (int)layer_end, seq_ids, (int)batch,
                                    (int)n_new, n_per, (const __nv_bfloat16*)k_new, (const __nv_bfloat16*)v_new,
                                    (int64_t)sl, (int64_t)sb, (int64_t)sh, (int64_t)st));

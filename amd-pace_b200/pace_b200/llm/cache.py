@@ -241,7 +241,8 @@ class KVCacheManager:
         self.defer_appends = False
         self._stage_k: Optional[torch.Tensor] = None   # [layers, B, H, 1, D] views of the staging buffer
         self._stage_v: Optional[torch.Tensor] = None
-        self._pending: set = set()                     # layers whose newest row is staged, not yet in the pool
+        self._pending: set = set()                     # layers whose newest row is staged, not yet committed
+        self._row_stored: set = set()                  # ... and of those, the layers whose row an attention launch has stored
         self.cache_objects: List[KVCacheBase] = [
             self.kv_cache_class(max_seq_length, manager=self, layer=i) for i in range(self.num_layers)
         ]
@@ -313,17 +314,37 @@ class KVCacheManager:
                 while hi + 1 < len(layers) and layers[hi + 1] == layers[hi] + 1:
                     hi += 1
                 a, b = layers[lo], layers[hi] + 1
+                # rows that the layers' decode launches have stored themselves need no second copy
+                stored = all(l in self._row_stored for l in range(a, b))
                 _C.check(_C.lib.pace_kv_append_layers(pool.ref, a, b, self.slots_dev.data_ptr(), len(self.slots), 1,
-                                                      None, k_all[a].data_ptr(), v_all[a].data_ptr(), sl, sb, sh, st,
+                                                      None, None if stored else k_all[a].data_ptr(),
+                                                      None if stored else v_all[a].data_ptr(), sl, sb, sh, st,
                                                       _stream_ptr(pool.device)), "pace_kv_append_layers")
                 lo = hi + 1
         self._pending.clear()
+        self._row_stored.clear()
 
     def __getitem__(self, idx: int) -> "KVCacheBase":
         return self.cache_objects[idx]
 
     def update_mask(self, attn_mask: torch.Tensor, input_size: int) -> torch.Tensor:
         return self.cache_objects[0].update_mask(attn_mask, input_size)
+
+    def advance_host_mirror(self, n: int) -> bool:
+        """Every layer appends ``n`` tokens to every sequence (a replayed decode step): advances the
+        host mirror of pages, lengths and capacities without touching the device.  Returns True when
+        some sequence needs new pages.  The layers of a manager move in lockstep, so the page
+        arithmetic is done once, not once per layer."""
+        counts = [n] * len(self.slots)
+        first = self.cache_objects[0]
+        grow = first._host_account(counts)
+        for c in self.cache_objects[1:]:
+            if len(c._lens) != len(first._lens):
+                grow |= c._host_account(counts)
+                continue
+            c._lens = [x + n for x in c._lens]
+            c._capacity = c._capacity_after(max(c._lens))
+        return grow
 
     def update_cache_with_beam_indices(self, beam_idx: torch.Tensor) -> None:
         """Beam gather (cache.py:106-116): ONE index-only kernel for all layers."""
@@ -394,6 +415,7 @@ class KVCacheManager:
     def release(self) -> None:
         if self.pool is not None and self.slots is not None:
             self._pending.clear()   # staged rows of sequences that are being dropped
+            self._row_stored.clear()
             if not self._owns_pool:
                 self.pool.release_slots(self.slots, self.slots_dev)
             self.slots = None
@@ -424,6 +446,7 @@ class KVCacheBase(ABC):
             manager.static_launch = manager.capturing = manager.skip_reserve = False
             manager.identity_slots = False
             manager.defer_appends, manager._stage_k, manager._stage_v, manager._pending = False, None, None, set()
+            manager._row_stored = set()
             manager.cache_objects = [self]
         self.manager = manager
         self.layer = layer
@@ -609,6 +632,7 @@ class KVCacheBase(ABC):
             if dst.data_ptr() != src.data_ptr() or dst.stride() != src.stride():
                 dst.copy_(src)
         mgr._pending.add(self.layer)
+        mgr._row_stored.discard(self.layer)
         if self.key is None:
             self.key, self.value = PagedKV(self, "k"), PagedKV(self, "v")
         return self.key, self.value

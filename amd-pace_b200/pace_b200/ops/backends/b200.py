@@ -147,6 +147,8 @@ def paged_attention(query: torch.Tensor, key: PagedKV, kv_start: Optional[torch.
         a.k_pending, a.v_pending = ks.data_ptr(), vs.data_ptr()
         a.pending_stride_b, a.pending_stride_h = ks.stride(0), ks.stride(1)
     stream = torch.cuda.current_stream(query.device).cuda_stream
+    if pending:
+        mgr._row_stored.add(cache.layer)    # the launch below puts the staged row in its slot of the pool
     with torch.cuda.device(query.device):
         if S == 1 and decode_kernel == "cuda":
             _C.check(_C.lib.pace_attn_decode_cuda_cores(C.byref(a), stream), "pace_attn_decode_cuda_cores")

@@ -100,7 +100,25 @@ class ClockSampler:
                 "samples": len(sm), "reasons": sorted(reasons)}
 
 
-def cpu_reference_line(steps: int, warmup: int, sample_layers: int):
+def workload_config(n_gpus: int) -> dict:
+    """The workload both arms are timed on: identical keys and values in the GPU line and in the
+    reference arm's line."""
+    return {"workload": WORKLOAD, "batch_per_gpu": CFG["batch"], "global_batch": CFG["batch"] * n_gpus,
+            "layers": CFG["n_layers"], "q_heads": CFG["hq"], "kv_heads": CFG["hkv"], "head_dim": CFG["d"],
+            "prompt_tokens": CFG["prompt"], "new_tokens": CFG["max_new"],
+            "parallelism": f"dp{n_gpus} (sequences sharded, no collective)"}
+
+
+CPU_SAMPLE_LAYERS, CPU_SAMPLE_WARMUP = 4, 2
+
+
+def cpu_reference_line(steps: int):
+    """The reference's CPU path on this host's cores, on a bounded sample of the workload: the same
+    batch, shapes and cache length as the GPU arm, over 4 of the 32 layers (every layer costs the same:
+    an append and an attention pass over its own cache), scaled to 32.  The reference's own classes when
+    its package has been staged under oracle/_ref/, else the restatement.  Always 2 warm-up steps; the step
+    time is the median over the timed steps, so both callers (the `cpu_baseline` leg of the GPU line and
+    the reference arm) report the same quantity whatever their step count."""
     from oracle.cpu_path import time_decode_tokens_per_s
     # every host core this process may run on (a launcher such as torchrun sets OMP_NUM_THREADS=1)
     try:
@@ -109,28 +127,55 @@ def cpu_reference_line(steps: int, warmup: int, sample_layers: int):
         cores = os.cpu_count() or 1
     torch.set_num_threads(max(1, cores))
     cores = torch.get_num_threads()
-    tps, step_s = time_decode_tokens_per_s(CFG["n_layers"], sample_layers, CFG["batch"], CFG["hq"], CFG["hkv"],
-                                           CFG["d"], CFG["prompt"], CFG["prompt"] + CFG["max_new"], steps, warmup)
-    sample = (f"{steps} decode steps over {sample_layers} of {CFG['n_layers']} layers (reference layout: BMC append + "
-              f"repeat_kv + torch CPU SDPA with additive mask), scaled to {CFG['n_layers']} layers")
-    return tps, step_s, cores, sample
+    tps, step_s, kind = time_decode_tokens_per_s(CFG["n_layers"], CPU_SAMPLE_LAYERS, CFG["batch"], CFG["hq"],
+                                                 CFG["hkv"], CFG["d"], CFG["prompt"], CFG["prompt"] + CFG["max_new"],
+                                                 steps, CPU_SAMPLE_WARMUP)
+    what = ("the reference's own BMCKVCache.update_cache + repeat_kv + MultiHeadAttention(NATIVE)" if kind == "reference"
+            else "restatement of the reference layout: BMC append + repeat_kv + torch CPU SDPA with additive mask")
+    sample = (f"median of {steps} decode steps over {CPU_SAMPLE_LAYERS} of {CFG['n_layers']} layers ({what}), "
+              f"scaled to {CFG['n_layers']} layers")
+    return tps, step_s, cores, kind, sample
 
 
 def run_reference(args, rank):
     if rank != 0:
         return
-    steps = max(1, min(args.steps, 20))
-    tps, step_s, cores, sample = cpu_reference_line(steps, max(1, min(args.warmup, 3)), sample_layers=4)
+    steps = max(3, min(args.steps, 20))
+    tps, step_s, cores, kind, sample = cpu_reference_line(steps)
     line = {"impl": "reference", "metric": "decode_tokens_per_s", "value": tps, "unit": "tokens/s",
             "n_gpus": args.gpus, "steps": steps, "warmup": args.warmup, "ms_per_step": step_s * 1e3,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": WORKLOAD, "batch": CFG["batch"], "note": "CPU port of the reference path"},
-            "cpu_baseline": {"value": tps, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": sample},
+            "config": workload_config(args.gpus),
+            "cpu_baseline": {"value": tps, "unit": "tokens/s", "cores": cores, "kind": kind, "sample": sample},
             "e2e": {"value": tps, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(line), flush=True)
 
 
+def pin_rank_to_cores(local_rank: int, world: int):
+    """Each rank keeps its own slice of the cores this process may run on - set before the CUDA context
+    and the pinned buffers exist, so that the rank's copies are driven from, and its pinned memory is
+    allocated near, cores no other rank uses (the reference's workers pin themselves the same way,
+    pace/utils/worker.py:49-62).  Returns the slice."""
+    try:
+        allowed = sorted(os.sched_getaffinity(0))
+    except AttributeError:
+        return None
+    if world <= 1 or len(allowed) < world:
+        return allowed
+    per = len(allowed) // world
+    mine = allowed[local_rank * per:(local_rank + 1) * per]
+    try:
+        os.sched_setaffinity(0, mine)
+    except OSError:
+        return allowed
+    return mine
+
+
+RANK_CORES = None
+
+
 def run_ours(args, rank, world, local_rank):
+    cores = RANK_CORES
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: the hot path has no CPU implementation")
     from pace_b200.llm.cache import KVCacheManager, KVCacheType
@@ -283,6 +328,28 @@ def run_ours(args, rank, world, local_rank):
         raise SystemExit("bench.py: the end-to-end step's host result differs from the device result")
     barrier()
 
+    # the step's copies alone, one direction at a time (same chunks, same pinned buffers, all ranks at
+    # once): which direction gives way when several ranks share the host's memory system
+    def copies_only(direction):
+        def fn():
+            for c in range(n_chunks):
+                if direction == "h2d":
+                    kvq[c * per:(c + 1) * per].copy_(host_in[c * per:(c + 1) * per], non_blocking=True)
+                else:
+                    host_out[c * per:(c + 1) * per].copy_(out_all[c * per:(c + 1) * per], non_blocking=True)
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        barrier()
+        t0 = time.perf_counter()
+        for _ in range(e2e_steps):
+            fn()
+            torch.cuda.current_stream().synchronize()
+        dt = time.perf_counter() - t0
+        barrier()
+        return dt * 1e3 / e2e_steps
+    h2d_ms, d2h_ms = copies_only("h2d"), copies_only("d2h")
+
     # ---- the decode-attention kernel alone: 32 back-to-back launches, one per layer.  With no append
     # between them consecutive launches are ordered one after the other (a programmatic dependent waits
     # for the launch in front), so this is the duration of an isolated launch; inside the step the
@@ -309,21 +376,43 @@ def run_ours(args, rank, world, local_rank):
     r1.record()
     torch.cuda.synchronize()
     alone_us = r0.elapsed_time(r1) * 1e3 / (roof_reps * L)
+    del rg
+
+    # ---- the same step at other cache lengths of the configuration's range (512 .. 768 tokens): the cache
+    # is rolled back or grown (untimed replays) to the wanted length, then a block of steps is timed ----
+    def alg_bytes_at(kv_len):
+        return B * (2 * Hkv * D * 2 * kv_len) + 2 * B * Hq * D * 2
+    peak, peak_kind = measured_hbm_peak()
+    sweep_steps = max(4, min(args.steps, 16))
+    by_len = {}
+    for target in (() if args.no_sweep else (512, 640, CFG["prompt"] + CFG["max_new"] - sweep_steps)):
+        cur = mgr[0].seq_len
+        if cur > target:
+            mgr.remove_cache(cur - target)
+        for _ in range(max(0, target - cur)):
+            graph.replay()
+        t_ms, _ = timed_block(sweep_steps)
+        mean_len = target + (sweep_steps + 1) / 2.0
+        us = t_ms * 1e3 / (sweep_steps * L)
+        by_len[str(target)] = {"kv_len_mean": mean_len, "us_per_launch": us,
+                               "frac": alg_bytes_at(mean_len) / (us * 1e-6) / 1e9 / peak}
+    mgr.pool.check_status()
     # Roofline over the timed region: the step is L x [append, attention] with the one-token appends
     # running beside the attention launches, so a launch's share of the step is step time / L (the
     # appends' time counts against the kernel).  Algorithmic bytes of one launch: K and V rows of every
     # cached token once, q in, o out (bf16, GQA), at the mean length of the timed steps.
     attn_us = ms * 1e3 / (args.steps * L)
     len_mean = len_after_timed - (args.steps + 1) / 2.0 + 1
-    alg_bytes = B * (2 * Hkv * D * 2 * len_mean) + 2 * B * Hq * D * 2
+    alg_bytes = alg_bytes_at(len_mean)
     achieved = alg_bytes / (attn_us * 1e-6) / 1e9
-    peak, peak_kind = measured_hbm_peak()
 
     # ---- reduce over ranks: slowest rank sets the time ----
     if world > 1:
-        t = torch.tensor([ms, e2e_ms, alone_us], device=dev, dtype=torch.float64)
+        t = torch.tensor([ms, e2e_ms, alone_us, h2d_ms, d2h_ms, max(block_ms), min(block_ms)], device=dev,
+                         dtype=torch.float64)
         torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
-        ms, e2e_ms, alone_us = (float(x) for x in t.tolist())
+        ms, e2e_ms, alone_us, h2d_ms, d2h_ms, blk_max, blk_min = (float(x) for x in t.tolist())
+        block_ms = [blk_min, ms, blk_max]
         attn_us = ms * 1e3 / (args.steps * L)
         achieved = alg_bytes / (attn_us * 1e-6) / 1e9
     tokens = B * args.steps * world
@@ -335,61 +424,86 @@ def run_ours(args, rank, world, local_rank):
         "metric": "decode_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "batch_per_gpu": B, "global_batch": B * world, "layers": L,
-                   "q_heads": Hq, "kv_heads": Hkv, "head_dim": D, "kv_len_start": len_after_timed - args.steps,
-                   "kv_len_end": len_after_timed, "page_tokens": mgr.pool.page_tokens,
-                   "l2": "inputs_larger_than_l2 (%.1f GB of K/V per step)" % (L * alg_bytes / 1e9),
-                   "parallelism": f"dp{world} (sequences sharded, no collective)",
-                   "launch": "one CUDA graph per step"},
+        "config": workload_config(world),
+        "timed_region": {"kv_len_start": len_after_timed - args.steps, "kv_len_end": len_after_timed,
+                         "page_tokens": mgr.pool.page_tokens,
+                         "l2": "inputs_larger_than_l2 (%.1f GB of K/V per step)" % (L * alg_bytes / 1e9),
+                         "launch": "one CUDA graph per step: 32 decode launches that take the step's new K/V row "
+                                   "from the staging buffer, then one commit of all layers",
+                         "blocks": n_blocks, "block_ms": block_ms,
+                         "block_spread": (max(block_ms) - min(block_ms)) / ms,
+                         "note": f"median of {n_blocks} blocks of --steps replays over the same lengths (the cache "
+                                 "is rolled back by --steps tokens between blocks)",
+                         "cores_of_this_rank": len(cores) if cores else None},
         "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": host_in.numel() * 2,
                 "d2h_bytes_per_step": host_out.numel() * 2, "steps": e2e_steps, "ms_per_step": e2e_ms / e2e_steps,
+                "h2d_only_ms_per_step": h2d_ms, "d2h_only_ms_per_step": d2h_ms,
                 "overlap": f"within a step only: copies in {n_chunks} chunks of {per} layers on side streams of the "
                            "step's CUDA graph; the host synchronises after every step"},
         "gpu_launches": (own_launches_per_step * args.steps + timed_reserves) * world,
-        "gpu_launches_note": (f"{own_launches_per_step} own kernels per step: {L} x [append, decode attention], plus the page "
-                              f"reservation kernel in the {timed_reserves} of {args.steps} steps in which a sequence reached a new page"),
+        "gpu_launches_note": (f"{own_launches_per_step} own kernels per step: {L} decode attention launches and the commit "
+                              f"of the step's rows, plus the page reservation kernel in the {timed_reserves} of "
+                              f"{args.steps} steps in which a sequence reached a new page"),
         "clocks": clocks,
         "roofline": {"bound": "hbm", "kernel": "attn_mma_kernel<128,1,4> (GQA decode, 4 query heads packed per MMA tile, two CTAs per SM)",
                      "achieved": achieved, "peak": peak,
                      "peak_kind": peak_kind, "unit": "GB/s", "frac": achieved / peak,
                      "frac_of_nominal_8TBs": achieved / 8000.0, "us_per_launch": attn_us,
-                     "us_per_launch_note": "timed step / launches: consecutive layers' launches overlap, the appends run beside them",
+                     "us_per_launch_note": "timed step / 32: the commit of the step's rows counts against the launches",
+                     "by_kv_len": by_len,
                      "us_per_launch_alone": alone_us, "kv_len": len_mean,
                      "frac_alone": (B * (2 * Hkv * D * 2 * lens_now) + 2 * B * Hq * D * 2) / (alone_us * 1e-6) / 1e9 / peak,
                      "alg_bytes_per_launch": alg_bytes, "traffic": None},
     }
+    if world == 1 and not args.no_aux:
+        # side numbers of the multi-token kernels on the same record: PARD verify (16 x 9 tokens over 1033
+        # cached) and a 512-token prefill chunk over 4096 cached, 4 layers each
+        mgr.release()
+        del mgr, graph, graph_e2e
+        torch.cuda.empty_cache()
+        aux = {}
+        for wl in ("verify", "prefill"):
+            a = aux_measure(wl, layers=4, head_dim=D, past=3584, steps=32)
+            aux[wl] = {"us_per_launch": a["us_per_launch"], "hbm_frac_of_measured": a["hbm"]["frac_of_measured"],
+                       "tflops": a["tensor"]["achieved_tflops"],
+                       "tensor_frac_of_measured_burst": a["tensor"]["frac_of_measured_burst"],
+                       "shape": f"B={a['batch']} q_len={a['q_len']} kv_len={a['kv_len']}"}
+        line["aux"] = {"verify_us": aux["verify"]["us_per_launch"], "prefill_tflops": aux["prefill"]["tflops"],
+                       "verify": aux["verify"], "prefill": aux["prefill"]}
     if world == 1 and not args.no_cpu_baseline:
-        tps, _, cores, sample = cpu_reference_line(steps=6, warmup=1, sample_layers=4)
-        line["cpu_baseline"] = {"value": tps, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": sample}
+        tps, _, cpu_cores, kind, sample = cpu_reference_line(steps=8)
+        line["cpu_baseline"] = {"value": tps, "unit": "tokens/s", "cores": cpu_cores, "kind": kind, "sample": sample}
     traffic_file = os.path.join(ROOT, "profiles", "attn_decode_traffic.json")
     if os.path.exists(traffic_file):
         try:
             t = json.load(open(traffic_file))
-            # DRAM bytes of the captured launch scale with the page rows a launch streams (whole
-            # pages leave DRAM: a sequence of n tokens reads ceil(n / page) pages)
-            P_ = mgr.pool.page_tokens
-            rows_now = B * ((int(len_mean) + P_ - 1) // P_) * P_
-            line["roofline"]["traffic"] = t["dram_bytes_per_launch"] * rows_now / t["page_rows_per_launch"]
+            # DRAM bytes of the captured launch scale with the rows a launch streams: whole pages, the
+            # partly filled last page in boxes of 16 rows
+            rows_now = B * ((int(len_mean) + 15) // 16) * 16
+            line["roofline"]["traffic"] = t["dram_bytes_per_launch"] * rows_now / t["rows_per_launch"]
         except Exception:
             pass
     print(json.dumps(line), flush=True)
 
 
 def run_aux(args):
-    """Side measurements of the multi-token attention kernels (not the bench line): PARD verify
-    (config 4: batch 16, 9 query tokens over 1033 cached) and a 512-token prefill chunk (config 3:
-    batch 8, 512 queries over a cache of `--past` + 512).  Times the attention kernel alone over
-    `--layers` layers visited round-robin (cold L2) and prints one JSON line."""
+    print(json.dumps(aux_measure(args.workload, min(args.layers, 8), args.head_dim, args.past, args.steps)), flush=True)
+
+
+def aux_measure(workload, layers, head_dim, past, steps):
+    """Side measurements of the multi-token attention kernels: PARD verify (config 4: batch 16, 9 query
+    tokens over 1033 cached) and a 512-token prefill chunk (config 3: batch 8, 512 queries over a cache
+    of `past` + 512).  Times the attention kernel alone over `layers` layers visited round-robin (cold
+    L2) and returns the figures as a dict."""
     from pace_b200.llm.cache import KVCacheManager, KVCacheType
     from pace_b200.ops import MultiHeadAttention
-    dev = torch.device("cuda", 0)
-    torch.cuda.set_device(dev)
-    L = min(args.layers, 8)
-    Hq, Hkv, D = CFG["hq"], CFG["hkv"], args.head_dim
-    if args.workload == "verify":
+    dev = torch.device("cuda", torch.cuda.current_device())
+    L = layers
+    Hq, Hkv, D = CFG["hq"], CFG["hkv"], head_dim
+    if workload == "verify":
         B, S, kv_len = 16, 9, 1024 + 9
     else:
-        B, S, kv_len = 8, 512, args.past + 512
+        B, S, kv_len = 8, 512, past + 512
 
     class Cfg:
         num_hidden_layers = L
@@ -421,7 +535,7 @@ def run_aux(args):
         graph.replay()
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    reps = max(1, args.steps // 8)
+    reps = max(1, steps // 8)
     e0.record()
     for _ in range(reps):
         graph.replay()
@@ -434,13 +548,14 @@ def run_aux(args):
     flops = sum(4 * Hq * D * (kv_len - S + s + 1) for s in range(S)) * B
     peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json"))) if os.path.exists(
         os.path.join(ROOT, "MEASURED_PEAKS.json")) else {"hbm_gbs": FALLBACK_HBM_GBS, "bf16_tflops": 1590.0}
-    line = {"workload": args.workload, "batch": B, "q_len": S, "kv_len": kv_len, "head_dim": D,
+    line = {"workload": workload, "batch": B, "q_len": S, "kv_len": kv_len, "head_dim": D,
             "page_tokens": mgr.pool.page_tokens, "us_per_launch": us,
             "hbm": {"alg_bytes": alg_bytes, "achieved_gbs": alg_bytes / us / 1e3,
                     "frac_of_measured": alg_bytes / us / 1e3 / peaks["hbm_gbs"]},
             "tensor": {"flops": flops, "achieved_tflops": flops / us / 1e6,
                        "frac_of_measured_burst": flops / us / 1e6 / peaks["bf16_tflops"]}}
-    print(json.dumps(line), flush=True)
+    mgr.release()
+    return line
 
 
 def run_rope(args):
@@ -633,6 +748,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-aux", action="store_true", help="skip the verify / prefill side numbers of the bench line")
+    ap.add_argument("--no-sweep", action="store_true", help="profiling aid: skip the timed blocks at other cache lengths")
     ap.add_argument("--layers", type=int, default=CFG["n_layers"],
                     help="profiling aid: fewer layers = less device memory; the bench line is only valid at 32")
     ap.add_argument("--workload", default="decode", choices=["decode", "verify", "prefill", "rope_append", "device_loop", "serving"],
@@ -648,6 +765,8 @@ def main():
     if args.impl == "reference":
         run_reference(args, rank)
         return
+    global RANK_CORES
+    RANK_CORES = pin_rank_to_cores(local_rank, world)
     if args.workload in ("rope_append", "device_loop", "serving"):
         if rank == 0:
             {"rope_append": run_rope, "device_loop": run_device_loop, "serving": run_serving}[args.workload](args)

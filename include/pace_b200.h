@@ -122,7 +122,9 @@ int pace_kv_append(const pace_kv_pool_t* pool, int32_t layer, const int32_t* seq
  * k_new / v_new are bf16 [layer][batch][n_kv_heads][n_new][head_dim] through element strides
  * (stride_l first; head_dim contiguous, rows 16-byte aligned); layer `layer_begin` is at offset 0.
  * Every listed layer's seq_len advances by the same counts.  pace_kv_reserve for the step must have
- * run (any one layer: pages are shared by all layers).  The kernel is ordered behind everything in
+ * run (any one layer: pages are shared by all layers).  k_new = v_new = NULL advances the lengths
+ * only: for a step whose rows every layer's attention launch has stored already
+ * (PACE_ATTN_PENDING_ROW).  The kernel is ordered behind everything in
  * front of it on the stream and in front of everything behind it (no programmatic overlap). */
 int pace_kv_append_layers(const pace_kv_pool_t* pool, int32_t layer_begin, int32_t layer_end,
                           const int32_t* seq_ids, int32_t batch, int32_t n_new, const int32_t* n_new_per_seq,

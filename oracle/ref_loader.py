@@ -1,9 +1,11 @@
 """Imports the reference's own Python modules, unmodified, from its source tree.
 
-TEST INFRASTRUCTURE ONLY, and only usable where the reference tree exists
-(it is located through $PACE_REF_ROOT, with a built-in default).  Used by
-tests/golden/make_golden.py to produce the committed golden vectors and by the
-CPU tests that re-check the oracle against the live reference when it is there.
+TEST INFRASTRUCTURE ONLY, and only usable where the reference tree exists: a
+checkout named by $PACE_REF_ROOT, else the copy of its `pace/` package that
+oracle/stage_ref.py puts under oracle/_ref/ (git-ignored).  Used by
+tests/golden/make_golden.py to produce the committed golden vectors, by the CPU
+tests that re-check the oracle against the live reference when it is there, and by
+the timed CPU baseline of bench.py.
 
 The reference package needs its compiled extension (`pace._C`) and a
 setup-generated version module at import time (pace/__init__.py:6-15); neither
@@ -19,7 +21,10 @@ import types
 
 
 def ref_root() -> str:
-    return os.environ.get("PACE_REF_ROOT", "/root/reference")
+    env = os.environ.get("PACE_REF_ROOT")
+    if env:
+        return env
+    return os.path.join(os.path.dirname(os.path.abspath(__file__)), "_ref")
 
 
 def available() -> bool:
