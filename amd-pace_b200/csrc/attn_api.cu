@@ -61,6 +61,36 @@ StreamNote stream_note(cudaStream_t stream) {
 
 using namespace pace;
 
+namespace pace {
+namespace {
+// Two warps wait on a barrier nobody ever arrives on: the first with a limit of `slow_iters` sleeping
+// probes, the second with the kernels' usual quarter second.  The first runs out, raises the CTA's
+// abort flag and the pool's PACE_DEV_WAIT_TIMEOUT bit; the second sees the flag and returns at once.
+__global__ void wait_selftest_kernel(int32_t* status, int slow_iters) {
+  __shared__ uint64_t bar;
+  __shared__ int abort_flag;
+  if (threadIdx.x == 0) {
+    mbar_init(&bar, 1);
+    abort_flag = 0;
+    fence_mbar_init();
+  }
+  __syncthreads();
+  const bool first = threadIdx.x < 32;
+  const bool ok = mbar_wait(&bar, 0, &abort_flag, first ? slow_iters : (1 << 18));
+  if (!ok && (threadIdx.x & 31) == 0) raise_status(status, PACE_DEV_WAIT_TIMEOUT);
+  __syncthreads();
+  if (threadIdx.x == 0) mbar_inval(&bar);
+}
+}  // namespace
+}  // namespace pace
+
+extern "C" int pace_selftest_wait_timeout(const pace_kv_pool_t* pool, int32_t limit_us, void* stream) {
+  if (!pool || !pool->status || limit_us < 1 || limit_us > 1000000) return PACE_ERR_INVALID;
+  wait_selftest_kernel<<<1, 64, 0, (cudaStream_t)stream>>>(pool->status, (int)limit_us);  // about a microsecond per probe
+  PACE_LAUNCH_CHECK("wait_selftest_kernel");
+  return PACE_OK;
+}
+
 extern "C" uint64_t pace_attn_workspace_bytes(int32_t batch, int32_t n_q_heads, int32_t n_kv_heads,
                                               int32_t head_dim, int32_t q_len) {
   if (batch <= 0 || n_q_heads <= 0 || n_kv_heads <= 0 || head_dim <= 0 || q_len <= 0) return 0;

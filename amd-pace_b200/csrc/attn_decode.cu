@@ -159,20 +159,24 @@ __global__ void __launch_bounds__(kThreads, 1) attn_decode_kernel(const DecodePa
   const int P = p.kv.page_tokens;
 
   // ---- prologue: barriers, per-sequence chunk counts, exclusive prefix ----
+  // (the pool's status word is asked for now and looked at behind the loads of the lengths: a launch on
+  // a pool where an earlier launch ran out of patience does nothing)
+  const int status_word = tid == kThreads - 1 ? load_status_word(p.kv.status) : 0;
   if (tid == 0) {
     for (int s = 0; s < n_stages; ++s) {
       mbar_init(&full_bar[s], 1);
       mbar_init(&empty_bar[s], kConsumerWarps);
     }
-    misc[0] = 0;
+    misc[0] = 0;  // the CTA's abort flag
     misc[1] = 0;
     fence_mbar_init();
   }
+  volatile int* abort = misc;
   for (int b = tid; b < p.batch; b += kThreads) {
     const int slot = view_slot(p.kv, b);
     prefix[b + 1] = slot < 0 ? 0 : chunks_of(p, view_len(p.kv, slot)) * Hkv;
   }
-  __syncthreads();
+  if (__syncthreads_or(pool_gave_up(status_word))) return;
   if (warp == 0) {  // inclusive scan, 32 entries per round
     int carry = 0;
     for (int base = 0; base < p.batch; base += 32) {
@@ -271,7 +275,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_decode_kernel(const DecodePa
           if (row0_n >= P) { row0_n = 0; lp_n = lp + 1; }
         }
         const int s = i % n_stages;
-        if (i >= n_stages && !mbar_wait(&empty_bar[s], ((i / n_stages) - 1) & 1)) { ok = false; break; }
+        if (i >= n_stages && !mbar_wait(&empty_bar[s], ((i / n_stages) - 1) & 1, abort)) { ok = false; break; }
         const int tok0 = whole_pages ? j * p.chunk_tokens : lp * P + row0;
         const int rows = whole_pages ? min(p.chunk_tokens, len - tok0) : min(min(kChunkRows, P - row0), len - tok0);
         const int my_rows = whole_pages ? max(0, min(P, rows - pi * P)) : rows;
@@ -355,7 +359,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_decode_kernel(const DecodePa
 
   for (int i = 0; i < n_my; ++i) {
     const int s = i % n_stages;
-    if (!mbar_wait(&full_bar[s], (i / n_stages) & 1)) {
+    if (!mbar_wait(&full_bar[s], (i / n_stages) & 1, abort)) {
       if (lane == 0) raise_status(p.kv.status, PACE_DEV_WAIT_TIMEOUT);
       return;  // every consumer warp times out on the same stage; nobody is left waiting on us
     }

@@ -385,6 +385,7 @@ __global__ void __launch_bounds__(threads_of(UMMA, MT * NS), MT * NS == 4 ? 2 : 
   uint64_t* res_empty = res_full + 2; // [2]
   uint64_t* umma_bars = res_empty + 2; // [20], tcgen05 variant only
   int* misc = reinterpret_cast<int*>(smem + sp.misc);
+  volatile int* abort = misc + 4;  // raised by the first role whose wait runs out (and from the start on a pool that has given up)
   int* sb_slot = reinterpret_cast<int*>(smem + sp.per_b);
   int* sb_len = sb_slot + p.batch;
   int* sb_kvs = sb_len + p.batch;
@@ -427,14 +428,16 @@ __global__ void __launch_bounds__(threads_of(UMMA, MT * NS), MT * NS == 4 ? 2 : 
     else if (k == 2 * n_stages) mbar_init(q_empty, NW);
     else if (k < 2 * n_stages + 3) mbar_init(&res_full[k - 2 * n_stages - 1], NW);
     else if (k < 2 * n_stages + 5) mbar_init(&res_empty[k - 2 * n_stages - 3], 1);
-    if (k == 30) misc[2] = 0;  // longest unit, in chunks (a maximum over the items, taken below)
+    if (k == 30) {
+      misc[2] = 0;  // longest unit, in chunks (a maximum over the items, taken below)
+      misc[4] = 0;  // the CTA's abort flag
+    }
     if (UMMA && k == 31) {
       // s_full[4], p_full[4] (one arrival per warp of the group), o_full[2], q_ready, drain[2], pub
       // (every softmax thread), xch (one arrival per softmax warp, like q_ready), p_free[4]
       for (int j = 0; j < 19; ++j)
         mbar_init(&umma_bars[j],
                   (j >= 4 && j < 8) ? 4 : (j == 10 || j == 14) ? 8 : (j == 13 ? kUmmaSoftmaxThreads : 1));
-      misc[4] = 0;  // abort flag
     }
     fence_mbar_init();
   }
@@ -575,6 +578,9 @@ __global__ void __launch_bounds__(threads_of(UMMA, MT * NS), MT * NS == 4 ? 2 : 
       fast_it1 = it1;
       const int b = it0 + lane;  // one lane per sequence this CTA touches
       int n = 0, slot = -1, len = 0;
+      // (the pool's status word travels beside the lengths: where an earlier launch ran out of patience,
+      // this one streams nothing and writes nothing until the host has cleared the word)
+      const int status_word = lane == 31 ? load_status_word(p.kv.status) : 0;
       if (b <= it1) {
         slot = view_slot(p.kv, b);
         if (slot >= 0) len = view_len(p.kv, slot) + (pend ? 1 : 0);
@@ -612,8 +618,9 @@ __global__ void __launch_bounds__(threads_of(UMMA, MT * NS), MT * NS == 4 ? 2 : 
       const int h0 = u0 - it0 * Hkv, h1 = (u1 - 1) - it1 * Hkv;
       x0 = (long long)prefix[it0] + (long long)h0 * ((prefix[it0 + 1] - prefix[it0]) / Hkv);
       x1 = (long long)prefix[it1] + (long long)(h1 + 1) * ((prefix[it1 + 1] - prefix[it1]) / Hkv);
+      const bool gave_up = pool_gave_up(__shfl_sync(0xffffffffu, status_word, 31));
       // query rows that see no key at all (nothing cached) get zeros
-      for (int u = u0; u < u1; ++u) {
+      for (int u = u0; u < u1 && !gave_up; ++u) {
         const int it = u / Hkv, h = u - it * Hkv;
         if (prefix[it + 1] != prefix[it]) continue;
         gdc_wait();  // (early K/V: a write to out)
@@ -626,7 +633,8 @@ __global__ void __launch_bounds__(threads_of(UMMA, MT * NS), MT * NS == 4 ? 2 : 
           }
         }
       }
-      n_my = (int)(x1 - x0);
+      n_my = gave_up ? 0 : (int)(x1 - x0);
+      if (gave_up && lane == 0) *abort = 1;
       if (spec_ok) {
         asm volatile("bar.sync 2, 64;" ::: "memory");
         n_spec = misc[3];
@@ -654,6 +662,7 @@ __global__ void __launch_bounds__(threads_of(UMMA, MT * NS), MT * NS == 4 ? 2 : 
     }
   } else {
   // ---- prologue, part 2: per-sequence lengths -> chunk prefix -> this CTA's range ----
+  const int status_word = tid == NTHR - 1 ? load_status_word(p.kv.status) : 0;  // (looked at behind the loads below)
   int my_slot[(kMaxItems + NTHR - 1) / NTHR];
   int my_len[(kMaxItems + NTHR - 1) / NTHR];
 #pragma unroll
@@ -689,7 +698,8 @@ __global__ void __launch_bounds__(threads_of(UMMA, MT * NS), MT * NS == 4 ? 2 : 
     }
   }
   fence_proxy_async();  // generic-proxy zero fill before async-proxy (TMA) writes to the same bytes
-  __syncthreads();
+  // an earlier launch on this pool ran out of patience: nothing is attempted until the host clears that
+  if (__syncthreads_or(pool_gave_up(status_word))) return;
   if (tid == 0) PACE_TRACE(3, 3);
   int saw_empty = 0;
   for (int it = tid; it < n_items; it += NTHR) {
@@ -872,12 +882,12 @@ __global__ void __launch_bounds__(threads_of(UMMA, MT * NS), MT * NS == 4 ? 2 : 
       if (lane == 0 && i == 0) PACE_TRACE(3, 9);
       if (!UMMA && part_idx > 0) {
         flush_q();
-        if (!mbar_wait(q_empty, (part_idx - 1) & 1)) { ok = false; break; }
+        if (!mbar_wait(q_empty, (part_idx - 1) & 1, abort)) { ok = false; break; }
       }
       for (bool first = true; j < j_end; ++j, ++i, first = false) {
         if (i >= n_stages) {
           if (!UMMA && MT == 1) flush_q();
-          if (!mbar_wait(&empty_bar[s], ph ^ 1)) { ok = false; break; }
+          if (!mbar_wait(&empty_bar[s], ph ^ 1, abort)) { ok = false; break; }
         }
         const int tok0 = whole_pages ? j * CT : lp * P + row0;
         const int rows = whole_pages ? min(CT, len - tok0) : min(min(kChunk, P - row0), len - tok0);
@@ -970,7 +980,7 @@ __global__ void __launch_bounds__(threads_of(UMMA, MT * NS), MT * NS == 4 ? 2 : 
       raise_status(p.kv.status, PACE_DEV_WAIT_TIMEOUT);
       // let copies already in flight land before the CTA's shared memory is released
       const int from = i > n_stages ? i - n_stages : 0;
-      for (int k = from; k < i; ++k) mbar_wait(&full_bar[k % n_stages], (k / n_stages) & 1);
+      for (int k = from; k < i; ++k) mbar_wait(&full_bar[k % n_stages], (k / n_stages) & 1);  // (never cut short)
     }
     if (lane == 0 && i < n_spec) {
       // speculative copies of pages beyond the unit's length: nobody consumes them, receive them here
@@ -1017,7 +1027,7 @@ __global__ void __launch_bounds__(threads_of(UMMA, MT * NS), MT * NS == 4 ? 2 : 
     // round trips happen here, off the consumers' path.
     for (int k = 0;; ++k) {
       const int rs = k % sp.n_res;
-      if (!mbar_wait(&res_full[rs], (k / sp.n_res) & 1)) {
+      if (!mbar_wait(&res_full[rs], (k / sp.n_res) & 1, abort)) {
         if (lane == 0) raise_status(p.kv.status, PACE_DEV_WAIT_TIMEOUT);
         return;
       }
@@ -1058,7 +1068,7 @@ __global__ void __launch_bounds__(threads_of(UMMA, MT * NS), MT * NS == 4 ? 2 : 
 
   for (int i = 0; i < n_my; ++i) {
     const int s = i % n_stages;
-    if (!mbar_wait(&full_bar[s], (i / n_stages) & 1)) {
+    if (!mbar_wait(&full_bar[s], (i / n_stages) & 1, abort)) {
       if (lane == 0) raise_status(p.kv.status, PACE_DEV_WAIT_TIMEOUT);
       return;
     }
@@ -1410,7 +1420,7 @@ __global__ void __launch_bounds__(threads_of(UMMA, MT * NS), MT * NS == 4 ? 2 : 
           }
         }
         }  // row-major accumulators
-        if (n_parts_done >= sp.n_res) ok_res = mbar_wait(&res_empty[rs], ((n_parts_done / sp.n_res) - 1) & 1);
+        if (n_parts_done >= sp.n_res) ok_res = mbar_wait(&res_empty[rs], ((n_parts_done / sp.n_res) - 1) & 1, abort);
         csync<CTHR>();
         for (int oi = tid; oi < live * D; oi += CTHR) {
           const int row = oi / D, d = oi - row * D;
@@ -1435,7 +1445,7 @@ __global__ void __launch_bounds__(threads_of(UMMA, MT * NS), MT * NS == 4 ? 2 : 
         }
       } else {
         // one warp owns its 16 rows outright: registers go straight to the result slot
-        if (n_parts_done >= sp.n_res) ok_res = mbar_wait(&res_empty[rs], ((n_parts_done / sp.n_res) - 1) & 1);
+        if (n_parts_done >= sp.n_res) ok_res = mbar_wait(&res_empty[rs], ((n_parts_done / sp.n_res) - 1) & 1, abort);
         if (row0 < live) {
 #pragma unroll
           for (int n = 0; n < ON; ++n)

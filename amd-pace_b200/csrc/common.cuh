@@ -221,16 +221,31 @@ __device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 // Bounded wait: true when the phase completed, false when it gave up (after about a quarter of a
-// second).
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+// second, or `slow_iters` sleeping probes).  `abort` is a flag in the CTA's shared memory: the first
+// role of a CTA whose wait runs out raises it, and every other wait of the CTA that is already
+// sleeping returns at once instead of sitting out its own quarter second.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort = nullptr,
+                                          int slow_iters = 1 << 18) {
   for (int i = 0; i < 64; ++i)
     if (mbar_try_wait(bar, parity)) return true;
-  for (int i = 0; i < (1 << 18); ++i) {
+  for (int i = 0; i < slow_iters; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
+    if (abort && *abort) return false;
     __nanosleep(64);
   }
+  if (abort) *abort = 1;
   return false;
 }
+// The pool's sticky status word, read without waiting for it: the load is issued here, the thread only
+// stalls where it first uses the value (pool_gave_up below).  null -> 0.
+__device__ __forceinline__ int load_status_word(const int32_t* status) {
+  int v = 0;
+  if (status) asm volatile("ld.volatile.global.s32 %0, [%1];" : "=r"(v) : "l"(status));
+  return v;
+}
+// True when the word says that an earlier launch ran out of patience: the launches behind it do
+// nothing (and return at once) until the host has cleared the word.
+__device__ __forceinline__ bool pool_gave_up(int status_word) { return (status_word & PACE_DEV_WAIT_TIMEOUT) != 0; }
 // global -> shared bulk copy through the TMA unit, completion on an mbarrier.
 // Both addresses 16-byte aligned, bytes a multiple of 16.
 __device__ __forceinline__ void bulk_g2s(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {

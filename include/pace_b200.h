@@ -83,6 +83,18 @@ int pace_kv_pool_bind(pace_kv_pool_t* pool, void* pages_mem, void* meta_mem); /*
 int pace_kv_pool_create(pace_kv_pool_t* pool);  /* cudaMalloc for pages+meta of the filled-in geometry, then reset */
 int pace_kv_pool_destroy(pace_kv_pool_t* pool); /* frees what pace_kv_pool_create allocated */
 int pace_kv_pool_reset(const pace_kv_pool_t* pool, void* stream); /* all slots empty, all pages free */
+/* Sticky status and the kernels' bounded waits.  Every in-kernel wait (on a ring stage, on a result
+ * slot) gives up after about a quarter of a second, raises PACE_DEV_WAIT_TIMEOUT and lets its thread
+ * block return; the first wait of a block to give up also releases the block's other waits, so a block
+ * leaves after one such interval, not one per role.  While the bit stands, every later attention launch
+ * on the pool returns at once without touching its output: the host reads the word
+ * (pace_kv_pool_query), deals with the cause and clears it (pace_kv_pool_clear_status) to restore
+ * service.  (No counterpart in the reference, which has no device.)
+ *
+ * pace_selftest_wait_timeout makes one wait run out on purpose, harmlessly: a one-block kernel waits on
+ * a barrier nobody arrives on for about limit_us microseconds (1 .. 1e6), gives up and raises the bit
+ * on this pool.  For health checks and for testing the host's handling of the bit. */
+int pace_selftest_wait_timeout(const pace_kv_pool_t* pool, int32_t limit_us, void* stream);
 /* Synchronising read of {status bits, free pages, 0, 0}. */
 int pace_kv_pool_query(const pace_kv_pool_t* pool, int32_t out[4], void* stream);
 int pace_kv_pool_clear_status(const pace_kv_pool_t* pool, void* stream);
