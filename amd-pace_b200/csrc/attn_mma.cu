@@ -548,6 +548,21 @@ __global__ void __launch_bounds__(threads_of(UMMA, MT * NS), MT * NS == 4 ? 2 : 
       }
       __syncwarp();
       asm volatile("bar.arrive 2, 64;" ::: "memory");  // the producer picks the two numbers up behind this
+      if (gdc_open) {
+        // Early K/V: the query rows (and the pending rows) may still be on their way from the kernel in
+        // front, so they are not READ before the wait below - but asking L2 for their lines is harmless
+        // whatever that kernel does to them afterwards (L2 is where its writes land), and when they have
+        // been sitting in DRAM it takes a DRAM round trip off the path from that kernel's end to this
+        // launch's first chunk.
+        const int q_rows = min(MR, p.q_len * G);
+        const int r = lane >> 1, sq = r / G, g = r - sq * G;  // two 128-byte lines per row of 128 elements
+        if (r < q_rows && (lane & 1) * 64 < D)
+          asm volatile("prefetch.global.L2 [%0];" ::"l"(p.q + (size_t)b0 * p.q_sb + (size_t)(h0s * G + g) * p.q_sh +
+                                                        (size_t)sq * p.q_ss + (lane & 1) * 64));
+        if (pend && lane >= 28 && (lane & 1) * 64 < D)
+          asm volatile("prefetch.global.L2 [%0];" ::"l"(((lane & 2) ? p.v_pend : p.k_pend) + (size_t)b0 * p.pend_sb +
+                                                        (size_t)h0s * p.pend_sh + (lane & 1) * 64));
+      }
       gdc_wait();  // (early K/V: the page copies above are out; what follows reads the step's own inputs)
       if (lane == 0) PACE_STAMP(7);
       if (qs) {

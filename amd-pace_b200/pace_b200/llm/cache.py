@@ -34,6 +34,7 @@ from typing import List, Optional, Sequence, Tuple, Union
 import torch
 
 from pace_b200 import _C
+from pace_b200 import torch_ops  # noqa: F401  (defines torch.ops.pace_b200.*)
 
 OVER_REMOVE_MSG = "Cannot remove more tokens than available in cache."
 KV_PAGE_TOKENS = 64
@@ -87,6 +88,9 @@ def _stream_ptr(device) -> int:
     return torch.cuda.current_stream(device).cuda_stream
 
 
+_OPS = torch.ops.pace_b200   # every device-side step of this module goes through the dispatcher ops
+
+
 class KVPool:
     """Device memory + descriptor of one paged pool (C struct pace_kv_pool_t)."""
 
@@ -119,6 +123,11 @@ class KVPool:
     @property
     def ref(self):
         return C.byref(self.desc)
+
+    @property
+    def handle(self) -> int:
+        """The pool as the ``torch.ops.pace_b200`` ops name it: the address of its descriptor."""
+        return C.addressof(self.desc)
 
     # -- slots -------------------------------------------------------------
     def alloc_slots(self, n: int) -> List[int]:
@@ -306,21 +315,17 @@ class KVCacheManager:
             return
         layers = sorted(self._pending)
         pool, k_all, v_all = self.pool, self._stage_k, self._stage_v
-        sl, sb, sh, st, _ = k_all.stride()
         lo = 0
-        with torch.cuda.device(pool.device):
-            while lo < len(layers):
-                hi = lo
-                while hi + 1 < len(layers) and layers[hi + 1] == layers[hi] + 1:
-                    hi += 1
-                a, b = layers[lo], layers[hi] + 1
-                # rows that the layers' decode launches have stored themselves need no second copy
-                stored = all(l in self._row_stored for l in range(a, b))
-                _C.check(_C.lib.pace_kv_append_layers(pool.ref, a, b, self.slots_dev.data_ptr(), len(self.slots), 1,
-                                                      None, None if stored else k_all[a].data_ptr(),
-                                                      None if stored else v_all[a].data_ptr(), sl, sb, sh, st,
-                                                      _stream_ptr(pool.device)), "pace_kv_append_layers")
-                lo = hi + 1
+        while lo < len(layers):
+            hi = lo
+            while hi + 1 < len(layers) and layers[hi + 1] == layers[hi] + 1:
+                hi += 1
+            a, b = layers[lo], layers[hi] + 1
+            # rows that the layers' decode launches have stored themselves need no second copy
+            stored = all(l in self._row_stored for l in range(a, b))
+            _OPS.kv_append_layers(pool.handle, pool.pages, pool.meta, a, b, self.slots_dev,
+                                  None if stored else k_all[a:b], None if stored else v_all[a:b])
+            lo = hi + 1
         self._pending.clear()
         self._row_stored.clear()
 
@@ -355,9 +360,7 @@ class KVCacheManager:
         idx = beam_idx.to(device=pool.device, dtype=torch.int64).contiguous()
         if idx.numel() != len(self.slots):
             raise ValueError("beam_idx must have one entry per cached sequence")
-        with torch.cuda.device(pool.device):
-            _C.check(_C.lib.pace_kv_gather(pool.ref, self.slots_dev.data_ptr(), idx.data_ptr(), len(self.slots),
-                                           _stream_ptr(pool.device)), "pace_kv_gather")
+        _OPS.kv_gather(pool.handle, pool.meta, self.slots_dev, idx)
         pool.shared_pages = True
         order = beam_idx.tolist()
         pages = [pool.host_pages[self.slots[j]] for j in order]
@@ -379,10 +382,7 @@ class KVCacheManager:
         pool = self.pool
         if len(live) == self.num_layers:
             scalar, dev = live[0]._remove_args(per_seq)
-            with torch.cuda.device(pool.device):
-                _C.check(_C.lib.pace_kv_truncate(pool.ref, 0, self.num_layers, self.slots_dev.data_ptr(),
-                                                 len(self.slots), scalar, dev, _stream_ptr(pool.device)),
-                         "pace_kv_truncate")
+            _OPS.kv_truncate(pool.handle, pool.meta, 0, self.num_layers, self.slots_dev, scalar, dev)
             for c in live:
                 c._apply_remove(per_seq)
         else:
@@ -521,8 +521,7 @@ class KVCacheBase(ABC):
             need_reserve = ((self.layer == 0 and not mgr.skip_reserve) if static
                             else (grow or (pool.shared_pages and self.layer == 0)))
             if need_reserve:
-                _C.check(_C.lib.pace_kv_reserve(pool.ref, self.layer, mgr.slots_dev.data_ptr(), B, n, nptr, sp),
-                         "pace_kv_reserve")
+                _OPS.kv_reserve(pool.handle, pool.meta, self.layer, mgr.slots_dev, n, n_dev)
         return pool, mgr, nptr, sp, n_dev
 
     def update_cache_rope(self, query: torch.Tensor, key: torch.Tensor, value: torch.Tensor, table_row: torch.Tensor,
@@ -559,18 +558,9 @@ class KVCacheBase(ABC):
         self._ndim = 4
         self.manager.commit()
         pool, mgr, nptr, sp, n_dev = self._begin_append(B, H, n, D, query.device, n_new_per_seq)
-        a = _C.RopeArgs()
-        a.q, (a.q_stride_b, a.q_stride_t, a.q_stride_h) = query.data_ptr(), query.stride()[:3]
-        a.k, (a.k_stride_b, a.k_stride_t, a.k_stride_h) = key.data_ptr(), key.stride()[:3]
-        a.v, (a.v_stride_b, a.v_stride_t, a.v_stride_h) = value.data_ptr(), value.stride()[:3]
-        a.q_out, (a.o_stride_b, a.o_stride_t, a.o_stride_h) = out.data_ptr(), out.stride()[:3]
-        a.table_row, a.row_stride_b = table_row.data_ptr(), table_row.stride(0)
         cos, sin = rope.device_tables(pool.device)
-        a.cos_table, a.sin_table, a.table_rows = cos.data_ptr(), sin.data_ptr(), cos.shape[0]
-        a.rotary_dim, a.gptj_pairs, a.n_q_heads = rope.rotary_dim, 0 if rope.is_neox_style else 1, Hq
-        with torch.cuda.device(pool.device):
-            _C.check(_C.lib.pace_kv_append_rope(pool.ref, self.layer, mgr.slots_dev.data_ptr(), B, n, nptr,
-                                                _C.byref(a), sp), "pace_kv_append_rope")
+        _OPS.kv_append_rope(pool.handle, pool.pages, pool.meta, self.layer, mgr.slots_dev, query, key, value, out,
+                            table_row, cos, sin, rope.rotary_dim, not rope.is_neox_style, n_dev)
         if self.key is None:
             self.key, self.value = PagedKV(self, "k"), PagedKV(self, "v")
         return out.transpose(1, 2), self.key, self.value
@@ -605,11 +595,7 @@ class KVCacheBase(ABC):
             return self._stage_row(key_states, value_states)
         mgr.commit()
         pool, mgr, nptr, sp, n_dev = self._begin_append(B, H, n, D, key_states.device, n_new_per_seq)
-        with torch.cuda.device(pool.device):
-            sb, sh, st, _ = key_states.stride()
-            _C.check(_C.lib.pace_kv_append(pool.ref, self.layer, mgr.slots_dev.data_ptr(), B, n, nptr,
-                                           key_states.data_ptr(), value_states.data_ptr(), sb, sh, st, sp),
-                     "pace_kv_append")
+        _OPS.kv_append(pool.handle, pool.pages, pool.meta, self.layer, mgr.slots_dev, key_states, value_states, n_dev)
         if self.key is None:
             self.key, self.value = PagedKV(self, "k"), PagedKV(self, "v")
         return self.key, self.value
@@ -684,7 +670,7 @@ class KVCacheBase(ABC):
             return (per_seq[0] if per_seq else 0), None
         dev = torch.tensor(per_seq, dtype=torch.int32, device=self.pool.device)
         self._keepalive = dev
-        return 0, dev.data_ptr()
+        return 0, dev
 
     def _apply_remove(self, per_seq: List[int]) -> None:
         self._lens = [have - r for have, r in zip(self._lens, per_seq)]
@@ -702,10 +688,7 @@ class KVCacheBase(ABC):
         self._check_remove(per_seq)
         pool, mgr = self.pool, self.manager
         scalar, dev = self._remove_args(per_seq)
-        with torch.cuda.device(pool.device):
-            _C.check(_C.lib.pace_kv_truncate(pool.ref, self.layer, self.layer + 1, mgr.slots_dev.data_ptr(),
-                                             len(mgr.slots), scalar, dev, _stream_ptr(pool.device)),
-                     "pace_kv_truncate")
+        _OPS.kv_truncate(pool.handle, pool.meta, self.layer, self.layer + 1, mgr.slots_dev, scalar, dev)
         self._apply_remove(per_seq)
 
     # -- gather --------------------------------------------------------------------
@@ -728,9 +711,7 @@ class KVCacheBase(ABC):
         k = torch.empty(B, pool.n_kv_heads, cap, pool.head_dim, dtype=torch.bfloat16, device=pool.device)
         v = torch.empty_like(k)
         if cap:
-            with torch.cuda.device(pool.device):
-                _C.check(_C.lib.pace_kv_read_dense(pool.ref, self.layer, mgr.slots_dev.data_ptr(), B, k.data_ptr(),
-                                                   v.data_ptr(), cap, _stream_ptr(pool.device)), "pace_kv_read_dense")
+            _OPS.kv_read_dense(pool.handle, pool.pages, self.layer, mgr.slots_dev, k, v)
         if self._ndim == 3:
             return k[:, 0], v[:, 0]
         return k, v

@@ -7,6 +7,7 @@ Re-hosts the part of the reference's ``Generator`` (pace/llm/generator.py) that 
   _speculate_tokens                    generator.py:638-667   one draft pass over history + (d-1) placeholders
   _postprocess_speculated_tokens       generator.py:669-713   accept / rollback
   _generate                            generator.py:715-818   the step loop
+  _beam_search                         generator.py:517-636   beams re-ordered every step, the cache with them
 
 What each step does to the caches follows the reference exactly: the draft cache takes
 history + d - 1 tokens and always gives d - 1 back; the target cache takes history + d tokens and
@@ -148,6 +149,53 @@ class Generator:
         self.kv_cache_manager.pool.check_status()
         return GeneratorOutput(output_token_ids=out, lengths=lengths, speculative_stats=stats)
 
+    # -- beam search -----------------------------------------------------------------------------
+    @staticmethod
+    def beam_step(logits: torch.Tensor, beam_scores: torch.Tensor, num_beams: int):
+        """One re-ranking step on the last position's logits ``[B * beams, V]``: every beam's continuations
+        are scored by summed log-probabilities and the best ``beams`` per prompt survive.  Returns
+        ``(beam_idx [B * beams], next_tokens [B * beams], new beam_scores)``; ``beam_idx[i]`` is the row of
+        the batch that row i continues - what the reference hands to
+        ``update_cache_with_beam_indices`` (generator.py:585-610).  Scoring is the length-penalty-free
+        core of the reference's sampler + ``BeamSearchScorer`` pair; EOS handling is not part of it."""
+        n, vocab = logits.shape
+        batch = n // num_beams
+        logp = torch.log_softmax(logits.float(), dim=-1) + beam_scores.view(n, 1)
+        top, flat = logp.view(batch, num_beams * vocab).topk(num_beams, dim=-1)
+        src = torch.div(flat, vocab, rounding_mode="floor")
+        beam_idx = (src + torch.arange(batch, device=logits.device).unsqueeze(1) * num_beams).view(n)
+        return beam_idx, (flat % vocab).view(n), top.reshape(n)
+
+    @torch.inference_mode()
+    def _beam_search(self, inputs: torch.Tensor) -> GeneratorOutput:
+        """Beam search over the paged cache (reference: generator.py:517-636).  Every step the surviving
+        beams are re-ordered and ``KVCacheManager.update_cache_with_beam_indices`` makes the cache follow:
+        on the paged pool that is an index-only kernel (block-table rows and lengths are permuted, pages
+        shared by several beams are reference-counted and copied on the next write), where the reference
+        moves every layer's whole K and V with ``index_select`` (cache.py:161-167)."""
+        nb = self.sampling_config.num_beams
+        ids = inputs.to(self.device).repeat_interleave(nb, dim=0)
+        batch = inputs.shape[0]
+        mask = torch.ones_like(ids)
+        scores = torch.zeros(batch, nb, dtype=torch.float32, device=self.device)
+        scores[:, 1:] = -1e9                      # all beams of a prompt start out identical: only one may win
+        scores = scores.view(-1)
+        for _ in range(self.sampling_config.max_new_tokens):
+            logits = self.model(ids, kv_cache=self.kv_cache_manager, attention_mask=mask).logits[:, -1]
+            beam_idx, tokens, scores = self.beam_step(logits, scores, nb)
+            ids = torch.cat([ids[beam_idx], tokens.unsqueeze(-1)], dim=-1)
+            mask = torch.cat([mask, mask.new_ones(mask.shape[0], 1)], dim=-1)
+            self.kv_cache_manager.update_cache_with_beam_indices(beam_idx)
+            self.trace.append(["target", "gather", beam_idx.tolist()])
+        best = scores.view(batch, nb).argmax(dim=-1) + torch.arange(batch, device=self.device) * nb
+        out = ids[best].cpu()
+        self.kv_cache_manager.pool.check_status()
+        return GeneratorOutput(output_token_ids=out, lengths=[out.shape[1]] * batch, speculative_stats=None)
+
     def generate(self, inputs: torch.Tensor, sampling_config: Optional[SamplingConfig] = None) -> GeneratorOutput:
         self.prepare_for_generate(inputs, sampling_config)
+        if self.sampling_config.num_beams > 1:
+            if self.pard_config is not None:
+                raise ValueError("beam search and PARD speculative decoding do not combine")
+            return self._beam_search(inputs)
         return self._generate(inputs)

@@ -19,6 +19,7 @@ from pace_b200.ops.enum import BackendType, DataType, OperatorType
 from pace_b200.ops.registry import backend_registry
 
 _workspaces: Dict[Tuple[int, int], torch.Tensor] = {}
+_OPS = torch.ops.pace_b200   # defined by pace_b200.torch_ops (imported with the cache module)
 
 
 def workspace(device: torch.device, nbytes: int) -> torch.Tensor:
@@ -118,46 +119,31 @@ def paged_attention(query: torch.Tensor, key: PagedKV, kv_start: Optional[torch.
         raise ValueError("out must be a bf16 [B, Hq, S, D] tensor (any strides, last dim contiguous) on the same device")
     nbytes = _C.lib.pace_attn_workspace_bytes(B, Hq, pool.n_kv_heads, D, S)
     ws = workspace(query.device, nbytes)
-    a = _C.AttnArgs()
-    a.pool = C.pointer(pool.desc)
-    a.layer, a.batch, a.n_q_heads, a.q_len = cache.layer, B, Hq, S
-    # a manager that owns its pool uses slots 0..B-1: NULL tells the kernels so and saves them a dependent load
-    a.seq_ids = None if mgr.identity_slots else mgr.slots_dev.data_ptr()
-    a.kv_start = kv_start.data_ptr() if kv_start is not None else None
-    a.q_lens = q_lens.data_ptr() if q_lens is not None else None
-    a.q = query.data_ptr()
-    a.q_stride_b, a.q_stride_h, a.q_stride_s = query.stride(0), query.stride(1), query.stride(2)
-    a.out = out.data_ptr()
-    a.o_stride_b, a.o_stride_h, a.o_stride_s = out.stride(0), out.stride(1), out.stride(2)
-    a.scale = float(scale) if scale is not None else 1.0 / math.sqrt(D)
-    a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel()
-    a.flags = 0
-    a.max_ctas = int(max_ctas)
+    flags = 0
     if whole_units is None:
         whole_units = S == 1 and even_lengths(cache._lens, pool.n_kv_heads, D, pool.page_tokens, query.device)
     if S == 1 and whole_units:
-        a.flags |= _C.ATTN_WHOLE_UNITS
+        flags |= _C.ATTN_WHOLE_UNITS
     if one_cta_per_sm:
-        a.flags |= _C.ATTN_ONE_CTA_PER_SM
+        flags |= _C.ATTN_ONE_CTA_PER_SM
     if no_early_kv:
-        a.flags |= _C.ATTN_NO_EARLY_KV
+        flags |= _C.ATTN_NO_EARLY_KV
+    k_pend = v_pend = None
     if pending:
-        ks, vs = mgr.staging(cache.layer)
-        a.flags |= _C.ATTN_PENDING_ROW
-        a.k_pending, a.v_pending = ks.data_ptr(), vs.data_ptr()
-        a.pending_stride_b, a.pending_stride_h = ks.stride(0), ks.stride(1)
-    stream = torch.cuda.current_stream(query.device).cuda_stream
-    if pending:
+        k_pend, v_pend = mgr.staging(cache.layer)
+        flags |= _C.ATTN_PENDING_ROW
         mgr._row_stored.add(cache.layer)    # the launch below puts the staged row in its slot of the pool
-    with torch.cuda.device(query.device):
-        if S == 1 and decode_kernel == "cuda":
-            _C.check(_C.lib.pace_attn_decode_cuda_cores(C.byref(a), stream), "pace_attn_decode_cuda_cores")
-        elif S == 1 and decode_kernel != "mma":
-            _C.check(_C.lib.pace_attn_decode(C.byref(a), stream), "pace_attn_decode")
-        elif S <= 64:
-            _C.check(_C.lib.pace_attn_verify(C.byref(a), stream), "pace_attn_verify")
-        else:
-            _C.check(_C.lib.pace_attn_prefill(C.byref(a), stream), "pace_attn_prefill")
+    if S == 1 and decode_kernel == "cuda":
+        op = _OPS.attn_decode_cuda_cores
+    elif S == 1 and decode_kernel != "mma":
+        op = _OPS.attn_decode
+    elif S <= 64:
+        op = _OPS.attn_verify
+    else:
+        op = _OPS.attn_prefill
+    # a manager that owns its pool uses slots 0..B-1: no seq_ids tells the kernels so and saves them a dependent load
+    op(pool.handle, pool.pages, cache.layer, query, out, None if mgr.identity_slots else mgr.slots_dev, kv_start, q_lens,
+       ws, float(scale) if scale is not None else 1.0 / math.sqrt(D), flags, k_pend, v_pend, int(max_ctas))
     return out
 
 

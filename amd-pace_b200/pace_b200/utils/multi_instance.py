@@ -12,9 +12,11 @@ import argparse
 import json
 import math
 import multiprocessing as mp
+import os
 import time
 
-from pace_b200.utils.worker import MultipleProcesses, Worker, box_throughput, shard_requests
+from pace_b200.utils.worker import (Dispatcher, MultipleProcesses, Worker, box_throughput, serve_items,
+                                    shard_requests)
 
 
 class _Cfg:
@@ -45,19 +47,24 @@ def _init_instance(rank, args):
     return {"rank": rank, "server": server, "cfg": cfg}
 
 
-def _serve(state, args, world, out_queue):
+def _serve(state, args, world, in_queue, out_queue):
+    """Takes request shards from the queue until the stop marker: normally its own one, and those of
+    instances that died when the dispatcher hands them out again."""
     import torch
     rank = state["rank"]
     lengths = make_prompt_lengths(args.requests_per_gpu * world, args.min_len, args.max_len, seed=7)
-    mine = shard_requests(len(lengths), world, rank)
-    g = torch.Generator().manual_seed(100 + rank)
-    prompts = [torch.randint(1, args.vocab, (lengths[i],), generator=g) for i in mine]
-    t0 = time.perf_counter()
-    _, stats = state["server"].run(prompts, args.new_tokens)
-    dt = time.perf_counter() - t0
-    # (wave admission separates prefill from decode time; continuous batching interleaves them)
-    out_queue.put((rank, stats.output_tokens, stats.prompt_tokens, dt, getattr(stats, "decode_s", dt),
-                   getattr(stats, "waves", None) or stats.steps))
+
+    def one_shard(shard):
+        mine = shard_requests(len(lengths), world, shard)
+        g = torch.Generator().manual_seed(100 + shard)
+        prompts = [torch.randint(1, args.vocab, (lengths[i],), generator=g) for i in mine]
+        t0 = time.perf_counter()
+        _, stats = state["server"].run(prompts, args.new_tokens)
+        dt = time.perf_counter() - t0
+        # (wave admission separates prefill from decode time; continuous batching interleaves them)
+        return (rank, stats.output_tokens, stats.prompt_tokens, dt, getattr(stats, "decode_s", dt),
+                getattr(stats, "waves", None) or stats.steps)
+    serve_items(rank, in_queue, out_queue, one_shard)
 
 
 def main():
@@ -76,15 +83,32 @@ def main():
     ap.add_argument("--kv-heads", type=int, default=8)
     ap.add_argument("--vocab", type=int, default=128256)
     ap.add_argument("--scheduler", choices=["continuous", "wave"], default="continuous")
+    ap.add_argument("--timeout-s", type=float, default=3600.0, help="give up when the shards are not served by then")
     args = ap.parse_args()
     ctx = mp.get_context("spawn")
-    out = ctx.Queue()
-    workers = [Worker(r, None, _init_instance, (r, args), _serve, (args, args.gpus, out), device_index=r, ctx=ctx)
+    inq, out = ctx.Queue(), ctx.Queue()
+    # every instance keeps its own slice of the host cores (the reference gives each instance
+    # physical_cores // instances, examples/multi_instance_pace.py:201-238)
+    try:
+        allowed = sorted(os.sched_getaffinity(0))
+    except AttributeError:
+        allowed = []
+    per = len(allowed) // args.gpus if args.gpus else 0
+    cores = [allowed[r * per:(r + 1) * per] if per else None for r in range(args.gpus)]
+    workers = [Worker(r, cores[r], _init_instance, (r, args), _serve, (args, args.gpus, inq, out), device_index=r, ctx=ctx)
                for r in range(args.gpus)]
     pool = MultipleProcesses(workers)
     pool.run()
-    results = [out.get() for _ in range(args.gpus)]
-    pool.join()
+    # one work item per instance: its shard of the requests; a dead instance's shard goes to a survivor
+    disp = Dispatcher(pool, inq, out, list(range(args.gpus)), poll_s=1.0)
+    by_shard = disp.run(timeout_s=args.timeout_s)
+    pool.join(60)
+    # per instance: tokens and seconds summed over the shards it served
+    per_rank = {}
+    for r in by_shard.values():
+        acc = per_rank.setdefault(r[0], [r[0], 0, 0, 0.0, 0.0, 0])
+        acc[1] += r[1]; acc[2] += r[2]; acc[3] += r[3]; acc[4] += r[4]; acc[5] += r[5]
+    results = [tuple(v) for v in per_rank.values()]
     agg, ref_style = box_throughput([(r[1], r[3]) for r in results], args.gpus)
     decode_tps = sum(r[1] for r in results) / max(r[4] for r in results)
     print(json.dumps({"n_gpus": args.gpus, "requests": args.requests_per_gpu * args.gpus,
@@ -92,7 +116,7 @@ def main():
                       "box_output_tokens_per_s": agg, "reference_style_tokens_per_s": ref_style,
                       "box_decode_tokens_per_s": decode_tps, "scheduler": args.scheduler,
                       "steps_or_waves_per_gpu": [r[5] for r in sorted(results)],
-                      "failed_workers": pool.failed()}))
+                      "failed_workers": pool.failed(), "requeued_shards": disp.requeued}))
 
 
 if __name__ == "__main__":

@@ -79,8 +79,84 @@ class MultipleProcesses:
             w.join(timeout)
 
     def failed(self) -> List[int]:
-        """Workers that exited abnormally (the dispatcher re-queues what they held)."""
+        """Workers that exited abnormally (``Dispatcher`` hands out again what they held)."""
         return [w.worker_id for w in self.workers if w.exitcode not in (0, None)]
+
+    def alive(self) -> List[int]:
+        return [w.worker_id for w in self.workers if w.exitcode is None]
+
+
+def serve_items(worker_id: int, ip_queue, op_queue, fn: Callable) -> None:
+    """A worker's loop under a ``Dispatcher``: take an item, say so, work on it, report the result."""
+    while True:
+        item = ip_queue.get()
+        if item is None:
+            return
+        op_queue.put(("take", worker_id, item, None))
+        op_queue.put(("done", worker_id, item, fn(item)))
+
+
+class Dispatcher:
+    """Hands work items (request shards, batch indices) to the workers through a queue and collects
+    one result per item.  The reference fills a queue and joins it
+    (examples/multi_instance_pace.py:204-238), which waits for ever when a worker dies with an item in
+    hand; here every wait has a time limit, dead workers are noticed between polls, and the items a
+    dead worker had taken are handed out again to the survivors.  An item lost between the queue and
+    its worker's announcement is found when the survivors fall idle.  Results are kept once per item
+    (the first to arrive), so handing an item out twice is harmless."""
+
+    def __init__(self, pool: MultipleProcesses, ip_queue, op_queue, items: Sequence, poll_s: float = 0.5):
+        self.pool, self.ip, self.op = pool, ip_queue, op_queue
+        self.items = list(items)
+        self.poll_s = poll_s
+        self.requeued: List = []
+
+    def run(self, timeout_s: Optional[float] = None) -> dict:
+        import queue as _queue
+        import time as _time
+        for it in self.items:
+            self.ip.put(it)
+        results: dict = {}
+        holding = {w.worker_id: set() for w in self.pool.workers}
+        buried = set()
+        deadline = None if timeout_s is None else _time.monotonic() + timeout_s
+        idle_polls = 0
+        while len(results) < len(self.items):
+            try:
+                kind, wid, item, res = self.op.get(timeout=self.poll_s)
+                idle_polls = 0
+                if kind == "take":
+                    holding[wid].add(item)
+                else:
+                    holding[wid].discard(item)
+                    results.setdefault(item, res)
+                continue
+            except _queue.Empty:
+                idle_polls += 1
+            for wid in self.pool.failed():
+                if wid in buried:
+                    continue
+                buried.add(wid)
+                for item in sorted(holding[wid]):
+                    if item not in results:
+                        self.requeued.append(item)
+                        self.ip.put(item)
+                holding[wid].clear()
+            alive = self.pool.alive()
+            if not alive:
+                raise RuntimeError(f"every worker has exited with {len(self.items) - len(results)} items undone")
+            # survivors idle, nothing announced, items still undone: one was lost on its way to a worker that died
+            if buried and idle_polls >= 4 and not any(holding[w] for w in alive):
+                for item in self.items:
+                    if item not in results and item not in self.requeued:
+                        self.requeued.append(item)
+                        self.ip.put(item)
+                idle_polls = 0
+            if deadline is not None and _time.monotonic() > deadline:
+                raise TimeoutError(f"{len(self.items) - len(results)} items undone after {timeout_s} s")
+        for _ in self.pool.alive():
+            self.ip.put(None)
+        return results
 
 
 # ---- request sharding and throughput accounting -----------------------------------------------

@@ -131,3 +131,68 @@ def test_batched_pard_with_forced_bernoulli_acceptance():
         assert [r[b] for r in removes_t] == [s["target_remove"] for s in tr]
     assert gen.kv_cache_manager.pool.seq_len()[0, :B].tolist() == gen.kv_cache_manager[0].seq_lens
     assert 1.0 < out.speculative_stats.mean_accepted_tokens < d
+
+
+def _golden_model(case):
+    from pace_b200.llm.models.llama import LlamaForCausalLM
+    cfg = Cfg(**case["cfg"], pad_token_id=0)
+    m = LlamaForCausalLM(cfg).to(torch.bfloat16)
+    m.load_state_dict(case["state"], strict=True)
+    return m.to(DEV).eval(), cfg
+
+
+def test_beam_loop_follows_the_reference_run():
+    """The reference model and the reference cache manager were driven through a 3-beam search on the CPU
+    (tests/golden/make_golden_beam.py: the cache follows the beams by index_select of every layer's K/V).
+    Teacher-forced with its token ids and beam indices, the paged cache - where the gather only permutes
+    block-table rows and the shared pages are copied on the next write - gives the same logits step by
+    step and ends with the same contents."""
+    from pace_b200.llm.cache import KVCacheManager, KVCacheType
+    case = torch.load(os.path.join(G_DIR, "beam_loop_case.pt"))
+    model, cfg = _golden_model(case)
+    steps, nb = case["steps"], case["num_beams"]
+    P = case["prompts"].shape[1]
+    mgr = KVCacheManager(cfg, P + steps, KVCacheType.BMC)
+    shared_seen = 0
+    with torch.inference_mode():
+        for t in range(steps):
+            ids = case["ids"][t].to(DEV)
+            out = model(ids, kv_cache=mgr, attention_mask=torch.ones_like(ids))
+            got = out.logits[:, -1].float().cpu()
+            err = (got - case["logits"][t]).abs()
+            assert err.max().item() < 2e-2 and err.mean().item() < 2e-3, (t, err.max().item(), err.mean().item())
+            mgr.update_cache_with_beam_indices(case["beam_idx"][t].to(DEV))
+            shared_seen = max(shared_seen, int(mgr.pool.page_ref().max().item()))
+    assert mgr.pool.shared_pages and shared_seen > 1            # beams did share pages, appends did copy on write
+    assert len(mgr) == case["seq_len"]
+    n = case["seq_len"]
+    for layer in range(2):
+        dk, dv = mgr[layer].read_dense()
+        assert (dk[:, :, :n].float().cpu() - case["k_cache"][layer].float()).abs().max().item() < 4e-2
+        assert (dv[:, :, :n].float().cpu() - case["v_cache"][layer].float()).abs().max().item() < 4e-2
+    mgr.pool.check_status()
+
+
+def test_beam_search_generate_calls_the_gather_every_step():
+    from pace_b200.llm.generator import Generator
+    from pace_b200.llm.configs import SamplingConfig
+    case = torch.load(os.path.join(G_DIR, "beam_loop_case.pt"))
+    model, cfg = _golden_model(case)
+    gen = Generator(model)
+    nb, steps = case["num_beams"], 6
+    out = gen.generate(case["prompts"], SamplingConfig(max_new_tokens=steps, num_beams=nb))
+    B, P = case["prompts"].shape
+    assert out.output_token_ids.shape == (B, P + steps) and torch.equal(out.output_token_ids[:, :P], case["prompts"])
+    gathers = [t for t in gen.trace if t[1] == "gather"]
+    assert len(gathers) == steps and all(len(g[2]) == B * nb for g in gathers)
+    # every beam index names a beam of the same prompt
+    for g in gathers:
+        assert all(i // nb == j // nb for j, i in enumerate(g[2]))
+    # the first step starts from identical beams: all survivors continue beam 0 of their prompt, as in the reference run
+    assert gathers[0][2] == case["beam_idx"][0].tolist()
+    assert gen.kv_cache_manager[0].seq_lens == [P + steps] * (B * nb)
+    # the re-ranking itself, against the recorded step of the reference run (CPU arithmetic on recorded logits)
+    scores = torch.zeros(B, nb)
+    scores[:, 1:] = -1e9
+    bi, tok, _ = Generator.beam_step(case["logits"][0], scores.view(-1), nb)
+    assert torch.equal(bi, case["beam_idx"][0]) and torch.equal(tok, case["tokens"][0])

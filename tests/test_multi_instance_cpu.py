@@ -7,8 +7,8 @@ import time
 import pytest
 import torch
 
-from pace_b200.utils.worker import (MultipleProcesses, Worker, box_throughput, fill_queue, reduce_step_time,
-                                    shard_requests)
+from pace_b200.utils.worker import (Dispatcher, MultipleProcesses, Worker, box_throughput, fill_queue,
+                                    reduce_step_time, serve_items, shard_requests)
 
 
 def test_shards_cover_every_request_once():
@@ -70,6 +70,7 @@ def _serve(state, ip_queue, op_queue, die_on):
         ip_queue.task_done()
 
 
+@pytest.mark.timeout(300)
 def test_workers_pull_batches_and_a_dead_worker_is_noticed():
     ctx = mp.get_context("spawn")
     ip, op = ctx.JoinableQueue(), ctx.Queue()
@@ -91,3 +92,54 @@ def test_workers_pull_batches_and_a_dead_worker_is_noticed():
         assert done == list(range(8))
     agg, _ = box_throughput([(t, s) for _, _, t, s in got], instances=2)
     assert agg > 0
+
+
+def _serve_dispatched(state, ip_queue, op_queue):
+    seen = []
+
+    def work(item):
+        seen.append(item)
+        if state["id"] == 0 and len(seen) == 2:
+            time.sleep(0.3)                                # (its announcement of the item has left the process by now)
+            os._exit(17)                                   # worker 0 is lost with its second item in hand
+        time.sleep(0.05)
+        return (state["id"], item * item)
+    serve_items(state["id"], ip_queue, op_queue, work)
+
+
+@pytest.mark.timeout(300)
+def test_dispatcher_hands_a_dead_workers_item_out_again():
+    """A worker process dies on the host between two items (exit, no GPU involved): the dispatcher
+    notices, hands the item it held to the survivor, and every item gets its one result; no wait is
+    without a time limit."""
+    ctx = mp.get_context("spawn")
+    ip, op = ctx.Queue(), ctx.Queue()
+    workers = [Worker(i, None, _init, (i,), _serve_dispatched, (ip, op), device_index=None, ctx=ctx) for i in range(2)]
+    pool = MultipleProcesses(workers)
+    pool.run()
+    disp = Dispatcher(pool, ip, op, list(range(8)), poll_s=0.2)
+    t0 = time.monotonic()
+    results = disp.run(timeout_s=120)
+    assert time.monotonic() - t0 < 60
+    pool.join(30)
+    assert sorted(results) == list(range(8))
+    assert all(results[i][1] == i * i for i in range(8))
+    assert pool.failed() == [0]
+    assert len(disp.requeued) >= 1                          # what worker 0 held when it died
+    assert all(results[i][0] == 1 for i in disp.requeued)   # ... was served by the survivor
+
+
+def _serve_nothing(state, ip_queue, op_queue):
+    os._exit(3)
+
+
+@pytest.mark.timeout(300)
+def test_dispatcher_gives_up_when_every_worker_is_gone():
+    ctx = mp.get_context("spawn")
+    ip, op = ctx.Queue(), ctx.Queue()
+    workers = [Worker(i, None, _init, (i,), _serve_nothing, (ip, op), device_index=None, ctx=ctx) for i in range(2)]
+    pool = MultipleProcesses(workers)
+    pool.run()
+    with pytest.raises(RuntimeError, match="every worker has exited"):
+        Dispatcher(pool, ip, op, [0, 1, 2], poll_s=0.2).run(timeout_s=60)
+    pool.join(30)
