@@ -40,7 +40,7 @@ def beam_step(logits, beam_scores, num_beams):
 
 def main():
     ref = ref_loader.load()
-    cfg = tiny_llama_config(layers=2, hidden=128, heads=4, kv_heads=2, ffn=256, vocab=64)
+    cfg = tiny_llama_config(layers=2, hidden=128, heads=2, kv_heads=1, ffn=256, vocab=64)
     model = build_ref_llama(ref, cfg, seed=21)
     g = torch.Generator().manual_seed(22)
     B, nb, P, steps = 2, 3, 70, 12            # 70-token prompts: the beams share a full 64-token page and a partial one

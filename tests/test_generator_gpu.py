@@ -190,7 +190,7 @@ def test_beam_search_generate_calls_the_gather_every_step():
         assert all(i // nb == j // nb for j, i in enumerate(g[2]))
     # the first step starts from identical beams: all survivors continue beam 0 of their prompt, as in the reference run
     assert gathers[0][2] == case["beam_idx"][0].tolist()
-    assert gen.kv_cache_manager[0].seq_lens == [P + steps] * (B * nb)
+    assert gen.kv_cache_manager[0].seq_lens == [P + steps - 1] * (B * nb)   # the last token is never fed back
     # the re-ranking itself, against the recorded step of the reference run (CPU arithmetic on recorded logits)
     scores = torch.zeros(B, nb)
     scores[:, 1:] = -1e9
