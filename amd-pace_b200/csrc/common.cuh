@@ -65,7 +65,8 @@ struct KVView {
   const __nv_bfloat16* k;       // base of this layer's K pages
   const __nv_bfloat16* v;       // base of this layer's V pages
   const int32_t* block_table;   // [max_seqs][max_pages_per_seq] or nullptr (page = slot)
-  const int32_t* seq_ids;       // [batch] or nullptr (slot = batch index)
+  const int32_t* seq_ids;       // [batch] or nullptr (slot = slot_base + batch index)
+  int32_t slot_base;            // first slot of a launch that covers a slice of an unlisted batch
   const int32_t* seq_len;       // this layer's [max_seqs] lengths or nullptr (use fixed_len)
   int32_t* status;              // sticky device status word or nullptr
   int32_t fixed_len;
@@ -86,6 +87,7 @@ inline KVView make_view(const pace_kv_pool_t* p, int layer, const int32_t* seq_i
   v.v = base + ((size_t)layer * 2 + 1) * region;
   v.block_table = p->block_table;
   v.seq_ids = seq_ids;
+  v.slot_base = 0;
   v.seq_len = p->seq_len + (size_t)layer * p->max_seqs;
   v.status = p->status;
   v.fixed_len = 0;
@@ -106,7 +108,7 @@ __device__ __forceinline__ void raise_status(int32_t* status, int bits) {
 
 // slot of batch row b, or -1 when out of range (status raised)
 __device__ __forceinline__ int view_slot(const KVView& kv, int b) {
-  int s = kv.seq_ids ? kv.seq_ids[b] : b;
+  int s = kv.seq_ids ? kv.seq_ids[b] : b + kv.slot_base;
   if (s < 0 || s >= kv.max_seqs) {
     raise_status(kv.status, PACE_DEV_BAD_INDEX);
     return -1;

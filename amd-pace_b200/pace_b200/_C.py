@@ -56,7 +56,9 @@ class RopeArgs(C.Structure):
                 ("q_out", C.c_void_p), ("o_stride_b", C.c_int64), ("o_stride_t", C.c_int64),
                 ("o_stride_h", C.c_int64), ("table_row", C.c_void_p), ("row_stride_b", C.c_int64),
                 ("cos_table", C.c_void_p), ("sin_table", C.c_void_p), ("table_rows", C.c_int32),
-                ("rotary_dim", C.c_int32), ("gptj_pairs", C.c_int32), ("n_q_heads", C.c_int32)]
+                ("rotary_dim", C.c_int32), ("gptj_pairs", C.c_int32), ("n_q_heads", C.c_int32),
+                ("k_stage", C.c_void_p), ("v_stage", C.c_void_p), ("stage_stride_b", C.c_int64),
+                ("stage_stride_h", C.c_int64), ("stage_stride_t", C.c_int64)]
 
 
 byref = C.byref

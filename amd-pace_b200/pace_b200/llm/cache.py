@@ -556,11 +556,18 @@ class KVCacheBase(ABC):
         if table_row.shape != (B, n) or table_row.dtype != torch.int32 or table_row.stride(1) != 1:
             raise ValueError("table_row must be an int32 [B, n] tensor")
         self._ndim = 4
-        self.manager.commit()
+        mgr = self.manager
+        staged = mgr.defer_appends and n == 1 and n_new_per_seq is None
+        if not staged or self.pending:
+            mgr.commit()     # a multi-token append, or a second token for this layer: the pool has to be up to date
         pool, mgr, nptr, sp, n_dev = self._begin_append(B, H, n, D, query.device, n_new_per_seq)
         cos, sin = rope.device_tables(pool.device)
+        ks, vs = mgr.staging(self.layer) if staged else (None, None)
         _OPS.kv_append_rope(pool.handle, pool.pages, pool.meta, self.layer, mgr.slots_dev, query, key, value, out,
-                            table_row, cos, sin, rope.rotary_dim, not rope.is_neox_style, n_dev)
+                            table_row, cos, sin, rope.rotary_dim, not rope.is_neox_style, n_dev, ks, vs)
+        if staged:           # the rotated key and the value sit in the staging rows; the decode launch takes them along
+            mgr._pending.add(self.layer)
+            mgr._row_stored.discard(self.layer)
         if self.key is None:
             self.key, self.value = PagedKV(self, "k"), PagedKV(self, "v")
         return out.transpose(1, 2), self.key, self.value

@@ -15,7 +15,6 @@ Differences that come from the path being on the GPU:
     batched speculative decoding needs; ``forward`` is the reference signature on top of it.
 """
 import math
-import os
 from typing import List, Optional, Sequence
 
 import torch
@@ -66,8 +65,7 @@ class FusedRope:
         self.op, self.table_row = op, table_row
 
 
-# PACE_FUSED_ROPE=0 keeps RoPE as separate elementwise ops in front of the append (A/B checks)
-FUSED_ROPE = os.environ.get("PACE_FUSED_ROPE", "1") != "0"
+FUSED_ROPE = True     # RoPE fused into the append kernel; False keeps it as separate elementwise ops (tests compare the two)
 
 
 class LlamaAttention(nn.Module):
@@ -184,12 +182,14 @@ class LlamaModel(nn.Module):
             q_lens = torch.tensor(list(n_new), dtype=torch.int32, device=new_ids.device)
         for idx, layer in enumerate(self.layers):
             hidden = layer(hidden, rope, kv_cache[idx], kv_start, n_new, q_lens)
+        kv_cache.commit()        # deferred decode appends: one launch advances every layer (a no-op otherwise)
         return self.norm(hidden)
 
     def forward_packed(self, tokens: torch.Tensor, pk: "Packed", kv_cache: KVCacheManager) -> torch.Tensor:
         hidden = self.embed_tokens(tokens)
         for idx, layer in enumerate(self.layers):
             hidden = layer.forward_packed(hidden, pk, kv_cache[idx])
+        kv_cache.commit()
         return self.norm(hidden)
 
 

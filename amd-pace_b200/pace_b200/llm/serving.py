@@ -137,6 +137,9 @@ class BatchStats:
     seconds: float = 0.0
     max_running: int = 0
     padded_tokens: int = 0            # token rows that went through the model in total
+    kv_bytes_read: int = 0            # K/V bytes the attention launches had to read (every layer, GQA, bf16)
+    kv_bytes_written: int = 0         # K/V bytes appended
+    admissions: int = 0               # steps in which at least one waiting request took a free slot
 
 
 class ContinuousBatcher:
@@ -201,8 +204,12 @@ class ContinuousBatcher:
         torch.cuda.synchronize(self.device)
         t0 = time.perf_counter()
         # the manager's batch is every slot, from the first pass on
+        cfg = self.model.config
+        row_bytes = cfg.num_hidden_layers * 2 * cfg.num_key_value_heads * (cfg.hidden_size // cfg.num_attention_heads) * 2
         while waiting or any(s is not None for s in self.slots):
+            n_wait = len(waiting)
             self._admit(waiting)
+            stats.admissions += int(len(waiting) < n_wait)
             counts = [0] * B
             budget = self.max_step_tokens
             for b, s in enumerate(self.slots):          # decoding sequences first: one token each
@@ -224,6 +231,12 @@ class ContinuousBatcher:
                 else:
                     pieces.append(torch.tensor([s.next_token]))
             tokens = torch.cat(pieces).to(self.device)
+            # a sequence's launch reads every cached row up to and including the step's own tokens, once
+            for b, s in enumerate(self.slots):
+                if s is not None and counts[b]:
+                    cached = s.fed if s.fed < len(s.prompt) else len(s.prompt) + len(s.out) - 1
+                    stats.kv_bytes_read += row_bytes * (cached + counts[b])
+                    stats.kv_bytes_written += row_bytes * counts[b]
             logits = self.model.forward_packed(tokens, counts, self.manager).logits
             picked = logits.float().argmax(dim=-1).tolist()
             done = []

@@ -31,7 +31,7 @@ _DEFS = {
                         "Tensor? k_all, Tensor? v_all) -> ()",
     "kv_append_rope": "(int pool, Tensor(a!) pages, Tensor(b!) meta, int layer, Tensor seq_ids, Tensor q, Tensor k, "
                       "Tensor v, Tensor(c!) q_out, Tensor table_row, Tensor cos, Tensor sin, int rotary_dim, "
-                      "bool gptj_pairs, Tensor? n_new_per_seq) -> ()",
+                      "bool gptj_pairs, Tensor? n_new_per_seq, Tensor(d!)? k_stage, Tensor(e!)? v_stage) -> ()",
     "kv_truncate": "(int pool, Tensor(a!) meta, int layer_begin, int layer_end, Tensor seq_ids, int remove_len, "
                    "Tensor? remove_per_seq) -> ()",
     "kv_gather": "(int pool, Tensor(a!) meta, Tensor seq_ids, Tensor beam_idx) -> ()",
@@ -83,7 +83,7 @@ def _kv_append_layers(pool, pages, meta, layer_begin, layer_end, seq_ids, k_all=
 
 
 def _kv_append_rope(pool, pages, meta, layer, seq_ids, q, k, v, q_out, table_row, cos, sin, rotary_dim, gptj_pairs,
-                    n_new_per_seq=None):
+                    n_new_per_seq=None, k_stage=None, v_stage=None):
     B, n, Hq, _ = q.shape
     a = _C.RopeArgs()
     a.q, (a.q_stride_b, a.q_stride_t, a.q_stride_h) = q.data_ptr(), q.stride()[:3]
@@ -93,6 +93,9 @@ def _kv_append_rope(pool, pages, meta, layer, seq_ids, q, k, v, q_out, table_row
     a.table_row, a.row_stride_b = table_row.data_ptr(), table_row.stride(0)
     a.cos_table, a.sin_table, a.table_rows = cos.data_ptr(), sin.data_ptr(), cos.shape[0]
     a.rotary_dim, a.gptj_pairs, a.n_q_heads = rotary_dim, int(gptj_pairs), Hq
+    if k_stage is not None:      # staged rows [B, H, n, D]: the pool is left as it is
+        a.k_stage, a.v_stage = k_stage.data_ptr(), v_stage.data_ptr()
+        a.stage_stride_b, a.stage_stride_h, a.stage_stride_t = k_stage.stride()[:3]
     with torch.cuda.device(pages.device):
         _C.check(_C.lib.pace_kv_append_rope(_pool(pool), layer, seq_ids.data_ptr(), B, n, _ptr(n_new_per_seq),
                                             C.byref(a), _stream(pages)), "pace_kv_append_rope")

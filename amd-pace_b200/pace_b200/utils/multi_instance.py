@@ -63,7 +63,8 @@ def _serve(state, args, world, in_queue, out_queue):
         dt = time.perf_counter() - t0
         # (wave admission separates prefill from decode time; continuous batching interleaves them)
         return (rank, stats.output_tokens, stats.prompt_tokens, dt, getattr(stats, "decode_s", dt),
-                getattr(stats, "waves", None) or stats.steps)
+                getattr(stats, "waves", None) or stats.steps, getattr(stats, "kv_bytes_read", 0),
+                getattr(stats, "admissions", None) or getattr(stats, "waves", 0))
     serve_items(rank, in_queue, out_queue, one_shard)
 
 
@@ -106,8 +107,9 @@ def main():
     # per instance: tokens and seconds summed over the shards it served
     per_rank = {}
     for r in by_shard.values():
-        acc = per_rank.setdefault(r[0], [r[0], 0, 0, 0.0, 0.0, 0])
-        acc[1] += r[1]; acc[2] += r[2]; acc[3] += r[3]; acc[4] += r[4]; acc[5] += r[5]
+        acc = per_rank.setdefault(r[0], [r[0], 0, 0, 0.0, 0.0, 0, 0, 0])
+        for i in range(1, 8):
+            acc[i] += r[i]
     results = [tuple(v) for v in per_rank.values()]
     agg, ref_style = box_throughput([(r[1], r[3]) for r in results], args.gpus)
     decode_tps = sum(r[1] for r in results) / max(r[4] for r in results)
@@ -115,7 +117,12 @@ def main():
                       "output_tokens": sum(r[1] for r in results), "prompt_tokens": sum(r[2] for r in results),
                       "box_output_tokens_per_s": agg, "reference_style_tokens_per_s": ref_style,
                       "box_decode_tokens_per_s": decode_tps, "scheduler": args.scheduler,
+                      "box_total_tokens_per_s": sum(r[1] + r[2] for r in results) / max(r[3] for r in results),
                       "steps_or_waves_per_gpu": [r[5] for r in sorted(results)],
+                      "admission_steps_per_gpu": [r[7] for r in sorted(results)],
+                      "seconds_per_gpu": [round(r[3], 2) for r in sorted(results)],
+                      "kv_read_gb_per_s_per_gpu": [round(r[6] / r[3] / 1e9, 1) for r in sorted(results)],
+                      "layers": args.layers,
                       "failed_workers": pool.failed(), "requeued_shards": disp.requeued}))
 
 

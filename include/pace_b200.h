@@ -175,6 +175,13 @@ typedef struct {
   int32_t rotary_dim;
   int32_t gptj_pairs;       /* 0: NeoX halves (d, d + rotary_dim / 2); 1: GPT-J pairs (2d, 2d + 1) */
   int32_t n_q_heads;
+  /* Deferred append (decode steps): when k_stage is not NULL the rotated keys and the values go to
+   * these staging rows, bf16 [batch][n_kv_heads][token][head_dim] through element strides, instead of
+   * the pool, and seq_len is left alone - the rows then ride along with the layer's decode launch
+   * (PACE_ATTN_PENDING_ROW) and are committed by pace_kv_append_layers. */
+  void* k_stage;
+  void* v_stage;
+  int64_t stage_stride_b, stage_stride_h, stage_stride_t;
 } pace_rope_args_t;
 int pace_kv_append_rope(const pace_kv_pool_t* pool, int32_t layer, const int32_t* seq_ids, int32_t batch,
                         int32_t n_new, const int32_t* n_new_per_seq, const pace_rope_args_t* rope, void* stream);

@@ -148,6 +148,27 @@ def test_large_tiles_ragged_counts_and_left_padding():
     mgr.pool.check_status()
 
 
+def test_batch_larger_than_one_launch_on_unlisted_slots():
+    """260 sequences x 5 query tiles are more work items than one launch takes: the batch goes out in two
+    launches, and on a manager that owns its pool (slots 0..B-1, no slot list is passed) the second
+    launch has to start at slot 204, not at slot 0."""
+    from pace_b200.llm.cache import KVCacheManager, KVCacheType
+    from pace_b200.ops import MultiHeadAttention
+    B, Hq, Hkv, D, S = 260, 8, 2, 128, 160
+    g = torch.Generator().manual_seed(260)
+    lens = [S + (7 * b) % 60 for b in range(B)]
+    ks = [torch.randn(Hkv, L, D, generator=g).bfloat16().to(DEV) for L in lens]
+    vs = [torch.randn(Hkv, L, D, generator=g).bfloat16().to(DEV) for L in lens]
+    q = torch.randn(B, S, Hq, D, generator=g).bfloat16().to(DEV).transpose(1, 2)
+    mgr = KVCacheManager(Cfg(1), 256, KVCacheType.BMC)
+    K, V = _fill(mgr, 0, ks, vs)
+    assert mgr.identity_slots
+    out = MultiHeadAttention()(q, K, V)
+    for b in (0, 1, 203, 204, 205, 259):
+        _check(out[b], _oracle(q[b:b + 1], ks[b:b + 1], vs[b:b + 1])[0])
+    mgr.pool.check_status()
+
+
 @pytest.mark.parametrize("grid", [1, 5, 37])
 def test_prefill_tiles_under_other_partitions(grid):
     """The same prefill chunk with the chunk stream cut for 1, 5 and 37 CTAs (cut units, partial
@@ -344,12 +365,17 @@ def test_dense_op_matches_reference_restatements(B, N, S, H, L, dtype):
     m = torch.randn(B, 1, 1, L, generator=g).to(dtype)
     out = MultiHeadAttention()(q.to(DEV), k.to(DEV), v.to(DEV), attention_mask=m.to(DEV))
     assert out.dtype == dtype and out.shape == q.shape
-    # the reference pins its op at 1e-1 for bf16 against both of these (test_sdpa.py:113-127);
-    # bf16 inputs are what the kernel computes on, so the fp32 case is compared at bf16 precision
+    # bf16 inputs are what the kernel computes on, so the fp32 case is compared at bf16 precision.
+    # Against NATIVE (fp32 accumulation over bf16 operands, the arithmetic of this kernel): the parity
+    # budget of the paged tests, 2e-2 / 2e-3.
     qb, kb, vb, mb = (t.bfloat16() for t in (q, k, v, m))
-    for want in (sdpa_native(qb, kb, vb, mb), sdpa_jit_restated(qb, kb, vb, mb)):
-        err = (out.float().cpu() - want.float()).abs()
-        assert err.max().item() < 4e-2 and err.mean().item() < 4e-3, (err.max().item(), err.mean().item())
+    _check(out, sdpa_native(qb, kb, vb, mb).float())
+    # Against the restatement of the JIT flavour, which rounds the [S, L] scores and the probabilities to bf16
+    # as that back end's four primitives do (attention_kernels.cpp:218-257): those two roundings alone put it
+    # up to 2e-2 away from NATIVE, so the budget is the sum.  (The reference pins its own op at 1e-1 against
+    # both, test_sdpa.py:113-127.)
+    err = (out.float().cpu() - sdpa_jit_restated(qb, kb, vb, mb).float()).abs()
+    assert err.max().item() < 4e-2 and err.mean().item() < 4e-3, (err.max().item(), err.mean().item())
 
 
 def test_dense_op_full_mask_rows_and_gqa():

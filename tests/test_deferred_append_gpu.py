@@ -282,3 +282,41 @@ def test_append_layers_through_the_c_abi():
                                         kv[1].data_ptr(), sl, sb, sh, st, stream) == _C.PACE_ERR_INVALID
     for m in mgrs:
         m.pool.check_status()
+
+
+def test_model_decode_with_staged_rope_rows_equals_immediate_appends():
+    """The re-hosted Llama decoding token by token: with deferred appends the RoPE kernel stages the rotated
+    key and the value, the layer's decode launch takes them along, and one commit per step advances every
+    layer.  Same logits (to a bf16 unit) and bit-identical caches as with the append inside every layer."""
+    from pace_b200.llm.cache import KVCacheManager, KVCacheType
+    from pace_b200.llm.models.llama import LlamaForCausalLM, random_init_
+
+    class MC:
+        hidden_size, intermediate_size, num_hidden_layers = 512, 512, 3
+        num_attention_heads, num_key_value_heads, vocab_size = 8, 2, 200
+        max_position_embeddings, rope_theta, rms_norm_eps, pad_token_id = 256, 500000.0, 1e-5, 0
+    cfg = MC()
+    model = random_init_(LlamaForCausalLM(cfg).to(torch.bfloat16), 7).to(DEV).eval()
+    g = torch.Generator().manual_seed(5)
+    B, P, steps = 5, 61, 9                       # the decode steps cross a 64-token page boundary
+    ids = torch.randint(1, cfg.vocab_size, (B, P + steps), generator=g).to(DEV)
+    runs = []
+    with torch.inference_mode():
+        for deferred in (False, True):
+            mgr = KVCacheManager(cfg, P + steps + 1, KVCacheType.BMC)
+            mgr.defer_appends = deferred
+            logits = []
+            mask = torch.ones(B, P, dtype=torch.long, device=DEV)
+            for t in range(steps + 1):
+                out = model(ids[:, : P + t], kv_cache=mgr, attention_mask=mask)
+                logits.append(out.logits[:, -1].float().clone())
+                mask = torch.cat([mask, mask.new_ones(B, 1)], dim=-1)
+                assert not mgr._pending                                  # the model's forward commits
+                assert mgr.pool.seq_len()[:, :B].tolist() == [[P + t] * B] * 3
+            runs.append((logits, [mgr[l].read_dense() for l in range(3)], mgr))
+    for a, b in zip(runs[0][0], runs[1][0]):
+        assert (a - b).abs().max().item() < 2e-2
+    for (k0, v0), (k1, v1) in zip(runs[0][1], runs[1][1]):
+        assert torch.equal(k0, k1) and torch.equal(v0, v1)
+    for r in runs:
+        r[2].pool.check_status()

@@ -72,3 +72,47 @@ def test_device_loop_stops_on_eos_and_pads_behind_it():
         assert got[b, :stop].tolist() == row[:stop]
         assert got[b, stop: loop.produced].eq(0).all()
     assert lens[0] <= 7
+
+
+def test_device_loop_teacher_forced_against_the_reference_run(golden_dir):
+    """The recorded run of the reference model on the CPU (tests/golden/llama_case.pt: its state dict, its
+    token ids, its logits after the prompt and after each of three decode steps): the device-resident step
+    is fed the reference's own next token before every replay, so its last-position logits stay comparable
+    with the recorded ones step by step; cache lengths and capacity end as the reference's BMC cache did."""
+    import os
+    from pace_b200.llm.cache import KVCacheManager, KVCacheType
+    from pace_b200.llm.device_loop import GreedyDeviceLoop
+    from pace_b200.llm.models.llama import LlamaForCausalLM
+    case = torch.load(os.path.join(golden_dir, "llama_case.pt"))
+    cfg = Cfg(**case["cfg"], pad_token_id=0)
+    model = LlamaForCausalLM(cfg).to(torch.bfloat16)
+    model.load_state_dict(case["state"], strict=True)
+    model = model.to(DEV).eval()
+    ids, P, steps = case["ids"].to(DEV), case["prompt_len"], case["steps"]
+    B = ids.shape[0]
+
+    def close(got, want, what):
+        err = (got.float().cpu() - want).abs()
+        assert err.max().item() < 2e-2 and err.mean().item() < 2e-3, (what, err.max().item(), err.mean().item())
+
+    mgr = KVCacheManager(cfg, P + steps, KVCacheType.BMC)
+    with torch.inference_mode():
+        out = model(ids[:, :P], kv_cache=mgr, attention_mask=torch.ones(B, P, dtype=torch.long, device=DEV))
+    close(out.logits[:, -1], case["logits"][0], "prompt")
+    # the loop's warm-up step is decode step 1: it is given the reference's token, not the argmax
+    loop = GreedyDeviceLoop(model, mgr, ids[:, P], torch.full((B,), P, device=DEV), max_new_tokens=steps,
+                            keep_logits=True)
+    close(loop.logits, case["logits"][1], "step 1")
+    for t in range(2, steps + 1):
+        loop.cur.copy_(ids[:, P + t - 1: P + t])            # teacher forcing: overwrite the token the step chose
+        loop.graph.replay()
+        torch.cuda.synchronize()
+        close(loop.logits, case["logits"][t], f"step {t}")
+    assert len(mgr) == case["seq_len"] and mgr[0].capacity == case["capacity"]
+    assert mgr.pool.seq_len()[:, :B].tolist() == [[case["seq_len"]] * B] * cfg.num_hidden_layers
+    n = case["seq_len"]
+    for layer in range(2):
+        dk, dv = mgr[layer].read_dense()
+        assert (dk[:, :, :n].float().cpu() - case["k_cache"][layer].float()).abs().max().item() < 4e-2
+        assert (dv[:, :, :n].float().cpu() - case["v_cache"][layer].float()).abs().max().item() < 4e-2
+    mgr.pool.check_status()
