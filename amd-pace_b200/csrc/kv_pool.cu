@@ -638,6 +638,30 @@ __global__ void gather_kernel(pace_kv_pool_t p, const int32_t* __restrict__ seq_
   }
 }
 
+// PARD acceptance, one thread per sequence (a handful of integer comparisons each).
+__global__ void pard_accept_kernel(const int64_t* __restrict__ drafts, const int64_t* __restrict__ target_next,
+                                   const int32_t* __restrict__ n_target, const uint8_t* __restrict__ forced, int batch, int d,
+                                   int32_t* __restrict__ keep_out, int32_t* __restrict__ target_remove,
+                                   int32_t* __restrict__ draft_remove, int64_t* __restrict__ kept) {
+  const int b = blockIdx.x * blockDim.x + threadIdx.x;
+  if (b >= batch) return;
+  const int64_t* dr = drafts + (size_t)b * d;
+  const int64_t* tn = target_next + (size_t)b * (d + 1);
+  const int nt = max(1, min(n_target[b], d + 1));
+  int keep = 0;
+  for (int i = 0; i < d - 1; ++i) {
+    const bool ok = forced ? forced[(size_t)b * (d - 1) + i] != 0 : (i < nt && tn[i] == dr[i]);
+    if (!ok) break;
+    ++keep;
+  }
+  ++keep;  // the target's own token is always kept
+  for (int i = 0; i < keep - 1; ++i) kept[(size_t)b * d + i] = forced ? dr[i] : tn[i];
+  kept[(size_t)b * d + keep - 1] = tn[min(keep - 1, nt - 1)];
+  keep_out[b] = keep;
+  target_remove[b] = d - keep > 0 ? d - keep + 1 : 0;
+  draft_remove[b] = d - 1;
+}
+
 // Dense read-back: one 16-byte vector per thread.
 __global__ void read_dense_kernel(pace_kv_pool_t p, int layer, const int32_t* __restrict__ seq_ids, int batch,
                                   uint4* __restrict__ k_out, uint4* __restrict__ v_out, int cap) {
@@ -950,6 +974,18 @@ int pace_kv_truncate(const pace_kv_pool_t* p, int32_t layer_begin, int32_t layer
                                                                     remove_len, remove_per);
   PACE_LAUNCH_CHECK("truncate_kernel");
   note_pool_write((cudaStream_t)stream);
+  return PACE_OK;
+}
+
+int pace_pard_accept(const int64_t* drafts, const int64_t* target_next, const int32_t* n_target, const uint8_t* forced,
+                     int32_t batch, int32_t d, int32_t* keep, int32_t* target_remove, int32_t* draft_remove, int64_t* kept,
+                     void* stream) {
+  if (!drafts || !target_next || !n_target || !keep || !target_remove || !draft_remove || !kept || batch < 0 || d < 1)
+    return PACE_ERR_INVALID;
+  if (batch == 0) return PACE_OK;
+  pard_accept_kernel<<<(batch + 127) / 128, 128, 0, (cudaStream_t)stream>>>(drafts, target_next, n_target, forced, batch, d,
+                                                                           keep, target_remove, draft_remove, kept);
+  PACE_LAUNCH_CHECK("pard_accept_kernel");
   return PACE_OK;
 }
 

@@ -252,6 +252,10 @@ class KVCacheManager:
         self._stage_v: Optional[torch.Tensor] = None
         self._pending: set = set()                     # layers whose newest row is staged, not yet committed
         self._row_stored: set = set()                  # ... and of those, the layers whose row an attention launch has stored
+        # Device-resident counts: appends and rollbacks whose per-sequence counts are CUDA tensors (the
+        # output of a kernel, e.g. PARD acceptance) are launched without the host ever seeing the numbers.
+        # The host mirror of lengths is then out of date until sync_host_mirror() reads the device's back.
+        self.host_mirror_stale = False
         self.cache_objects: List[KVCacheBase] = [
             self.kv_cache_class(max_seq_length, manager=self, layer=i) for i in range(self.num_layers)
         ]
@@ -370,12 +374,39 @@ class KVCacheManager:
             if c._lens:
                 c._lens = [c._lens[j] for j in order]
 
+    def sync_host_mirror(self) -> None:
+        """Reads the device's lengths and page counts back (one synchronisation) after appends or
+        rollbacks with device-resident counts.  The reported BMC capacity is re-derived from the
+        lengths as they are now (the reference's capacity never shrinks on a rollback; a caller that
+        needs that history keeps its counts on the host)."""
+        if self.slots is None:
+            return
+        self.commit()
+        pool = self.pool
+        lens = pool.seq_len()[:, self.slots_dev.long()].cpu().tolist()
+        pages = pool.seq_pages()[self.slots_dev.long()].cpu().tolist()
+        for c, row in zip(self.cache_objects, lens):
+            c._lens = [int(x) for x in row]
+            c._capacity = max(c._capacity, c._capacity_after(max(c._lens))) if c._lens else 0
+        for s_, n in zip(self.slots, pages):
+            pool.host_pages[s_] = int(n)
+        pool.host_free_pages = pool.query()[1]
+        self.host_mirror_stale = False
+
     def remove_cache(self, remove_len) -> None:
-        """Rollback on every layer (cache.py:118-123): one kernel, no K/V bytes moved."""
+        """Rollback on every layer (cache.py:118-123): one kernel, no K/V bytes moved.  A CUDA int32
+        tensor of per-sequence counts is consumed on the device (no host check: over-removal raises the
+        pool's PACE_DEV_OVER_REMOVE bit instead of the ValueError)."""
         live = [c for c in self.cache_objects if c.key is not None]
         if not live:
             return
         self.commit()
+        if isinstance(remove_len, torch.Tensor) and remove_len.is_cuda:
+            if remove_len.dtype != torch.int32 or remove_len.numel() != len(self.slots):
+                raise ValueError("device-resident remove counts must be an int32 tensor with one entry per sequence")
+            _OPS.kv_truncate(self.pool.handle, self.pool.meta, 0, self.num_layers, self.slots_dev, 0, remove_len)
+            self.host_mirror_stale = True
+            return
         per_seq = live[0]._normalise_remove(remove_len)
         for c in live:
             c._check_remove(per_seq)
@@ -447,6 +478,7 @@ class KVCacheBase(ABC):
             manager.identity_slots = False
             manager.defer_appends, manager._stage_k, manager._stage_v, manager._pending = False, None, None, set()
             manager._row_stored = set()
+            manager.host_mirror_stale = False
             manager.cache_objects = [self]
         self.manager = manager
         self.layer = layer
@@ -557,6 +589,25 @@ class KVCacheBase(ABC):
             raise ValueError("table_row must be an int32 [B, n] tensor")
         self._ndim = 4
         mgr = self.manager
+        if isinstance(n_new_per_seq, torch.Tensor):
+            # device-resident counts (int32 [B], each <= n): nothing about them reaches the host.  The first
+            # layer's reservation provides the pages for all layers (they share the block table).
+            if not n_new_per_seq.is_cuda or n_new_per_seq.dtype != torch.int32 or n_new_per_seq.numel() != B:
+                raise ValueError("device-resident counts must be a CUDA int32 tensor with one entry per sequence")
+            mgr.commit()
+            mgr._ensure_pool(B, H, D, query.device)
+            pool = self.pool
+            if not self._lens:
+                self._lens = [0] * B
+            if self.layer == 0:
+                _OPS.kv_reserve(pool.handle, pool.meta, 0, mgr.slots_dev, n, n_new_per_seq)
+            cos, sin = rope.device_tables(pool.device)
+            _OPS.kv_append_rope(pool.handle, pool.pages, pool.meta, self.layer, mgr.slots_dev, query, key, value, out,
+                                table_row, cos, sin, rope.rotary_dim, not rope.is_neox_style, n_new_per_seq, None, None)
+            mgr.host_mirror_stale = True
+            if self.key is None:
+                self.key, self.value = PagedKV(self, "k"), PagedKV(self, "v")
+            return out.transpose(1, 2), self.key, self.value
         staged = mgr.defer_appends and n == 1 and n_new_per_seq is None
         if not staged or self.pending:
             mgr.commit()     # a multi-token append, or a second token for this layer: the pool has to be up to date

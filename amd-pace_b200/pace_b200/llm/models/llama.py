@@ -178,7 +178,9 @@ class LlamaModel(nn.Module):
         else:
             rope = self.rotary_emb(hidden, position_ids)
         q_lens = None
-        if n_new is not None:
+        if isinstance(n_new, torch.Tensor):
+            q_lens = n_new           # device-resident counts: used as they are, by the append and by the attention
+        elif n_new is not None:
             q_lens = torch.tensor(list(n_new), dtype=torch.int32, device=new_ids.device)
         for idx, layer in enumerate(self.layers):
             hidden = layer(hidden, rope, kv_cache[idx], kv_start, n_new, q_lens)
@@ -232,6 +234,19 @@ class LlamaForCausalLM(nn.Module):
         hidden = self.model.forward_tokens(new_ids, kv_cache, position_ids, None, ragged)
         return ModelOutput(logits=self.lm_head(hidden))
 
+
+    def forward_device_ragged(self, new_ids: torch.Tensor, n_new: torch.Tensor, kv_cache: KVCacheManager,
+                              slots: Optional[torch.Tensor] = None) -> ModelOutput:
+        """``forward_ragged`` with the counts on the device: ``n_new`` is a CUDA int32 ``[B]`` tensor (the
+        output of a kernel), positions continue from the lengths the device holds, and nothing is read
+        back - the host never learns how many tokens each sequence took.  The cache must exist already
+        (a prompt pass has run)."""
+        pool = kv_cache.pool
+        base = pool.seq_len()[0].index_select(0, kv_cache.slots_dev.long()).long().unsqueeze(1)
+        position_ids = base + torch.arange(new_ids.shape[1], device=new_ids.device).unsqueeze(0)
+        position_ids.clamp_(max=self.config.max_position_embeddings - 1)
+        hidden = self.model.forward_tokens(new_ids, kv_cache, position_ids, None, n_new)
+        return ModelOutput(logits=self.lm_head(hidden))
 
     # -- packed form used by continuous batching ----------------------------------------------------
     def forward_packed(self, tokens: torch.Tensor, counts: Sequence[int], kv_cache: KVCacheManager) -> ModelOutput:

@@ -35,6 +35,8 @@ _DEFS = {
     "kv_truncate": "(int pool, Tensor(a!) meta, int layer_begin, int layer_end, Tensor seq_ids, int remove_len, "
                    "Tensor? remove_per_seq) -> ()",
     "kv_gather": "(int pool, Tensor(a!) meta, Tensor seq_ids, Tensor beam_idx) -> ()",
+    "pard_accept": "(Tensor drafts, Tensor target_next, Tensor n_target, Tensor? forced, Tensor(a!) keep, "
+                   "Tensor(b!) target_remove, Tensor(c!) draft_remove, Tensor(d!) kept) -> ()",
     "kv_read_dense": "(int pool, Tensor pages, int layer, Tensor seq_ids, Tensor(a!) k_out, Tensor(b!) v_out) -> ()",
 }
 _ATTN = ("(int pool, Tensor(a!) pages, int layer, Tensor q, Tensor(b!) out, Tensor? seq_ids, Tensor? kv_start, "
@@ -113,6 +115,14 @@ def _kv_gather(pool, meta, seq_ids, beam_idx):
                                        _stream(meta)), "pace_kv_gather")
 
 
+def _pard_accept(drafts, target_next, n_target, forced, keep, target_remove, draft_remove, kept):
+    B, d = drafts.shape
+    with torch.cuda.device(drafts.device):
+        _C.check(_C.lib.pace_pard_accept(drafts.data_ptr(), target_next.data_ptr(), n_target.data_ptr(), _ptr(forced), B, d,
+                                         keep.data_ptr(), target_remove.data_ptr(), draft_remove.data_ptr(),
+                                         kept.data_ptr(), _stream(drafts)), "pace_pard_accept")
+
+
 def _kv_read_dense(pool, pages, layer, seq_ids, k_out, v_out):
     with torch.cuda.device(pages.device):
         _C.check(_C.lib.pace_kv_read_dense(_pool(pool), layer, seq_ids.data_ptr(), seq_ids.numel(), k_out.data_ptr(),
@@ -146,7 +156,7 @@ def _attn(entry: str):
 
 _IMPLS = {"kv_reserve": _kv_reserve, "kv_append": _kv_append, "kv_append_layers": _kv_append_layers,
           "kv_append_rope": _kv_append_rope, "kv_truncate": _kv_truncate, "kv_gather": _kv_gather,
-          "kv_read_dense": _kv_read_dense, "attn_decode": _attn("pace_attn_decode"),
+          "kv_read_dense": _kv_read_dense, "pard_accept": _pard_accept, "attn_decode": _attn("pace_attn_decode"),
           "attn_decode_cuda_cores": _attn("pace_attn_decode_cuda_cores"), "attn_verify": _attn("pace_attn_verify"),
           "attn_prefill": _attn("pace_attn_prefill")}
 for _n, _f in _IMPLS.items():

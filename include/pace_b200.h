@@ -195,6 +195,25 @@ int pace_kv_truncate(const pace_kv_pool_t* pool, int32_t layer_begin, int32_t la
                      const int32_t* seq_ids, int32_t batch, int32_t remove_len,
                      const int32_t* remove_per_seq, void* stream);
 
+/* ---- PARD acceptance ---------------------------------------------------------
+ * Reference: Generator._postprocess_speculated_tokens (pace/llm/generator.py:669-713), one sequence
+ * at a time on the host there.  Per sequence b of the batch: accept the leading matches among the
+ * first d - 1 draft tokens (draft i is accepted while target_next[b][i] == drafts[b][i] and
+ * i < n_target[b]; with `forced` given, while forced[b][i] != 0 instead), always keep one more token
+ * (the target's own), and say how far the two caches roll back:
+ *     keep[b]          = 1 + accepted                                  in [1, d]
+ *     target_remove[b] = d - keep + 1  if keep < d,  else 0            (generator.py:696-702)
+ *     draft_remove[b]  = d - 1                                         (generator.py:706)
+ *     kept[b][0 .. keep)  the tokens that join the history: the accepted ones (the target's tokens;
+ *                         the drafts when acceptance is forced) and then target_next[b][min(keep - 1, n_target[b] - 1)]
+ * The arrays feed pace_kv_truncate (remove_per_seq) and the next step's ragged counts directly:
+ * nothing of a speculative step has to come back to the host.  drafts int64 [batch][d], target_next
+ * int64 [batch][d + 1] (n_target[b] of them valid), forced uint8 [batch][d - 1] or NULL, kept int64
+ * [batch][d]; all device. */
+int pace_pard_accept(const int64_t* drafts, const int64_t* target_next, const int32_t* n_target,
+                     const uint8_t* forced, int32_t batch, int32_t d, int32_t* keep, int32_t* target_remove,
+                     int32_t* draft_remove, int64_t* kept, void* stream);
+
 /* ---- beam gather ----------------------------------------------------------
  * Reference: KVCacheBase.update_cache_with_beam_indices (cache.py:161-167):
  * row i of the batch becomes a copy of old row beam_idx[i].  Index-only here: the
