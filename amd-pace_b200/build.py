@@ -13,7 +13,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(HERE)
 CSRC = os.path.join(HERE, "csrc")
 OUT = os.path.join(HERE, "pace_b200", "libpace_b200.so")
-SOURCES = ["kv_pool.cu", "attn_decode.cu", "attn_mma.cu", "attn_api.cu"]
+SOURCES = ["kv_pool.cu", "attn_decode.cu", "attn_mma.cu", "attn_api.cu", "linear_skinny.cu"]
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
          "--use_fast_math", "-Xcompiler", "-fPIC", "-I", os.path.join(ROOT, "include"), "-I", CSRC] + \

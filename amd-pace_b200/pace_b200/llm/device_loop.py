@@ -20,6 +20,7 @@ import torch
 
 from pace_b200.llm.cache import KVCacheManager
 from pace_b200.llm.graph import StepGraph
+from pace_b200.ops.linear import linear
 
 
 class GreedyDeviceLoop:
@@ -51,7 +52,7 @@ class GreedyDeviceLoop:
 
         def one_token():
             hidden = model.model.forward_tokens(self.cur, manager, self.pos, kv_start)
-            last = model.lm_head(hidden)[:, -1].float()
+            last = linear(hidden, model.lm_head.weight)[:, -1].float()
             if self.logits is not None:
                 self.logits.copy_(last)
             nxt = last.argmax(dim=-1)

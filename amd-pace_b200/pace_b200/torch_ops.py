@@ -39,6 +39,7 @@ _DEFS = {
                    "Tensor(b!) target_remove, Tensor(c!) draft_remove, Tensor(d!) kept) -> ()",
     "kv_read_dense": "(int pool, Tensor pages, int layer, Tensor seq_ids, Tensor(a!) k_out, Tensor(b!) v_out) -> ()",
 }
+_DEFS["linear_skinny"] = "(Tensor x, Tensor weight, Tensor(a!) out, Tensor(b!) workspace) -> ()"
 _ATTN = ("(int pool, Tensor(a!) pages, int layer, Tensor q, Tensor(b!) out, Tensor? seq_ids, Tensor? kv_start, "
          "Tensor? q_lens, Tensor(c!) workspace, float scale, int flags, Tensor? k_pending, Tensor? v_pending, "
          "int max_ctas) -> ()")
@@ -123,6 +124,15 @@ def _pard_accept(drafts, target_next, n_target, forced, keep, target_remove, dra
                                          kept.data_ptr(), _stream(drafts)), "pace_pard_accept")
 
 
+def _linear_skinny(x, weight, out, workspace):
+    M, K = x.shape
+    N = weight.shape[0]
+    with torch.cuda.device(x.device):
+        _C.check(_C.lib.pace_linear_skinny(x.data_ptr(), x.stride(0), weight.data_ptr(), weight.stride(0), out.data_ptr(),
+                                           out.stride(0), M, N, K, workspace.data_ptr(), workspace.numel(), None,
+                                           _stream(x)), "pace_linear_skinny")
+
+
 def _kv_read_dense(pool, pages, layer, seq_ids, k_out, v_out):
     with torch.cuda.device(pages.device):
         _C.check(_C.lib.pace_kv_read_dense(_pool(pool), layer, seq_ids.data_ptr(), seq_ids.numel(), k_out.data_ptr(),
@@ -156,7 +166,7 @@ def _attn(entry: str):
 
 _IMPLS = {"kv_reserve": _kv_reserve, "kv_append": _kv_append, "kv_append_layers": _kv_append_layers,
           "kv_append_rope": _kv_append_rope, "kv_truncate": _kv_truncate, "kv_gather": _kv_gather,
-          "kv_read_dense": _kv_read_dense, "pard_accept": _pard_accept, "attn_decode": _attn("pace_attn_decode"),
+          "kv_read_dense": _kv_read_dense, "pard_accept": _pard_accept, "linear_skinny": _linear_skinny, "attn_decode": _attn("pace_attn_decode"),
           "attn_decode_cuda_cores": _attn("pace_attn_decode_cuda_cores"), "attn_verify": _attn("pace_attn_verify"),
           "attn_prefill": _attn("pace_attn_prefill")}
 for _n, _f in _IMPLS.items():

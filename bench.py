@@ -735,6 +735,55 @@ def run_serving(args):
     print(json.dumps(res), flush=True)
 
 
+def run_linear(args):
+    """Side measurement of the weight-streaming linear kernel on the four layer shapes of a
+    Llama-3.1-8B-shaped decode step (batch 32): fused QKV 4096 -> 6144, o_proj 4096 -> 4096, gate+up
+    4096 -> 28672, down 14336 -> 4096.  Several weight matrices per shape are visited round-robin inside
+    one CUDA graph (more bytes than L2 holds, every launch streams from DRAM; consecutive launches overlap
+    the way they do inside a decoder layer); the same chain through the library GEMM beside it."""
+    from pace_b200.ops.linear import linear_skinny as linear
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    peak, _ = measured_hbm_peak()
+    g = torch.Generator(device=dev).manual_seed(3)
+    out = {"workload": "linear", "tokens": 32, "peak_gbs": peak, "shapes": {}}
+    for name, n, k in (("qkv", 6144, 4096), ("o_proj", 4096, 4096), ("gate_up", 28672, 4096), ("down", 4096, 14336)):
+        copies = max(2, int(400e6 // (n * k * 2)) + 1)
+        ws = [(torch.randn(n, k, device=dev, generator=g, dtype=torch.float32) * 0.02).bfloat16() for _ in range(copies)]
+        x = torch.randn(32, k, device=dev, generator=g, dtype=torch.float32).bfloat16()
+        res = {}
+        for impl, fn in (("skinny", linear), ("library", torch.nn.functional.linear)):
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                for w in ws:
+                    fn(x, w)
+            side.synchronize()
+            gr = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(gr, stream=side):
+                for w in ws:
+                    fn(x, w)
+            for _ in range(3):
+                gr.replay()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            reps = 10
+            e0.record()
+            for _ in range(reps):
+                gr.replay()
+            e1.record()
+            torch.cuda.synchronize()
+            res[impl] = e0.elapsed_time(e1) * 1e3 / (reps * copies)
+            del gr
+        nbytes = n * k * 2 + 32 * (n + k) * 2
+        out["shapes"][name] = {"n": n, "k": k, "us_skinny": res["skinny"], "us_library": res["library"],
+                               "gbs_skinny": nbytes / res["skinny"] / 1e3, "frac_skinny": nbytes / res["skinny"] / 1e3 / peak,
+                               "frac_library": nbytes / res["library"] / 1e3 / peak}
+        del ws
+        torch.cuda.empty_cache()
+    print(json.dumps(out), flush=True)
+
+
 def main():
     # stdout carries the JSON line and nothing else: whatever native libraries print to file descriptor 1
     # (NCCL's version banner on some ranks) goes to stderr, Python's own prints keep the real stdout
@@ -752,7 +801,7 @@ def main():
     ap.add_argument("--no-sweep", action="store_true", help="profiling aid: skip the timed blocks at other cache lengths")
     ap.add_argument("--layers", type=int, default=CFG["n_layers"],
                     help="profiling aid: fewer layers = less device memory; the bench line is only valid at 32")
-    ap.add_argument("--workload", default="decode", choices=["decode", "verify", "prefill", "rope_append", "device_loop", "serving"],
+    ap.add_argument("--workload", default="decode", choices=["decode", "verify", "prefill", "rope_append", "device_loop", "serving", "linear"],
                     help="decode = the bench line; verify / prefill = side measurements of the multi-token kernels")
     ap.add_argument("--past", type=int, default=3584, help="prefill side measurement: tokens cached before the chunk")
     ap.add_argument("--head-dim", type=int, default=128, choices=[64, 128])
@@ -767,9 +816,10 @@ def main():
         return
     global RANK_CORES
     RANK_CORES = pin_rank_to_cores(local_rank, world)
-    if args.workload in ("rope_append", "device_loop", "serving"):
+    if args.workload in ("rope_append", "device_loop", "serving", "linear"):
         if rank == 0:
-            {"rope_append": run_rope, "device_loop": run_device_loop, "serving": run_serving}[args.workload](args)
+            {"rope_append": run_rope, "device_loop": run_device_loop, "serving": run_serving,
+             "linear": run_linear}[args.workload](args)
         return
     if args.workload != "decode":
         if rank == 0:

@@ -347,6 +347,22 @@ int pace_attention_dense(const void* q, const void* k, const void* v, const void
                          int32_t mask_rows, void* out, int32_t B, int32_t N, int32_t Nkv, int32_t S, int32_t L,
                          int32_t H, void* workspace, uint64_t workspace_bytes, void* stream);
 
+/* ---- weight-streaming linear layer for decode steps ------------------------------
+ * Reference: the Linear operator's GEMM back ends on a decoder layer's projections and MLP
+ * (pace/ops/backends/tpp.py:19-63, pace/ops/backends/imbps.py:19-92, csrc/ops/libxsmm_linear.cpp:225-241).
+ * y[M][N] = x[M][K] w[N][K]^T, bf16 in and out, fp32 accumulation, no bias; M <= 32 tokens, N and K
+ * multiples of 128 (PACE_ERR_UNSUPPORTED otherwise: larger token counts are compute-bound and belong to
+ * a library GEMM).  Row pitches are in elements (x_stride, w_stride multiples of 8, bases 16-byte
+ * aligned).  `workspace` is pace_linear_workspace_bytes(largest N) bytes of 32-byte aligned device memory, zeroed once
+ * after allocation and not shared by launches that can overlap on the GPU (one per stream); the kernel
+ * leaves it zeroed.  `status` (device, may be NULL) takes PACE_DEV_WAIT_TIMEOUT if a bounded wait runs
+ * out.  Launched as a programmatic dependent: the weights are fetched while the kernel in front still
+ * runs, only x waits for it. */
+uint64_t pace_linear_workspace_bytes(int32_t n_max);
+int pace_linear_skinny(const void* x, int64_t x_stride, const void* w, int64_t w_stride, void* y, int64_t y_stride,
+                       int32_t M, int32_t N, int32_t K, void* workspace, uint64_t workspace_bytes, int32_t* status,
+                       void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -56,3 +56,23 @@ def test_cpu_tensors_are_refused():
     x = torch.zeros(2, 1, 10, 64, dtype=torch.bfloat16)
     with pytest.raises(RuntimeError, match="no CPU path"):
         c.update_cache(x, x, concat_dim=2)
+
+
+def test_dispatcher_ops_are_registered_without_a_gpu():
+    """torch.ops.pace_b200.* (what the cache and attention classes call) exist as soon as the package is
+    imported, each with a CUDA kernel and a meta kernel; called with CPU tensors they raise the dispatcher's
+    own "no kernel for CPU" error rather than computing anything."""
+    import torch
+    import pace_b200.torch_ops  # noqa: F401
+    names = ["kv_reserve", "kv_append", "kv_append_layers", "kv_append_rope", "kv_truncate", "kv_gather",
+             "kv_read_dense", "pard_accept", "linear_skinny", "attn_decode", "attn_decode_cuda_cores",
+             "attn_verify", "attn_prefill"]
+    for n in names:
+        op = getattr(torch.ops.pace_b200, n)
+        assert torch._C._dispatch_has_kernel_for_dispatch_key(f"pace_b200::{n}", "CUDA"), n
+        assert torch._C._dispatch_has_kernel_for_dispatch_key(f"pace_b200::{n}", "Meta"), n
+        assert not torch._C._dispatch_has_kernel_for_dispatch_key(f"pace_b200::{n}", "CPU"), n
+        assert op.default._schema.name == f"pace_b200::{n}"
+    x = torch.zeros(4, 256, dtype=torch.bfloat16)
+    with pytest.raises((NotImplementedError, RuntimeError)):
+        torch.ops.pace_b200.linear_skinny(x, torch.zeros(256, 256, dtype=torch.bfloat16), x.new_zeros(4), x.new_zeros(4, 256))
