@@ -143,8 +143,8 @@ struct SmemPlan {
   int ring, metas, qbuf, mg, res, bars, misc, per_b, prefix, total;
   int res_slot_bytes, n_res, mg_stride;
 };
-// (umma: the tcgen05 variant keeps a swizzled 128-row Q tile instead of the padded Q rows, and needs
-// neither the merge buffer nor the result slots)
+// (umma: the tcgen05 variant keeps its Q tile in tensor memory and needs neither the padded Q rows,
+// the merge buffer nor the result slots)
 __host__ __device__ inline SmemPlan plan_smem(int D, int MT, int NS, int n_stages, int live_max, int batch,
                                               int n_items, bool umma = false) {
   SmemPlan s;
@@ -160,7 +160,7 @@ __host__ __device__ inline SmemPlan plan_smem(int D, int MT, int NS, int n_stage
   // (mma.sync kernels: only the live rows are ever written; a fragment load of the padding rows of the
   // last 8-row group and beyond reads whatever follows in shared memory, which no live row depends on)
   const int q_rows = MR < ((live_max + 7) & ~7) ? MR : ((live_max + 7) & ~7);
-  s.qbuf = umma ? take(MR * D * 2, 1024) : take(q_rows * QS, 128);
+  s.qbuf = umma ? take(16, 16) : take(q_rows * QS, 128);  // (the tcgen05 variant keeps its Q tile in tensor memory)
   s.mg_stride = D + 8;  // floats; the pad spreads the rows of a fragment over the banks
   s.mg = take(umma ? 16 : (NS > 1 ? NS * live_max * (s.mg_stride + 2) * 4 : 16), 16);
   s.n_res = live_max <= 64 ? 2 : 1;
@@ -433,8 +433,8 @@ __global__ void __launch_bounds__(threads_of(UMMA, MT * NS), MT * NS == 4 ? 2 : 
       misc[4] = 0;  // the CTA's abort flag
     }
     if (UMMA && k == 31) {
-      // s_full[4], p_full[4] (one arrival per warp of the group), o_full[2], q_ready, drain[2], pub
-      // (every softmax thread), xch (one arrival per softmax warp, like q_ready), p_free[4]
+      // s_full[2] (+2 unused), p_full[2] and s_free[2] (one arrival per warp of the group), o_full[2],
+      // q_ready, drain[2], pub (every softmax thread), xch (one arrival per softmax warp, like q_ready)
       for (int j = 0; j < 19; ++j)
         mbar_init(&umma_bars[j],
                   (j >= 4 && j < 8) ? 4 : (j == 10 || j == 14) ? 8 : (j == 13 ? kUmmaSoftmaxThreads : 1));
@@ -1014,19 +1014,19 @@ __global__ void __launch_bounds__(threads_of(UMMA, MT * NS), MT * NS == 4 ? 2 : 
     uc.empty_bar = empty_bar;
     uc.s_full = umma_bars;
     uc.p_full = umma_bars + 4;
+    uc.s_free = umma_bars + 6;
     uc.o_full = umma_bars + 8;
     uc.q_ready = umma_bars + 10;
     uc.drain = umma_bars + 11;
     uc.pub = umma_bars + 13;
     uc.xch = umma_bars + 14;
-    uc.p_free = umma_bars + 15;
-    uc.qsw = qbuf;
     uc.tmem_slot = reinterpret_cast<uint32_t*>(misc + 5);
     uc.flag = misc + 6;
     uc.abort = misc + 4;
     uc.n_my = n_my;
     uc.n_stages = n_stages;
     uc.cta = cta;
+    uc.pair_wait = p.live_max >= kUmmaRows;
 #ifdef PACE_TIMING
     uc.trace = trace;
     uc.stamps = stamps;

@@ -7,12 +7,19 @@
 // The chunks of a CTA's range are dealt alternately to two softmax warpgroups (A: even, B: odd).
 // Each group has its own running (max, sum) and O accumulator, so the two never wait for one another
 // while a unit part streams; the two accumulators are merged when the part ends.  Tensor memory:
-//     columns [0, 256)               four score buffers, 128 x 64 fp32; chunk i uses buffer i % 4
+//     columns [0, 64) / [64, 128)    S_A / S_B: the scores of the chunk a group works on, 128 x 64 fp32
+//     columns [128, 160) / [160, 192) P_A / P_B: its probabilities, 128 x 64 bf16 (two per column)
+//     columns [192, 256)             the Q tile, 128 x D bf16 (two elements per column)
 //     columns [256, 384) / [384, 512) O_A / O_B, 128 x D fp32
-// A softmax thread owns one query row (TMEM lane == row): tcgen05.ld the row of S, online softmax in
-// registers, P written over the first 32 columns of the same score buffer as packed bf16 pairs; the
-// second MMA takes it from there as its A operand.  Q sits in shared memory (K-major, 128-byte
-// swizzle) next to the K/V ring.  O is rescaled in TMEM
+// A softmax thread owns one query row (TMEM lane == row): tcgen05.ld the row of S - which hands the
+// score buffer back at once, so the QK of the group's next chunk runs while this one's softmax does -
+// online softmax in registers, P stored to the group's P buffer as packed bf16 pairs once the PV of its
+// previous chunk has completed; the second MMA takes it from there as its A operand.  Q sits in tensor memory as well (each softmax
+// thread stores its own row once per unit part) and is the A operand of the first MMA: with Q in
+// shared memory every chunk re-read the whole 32 KB tile, a third of the SM's shared-memory traffic
+// (Q 32 KB + K 16 KB + V 16 KB read, 32 KB written by the TMA unit per chunk), and shared-memory
+// bandwidth, not the tensor pipe, paced the MMAs (86 cycles per QK instruction against 32).
+// O is rescaled in TMEM
 // only when a row's running maximum grows by more than 2^8 (the result is exact either way:
 // numerator and denominator share whatever maximum was used).
 //
@@ -28,8 +35,8 @@ constexpr int kUmmaSoftmaxThreads = 256;  // two warpgroups
 // the schedulers of the softmax warps that hold a verify tile's live rows, measured the same.)
 constexpr int kUmmaQkWarp = 9, kUmmaPvWarp = 10;
 constexpr int kTmemCols = 512;          // the whole tensor memory of the SM:
-constexpr uint32_t kTmemO = 256;        //   [0, 256) four score buffers, [256, 512) O of group A and B
-constexpr int kScoreBufs = 4;
+constexpr uint32_t kTmemO = 256;        //   [0, 128) S_A S_B, [128, 192) P_A P_B, [192, 256) Q, [256, 512) O_A O_B
+constexpr uint32_t kTmemP = 128, kTmemQ = 192;
 constexpr float kLazyRescale = 8.0f;    // log2 units
 #ifndef PACE_SOFTMAX_BACKOFF_NS
 #define PACE_SOFTMAX_BACKOFF_NS 100
@@ -39,14 +46,13 @@ constexpr unsigned kSoftmaxBackoffNs = PACE_SOFTMAX_BACKOFF_NS;  // a waiting so
 struct UmmaCtx {
   unsigned char* ring;    // [n_stages][K | V] as the TMA boxes land
   const MetaM* metas;
-  unsigned char* qsw;     // Q tile, K-major 128-byte-swizzled: [D/64][128 rows][128 B]
   uint64_t* full_bar;
   uint64_t* empty_bar;
-  uint64_t* s_full;       // [4] per score buffer: QK^T of a chunk has landed in TMEM
-  uint64_t* p_full;       // [4] per score buffer: P is in place (and O has been rescaled); one arrival per warp of the group
-  uint64_t* o_full;       // [2] per group: PV of a chunk has been accumulated
-  uint64_t* q_ready;      // the Q tile of a unit part is in shared memory (one arrival per softmax warp)
-  uint64_t* p_free;       // [4] per score buffer: the PV that read P from it has completed
+  uint64_t* s_full;       // [2] per group: QK^T of its chunk has landed in TMEM
+  uint64_t* s_free;       // [2] per group: every row of S is in registers (one arrival per warp of the group)
+  uint64_t* p_full;       // [2] per group: P is in place (and O has been rescaled); one arrival per warp of the group
+  uint64_t* o_full;       // [2] per group: PV of a chunk has been accumulated (and has read P)
+  uint64_t* q_ready;      // the Q tile of a unit part is in tensor memory (one arrival per softmax warp)
   uint64_t* drain;        // [2] every MMA an issuer warp issued has completed
   uint64_t* pub;          // meeting point of the 256 softmax threads while a cut unit is published
   uint64_t* xch;          // the two groups have posted their (max, sum) of a part (one arrival per warp)
@@ -54,6 +60,7 @@ struct UmmaCtx {
   int* flag;              // "this CTA arrived last" broadcast
   volatile int* abort;
   int n_my, n_stages, cta;
+  bool pair_wait;         // QK issuer: wait for a chunk's pair partner instead of probing for it
 #ifdef PACE_TIMING
   unsigned long long* trace;
   unsigned long long* stamps;
@@ -103,6 +110,27 @@ __device__ __forceinline__ void umma_bf16_ts(uint32_t tmem_d, uint32_t tmem_a, u
       :
       : "r"(tmem_d), "r"(tmem_a), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u)
       : "memory");
+}
+// Blackwell's two-wide fp32 arithmetic and three-input maximum: a row of 64 scores takes 32 instructions
+// for the maximum, 32 for scale-and-shift and 32 for the row sum instead of 64 each - the softmax
+// warps share their schedulers' issue slots with each other and the exp2 unit is the pipe to keep busy.
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ void unpack64(uint64_t v, uint32_t& lo, uint32_t& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=r"(lo), "=r"(hi) : "l"(v));
 }
 __device__ __forceinline__ uint64_t pack64(uint32_t lo, uint32_t hi) {
   uint64_t d;
@@ -179,105 +207,121 @@ __device__ __forceinline__ bool umma_wait(uint64_t* bar, uint32_t parity, volati
 }
 
 
-// ---- the two MMA issuers: one lane of warp 9 issues every QK, one lane of warp 10 every PV ----
-// Chunk i of this CTA's range (counted over the whole range, not per unit part) uses score buffer
-// i % 4 and belongs to softmax group i & 1.  One issuing thread's dependent instruction stream
-// (barrier probes, descriptor arithmetic, a dozen tcgen05.mma per chunk) was what paced the whole
-// pipeline, hence two of them:
-//   QK issuer:  wait K/V of chunk i, wait until PV(i - 4) has left score buffer i % 4, issue QK(i)
-//   PV issuer:  wait P(i), issue PV(i), release the ring stage, the group's O and the score buffer
-// so scores are computed up to four chunks ahead of the softmax warps.  Only one lane runs each
-// loop: votes or shuffles that keep 32 lanes in agreement would only add latency.
+// ---- the two MMA issuers: warp 9 issues every QK, warp 10 every PV ----
+// Chunk i of this CTA's range (counted over the whole range, not per unit part) belongs to softmax
+// group i & 1 and uses that group's score and probability buffers.
+//   QK issuer:  wait K/V of chunk i, wait until the group has taken the scores of its previous chunk
+//               into registers, issue QK(i)
+//   PV issuer:  wait P(i), issue PV(i), release the ring stage and the group's O / P
+// so a group's next scores are computed while it works on the current ones.
 constexpr uint32_t kDescHi = (1024u >> 4) | (1u << 14) | (2u << 29);  // SBO 1024 B, version 1, 128-byte swizzle
 
+// The issuer warps run their loops with all 32 lanes in step and one elected lane issuing: every value
+// an MMA takes (descriptors, tensor-memory addresses) then depends only on votes and loop counters, which
+// the compiler can keep in the uniform datapath the instruction reads its operands from.  With a single
+// lane running the loop they lived in ordinary registers and each instruction paid for moving them
+// over (≈85 cycles per MMA measured, against 32 of tensor-pipe time).
 __device__ __forceinline__ bool issuer_wait(const UmmaCtx& c, uint64_t* bar, uint32_t parity) {
   for (int k = 0; k < (1 << 20); ++k) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if ((k & 15) == 15 && *c.abort) break;
+    if (__all_sync(0xffffffffu, mbar_try_wait(bar, parity))) return true;
+    if ((k & 15) == 15 && __any_sync(0xffffffffu, *c.abort != 0)) break;
   }
   *c.abort = 1;
   return false;
+}
+__device__ __forceinline__ bool issuer_probe(uint64_t* bar, uint32_t parity) {
+  return __all_sync(0xffffffffu, mbar_test_wait(bar, parity));
+}
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(pred));
+  return pred != 0;
 }
 
 template <int D>
 __device__ __forceinline__ void umma_issue_qk(const UmmaCtx& c, uint32_t tmem, int lane) {
   constexpr int HALF_B = kChunk * 128;
   constexpr uint32_t IDESC_QK1 = umma_idesc(kChunk, false), IDESC_QK2 = umma_idesc(2 * kChunk, false);
-  constexpr int QHALF = kUmmaRows * 128;
   // Ring layout: [K column block 0 of every stage][K column block 1 ...][V of every stage].  The K rows
   // of stages s and s + 1 are contiguous, so one set of MMAs with N = 128 computes the scores of two
-  // chunks into two adjacent score buffers whenever neither the ring nor the buffers wrap in between
-  // (half the instructions per key: the issue rate of this thread is what bounds the kernel).
+  // chunks into two adjacent score buffers whenever neither the ring nor the buffers wrap in between.
   // Descriptors differ from one instruction to the next only in the start-address field (units of
   // 16 bytes): everything else is folded into constants.
   const uint32_t k_lo0 = (smem_u32(c.ring) >> 4) | (1u << 16);  // K-major: LBO unused (1)
   const uint32_t k_half = (uint32_t)c.n_stages * (HALF_B >> 4);  // from one 64-column block of K to the next
-  const uint32_t q_lo = (smem_u32(c.qsw) >> 4) | (1u << 16);
-  if (lane == 0) {
-    int s = 0, ph = 0, b = 0, phb = 1;  // ring stage / its phase, score buffer / phase of its previous use
-    int part = 0, left = 0;             // chunks left in the current unit part
-    for (int i = 0; i < c.n_my;) {
+  const uint32_t tQ = tmem + kTmemQ;  // 16 elements of every row per MMA: 8 columns
+  const bool leader = elect_one();
+  int s = 0, ph = 0;       // ring stage / its phase
+  int part = 0, left = 0;  // chunks left in the current unit part
+  int used_a = 0, used_b = 0;  // QKs issued into S_A / S_B
+  for (int i = 0; i < c.n_my;) {
 #ifdef PACE_TIMING
-      const long long cq0 = clock64();
+    const long long cq0 = clock64();
 #endif
-      if (!issuer_wait(c, &c.full_bar[s], ph)) break;
+    if (!issuer_wait(c, &c.full_bar[s], ph)) break;
 #ifdef PACE_TIMING
-      PACE_UCLK(c, 12, i, clock64() - cq0);
-      const long long cq1 = clock64();
+    if (lane == 0) PACE_UCLK(c, 12, i, clock64() - cq0);
+    const long long cq1 = clock64();
 #endif
-      if (left == 0) {  // first chunk of a unit part: its Q tile
-        left = c.metas[s].pad;
-        if (left < 1 || !issuer_wait(c, c.q_ready, part & 1)) {
-          *c.abort = 1;
-          break;
-        }
-        ++part;
+    if (__all_sync(0xffffffffu, left == 0)) {  // first chunk of a unit part: its Q tile
+      left = c.metas[s].pad;
+      if (__any_sync(0xffffffffu, left < 1) || !issuer_wait(c, c.q_ready, part & 1)) {
+        *c.abort = 1;
+        break;
       }
-      // Two chunks with one set of MMAs only when the second one costs no waiting: its K has landed and
-      // its score buffer is free already (probes, not waits: holding the first chunk back for the second
-      // lengthens the time a ring stage stays occupied, which is what bounds short streams like verify).
-      bool two = left >= 2 && s + 1 < c.n_stages && b + 1 < kScoreBufs;
-      {
-        const bool w2 = i >= kScoreBufs;
-        const bool r1 = !two || mbar_test_wait(&c.full_bar[s + 1], ph);
-        const bool r2 = !w2 || mbar_test_wait(&c.p_free[b], phb);
-        const bool r3 = !(two && i + 1 >= kScoreBufs) || mbar_test_wait(&c.p_free[b + 1], phb);
-        two = two && r1 && r3;
-        if (!r2 && !issuer_wait(c, &c.p_free[b], phb)) break;
-      }
-      tc_fence_after();  // the PVs that read P from these buffers are done
-#ifdef PACE_TIMING
-      PACE_UCLK(c, 13, i, clock64() - cq1);
-      const long long ck0 = clock64();
-#endif
-      const uint32_t k_lo = k_lo0 + (uint32_t)s * (HALF_B >> 4);
-      const uint32_t tS = tmem + (uint32_t)b * kChunk;
-      const uint32_t idesc = two ? IDESC_QK2 : IDESC_QK1;
-#pragma unroll
-      for (int kk = 0; kk < D / 16; ++kk)
-        umma_bf16(tS, pack64(q_lo + (kk >> 2) * (QHALF >> 4) + (kk & 3) * 2, kDescHi),
-                  pack64(k_lo + (kk >> 2) * k_half + (kk & 3) * 2, kDescHi), idesc, kk ? 1u : 0u);
-      umma_commit(&c.s_full[b]);
-      if (two) umma_commit(&c.s_full[b + 1]);
-#ifdef PACE_TIMING
-      PACE_UCLK(c, 1, i, clock64() - ck0);
-#endif
-      PACE_UTRACE(c, 8, i);
-      const int n = two ? 2 : 1;
-      i += n;
-      left -= n;
-      s += n;
-      if (s >= c.n_stages) {
-        s = 0;
-        ph ^= 1;
-      }
-      b += n;
-      if (b >= kScoreBufs) {
-        b = 0;
-        phb ^= 1;
+      ++part;
+    }
+    const int g = i & 1;
+    // An even chunk and its odd neighbour with one set of MMAs (N = 128 over S_A and S_B).  Short streams
+    // (verify: mostly padding rows, a dozen chunks) pair only when the second chunk costs no waiting: its K
+    // has landed and group B has taken its previous scores already.
+    bool two = g == 0 && __all_sync(0xffffffffu, left >= 2) && s + 1 < c.n_stages;
+    if (two) {
+      if (c.pair_wait) {
+        // Full tiles (prefill): always pair, and wait for the second chunk.  Both groups then get their
+        // scores at once and work side by side, and this loop's fixed cost (barrier probes, votes, the
+        // commit) is paid once per two chunks; alternating single chunks it paced the whole pipeline.
+        if (!issuer_wait(c, &c.full_bar[s + 1], ph)) break;
+        if (used_b > 0 && !issuer_wait(c, &c.s_free[1], (used_b - 1) & 1)) break;
+      } else {
+        two = issuer_probe(&c.full_bar[s + 1], ph) && (used_b == 0 || issuer_probe(&c.s_free[1], (used_b - 1) & 1));
       }
     }
-    // nothing may still be writing tensor memory when it is handed back
+    const int used_g = g ? used_b : used_a;
+    if (used_g > 0 && !issuer_wait(c, &c.s_free[g], (used_g - 1) & 1)) break;
+    tc_fence_after();  // the tcgen05.ld that read these buffers are done
+#ifdef PACE_TIMING
+    if (lane == 0) PACE_UCLK(c, 13, i, clock64() - cq1);
+    const long long ck0 = clock64();
+#endif
+    const uint32_t k_lo = k_lo0 + (uint32_t)s * (HALF_B >> 4);
+    const uint32_t tS = tmem + (uint32_t)g * kChunk;
+    const uint32_t idesc = two ? IDESC_QK2 : IDESC_QK1;
+    if (leader) {
+#pragma unroll
+      for (int kk = 0; kk < D / 16; ++kk)
+        umma_bf16_ts(tS, tQ + kk * 8, pack64(k_lo + (kk >> 2) * k_half + (kk & 3) * 2, kDescHi), idesc, kk ? 1u : 0u);
+      umma_commit(&c.s_full[g]);
+      if (two) umma_commit(&c.s_full[1]);
+    }
+    __syncwarp();
+#ifdef PACE_TIMING
+    if (lane == 0) PACE_UCLK(c, 1, i, clock64() - ck0);
+    if (lane == 0) PACE_UTRACE(c, 8, i);
+#endif
+    const int n = two ? 2 : 1;
+    if (g == 0) ++used_a;
+    if (g == 1 || two) ++used_b;
+    i += n;
+    left -= n;
+    s += n;
+    if (s >= c.n_stages) {
+      s = 0;
+      ph ^= 1;
+    }
+  }
+  // nothing may still be writing tensor memory when it is handed back
+  if (leader) {
     umma_commit(&c.drain[0]);
     for (int k = 0; k < (1 << 20) && !mbar_try_wait(&c.drain[0], 0); ++k) __nanosleep(64);
   }
@@ -290,54 +334,57 @@ __device__ __forceinline__ void umma_issue_pv(const UmmaCtx& c, uint32_t tmem, i
   constexpr uint32_t IDESC_PV = umma_idesc(D, true);
   // V of stage s sits behind the K blocks of all stages; MN-major: LBO = next 64 columns
   const uint32_t v_lo0 = ((smem_u32(c.ring) + (uint32_t)c.n_stages * KVB) >> 4) | ((uint32_t)(HALF_B >> 4) << 16);
-  if (lane == 0) {
-    int s = 0, ph = 0, b = 0, phb = 0;
-    int left = 0, j = 0;  // chunks left in / done of the current unit part
-    for (int i = 0; i < c.n_my; ++i) {
-      if (left == 0) {  // first chunk of a unit part: how many chunks it has
-        if (!issuer_wait(c, &c.full_bar[s], ph)) break;
-        left = c.metas[s].pad;
-        j = 0;
-        if (left < 1) {
-          *c.abort = 1;
-          break;
-        }
+  const bool leader = elect_one();
+  int s = 0, ph = 0;
+  int left = 0, j = 0;   // chunks left in / done of the current unit part
+  int used_a = 0, used_b = 0;  // PVs issued for group A / B
+  for (int i = 0; i < c.n_my; ++i) {
+    if (__all_sync(0xffffffffu, left == 0)) {  // first chunk of a unit part: how many chunks it has
+      if (!issuer_wait(c, &c.full_bar[s], ph)) break;
+      left = c.metas[s].pad;
+      j = 0;
+      if (__any_sync(0xffffffffu, left < 1)) {
+        *c.abort = 1;
+        break;
       }
-      --left;
+    }
+    --left;
 #ifdef PACE_TIMING
-      const long long cw0 = clock64();
+    const long long cw0 = clock64();
 #endif
-      if (!issuer_wait(c, &c.p_full[b], phb)) break;
-      tc_fence_after();  // P was written with tcgen05.st
+    const int w = i & 1;
+    if (!issuer_wait(c, &c.p_full[w], (w ? used_b : used_a) & 1)) break;
+    tc_fence_after();  // P was written with tcgen05.st
 #ifdef PACE_TIMING
-      PACE_UCLK(c, 3, i, clock64() - cw0);
-      PACE_UTRACE(c, 9, i);
-      const long long ck0 = clock64();
+    if (lane == 0) PACE_UCLK(c, 3, i, clock64() - cw0);
+    if (lane == 0) PACE_UTRACE(c, 9, i);
+    const long long ck0 = clock64();
 #endif
-      const int w = i & 1;
-      const uint32_t v_lo = v_lo0 + (uint32_t)s * (KVB >> 4);
-      const uint32_t tO = tmem + kTmemO + (uint32_t)w * 128, tP = tmem + (uint32_t)b * kChunk;
-      umma_bf16_ts(tO, tP, pack64(v_lo, kDescHi), IDESC_PV, j < 2 ? 0u : 1u);
+    const uint32_t v_lo = v_lo0 + (uint32_t)s * (KVB >> 4);
+    const uint32_t tO = tmem + kTmemO + (uint32_t)w * 128, tP = tmem + kTmemP + (uint32_t)w * 32;
+    const uint32_t acc0 = j < 2 ? 0u : 1u;
+    if (leader) {
+      umma_bf16_ts(tO, tP, pack64(v_lo, kDescHi), IDESC_PV, acc0);
 #pragma unroll
       for (int k = 1; k < 4; ++k)  // 16 keys per instruction
         umma_bf16_ts(tO, tP + k * 8, pack64(v_lo + k * (2048 >> 4), kDescHi), IDESC_PV, 1u);
-      umma_commit(&c.p_free[b]);     // the score buffer may take QK(i + 4)
       umma_commit(&c.empty_bar[s]);  // K and V of this stage have been consumed
-      umma_commit(&c.o_full[w]);
-#ifdef PACE_TIMING
-      PACE_UCLK(c, 2, i, clock64() - ck0);
-#endif
-      PACE_UTRACE(c, 10, i);
-      ++j;
-      if (++s == c.n_stages) {
-        s = 0;
-        ph ^= 1;
-      }
-      if (++b == kScoreBufs) {
-        b = 0;
-        phb ^= 1;
-      }
+      umma_commit(&c.o_full[w]);     // O_w holds the chunk; P_w may be rewritten
     }
+    __syncwarp();
+#ifdef PACE_TIMING
+    if (lane == 0) PACE_UCLK(c, 2, i, clock64() - ck0);
+    if (lane == 0) PACE_UTRACE(c, 10, i);
+#endif
+    if (w) ++used_b;
+    else ++used_a;
+    ++j;
+    if (++s == c.n_stages) {
+      s = 0;
+      ph ^= 1;
+    }
+  }
+  if (leader) {
     umma_commit(&c.drain[1]);
     for (int k = 0; k < (1 << 20) && !mbar_try_wait(&c.drain[1], 0); ++k) __nanosleep(64);
   }
@@ -460,15 +507,19 @@ __device__ __forceinline__ void umma_softmax(const MmaParams& p, const UmmaCtx& 
       const uint4* src = reinterpret_cast<const uint4*>(p.q + (size_t)fin.b * p.q_sb + (size_t)(fin.h * G + g) * p.q_sh +
                                                         (size_t)sq * p.q_ss);
       out_row = p.out + (size_t)fin.b * p.o_sb + (size_t)(fin.h * G + g) * p.o_sh + (size_t)sq * p.o_ss;
-      // each group writes half of the row's 16-byte pieces, at their swizzled places
-      unsigned char* qrow = c.qsw + row * 128;
+      // each group stores half of the row: D / 2 elements = D / 4 columns (a 16-byte piece is four columns)
+      {
+        uint32_t qv[D / 4];
 #pragma unroll
-      for (int k = 0; k < D / 16; ++k) {
-        const int cc = wg * (D / 16) + k;
-        const uint4 v = live ? __ldg(src + cc) : make_uint4(0, 0, 0, 0);
-        *reinterpret_cast<uint4*>(qrow + (cc >> 3) * (MR * 128) + (((cc & 7) ^ (row & 7)) << 4)) = v;
+        for (int k = 0; k < D / 16; ++k) {
+          const uint4 v = live ? __ldg(src + wg * (D / 16) + k) : make_uint4(0, 0, 0, 0);
+          qv[4 * k] = v.x; qv[4 * k + 1] = v.y; qv[4 * k + 2] = v.z; qv[4 * k + 3] = v.w;
+        }
+        const uint32_t tQ = t_lane + kTmemQ + (uint32_t)wg * (D / 4);
+        if constexpr (D == 128) tmem_st32(tQ, qv);
+        else tmem_st16(tQ, qv);
+        tmem_wait_st();
       }
-      fence_proxy_async();  // generic-proxy writes before the tensor core's async-proxy reads
       tc_fence_before();    // (this thread's reads of O for the previous part are done as well)
       __syncwarp();
       if (lane == 0) mbar_arrive(c.q_ready);
@@ -483,8 +534,8 @@ __device__ __forceinline__ void umma_softmax(const MmaParams& p, const UmmaCtx& 
     // neither is a wait for its K/V to land.
     const bool uniform_chunks = p.pages_per_chunk > 0;
     for (int j = j_first; j < n_part; j += 2) {
-      const int i = i0 + j, b = i & (kScoreBufs - 1);
-      const uint32_t tS = t_lane + (uint32_t)b * kChunk;
+      const int i = i0 + j;
+      const uint32_t tS = t_lane + (uint32_t)wg * kChunk, tP = t_lane + kTmemP + (uint32_t)wg * 32;
       int rows = p.chunk_tokens, tok0 = tok0_part + j * p.chunk_tokens;
       if (!uniform_chunks) {
         const int s = i % c.n_stages;
@@ -493,7 +544,7 @@ __device__ __forceinline__ void umma_softmax(const MmaParams& p, const UmmaCtx& 
         tok0 = c.metas[s].tok0;
       }
       if (tid == 0) PACE_UTRACE(c, 4, i);
-      if (!umma_wait(&c.s_full[b], (i / kScoreBufs) & 1, c.abort)) return;
+      if (!umma_wait(&c.s_full[wg], cnt & 1, c.abort)) return;
       tc_fence_after();
       if (tid == 0) PACE_UTRACE(c, 5, i);
 #ifdef PACE_UMMA_NO_SOFTMAX
@@ -506,6 +557,10 @@ __device__ __forceinline__ void umma_softmax(const MmaParams& p, const UmmaCtx& 
         tmem_ld32(tS, sr[0]);
         tmem_ld32(tS + 32, sr[1]);
         tmem_wait_ld();
+        // the scores are in registers: the buffer goes back to the QK issuer at once
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&c.s_free[wg]);
         const int lo = max(0, kvs - tok0), hi = min(rows, lim - tok0);  // visible keys of the chunk: [lo, hi)
         // (Rows of padding need no mask: their Q is zero, their scores are finite and nothing of them
         // is ever stored - a warp of a few live rows would otherwise mask on every chunk.)
@@ -517,7 +572,8 @@ __device__ __forceinline__ void umma_softmax(const MmaParams& p, const UmmaCtx& 
         }
         float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-        for (int k = 0; k < 64; ++k) mx4[k & 3] = fmaxf(mx4[k & 3], __uint_as_float(sr[k >> 5][k & 31]));
+        for (int k = 0; k < 32; ++k)
+          mx4[k & 3] = max3(mx4[k & 3], __uint_as_float(sr[k >> 4][(2 * k) & 31]), __uint_as_float(sr[k >> 4][(2 * k + 1) & 31]));
         const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale;  // scale > 0
         // ---- running maximum; O is rescaled only when some row of the warp moved by more than 2^8 ----
         const bool grow = mx > m_used + kLazyRescale;
@@ -541,28 +597,49 @@ __device__ __forceinline__ void umma_softmax(const MmaParams& p, const UmmaCtx& 
           l *= alpha;
           m_used = m_new;
         }
-        // ---- P = 2^(s * scale - m), row sum, bf16 pairs written over the scores ----
+        // ---- P = 2^(s * scale - m), row sum, bf16 pairs into the group's P buffer ----
+        // (the PV of the group's previous chunk has read the buffer: its completion is o_full's phase)
+        if (cnt > 0) {
+          if (!umma_wait(&c.o_full[wg], (cnt - 1) & 1, c.abort)) return;
+          tc_fence_after();
+        }
         const float ne = (m_used == -INFINITY) ? 0.f : -m_used;
-        float l4[4] = {0.f, 0.f, 0.f, 0.f};
+        const uint64_t scale2 = pack64(__float_as_uint(scale), __float_as_uint(scale));
+        const uint64_t ne2 = pack64(__float_as_uint(ne), __float_as_uint(ne));
+        uint64_t l2[2] = {0ull, 0ull};
 #pragma unroll
         for (int hf = 0; hf < 2; ++hf) {
           uint32_t pk[16];
 #pragma unroll
           for (int k = 0; k < 16; ++k) {
-            const float p0 = fast_exp2(fmaf(__uint_as_float(sr[hf][2 * k]), scale, ne));
-            const float p1 = fast_exp2(fmaf(__uint_as_float(sr[hf][2 * k + 1]), scale, ne));
-            l4[k & 3] += p0 + p1;
+            uint32_t x0, x1;
+            unpack64(fma2(pack64(sr[hf][2 * k], sr[hf][2 * k + 1]), scale2, ne2), x0, x1);
+            const float p0 = fast_exp2(__uint_as_float(x0)), p1 = fast_exp2(__uint_as_float(x1));
+            l2[k & 1] = add2(l2[k & 1], pack64(__float_as_uint(p0), __float_as_uint(p1)));
             pk[k] = f2_to_bf2(p0, p1);
           }
-          tmem_st16(tS + hf * 16, pk);
+          tmem_st16(tP + hf * 16, pk);
         }
-        l += (l4[0] + l4[1]) + (l4[2] + l4[3]);
+        {
+          uint32_t a0, a1, b0, b1;
+          unpack64(l2[0], a0, a1);
+          unpack64(l2[1], b0, b1);
+          l += (__uint_as_float(a0) + __uint_as_float(a1)) + (__uint_as_float(b0) + __uint_as_float(b1));
+        }
         tmem_wait_st();
+      }
+      else {
+        // A warp of padding rows keeps the barriers in step - and in order: its arrival for this chunk's
+        // P must not reach the barrier while the phase of the group's previous chunk is still open
+        // (the scores of the next chunk can be there before the live warps have finished this one).
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&c.s_free[wg]);
+        if (cnt > 0 && !umma_wait(&c.o_full[wg], (cnt - 1) & 1, c.abort)) return;
       }
       if (tid == 0) PACE_UTRACE(c, 6, i);
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&c.p_full[b]);
+      if (lane == 0) mbar_arrive(&c.p_full[wg]);
       if (tid == 0) PACE_UTRACE(c, 7, i);
       ++cnt;
     }
@@ -579,8 +656,7 @@ __device__ __forceinline__ void umma_softmax(const MmaParams& p, const UmmaCtx& 
     const int j_last_mine = ((n_part - 1) & 1) == j_first ? n_part - 1 : n_part - 2;
     const int j_last_other = ((n_part - 1) & 1) == j_first ? n_part - 2 : n_part - 1;
     if (has_mine) {
-      tmem_st2(t_lane + (uint32_t)((i0 + j_last_mine) & (kScoreBufs - 1)) * kChunk + 32, __float_as_uint(m_used),
-               __float_as_uint(l));
+      tmem_st2(t_lane + (uint32_t)wg * kChunk, __float_as_uint(m_used), __float_as_uint(l));
       tmem_wait_st();
     }
     tc_fence_before();
@@ -592,7 +668,7 @@ __device__ __forceinline__ void umma_softmax(const MmaParams& p, const UmmaCtx& 
     float m_o = -INFINITY, l_o = 0.f;
     if (has_other) {
       uint32_t xm, xl;
-      tmem_ld2(t_lane + (uint32_t)((i0 + j_last_other) & (kScoreBufs - 1)) * kChunk + 32, xm, xl);
+      tmem_ld2(t_lane + (uint32_t)(wg ^ 1) * kChunk, xm, xl);
       tmem_wait_ld();
       m_o = __uint_as_float(xm);
       l_o = __uint_as_float(xl);
