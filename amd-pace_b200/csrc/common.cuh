@@ -3,6 +3,8 @@
 
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
+
+#include <cstdio>
 #include <stdint.h>
 
 #include "pace_b200.h"
@@ -248,6 +250,33 @@ __device__ __forceinline__ int load_status_word(const int32_t* status) {
 // True when the word says that an earlier launch ran out of patience: the launches behind it do
 // nothing (and return at once) until the host has cleared the word.
 __device__ __forceinline__ bool pool_gave_up(int status_word) { return (status_word & PACE_DEV_WAIT_TIMEOUT) != 0; }
+// ---- op timing behind PACE_LOG_LEVEL=profile (host side) ----
+// Stands where the reference wraps its operators in PROFILE_PACE_FUNCTION (csrc/core/logging.h:144-212,
+// use at csrc/ops/attention.cpp:24): one line "pace::<name>,<info>,<milliseconds>" per call.  Here the
+// time is the device time between two CUDA events recorded around the entry point's launches; lines are
+// written when the events have completed (the next profiled call, pace_profile_flush or process exit),
+// never by waiting inside the call.  Calls made during a stream capture are not timed.
+bool profile_enabled();
+void profile_begin(const char* name, cudaStream_t stream, cudaEvent_t* e0);
+void profile_end(const char* name, const char* info, cudaStream_t stream, cudaEvent_t e0);
+struct OpTimer {
+  const char* name;
+  cudaStream_t stream;
+  cudaEvent_t e0 = nullptr;
+  char info[96];
+  bool on;
+  OpTimer(const char* n, void* s) : name(n), stream((cudaStream_t)s), on(profile_enabled()) {
+    info[0] = 0;
+    if (on) profile_begin(name, stream, &e0);
+  }
+  ~OpTimer() {
+    if (on && e0) profile_end(name, info, stream, e0);
+  }
+};
+#define PACE_PROFILE(name, stream, ...)                                       \
+  pace::OpTimer pace_op_timer_(name, stream);                                 \
+  if (pace_op_timer_.on) snprintf(pace_op_timer_.info, sizeof(pace_op_timer_.info), __VA_ARGS__)
+
 // global -> shared bulk copy through the TMA unit, completion on an mbarrier.
 // Both addresses 16-byte aligned, bytes a multiple of 16.
 __device__ __forceinline__ void bulk_g2s(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {

@@ -832,6 +832,7 @@ int pace_kv_append(const pace_kv_pool_t* p, int32_t layer, const int32_t* seq_id
     return PACE_ERR_INVALID;
   if (batch == 0 || n_new == 0) return PACE_OK;
   if (!k_new || !v_new) return PACE_ERR_INVALID;
+  PACE_PROFILE("kv_append", stream, "layer=%d batch=%d n_new=%d", layer, batch, n_new);
   // 16-byte vector moves: bases and strides must keep rows 16-byte aligned
   if (((uintptr_t)k_new & 15) || ((uintptr_t)v_new & 15) || (sb & 7) || (sh & 7) || (st & 7)) return PACE_ERR_INVALID;
   const long long warps = (long long)batch * n_new * p->n_kv_heads;
@@ -867,6 +868,8 @@ int pace_kv_append_layers(const pace_kv_pool_t* p, int32_t layer_begin, int32_t 
     return PACE_ERR_INVALID;
   if (batch == 0 || n_new == 0 || layer_begin == layer_end) return PACE_OK;
   const bool lengths_only = !k_new && !v_new;  // the rows are in the pool already
+  PACE_PROFILE("kv_append_layers", stream, "layers=%d..%d batch=%d n_new=%d rows=%d", layer_begin, layer_end, batch, n_new,
+               lengths_only ? 0 : 1);
   if (!lengths_only && (!k_new || !v_new)) return PACE_ERR_INVALID;
   if (!lengths_only &&
       (((uintptr_t)k_new & 15) || ((uintptr_t)v_new & 15) || (sl & 7) || (sb & 7) || (sh & 7) || (st & 7)))
@@ -908,6 +911,7 @@ int pace_kv_append_rope(const pace_kv_pool_t* p, int32_t layer, const int32_t* s
     return PACE_ERR_INVALID;
   if (batch == 0 || n_new == 0) return PACE_OK;
   if (!a->q || !a->k || !a->v || !a->q_out || !a->table_row || !a->cos_table || !a->sin_table) return PACE_ERR_INVALID;
+  PACE_PROFILE("kv_append_rope", stream, "layer=%d batch=%d n_new=%d", layer, batch, n_new);
   if (a->n_q_heads < 1 || a->table_rows < 1 || a->rotary_dim < 16 || a->rotary_dim > p->head_dim || (a->rotary_dim & 15))
     return PACE_ERR_INVALID;
   // 16-byte vector moves: bases and strides must keep rows 16-byte aligned
@@ -970,6 +974,7 @@ int pace_kv_truncate(const pace_kv_pool_t* p, int32_t layer_begin, int32_t layer
     return PACE_ERR_INVALID;
   const int n = batch * (layer_end - layer_begin);
   if (n == 0) return PACE_OK;
+  PACE_PROFILE("kv_truncate", stream, "layers=%d..%d batch=%d", layer_begin, layer_end, batch);
   truncate_kernel<<<(n + 255) / 256, 256, 0, (cudaStream_t)stream>>>(*p, layer_begin, layer_end, seq_ids, batch,
                                                                     remove_len, remove_per);
   PACE_LAUNCH_CHECK("truncate_kernel");
@@ -993,6 +998,7 @@ int pace_kv_gather(const pace_kv_pool_t* p, const int32_t* seq_ids, const int64_
                    void* stream) {
   if (!pool_ok(p) || !seq_ids || !beam_idx || batch < 0 || batch > p->max_seqs) return PACE_ERR_INVALID;
   if (batch == 0) return PACE_OK;
+  PACE_PROFILE("kv_gather", stream, "batch=%d", batch);
   gather_kernel<<<1, 256, 0, (cudaStream_t)stream>>>(*p, seq_ids, beam_idx, batch);
   PACE_LAUNCH_CHECK("gather_kernel");
   note_pool_write((cudaStream_t)stream);

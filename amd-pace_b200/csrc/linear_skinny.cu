@@ -402,6 +402,7 @@ extern "C" int pace_linear_skinny(const void* x, int64_t x_stride, const void* w
     return PACE_ERR_INVALID;
   if (x_stride < K || w_stride < K || y_stride < N) return PACE_ERR_INVALID;
   if (workspace_bytes < pace_linear_workspace_bytes(N)) return PACE_ERR_INVALID;
+  PACE_PROFILE("linear_skinny", stream, "x=[%d,%d] w=[%d,%d]", M, K, N, K);
   CUtensorMap tmW, tmX;
   {
     std::lock_guard<std::mutex> lk(g_wmap_mu);

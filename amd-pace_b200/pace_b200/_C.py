@@ -95,6 +95,8 @@ _SIGS = {
     "pace_attn_decode_static": (C.c_int, [C.POINTER(AttnArgs), C.c_void_p]),
     "pace_attn_verify": (C.c_int, [C.POINTER(AttnArgs), C.c_void_p]),
     "pace_attn_prefill": (C.c_int, [C.POINTER(AttnArgs), C.c_void_p]),
+    "pace_profile_enabled": (C.c_int, []),
+    "pace_profile_flush": (C.c_int, []),
     "pace_linear_workspace_bytes": (C.c_uint64, [C.c_int32]),
     "pace_linear_skinny": (C.c_int, [C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_int32,
                                      C.c_int32, C.c_int32, C.c_void_p, C.c_uint64, C.c_void_p, C.c_void_p]),

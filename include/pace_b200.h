@@ -347,6 +347,19 @@ int pace_attention_dense(const void* q, const void* k, const void* v, const void
                          int32_t mask_rows, void* out, int32_t B, int32_t N, int32_t Nkv, int32_t S, int32_t L,
                          int32_t H, void* workspace, uint64_t workspace_bytes, void* stream);
 
+/* ---- op timing -------------------------------------------------------------------
+ * Reference: PROFILE_PACE_FUNCTION / TimingLogger (csrc/core/logging.h:144-212, used at
+ * csrc/ops/attention.cpp:24), switched on by the environment variable PACE_LOG_LEVEL=profile.
+ * With that value set when the library is loaded, the attention, append, rollback, gather and linear
+ * entry points record a CUDA event on their stream before and after their launches and a line
+ *     [PACE profile] pace::<op>,<shapes>,<milliseconds>
+ * goes to stderr once both events have completed: at a later profiled call, at pace_profile_flush
+ * (which waits for the outstanding ones and returns how many it wrote or dropped) or at process exit.
+ * The time is device time between the two events.  Calls made while their stream is being captured
+ * into a CUDA graph are not timed.  No other value of the variable changes anything. */
+int pace_profile_enabled(void);
+int pace_profile_flush(void);
+
 /* ---- weight-streaming linear layer for decode steps ------------------------------
  * Reference: the Linear operator's GEMM back ends on a decoder layer's projections and MLP
  * (pace/ops/backends/tpp.py:19-63, pace/ops/backends/imbps.py:19-92, csrc/ops/libxsmm_linear.cpp:225-241).

@@ -76,3 +76,20 @@ def test_dispatcher_ops_are_registered_without_a_gpu():
     x = torch.zeros(4, 256, dtype=torch.bfloat16)
     with pytest.raises((NotImplementedError, RuntimeError)):
         torch.ops.pace_b200.linear_skinny(x, torch.zeros(256, 256, dtype=torch.bfloat16), x.new_zeros(4), x.new_zeros(4, 256))
+
+
+def test_profile_switch_follows_the_environment():
+    """PACE_LOG_LEVEL=profile (the reference's switch, README "verbose" table) turns the op timer on; any
+    other value leaves it off.  Read once, when the library is loaded: checked in child processes."""
+    import subprocess
+    import sys
+    code = ("import sys; sys.path.insert(0, %r); from pace_b200 import _C; "
+            "print(_C.lib.pace_profile_enabled(), _C.lib.pace_profile_flush())" % os.path.join(ROOT, "amd-pace_b200"))
+    for value, want in (("profile", "1 0"), ("debug", "0 0"), (None, "0 0")):
+        env = dict(os.environ)
+        env.pop("PACE_LOG_LEVEL", None)
+        if value is not None:
+            env["PACE_LOG_LEVEL"] = value
+        out = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True, timeout=300)
+        assert out.returncode == 0, out.stderr
+        assert out.stdout.strip().splitlines()[-1] == want
