@@ -33,9 +33,12 @@ namespace {
 // Threads of a CTA with nw consumer warps: + producer warp + epilogue warp (tcgen05 variant: + producer
 // warp + two MMA issuer warps).  Eight consumer warps and one CTA per SM, or - decode only - four and
 // two CTAs per SM, so that CTAs of the next launch on the stream move in beside CTAs of this one.
-__host__ __device__ constexpr int threads_of(bool umma, int nw = 8) { return nw * 32 + (umma ? 96 : 64); }
+__host__ __device__ constexpr int threads_of(bool umma, int nw = 8) { return nw * 32 + (umma ? 128 : 64); }
 constexpr int kChunk = 64;
 constexpr int kMaxStagesM = 8;
+#ifndef PACE_UMMA_FULL_TILE_PAIR_MODE
+#define PACE_UMMA_FULL_TILE_PAIR_MODE 0
+#endif
 constexpr int kMaxItems = 1024;
 
 struct MetaM {  // one 64-byte record per ring stage, written by the producer
@@ -1020,13 +1023,14 @@ __global__ void __launch_bounds__(threads_of(UMMA, MT * NS), MT * NS == 4 ? 2 : 
     uc.drain = umma_bars + 11;
     uc.pub = umma_bars + 13;
     uc.xch = umma_bars + 14;
+    uc.drain_b = umma_bars + 15;
     uc.tmem_slot = reinterpret_cast<uint32_t*>(misc + 5);
     uc.flag = misc + 6;
     uc.abort = misc + 4;
     uc.n_my = n_my;
     uc.n_stages = n_stages;
     uc.cta = cta;
-    uc.pair_wait = p.live_max >= kUmmaRows;
+    uc.pair_mode = p.live_max >= kUmmaRows ? PACE_UMMA_FULL_TILE_PAIR_MODE : 1;
 #ifdef PACE_TIMING
     uc.trace = trace;
     uc.stamps = stamps;
@@ -1617,6 +1621,10 @@ int launch_mma(MmaParams& p, const CUtensorMap& tmK, const CUtensorMap& tmV, int
   int ns = kMaxStagesM;
   while (ns >= 2 && plan_smem(D, MT, NS, ns, p.live_max, p.batch, n_items, UMMA).total > budget) --ns;
   if (ns < 2) return PACE_ERR_UNSUPPORTED;
+  // tcgen05 variant on full tiles: one QK covers the chunks of two neighbouring stages; with an odd ring
+  // the last stage has no neighbour, every seventh chunk went alone and the two softmax groups fell out
+  // of step for a thousand cycles each time
+  if (UMMA && PACE_UMMA_FULL_TILE_PAIR_MODE == 2 && p.live_max >= MR && (ns & 1)) --ns;
   p.n_stages = ns;
   const size_t smem_bytes = plan_smem(D, MT, NS, ns, p.live_max, p.batch, n_items, UMMA).total;
   // Early K/V streaming: only the short prologue of whole-unit decode has it, and only when this

@@ -31,9 +31,10 @@ namespace {
 
 constexpr int kUmmaRows = 128;          // query rows per tile (UMMA M)
 constexpr int kUmmaSoftmaxThreads = 256;  // two warpgroups
-// Warps 0-7: softmax; 8: producer; 9: QK issuer; 10: PV issuer.  (Issuers on warps 10 and 11, away from
+// Warps 0-7: softmax; 8: producer; 9: QK issuer (of group A's chunks when the work is split); 10: PV issuer;
+// 11: QK issuer of group B's chunks.  (Issuers on warps 10 and 11, away from
 // the schedulers of the softmax warps that hold a verify tile's live rows, measured the same.)
-constexpr int kUmmaQkWarp = 9, kUmmaPvWarp = 10;
+constexpr int kUmmaQkWarp = 9, kUmmaPvWarp = 10, kUmmaQkWarpB = 11;
 constexpr int kTmemCols = 512;          // the whole tensor memory of the SM:
 constexpr uint32_t kTmemO = 256;        //   [0, 128) S_A S_B, [128, 192) P_A P_B, [192, 256) Q, [256, 512) O_A O_B
 constexpr uint32_t kTmemP = 128, kTmemQ = 192;
@@ -54,13 +55,14 @@ struct UmmaCtx {
   uint64_t* o_full;       // [2] per group: PV of a chunk has been accumulated (and has read P)
   uint64_t* q_ready;      // the Q tile of a unit part is in tensor memory (one arrival per softmax warp)
   uint64_t* drain;        // [2] every MMA an issuer warp issued has completed
+  uint64_t* drain_b;      // the same for the second QK issuer
   uint64_t* pub;          // meeting point of the 256 softmax threads while a cut unit is published
   uint64_t* xch;          // the two groups have posted their (max, sum) of a part (one arrival per warp)
   uint32_t* tmem_slot;    // where tcgen05.alloc wrote the base address
   int* flag;              // "this CTA arrived last" broadcast
   volatile int* abort;
   int n_my, n_stages, cta;
-  bool pair_wait;         // QK issuer: wait for a chunk's pair partner instead of probing for it
+  int pair_mode;          // QK issuer: 0 one chunk per QK, 1 two when the partner costs no waiting, 2 always two
 #ifdef PACE_TIMING
   unsigned long long* trace;
   unsigned long long* stamps;
@@ -238,8 +240,11 @@ __device__ __forceinline__ bool elect_one() {
   return pred != 0;
 }
 
+// mine: -1 = this warp issues every QK (chunks may pair); 0 / 1 = only the chunks of group A / B, one
+// chunk per QK (full tiles: the loop's fixed cost - barrier probes, votes, fences, the commit - is about
+// as long as the MMAs themselves, and one warp walking every chunk paced the whole pipeline).
 template <int D>
-__device__ __forceinline__ void umma_issue_qk(const UmmaCtx& c, uint32_t tmem, int lane) {
+__device__ __forceinline__ void umma_issue_qk(const UmmaCtx& c, uint32_t tmem, int lane, int mine) {
   constexpr int HALF_B = kChunk * 128;
   constexpr uint32_t IDESC_QK1 = umma_idesc(kChunk, false), IDESC_QK2 = umma_idesc(2 * kChunk, false);
   // Ring layout: [K column block 0 of every stage][K column block 1 ...][V of every stage].  The K rows
@@ -272,15 +277,21 @@ __device__ __forceinline__ void umma_issue_qk(const UmmaCtx& c, uint32_t tmem, i
       ++part;
     }
     const int g = i & 1;
+    if (mine >= 0 && g != mine) {  // the other QK issuer's chunk: only keep the ring position in step
+      ++i;
+      --left;
+      if (++s == c.n_stages) {
+        s = 0;
+        ph ^= 1;
+      }
+      continue;
+    }
     // An even chunk and its odd neighbour with one set of MMAs (N = 128 over S_A and S_B).  Short streams
     // (verify: mostly padding rows, a dozen chunks) pair only when the second chunk costs no waiting: its K
     // has landed and group B has taken its previous scores already.
-    bool two = g == 0 && __all_sync(0xffffffffu, left >= 2) && s + 1 < c.n_stages;
+    bool two = mine < 0 && c.pair_mode != 0 && g == 0 && __all_sync(0xffffffffu, left >= 2) && s + 1 < c.n_stages;
     if (two) {
-      if (c.pair_wait) {
-        // Full tiles (prefill): always pair, and wait for the second chunk.  Both groups then get their
-        // scores at once and work side by side, and this loop's fixed cost (barrier probes, votes, the
-        // commit) is paid once per two chunks; alternating single chunks it paced the whole pipeline.
+      if (c.pair_mode == 2) {
         if (!issuer_wait(c, &c.full_bar[s + 1], ph)) break;
         if (used_b > 0 && !issuer_wait(c, &c.s_free[1], (used_b - 1) & 1)) break;
       } else {
@@ -321,9 +332,10 @@ __device__ __forceinline__ void umma_issue_qk(const UmmaCtx& c, uint32_t tmem, i
     }
   }
   // nothing may still be writing tensor memory when it is handed back
+  uint64_t* const drain = mine == 1 ? c.drain_b : &c.drain[0];
   if (leader) {
-    umma_commit(&c.drain[0]);
-    for (int k = 0; k < (1 << 20) && !mbar_try_wait(&c.drain[0], 0); ++k) __nanosleep(64);
+    umma_commit(drain);
+    for (int k = 0; k < (1 << 20) && !mbar_try_wait(drain, 0); ++k) __nanosleep(64);
   }
   __syncwarp();
 }
@@ -746,8 +758,8 @@ __device__ __forceinline__ void umma_softmax(const MmaParams& p, const UmmaCtx& 
   }
 }
 
-// Entry of warps 0..7, 9 and 10 of a CTA that has work: warp 9 owns the tensor memory and issues
-// the QK MMAs, warp 10 the PV MMAs, warps 0..7 are the two softmax groups.  Every wait inside is bounded and every path ends at
+// Entry of warps 0..7 and 9..11 of a CTA that has work: warp 9 owns the tensor memory and issues QK MMAs
+// (warp 11 those of group B's chunks on full tiles), warp 10 the PV MMAs, warps 0..7 are the two softmax groups.  Every wait inside is bounded and every path ends at
 // the barrier in front of the deallocation: a CTA never exits holding tensor memory.
 template <int D>
 __device__ __forceinline__ void umma_consumer(const MmaParams& p, const UmmaCtx& c, int tid) {
@@ -760,10 +772,12 @@ __device__ __forceinline__ void umma_consumer(const MmaParams& p, const UmmaCtx&
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
   tc_fence_before();
-  asm volatile("bar.sync 3, 320;" ::: "memory");
+  asm volatile("bar.sync 3, 352;" ::: "memory");
   tc_fence_after();
   const uint32_t tmem = *reinterpret_cast<volatile uint32_t*>(c.tmem_slot);
-  if (warp == kUmmaQkWarp) umma_issue_qk<D>(c, tmem, lane);
+  const bool split_qk = c.pair_mode == 0;
+  if (warp == kUmmaQkWarp) umma_issue_qk<D>(c, tmem, lane, split_qk ? 0 : -1);
+  else if (warp == kUmmaQkWarpB) { if (split_qk) umma_issue_qk<D>(c, tmem, lane, 1); }
   else if (warp == kUmmaPvWarp) umma_issue_pv<D>(c, tmem, lane);
   else umma_softmax<D>(p, c, tmem, tid);
   if (lane == 0 && *c.abort) raise_status(p.kv.status, PACE_DEV_WAIT_TIMEOUT);
@@ -771,7 +785,7 @@ __device__ __forceinline__ void umma_consumer(const MmaParams& p, const UmmaCtx&
   if (tid == 0) { unsigned long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_)); c.stamps[5] = t_; }
 #endif
   tc_fence_before();
-  asm volatile("bar.sync 3, 320;" ::: "memory");
+  asm volatile("bar.sync 3, 352;" ::: "memory");
   if (owner) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols) : "memory");
