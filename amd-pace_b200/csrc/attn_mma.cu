@@ -163,7 +163,8 @@ __host__ __device__ inline SmemPlan plan_smem(int D, int MT, int NS, int n_stage
   // (mma.sync kernels: only the live rows are ever written; a fragment load of the padding rows of the
   // last 8-row group and beyond reads whatever follows in shared memory, which no live row depends on)
   const int q_rows = MR < ((live_max + 7) & ~7) ? MR : ((live_max + 7) & ~7);
-  s.qbuf = umma ? take(16, 16) : take(q_rows * QS, 128);  // (the tcgen05 variant keeps its Q tile in tensor memory)
+  // (the tcgen05 variant keeps its Q tile in tensor memory; with two tiles per unit the second one's is here)
+  s.qbuf = umma ? (MT == 16 ? take(128 * D * 2, 1024) : take(16, 16)) : take(q_rows * QS, 128);
   s.mg_stride = D + 8;  // floats; the pad spreads the rows of a fragment over the banks
   s.mg = take(umma ? 16 : (NS > 1 ? NS * live_max * (s.mg_stride + 2) * 4 : 16), 16);
   s.n_res = live_max <= 64 ? 2 : 1;
@@ -325,14 +326,15 @@ __device__ __forceinline__ void fence_proxy_async_all() {
 }
 
 template <int D, int MT, int NS, bool UMMA = false>
-__global__ void __launch_bounds__(threads_of(UMMA, MT * NS), MT * NS == 4 ? 2 : 1)
+__global__ void __launch_bounds__(threads_of(UMMA, UMMA ? 8 : MT * NS), (!UMMA && MT * NS == 4) ? 2 : 1)
     attn_mma_kernel(const MmaParams p, const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
                     const __grid_constant__ CUtensorMap tmS) {
-  constexpr int NW = MT * NS;      // consumer warps
+  constexpr int NW = UMMA ? 8 : MT * NS;  // consumer warps (the tcgen05 variant: eight softmax warps whatever the tile)
+  constexpr bool WIDE = UMMA && MT == 16;  // 256 query rows per unit: two 128-row tiles share every K/V chunk
   constexpr int CTHR = NW * 32;
   static_assert(NW == 8 || (NW == 4 && MT == 1 && !UMMA), "eight consumer warps, or four in the two-per-SM decode form");
   constexpr int NTHR = threads_of(UMMA, NW);
-  static_assert(!UMMA || (MT == 8 && NS == 1), "the tcgen05 variant works on whole 128-row tiles");
+  static_assert(!UMMA || ((MT == 8 || MT == 16) && NS == 1), "the tcgen05 variant works on 128-row tiles, one or two per unit");
   // How the NS warps of a row tile share the key stream: DG groups of SL warps; chunk i goes to group
   // i % DG, whose warps cut its keys into SL slices.  Verify tiles (MT, NS >= 2): DG = NS, whole chunks
   // are dealt round-robin to the warps, so NS chunks are in flight in the tensor pipe at a time and a
@@ -427,7 +429,7 @@ __global__ void __launch_bounds__(threads_of(UMMA, MT * NS), MT * NS == 4 ? 2 : 
   if (tid >= NTHR - 32) {
     const int k = tid - (NTHR - 32);
     if (k < n_stages) mbar_init(&full_bar[k], 1);
-    else if (k < 2 * n_stages) mbar_init(&empty_bar[k - n_stages], UMMA ? 1 : NW);
+    else if (k < 2 * n_stages) mbar_init(&empty_bar[k - n_stages], UMMA ? (WIDE ? 2 : 1) : NW);  // (wide: one commit per group's PV)
     else if (k == 2 * n_stages) mbar_init(q_empty, NW);
     else if (k < 2 * n_stages + 3) mbar_init(&res_full[k - 2 * n_stages - 1], NW);
     else if (k < 2 * n_stages + 5) mbar_init(&res_empty[k - 2 * n_stages - 3], 1);
@@ -1030,12 +1032,13 @@ __global__ void __launch_bounds__(threads_of(UMMA, MT * NS), MT * NS == 4 ? 2 : 
     uc.n_my = n_my;
     uc.n_stages = n_stages;
     uc.cta = cta;
-    uc.pair_mode = p.live_max >= kUmmaRows ? PACE_UMMA_FULL_TILE_PAIR_MODE : 1;
+    uc.pair_mode = p.live_max >= kUmmaRows ? PACE_UMMA_FULL_TILE_PAIR_MODE : 1;  // (the wide form pairs nothing)
 #ifdef PACE_TIMING
     uc.trace = trace;
     uc.stamps = stamps;
 #endif
-    umma_consumer<D>(p, uc, tid);
+    uc.qsw = qbuf;
+    umma_consumer<D, WIDE>(p, uc, tid);
     return;
   }
 
@@ -1613,7 +1616,7 @@ template <int D, int MT, int NS, bool UMMA = false>
 int launch_mma(MmaParams& p, const CUtensorMap& tmK, const CUtensorMap& tmV, int grid, cudaStream_t stream,
                const MmaExtra& ex) {
   constexpr int MR = 16 * MT;
-  constexpr int NW = MT * NS;
+  constexpr int NW = UMMA ? 8 : MT * NS;
   const int n_items = p.batch * p.n_qt;
   p.live_max = p.G * p.q_len < MR ? p.G * p.q_len : MR;
   // two CTAs per SM (four consumer warps): 228 KB of shared memory less 1 KB the system keeps per CTA
@@ -1665,7 +1668,7 @@ int launch_mma(MmaParams& p, const CUtensorMap& tmK, const CUtensorMap& tmV, int
 uint64_t mma_workspace_bytes(int n_q_heads, int n_kv_heads, int head_dim, int q_len) {
   const int G = n_q_heads / (n_kv_heads > 0 ? n_kv_heads : 1);
   const int M = G * q_len;
-  const int MT = M >= kUmmaMinRows ? 8 : M <= 16 ? 1 : M <= 32 ? 2 : M <= 64 ? 4 : 8;
+  const int MT = M >= 2 * 128 ? 16 : M >= kUmmaMinRows ? 8 : M <= 16 ? 1 : M <= 32 ? 2 : M <= 64 ? 4 : 8;
   const int ctas = (MT == 1 ? 2 : 1) * sm_count_m();  // decode runs two four-warp CTAs per SM
   return kWorkspaceCounterBytes + (uint64_t)ctas * 2 * (16 * MT) * (head_dim + 2) * sizeof(float) + 256;
 }
@@ -1694,7 +1697,9 @@ int run_mma(const KVView& kv, const CUtensorMap& tmK, const CUtensorMap& tmV, in
       return PACE_ERR_INVALID;
   }
   const bool umma = M >= kUmmaMinRows && !mask && !((uintptr_t)out & 15) && !(o_sb & 7) && !(o_sh & 7) && !(o_ss & 7);
-  const int MT = umma ? 8 : M <= 16 ? 1 : M <= 32 ? 2 : M <= 64 ? 4 : 8;
+  // two 128-row tiles per unit from 256 query rows on (chunked prefill): they share each K/V chunk fetched
+  const bool wide = umma && M >= 2 * kUmmaRows;
+  const int MT = umma ? (wide ? 16 : 8) : M <= 16 ? 1 : M <= 32 ? 2 : M <= 64 ? 4 : 8;
   const int MR = 16 * MT;
   int grid = sm_count_m();
   auto workspace_for = [&](int ctas) { return kWorkspaceCounterBytes + (uint64_t)ctas * 2 * MR * (D + 2) * sizeof(float); };
@@ -1771,7 +1776,10 @@ int run_mma(const KVView& kv, const CUtensorMap& tmK, const CUtensorMap& tmV, in
     int rc = PACE_ERR_UNSUPPORTED;
 #define PACE_MMA_CASE(DD, MM, NN) \
   if (D == DD && MT == MM) rc = launch_mma<DD, MM, NN>(p, tmK, tmV, grid, stream, ex);
-    if (umma) {
+    if (umma && wide) {
+      if (D == 128) rc = launch_mma<128, 16, 1, true>(p, tmK, tmV, grid, stream, ex);
+      if (D == 64) rc = launch_mma<64, 16, 1, true>(p, tmK, tmV, grid, stream, ex);
+    } else if (umma) {
       if (D == 128) rc = launch_mma<128, 8, 1, true>(p, tmK, tmV, grid, stream, ex);
       if (D == 64) rc = launch_mma<64, 8, 1, true>(p, tmK, tmV, grid, stream, ex);
     } else {

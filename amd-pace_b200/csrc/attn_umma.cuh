@@ -32,13 +32,20 @@ namespace {
 constexpr int kUmmaRows = 128;          // query rows per tile (UMMA M)
 constexpr int kUmmaSoftmaxThreads = 256;  // two warpgroups
 // Warps 0-7: softmax; 8: producer; 9: QK issuer (of group A's chunks when the work is split); 10: PV issuer;
-// 11: QK issuer of group B's chunks.  (Issuers on warps 10 and 11, away from
+// 11: narrow form on full tiles: QK issuer of group B's chunks; wide form: PV issuer of group B.  (Issuers on warps 10 and 11, away from
 // the schedulers of the softmax warps that hold a verify tile's live rows, measured the same.)
-constexpr int kUmmaQkWarp = 9, kUmmaPvWarp = 10, kUmmaQkWarpB = 11;
+constexpr int kUmmaQkWarp = 9, kUmmaPvWarp = 10, kUmmaWarpB = 11;
 constexpr int kTmemCols = 512;          // the whole tensor memory of the SM:
 constexpr uint32_t kTmemO = 256;        //   [0, 128) S_A S_B, [128, 192) P_A P_B, [192, 256) Q, [256, 512) O_A O_B
 constexpr uint32_t kTmemP = 128, kTmemQ = 192;
 constexpr float kLazyRescale = 8.0f;    // log2 units
+#ifndef PACE_WIDE_POLY_EVERY
+#define PACE_WIDE_POLY_EVERY 2
+#endif
+// Wide form: every n-th pair of a row's scores takes 2^x on the FMA pipe (0: none).  Both groups are in
+// their exp2 phase at the same time there (they wait for the same K/V chunk) and the one exp2 unit per
+// scheduler serves two warps: 1150 cycles per chunk for 2 x 64 exp2 per lane, measured.
+constexpr int kWidePolyEvery = PACE_WIDE_POLY_EVERY;
 #ifndef PACE_SOFTMAX_BACKOFF_NS
 #define PACE_SOFTMAX_BACKOFF_NS 100
 #endif
@@ -55,7 +62,8 @@ struct UmmaCtx {
   uint64_t* o_full;       // [2] per group: PV of a chunk has been accumulated (and has read P)
   uint64_t* q_ready;      // the Q tile of a unit part is in tensor memory (one arrival per softmax warp)
   uint64_t* drain;        // [2] every MMA an issuer warp issued has completed
-  uint64_t* drain_b;      // the same for the second QK issuer
+  uint64_t* drain_b;      // the same for warp 11 (second QK issuer or second PV issuer)
+  unsigned char* qsw;     // wide form: tile B's Q, K-major 128-byte-swizzled: [D/64][128 rows][128 B]
   uint64_t* pub;          // meeting point of the 256 softmax threads while a cut unit is published
   uint64_t* xch;          // the two groups have posted their (max, sum) of a part (one arrival per warp)
   uint32_t* tmem_slot;    // where tcgen05.alloc wrote the base address
@@ -130,6 +138,35 @@ __device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
   uint64_t d;
   asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
   return d;
+}
+// 2^x for two values at once on the FMA pipe (any x; below -126 the result is 2^-126): round to the
+// nearest integer with the 1.5 * 2^23 trick, a degree-3 polynomial for 2^f on [-0.5, 0.5] (relative error
+// 1e-4, a twentieth of the bf16 rounding of P) and the integer part added into the exponent field.
+__device__ __forceinline__ void exp2_poly2(float x0, float x1, float& p0, float& p1) {
+  const uint32_t kMagic = 0x4B400000u, kNegMagic = 0xCB400000u, kNegOne = 0xBF800000u;  // 1.5 * 2^23, -1.5 * 2^23, -1.0
+  x0 = fmaxf(x0, -126.f);
+  x1 = fmaxf(x1, -126.f);
+  uint64_t x, r, f, q;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(x) : "r"(__float_as_uint(x0)), "r"(__float_as_uint(x1)));
+  uint64_t magic, neg_magic, neg_one, c0, c1, c2, c3;
+  asm("mov.b64 %0, {%1, %1};" : "=l"(magic) : "r"(kMagic));
+  asm("mov.b64 %0, {%1, %1};" : "=l"(neg_magic) : "r"(kNegMagic));
+  asm("mov.b64 %0, {%1, %1};" : "=l"(neg_one) : "r"(kNegOne));
+  asm("mov.b64 %0, {%1, %1};" : "=l"(c0) : "r"(__float_as_uint(0.9999281764f)));
+  asm("mov.b64 %0, {%1, %1};" : "=l"(c1) : "r"(__float_as_uint(0.6932609677f)));
+  asm("mov.b64 %0, {%1, %1};" : "=l"(c2) : "r"(__float_as_uint(0.2426091731f)));
+  asm("mov.b64 %0, {%1, %1};" : "=l"(c3) : "r"(__float_as_uint(0.05517086014f)));
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(x), "l"(magic));  // low mantissa bits: the rounded integer
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(f) : "l"(r), "l"(neg_magic));
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(f) : "l"(f), "l"(neg_one), "l"(x));  // x - round(x)
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(q) : "l"(c3), "l"(f), "l"(c2));
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(q) : "l"(q), "l"(f), "l"(c1));
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(q) : "l"(q), "l"(f), "l"(c0));
+  uint32_t r0, r1, q0, q1;
+  asm("mov.b64 {%0, %1}, %2;" : "=r"(r0), "=r"(r1) : "l"(r));
+  asm("mov.b64 {%0, %1}, %2;" : "=r"(q0), "=r"(q1) : "l"(q));
+  p0 = __uint_as_float(q0 + (r0 << 23));
+  p1 = __uint_as_float(q1 + (r1 << 23));
 }
 __device__ __forceinline__ void unpack64(uint64_t v, uint32_t& lo, uint32_t& hi) {
   asm("mov.b64 {%0, %1}, %2;" : "=r"(lo), "=r"(hi) : "l"(v));
@@ -243,7 +280,9 @@ __device__ __forceinline__ bool elect_one() {
 // mine: -1 = this warp issues every QK (chunks may pair); 0 / 1 = only the chunks of group A / B, one
 // chunk per QK (full tiles: the loop's fixed cost - barrier probes, votes, fences, the commit - is about
 // as long as the MMAs themselves, and one warp walking every chunk paced the whole pipeline).
-template <int D>
+// Wide form (W): warp 9 issues both tiles' QK of every chunk: tile A's Q from tensor memory into S_A, tile B's
+// from shared memory into S_B.
+template <int D, bool W>
 __device__ __forceinline__ void umma_issue_qk(const UmmaCtx& c, uint32_t tmem, int lane, int mine) {
   constexpr int HALF_B = kChunk * 128;
   constexpr uint32_t IDESC_QK1 = umma_idesc(kChunk, false), IDESC_QK2 = umma_idesc(2 * kChunk, false);
@@ -255,6 +294,8 @@ __device__ __forceinline__ void umma_issue_qk(const UmmaCtx& c, uint32_t tmem, i
   const uint32_t k_lo0 = (smem_u32(c.ring) >> 4) | (1u << 16);  // K-major: LBO unused (1)
   const uint32_t k_half = (uint32_t)c.n_stages * (HALF_B >> 4);  // from one 64-column block of K to the next
   const uint32_t tQ = tmem + kTmemQ;  // 16 elements of every row per MMA: 8 columns
+  const uint32_t q_lo = (smem_u32(c.qsw) >> 4) | (1u << 16);  // (wide form: tile B's Q, K-major in shared memory)
+  constexpr int QHALF = kUmmaRows * 128;
   const bool leader = elect_one();
   int s = 0, ph = 0;       // ring stage / its phase
   int part = 0, left = 0;  // chunks left in the current unit part
@@ -275,6 +316,44 @@ __device__ __forceinline__ void umma_issue_qk(const UmmaCtx& c, uint32_t tmem, i
         break;
       }
       ++part;
+    }
+    if constexpr (W) {
+      // wide form: both tiles' scores of the chunk, A then B.  Tile B's are computed once tile A's rows of
+      // the same chunk are in registers, so that the two groups' exp2 phases (one unit per scheduler)
+      // coincide less.
+      const uint32_t k_lo = k_lo0 + (uint32_t)s * (HALF_B >> 4);
+      if (used_a > 0 && !issuer_wait(c, &c.s_free[0], (used_a - 1) & 1)) break;
+      tc_fence_after();
+      if (leader) {
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk)
+          umma_bf16_ts(tmem, tQ + kk * 8, pack64(k_lo + (kk >> 2) * k_half + (kk & 3) * 2, kDescHi), IDESC_QK1, kk ? 1u : 0u);
+        umma_commit(&c.s_full[0]);
+      }
+      __syncwarp();
+      ++used_a;
+      if (used_b > 0 && !issuer_wait(c, &c.s_free[1], (used_b - 1) & 1)) break;
+      if (!issuer_wait(c, &c.s_free[0], used_b & 1)) break;
+      tc_fence_after();
+      if (leader) {
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk)
+          umma_bf16(tmem + kChunk, pack64(q_lo + (kk >> 2) * (QHALF >> 4) + (kk & 3) * 2, kDescHi),
+                    pack64(k_lo + (kk >> 2) * k_half + (kk & 3) * 2, kDescHi), IDESC_QK1, kk ? 1u : 0u);
+        umma_commit(&c.s_full[1]);
+      }
+      __syncwarp();
+      ++used_b;
+#ifdef PACE_TIMING
+      if (lane == 0) PACE_UTRACE(c, 8, i);
+#endif
+      ++i;
+      --left;
+      if (++s == c.n_stages) {
+        s = 0;
+        ph ^= 1;
+      }
+      continue;
     }
     const int g = i & 1;
     if (mine >= 0 && g != mine) {  // the other QK issuer's chunk: only keep the ring position in step
@@ -340,8 +419,10 @@ __device__ __forceinline__ void umma_issue_qk(const UmmaCtx& c, uint32_t tmem, i
   __syncwarp();
 }
 
-template <int D>
-__device__ __forceinline__ void umma_issue_pv(const UmmaCtx& c, uint32_t tmem, int lane) {
+// mine: -1 = every PV (narrow form); 0 / 1 = group A's / B's of every chunk (wide form: the two groups do
+// not wait for one another anywhere, the ring stage goes back once both PVs have read it)
+template <int D, bool W>
+__device__ __forceinline__ void umma_issue_pv(const UmmaCtx& c, uint32_t tmem, int lane, int mine) {
   constexpr int KVB = kChunk * D * 2, HALF_B = kChunk * 128;
   constexpr uint32_t IDESC_PV = umma_idesc(D, true);
   // V of stage s sits behind the K blocks of all stages; MN-major: LBO = next 64 columns
@@ -364,41 +445,48 @@ __device__ __forceinline__ void umma_issue_pv(const UmmaCtx& c, uint32_t tmem, i
 #ifdef PACE_TIMING
     const long long cw0 = clock64();
 #endif
-    const int w = i & 1;
-    if (!issuer_wait(c, &c.p_full[w], (w ? used_b : used_a) & 1)) break;
-    tc_fence_after();  // P was written with tcgen05.st
-#ifdef PACE_TIMING
-    if (lane == 0) PACE_UCLK(c, 3, i, clock64() - cw0);
-    if (lane == 0) PACE_UTRACE(c, 9, i);
-    const long long ck0 = clock64();
-#endif
     const uint32_t v_lo = v_lo0 + (uint32_t)s * (KVB >> 4);
-    const uint32_t tO = tmem + kTmemO + (uint32_t)w * 128, tP = tmem + kTmemP + (uint32_t)w * 32;
-    const uint32_t acc0 = j < 2 ? 0u : 1u;
-    if (leader) {
-      umma_bf16_ts(tO, tP, pack64(v_lo, kDescHi), IDESC_PV, acc0);
-#pragma unroll
-      for (int k = 1; k < 4; ++k)  // 16 keys per instruction
-        umma_bf16_ts(tO, tP + k * 8, pack64(v_lo + k * (2048 >> 4), kDescHi), IDESC_PV, 1u);
-      umma_commit(&c.empty_bar[s]);  // K and V of this stage have been consumed
-      umma_commit(&c.o_full[w]);     // O_w holds the chunk; P_w may be rewritten
-    }
-    __syncwarp();
+    bool ok = true;
+    // narrow: the chunk's group; wide: both groups, A then B
+    {
+      const int w = W ? mine : (i & 1);
+      if (!issuer_wait(c, &c.p_full[w], (w ? used_b : used_a) & 1)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after();  // P was written with tcgen05.st
 #ifdef PACE_TIMING
-    if (lane == 0) PACE_UCLK(c, 2, i, clock64() - ck0);
-    if (lane == 0) PACE_UTRACE(c, 10, i);
+      if (lane == 0 && w == 0) PACE_UCLK(c, 3, i, clock64() - cw0);
+      if (lane == 0 && w == 0) PACE_UTRACE(c, 9, i);
 #endif
-    if (w) ++used_b;
-    else ++used_a;
+      const uint32_t tO = tmem + kTmemO + (uint32_t)w * 128, tP = tmem + kTmemP + (uint32_t)w * 32;
+      const uint32_t acc0 = (W ? j < 1 : j < 2) ? 0u : 1u;  // a group's first chunk of the part overwrites O
+      if (leader) {
+        umma_bf16_ts(tO, tP, pack64(v_lo, kDescHi), IDESC_PV, acc0);
+#pragma unroll
+        for (int k = 1; k < 4; ++k)  // 16 keys per instruction
+          umma_bf16_ts(tO, tP + k * 8, pack64(v_lo + k * (2048 >> 4), kDescHi), IDESC_PV, 1u);
+        umma_commit(&c.empty_bar[s]);  // K and V of this stage have been consumed (wide form: by this group)
+        umma_commit(&c.o_full[w]);                          // O_w holds the chunk; P_w may be rewritten
+      }
+      __syncwarp();
+      if (w) ++used_b;
+      else ++used_a;
+    }
+    if (!ok) break;
+#ifdef PACE_TIMING
+    if (lane == 0 && mine <= 0) PACE_UTRACE(c, 10, i);
+#endif
     ++j;
     if (++s == c.n_stages) {
       s = 0;
       ph ^= 1;
     }
   }
+  uint64_t* const drain = mine == 1 ? c.drain_b : &c.drain[1];
   if (leader) {
-    umma_commit(&c.drain[1]);
-    for (int k = 0; k < (1 << 20) && !mbar_try_wait(&c.drain[1], 0); ++k) __nanosleep(64);
+    umma_commit(drain);
+    for (int k = 0; k < (1 << 20) && !mbar_try_wait(drain, 0); ++k) __nanosleep(64);
   }
   __syncwarp();
 }
@@ -406,9 +494,9 @@ __device__ __forceinline__ void umma_issue_pv(const UmmaCtx& c, uint32_t tmem, i
 // Merge of a unit's partials by its last arriver (all softmax threads; every partial is in the
 // workspace).  A thread owns four adjacent output elements at a time and keeps the loads of two such
 // groups times four partials in flight: the loop is bound by L2 latency, not by arithmetic.
-template <int D>
+template <int D, bool W>
 __device__ __forceinline__ void umma_merge(const MmaParams& p, const ResMeta& rm, int t) {
-  constexpr int MR = kUmmaRows, REC = MR * (D + 2), V4 = D / 4, U = 2;
+  constexpr int MR = W ? 2 * kUmmaRows : kUmmaRows, REC = MR * (D + 2), V4 = D / 4, U = 2;
   const int G = p.G, total = rm.live * V4;
   for (int e0 = t; e0 < total; e0 += kUmmaSoftmaxThreads * U) {
     int row[U], col[U];
@@ -470,11 +558,18 @@ __device__ __forceinline__ void umma_merge(const MmaParams& p, const ResMeta& rm
   }
 }
 
-// ---- the softmax warps: thread (group w, row r) owns query row r for the chunks dealt to group w ----
-template <int D>
+// ---- the softmax warps ----
+// Narrow form (W false, 128 query rows per unit): thread (group w, row r) owns query row r for the chunks
+// dealt to group w (A: even, B: odd); the two groups' accumulators are merged when the part ends.
+// Wide form (W true, 256 query rows per unit): group w owns rows 128 w .. 128 w + 127 and works on every
+// chunk - two query tiles share each K/V chunk the CTA fetches, which halves the L2 -> SM traffic per flop
+// (with one tile per fetch the launch was pinned at about 5 TB/s of it, sixteen tiles pulling every K/V
+// byte).  Tile A's Q sits in tensor memory, tile B's in shared memory.
+template <int D, bool W>
 __device__ __forceinline__ void umma_softmax(const MmaParams& p, const UmmaCtx& c, uint32_t tmem, int tid) {
-  constexpr int MR = kUmmaRows, REC = MR * (D + 2);
+  constexpr int MR = W ? 2 * kUmmaRows : kUmmaRows, REC = MR * (D + 2);
   const int wg = tid >> 7, row = tid & 127, lane = tid & 31, G = p.G;
+  const int urow = W ? tid : row;  // the row inside the unit
   const uint32_t t_lane = tmem + ((uint32_t)(row & ~31) << 16);  // this warp's 32 TMEM lanes
   const uint32_t tO = t_lane + kTmemO + (uint32_t)wg * 128, tOo = t_lane + kTmemO + (uint32_t)(wg ^ 1) * 128;
   const float scale = p.scale_log2;
@@ -512,15 +607,15 @@ __device__ __forceinline__ void umma_softmax(const MmaParams& p, const UmmaCtx& 
       fin.first_cta = meta->first_cta;
       fin.first_slot = meta->first_slot;
       fin.unit = meta->unit;
-      const int r = r_lo + row;
+      const int r = r_lo + urow;
       live = r < R;
       const int sq = r / G, g = r - sq * G;
       lim = live ? (p.causal ? kv_len - S + sq + 1 : kv_len) : 0;  // first key this row does NOT see
       const uint4* src = reinterpret_cast<const uint4*>(p.q + (size_t)fin.b * p.q_sb + (size_t)(fin.h * G + g) * p.q_sh +
                                                         (size_t)sq * p.q_ss);
       out_row = p.out + (size_t)fin.b * p.o_sb + (size_t)(fin.h * G + g) * p.o_sh + (size_t)sq * p.o_ss;
-      // each group stores half of the row: D / 2 elements = D / 4 columns (a 16-byte piece is four columns)
-      {
+      if constexpr (!W) {
+        // each group stores half of the row: D / 2 elements = D / 4 columns (a 16-byte piece is four columns)
         uint32_t qv[D / 4];
 #pragma unroll
         for (int k = 0; k < D / 16; ++k) {
@@ -531,21 +626,47 @@ __device__ __forceinline__ void umma_softmax(const MmaParams& p, const UmmaCtx& 
         if constexpr (D == 128) tmem_st32(tQ, qv);
         else tmem_st16(tQ, qv);
         tmem_wait_st();
+      } else if (wg == 0) {
+        // tile A: the whole row into tensor memory, D / 2 columns
+#pragma unroll
+        for (int hq = 0; hq < 2; ++hq) {
+          uint32_t qv[D / 4];
+#pragma unroll
+          for (int k = 0; k < D / 16; ++k) {
+            const uint4 v = live ? __ldg(src + hq * (D / 16) + k) : make_uint4(0, 0, 0, 0);
+            qv[4 * k] = v.x; qv[4 * k + 1] = v.y; qv[4 * k + 2] = v.z; qv[4 * k + 3] = v.w;
+          }
+          const uint32_t tQ = t_lane + kTmemQ + (uint32_t)hq * (D / 4);
+          if constexpr (D == 128) tmem_st32(tQ, qv);
+          else tmem_st16(tQ, qv);
+        }
+        tmem_wait_st();
+      } else {
+        // tile B: the row's 16-byte pieces into shared memory at their swizzled places (K-major, 128-byte swizzle)
+        unsigned char* qrow = c.qsw + row * 128;
+#pragma unroll
+        for (int cc = 0; cc < D / 8; ++cc) {
+          const uint4 v = live ? __ldg(src + cc) : make_uint4(0, 0, 0, 0);
+          *reinterpret_cast<uint4*>(qrow + (cc >> 3) * (kUmmaRows * 128) + (((cc & 7) ^ (row & 7)) << 4)) = v;
+        }
+        fence_proxy_async();  // generic-proxy writes before the tensor core's async-proxy reads
       }
       tc_fence_before();    // (this thread's reads of O for the previous part are done as well)
       __syncwarp();
       if (lane == 0) mbar_arrive(c.q_ready);
     }
     if (n_part < 1) return;
-    const bool warp_live = (row & ~31) < fin.live;  // a warp of padding rows only keeps the barriers in step
+    const bool warp_live = (urow & ~31) < fin.live;  // a warp of padding rows only keeps the barriers in step
     float m_used = -INFINITY, l = 0.f;
 
-    const int j_first = (i0 ^ wg) & 1;  // this group takes the chunks whose index in the CTA's range has its parity
+    // narrow: this group takes the chunks whose index in the CTA's range has its parity; wide: every chunk
+    const int j_first = W ? 0 : (i0 ^ wg) & 1;
+    constexpr int j_step = W ? 1 : 2;
     // With whole pages per chunk every chunk of a part starts chunk_tokens after the one before and
     // the row's own limit already bounds what it holds: nothing of the chunk's record is needed, and
     // neither is a wait for its K/V to land.
     const bool uniform_chunks = p.pages_per_chunk > 0;
-    for (int j = j_first; j < n_part; j += 2) {
+    for (int j = j_first; j < n_part; j += j_step) {
       const int i = i0 + j;
       const uint32_t tS = t_lane + (uint32_t)wg * kChunk, tP = t_lane + kTmemP + (uint32_t)wg * 32;
       int rows = p.chunk_tokens, tok0 = tok0_part + j * p.chunk_tokens;
@@ -569,6 +690,7 @@ __device__ __forceinline__ void umma_softmax(const MmaParams& p, const UmmaCtx& 
         tmem_ld32(tS, sr[0]);
         tmem_ld32(tS + 32, sr[1]);
         tmem_wait_ld();
+        if (tid == 0) PACE_UTRACE(c, 14, i);
         // the scores are in registers: the buffer goes back to the QK issuer at once
         tc_fence_before();
         __syncwarp();
@@ -612,9 +734,11 @@ __device__ __forceinline__ void umma_softmax(const MmaParams& p, const UmmaCtx& 
         // ---- P = 2^(s * scale - m), row sum, bf16 pairs into the group's P buffer ----
         // (the PV of the group's previous chunk has read the buffer: its completion is o_full's phase)
         if (cnt > 0) {
+          if (tid == 0) PACE_UTRACE(c, 11, i);
           if (!umma_wait(&c.o_full[wg], (cnt - 1) & 1, c.abort)) return;
           tc_fence_after();
         }
+        if (tid == 0) PACE_UTRACE(c, 15, i);
         const float ne = (m_used == -INFINITY) ? 0.f : -m_used;
         const uint64_t scale2 = pack64(__float_as_uint(scale), __float_as_uint(scale));
         const uint64_t ne2 = pack64(__float_as_uint(ne), __float_as_uint(ne));
@@ -626,7 +750,13 @@ __device__ __forceinline__ void umma_softmax(const MmaParams& p, const UmmaCtx& 
           for (int k = 0; k < 16; ++k) {
             uint32_t x0, x1;
             unpack64(fma2(pack64(sr[hf][2 * k], sr[hf][2 * k + 1]), scale2, ne2), x0, x1);
-            const float p0 = fast_exp2(__uint_as_float(x0)), p1 = fast_exp2(__uint_as_float(x1));
+            float p0, p1;
+            if (W && kWidePolyEvery > 0 && (k % (kWidePolyEvery > 0 ? kWidePolyEvery : 1)) == kWidePolyEvery - 1) {
+              exp2_poly2(__uint_as_float(x0), __uint_as_float(x1), p0, p1);
+            } else {
+              p0 = fast_exp2(__uint_as_float(x0));
+              p1 = fast_exp2(__uint_as_float(x1));
+            }
             l2[k & 1] = add2(l2[k & 1], pack64(__float_as_uint(p0), __float_as_uint(p1)));
             pk[k] = f2_to_bf2(p0, p1);
           }
@@ -638,6 +768,7 @@ __device__ __forceinline__ void umma_softmax(const MmaParams& p, const UmmaCtx& 
           unpack64(l2[1], b0, b1);
           l += (__uint_as_float(a0) + __uint_as_float(a1)) + (__uint_as_float(b0) + __uint_as_float(b1));
         }
+        if (tid == 0) PACE_UTRACE(c, 0, i);
         tmem_wait_st();
       }
       else {
@@ -656,75 +787,109 @@ __device__ __forceinline__ void umma_softmax(const MmaParams& p, const UmmaCtx& 
       ++cnt;
     }
 
-    // ================= end of a unit part: the two groups' accumulators meet =================
+    // ================= end of a unit part =================
     if (tid == 0) PACE_USTAMP(c, 3);
-    const bool has_mine = j_first < n_part, has_other = (j_first ^ 1) < n_part;  // (a part of one chunk leaves a group empty-handed)
-    if (has_mine && !umma_wait(&c.o_full[wg], (cnt - 1) & 1, c.abort)) return;
-    // Each row's (reference maximum, sum) crosses to the other group through tensor memory: columns 32
-    // and 33 of the score buffer of the group's own last chunk, which hold nothing any more (P, packed
-    // bf16, sits in columns 0..31 and its PV MMA has completed; the next QK into the buffer waits for the
-    // next part's Q).  Both groups' warp w own the same 32 TMEM lanes, so no shared memory is needed -
-    // the 2 KB it took are what a sixth ring stage was short of.
-    const int j_last_mine = ((n_part - 1) & 1) == j_first ? n_part - 1 : n_part - 2;
-    const int j_last_other = ((n_part - 1) & 1) == j_first ? n_part - 2 : n_part - 1;
-    if (has_mine) {
-      tmem_st2(t_lane + (uint32_t)wg * kChunk, __float_as_uint(m_used), __float_as_uint(l));
-      tmem_wait_st();
-    }
-    tc_fence_before();
-    __syncwarp();
-    if (lane == 0) mbar_arrive(c.xch);
-    if (!umma_wait(c.xch, n_xch & 1, c.abort)) return;
-    ++n_xch;
-    tc_fence_after();
-    float m_o = -INFINITY, l_o = 0.f;
-    if (has_other) {
-      uint32_t xm, xl;
-      tmem_ld2(t_lane + (uint32_t)(wg ^ 1) * kChunk, xm, xl);
-      tmem_wait_ld();
-      m_o = __uint_as_float(xm);
-      l_o = __uint_as_float(xl);
-    }
-    const float M = fmaxf(m_used, m_o);
-    const float f_m = (m_used == -INFINITY) ? 0.f : fast_exp2(m_used - M);
-    const float f_o = (m_o == -INFINITY) ? 0.f : fast_exp2(m_o - M);
-    const float den = l * f_m + l_o * f_o;
-    // group A takes the lower half of the head dimension, group B the upper half
+    float M = m_used, den = l;
     float* rec = p.parts + ((size_t)c.cta * 2 + (fin.mode == 2 ? 1 : 0)) * REC;
-    if (warp_live) {
-      const float inv = den > 0.f ? 1.0f / den : 0.f;
-      const float s_m = fin.mode == 0 ? f_m * inv : f_m, s_o = fin.mode == 0 ? f_o * inv : f_o;
+    if constexpr (W) {
+      // wide: the group's own rows, the whole head dimension; nothing to merge inside the CTA
+      if (!umma_wait(&c.o_full[wg], (cnt - 1) & 1, c.abort)) return;
+      tc_fence_after();
+      if (warp_live) {
+        const float inv = den > 0.f ? 1.0f / den : 0.f;
+        const float s_m = fin.mode == 0 ? inv : 1.f;
 #pragma unroll
-      for (int d0 = wg * (D / 2); d0 < (wg + 1) * (D / 2); d0 += 32) {
-        float v[32];
-#pragma unroll
-        for (int k = 0; k < 32; ++k) v[k] = 0.f;
-        if (has_mine) {
+        for (int d0 = 0; d0 < D; d0 += 32) {
           uint32_t om[32];
+          float v[32];
           tmem_ld32(tO + d0, om);
           tmem_wait_ld();
 #pragma unroll
           for (int k = 0; k < 32; ++k) v[k] = __uint_as_float(om[k]) * s_m;
+          if (live) {
+            if (fin.mode == 0) {
+#pragma unroll
+              for (int q4 = 0; q4 < 4; ++q4)
+                *reinterpret_cast<uint4*>(out_row + d0 + q4 * 8) =
+                    make_uint4(f2_to_bf2(v[q4 * 8], v[q4 * 8 + 1]), f2_to_bf2(v[q4 * 8 + 2], v[q4 * 8 + 3]),
+                               f2_to_bf2(v[q4 * 8 + 4], v[q4 * 8 + 5]), f2_to_bf2(v[q4 * 8 + 6], v[q4 * 8 + 7]));
+            } else {
+#pragma unroll
+              for (int q4 = 0; q4 < 8; ++q4)
+                *reinterpret_cast<float4*>(rec + urow * D + d0 + q4 * 4) =
+                    make_float4(v[q4 * 4], v[q4 * 4 + 1], v[q4 * 4 + 2], v[q4 * 4 + 3]);
+            }
+          }
         }
-        if (has_other) {
-          uint32_t oo[32];
-          tmem_ld32(tOo + d0, oo);
-          tmem_wait_ld();
-#pragma unroll
-          for (int k = 0; k < 32; ++k) v[k] = fmaf(__uint_as_float(oo[k]), s_o, v[k]);
-        }
-        if (live) {
-          if (fin.mode == 0) {
-#pragma unroll
-            for (int q4 = 0; q4 < 4; ++q4)
-              *reinterpret_cast<uint4*>(out_row + d0 + q4 * 8) =
-                  make_uint4(f2_to_bf2(v[q4 * 8], v[q4 * 8 + 1]), f2_to_bf2(v[q4 * 8 + 2], v[q4 * 8 + 3]),
-                             f2_to_bf2(v[q4 * 8 + 4], v[q4 * 8 + 5]), f2_to_bf2(v[q4 * 8 + 6], v[q4 * 8 + 7]));
-          } else {
-#pragma unroll
-            for (int q4 = 0; q4 < 8; ++q4)
-              *reinterpret_cast<float4*>(rec + row * D + d0 + q4 * 4) =
-                  make_float4(v[q4 * 4], v[q4 * 4 + 1], v[q4 * 4 + 2], v[q4 * 4 + 3]);
+      }
+    } else {
+      const bool has_mine = j_first < n_part, has_other = (j_first ^ 1) < n_part;  // (a part of one chunk leaves a group empty-handed)
+      if (has_mine && !umma_wait(&c.o_full[wg], (cnt - 1) & 1, c.abort)) return;
+      // Each row's (reference maximum, sum) crosses to the other group through tensor memory: columns 32
+      // and 33 of the score buffer of the group's own last chunk, which hold nothing any more (P, packed
+      // bf16, sits in columns 0..31 and its PV MMA has completed; the next QK into the buffer waits for the
+      // next part's Q).  Both groups' warp w own the same 32 TMEM lanes, so no shared memory is needed -
+      // the 2 KB it took are what a sixth ring stage was short of.
+      const int j_last_mine = ((n_part - 1) & 1) == j_first ? n_part - 1 : n_part - 2;
+      const int j_last_other = ((n_part - 1) & 1) == j_first ? n_part - 2 : n_part - 1;
+      if (has_mine) {
+        tmem_st2(t_lane + (uint32_t)wg * kChunk, __float_as_uint(m_used), __float_as_uint(l));
+        tmem_wait_st();
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(c.xch);
+      if (!umma_wait(c.xch, n_xch & 1, c.abort)) return;
+      ++n_xch;
+      tc_fence_after();
+      float m_o = -INFINITY, l_o = 0.f;
+      if (has_other) {
+        uint32_t xm, xl;
+        tmem_ld2(t_lane + (uint32_t)(wg ^ 1) * kChunk, xm, xl);
+        tmem_wait_ld();
+        m_o = __uint_as_float(xm);
+        l_o = __uint_as_float(xl);
+      }
+      M = fmaxf(m_used, m_o);
+      const float f_m = (m_used == -INFINITY) ? 0.f : fast_exp2(m_used - M);
+      const float f_o = (m_o == -INFINITY) ? 0.f : fast_exp2(m_o - M);
+      den = l * f_m + l_o * f_o;
+      // group A takes the lower half of the head dimension, group B the upper half
+      if (warp_live) {
+        const float inv = den > 0.f ? 1.0f / den : 0.f;
+        const float s_m = fin.mode == 0 ? f_m * inv : f_m, s_o = fin.mode == 0 ? f_o * inv : f_o;
+  #pragma unroll
+        for (int d0 = wg * (D / 2); d0 < (wg + 1) * (D / 2); d0 += 32) {
+          float v[32];
+  #pragma unroll
+          for (int k = 0; k < 32; ++k) v[k] = 0.f;
+          if (has_mine) {
+            uint32_t om[32];
+            tmem_ld32(tO + d0, om);
+            tmem_wait_ld();
+  #pragma unroll
+            for (int k = 0; k < 32; ++k) v[k] = __uint_as_float(om[k]) * s_m;
+          }
+          if (has_other) {
+            uint32_t oo[32];
+            tmem_ld32(tOo + d0, oo);
+            tmem_wait_ld();
+  #pragma unroll
+            for (int k = 0; k < 32; ++k) v[k] = fmaf(__uint_as_float(oo[k]), s_o, v[k]);
+          }
+          if (live) {
+            if (fin.mode == 0) {
+  #pragma unroll
+              for (int q4 = 0; q4 < 4; ++q4)
+                *reinterpret_cast<uint4*>(out_row + d0 + q4 * 8) =
+                    make_uint4(f2_to_bf2(v[q4 * 8], v[q4 * 8 + 1]), f2_to_bf2(v[q4 * 8 + 2], v[q4 * 8 + 3]),
+                               f2_to_bf2(v[q4 * 8 + 4], v[q4 * 8 + 5]), f2_to_bf2(v[q4 * 8 + 6], v[q4 * 8 + 7]));
+            } else {
+  #pragma unroll
+              for (int q4 = 0; q4 < 8; ++q4)
+                *reinterpret_cast<float4*>(rec + row * D + d0 + q4 * 4) =
+                    make_float4(v[q4 * 4], v[q4 * 4 + 1], v[q4 * 4 + 2], v[q4 * 4 + 3]);
+            }
           }
         }
       }
@@ -734,9 +899,9 @@ __device__ __forceinline__ void umma_softmax(const MmaParams& p, const UmmaCtx& 
     if (tid == 0) PACE_USTAMP(c, 4);
     if (fin.mode == 0) continue;
     // cut unit: the fp32 partial is in the workspace; arrival count, merge by the last arriver
-    if (live && wg == 0) {
-      rec[MR * D + row] = M;
-      rec[MR * D + MR + row] = den;
+    if (live && (W || wg == 0)) {
+      rec[MR * D + urow] = M;
+      rec[MR * D + MR + urow] = den;
     }
     __threadfence();
     if (!group_sync()) return;
@@ -752,7 +917,7 @@ __device__ __forceinline__ void umma_softmax(const MmaParams& p, const UmmaCtx& 
     if (tid == 0) PACE_USTAMP(c, 6);
     if (is_last) {
       __threadfence();
-      umma_merge<D>(p, fin, tid);
+      umma_merge<D, W>(p, fin, tid);
     }
     if (tid == 0) PACE_USTAMP(c, 7);
   }
@@ -761,7 +926,7 @@ __device__ __forceinline__ void umma_softmax(const MmaParams& p, const UmmaCtx& 
 // Entry of warps 0..7 and 9..11 of a CTA that has work: warp 9 owns the tensor memory and issues QK MMAs
 // (warp 11 those of group B's chunks on full tiles), warp 10 the PV MMAs, warps 0..7 are the two softmax groups.  Every wait inside is bounded and every path ends at
 // the barrier in front of the deallocation: a CTA never exits holding tensor memory.
-template <int D>
+template <int D, bool W>
 __device__ __forceinline__ void umma_consumer(const MmaParams& p, const UmmaCtx& c, int tid) {
   const int warp = tid >> 5, lane = tid & 31;
   const bool owner = warp == kUmmaQkWarp;
@@ -775,11 +940,13 @@ __device__ __forceinline__ void umma_consumer(const MmaParams& p, const UmmaCtx&
   asm volatile("bar.sync 3, 352;" ::: "memory");
   tc_fence_after();
   const uint32_t tmem = *reinterpret_cast<volatile uint32_t*>(c.tmem_slot);
-  const bool split_qk = c.pair_mode == 0;
-  if (warp == kUmmaQkWarp) umma_issue_qk<D>(c, tmem, lane, split_qk ? 0 : -1);
-  else if (warp == kUmmaQkWarpB) { if (split_qk) umma_issue_qk<D>(c, tmem, lane, 1); }
-  else if (warp == kUmmaPvWarp) umma_issue_pv<D>(c, tmem, lane);
-  else umma_softmax<D>(p, c, tmem, tid);
+  const bool split_qk = !W && c.pair_mode == 0;
+  if (warp == kUmmaQkWarp) umma_issue_qk<D, W>(c, tmem, lane, split_qk ? 0 : -1);
+  else if (warp == kUmmaWarpB) {
+    if (W) umma_issue_pv<D, W>(c, tmem, lane, 1);
+    else if (split_qk) umma_issue_qk<D, W>(c, tmem, lane, 1);
+  } else if (warp == kUmmaPvWarp) umma_issue_pv<D, W>(c, tmem, lane, W ? 0 : -1);
+  else umma_softmax<D, W>(p, c, tmem, tid);
   if (lane == 0 && *c.abort) raise_status(p.kv.status, PACE_DEV_WAIT_TIMEOUT);
 #ifdef PACE_TIMING
   if (tid == 0) { unsigned long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_)); c.stamps[5] = t_; }
