@@ -732,20 +732,13 @@ __device__ __forceinline__ void umma_softmax(const MmaParams& p, const UmmaCtx& 
           m_used = m_new;
         }
         // ---- P = 2^(s * scale - m), row sum, bf16 pairs into the group's P buffer ----
-        // (the PV of the group's previous chunk has read the buffer: its completion is o_full's phase)
-        if (cnt > 0) {
-          if (tid == 0) PACE_UTRACE(c, 11, i);
-          if (!umma_wait(&c.o_full[wg], (cnt - 1) & 1, c.abort)) return;
-          tc_fence_after();
-        }
-        if (tid == 0) PACE_UTRACE(c, 15, i);
         const float ne = (m_used == -INFINITY) ? 0.f : -m_used;
         const uint64_t scale2 = pack64(__float_as_uint(scale), __float_as_uint(scale));
         const uint64_t ne2 = pack64(__float_as_uint(ne), __float_as_uint(ne));
         uint64_t l2[2] = {0ull, 0ull};
+        uint32_t pk[2][16];
 #pragma unroll
         for (int hf = 0; hf < 2; ++hf) {
-          uint32_t pk[16];
 #pragma unroll
           for (int k = 0; k < 16; ++k) {
             uint32_t x0, x1;
@@ -758,9 +751,20 @@ __device__ __forceinline__ void umma_softmax(const MmaParams& p, const UmmaCtx& 
               p1 = fast_exp2(__uint_as_float(x1));
             }
             l2[k & 1] = add2(l2[k & 1], pack64(__float_as_uint(p0), __float_as_uint(p1)));
-            pk[k] = f2_to_bf2(p0, p1);
+            pk[hf][k] = f2_to_bf2(p0, p1);
           }
-          tmem_st16(tP + hf * 16, pk);
+          if (hf == 0) {
+            // The PV of the group's previous chunk has to have read the buffer (its completion is o_full's
+            // phase) before the first store; asked for here, half a row's arithmetic after the scores came,
+            // the answer is there without waiting.
+            if (tid == 0) PACE_UTRACE(c, 11, i);
+            if (cnt > 0) {
+              if (!umma_wait(&c.o_full[wg], (cnt - 1) & 1, c.abort)) return;
+              tc_fence_after();
+            }
+            if (tid == 0) PACE_UTRACE(c, 15, i);
+          }
+          tmem_st16(tP + hf * 16, pk[hf]);
         }
         {
           uint32_t a0, a1, b0, b1;

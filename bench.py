@@ -465,10 +465,15 @@ def run_ours(args, rank, world, local_rank):
         for wl in ("verify", "prefill"):
             a = aux_measure(wl, layers=4, head_dim=D, past=3584, steps=32)
             aux[wl] = {"us_per_launch": a["us_per_launch"], "hbm_frac_of_measured": a["hbm"]["frac_of_measured"],
+                       "us_best_single_launch": a["us_best_single_launch"],
                        "tflops": a["tensor"]["achieved_tflops"],
                        "tensor_frac_of_measured_burst": a["tensor"]["frac_of_measured_burst"],
+                       "tensor_frac_of_measured_sustained": a["tensor"]["frac_of_measured_sustained"],
+                       "tflops_best_single_launch": a["tensor"]["achieved_tflops_best_single_launch"],
+                       "best_single_launch_frac_of_measured_burst": a["tensor"]["best_single_launch_frac_of_measured_burst"],
                        "shape": f"B={a['batch']} q_len={a['q_len']} kv_len={a['kv_len']}"}
         line["aux"] = {"verify_us": aux["verify"]["us_per_launch"], "prefill_tflops": aux["prefill"]["tflops"],
+                       "prefill_tflops_best_single_launch": aux["prefill"]["tflops_best_single_launch"],
                        "verify": aux["verify"], "prefill": aux["prefill"]}
     if world == 1 and not args.no_cpu_baseline:
         tps, _, cpu_cores, kind, sample = cpu_reference_line(steps=8)
@@ -542,6 +547,20 @@ def aux_measure(workload, layers, head_dim, past, steps):
     e1.record()
     torch.cuda.synchronize()
     us = e0.elapsed_time(e1) * 1e3 / (reps * L)
+    # The loop above runs for tens of milliseconds at full load: the SM clock settles where the power cap
+    # puts it, which is what MEASURED_PEAKS calls "sustained".  Its "burst" figure is the best of ten single
+    # GEMMs; the like-for-like number here is the best of ten single launches (cold L2: a different layer
+    # each time), each timed on its own.
+    singles = []
+    with torch.cuda.stream(side):
+        for n in range(10):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            mha(q, *hs[n % L], out=out)
+            b.record()
+            b.synchronize()
+            singles.append(a.elapsed_time(b) * 1e3)
+    us_best = min(singles)
     mgr.pool.check_status()
     alg_bytes = B * (2 * Hkv * D * 2 * kv_len) + 2 * B * Hq * D * 2 * S
     # causal: query s sees past + s + 1 keys; 4 flops per (query head, key, dim)
@@ -552,8 +571,15 @@ def aux_measure(workload, layers, head_dim, past, steps):
             "page_tokens": mgr.pool.page_tokens, "us_per_launch": us,
             "hbm": {"alg_bytes": alg_bytes, "achieved_gbs": alg_bytes / us / 1e3,
                     "frac_of_measured": alg_bytes / us / 1e3 / peaks["hbm_gbs"]},
+            "us_best_single_launch": us_best,
             "tensor": {"flops": flops, "achieved_tflops": flops / us / 1e6,
-                       "frac_of_measured_burst": flops / us / 1e6 / peaks["bf16_tflops"]}}
+                       "frac_of_measured_burst": flops / us / 1e6 / peaks["bf16_tflops"],
+                       "frac_of_measured_sustained": flops / us / 1e6 / peaks.get("bf16_tflops_sustained", peaks["bf16_tflops"]),
+                       "achieved_tflops_best_single_launch": flops / us_best / 1e6,
+                       "best_single_launch_frac_of_measured_burst": flops / us_best / 1e6 / peaks["bf16_tflops"],
+                       "note": "achieved_tflops: back-to-back launches for tens of ms (clock under the power cap, compare "
+                               "with the sustained GEMM figure); best_single_launch: best of 10 launches timed one by one "
+                               "(compare with the burst GEMM figure, itself a best of 10)"}}
     mgr.release()
     return line
 
