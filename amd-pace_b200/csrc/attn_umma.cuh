@@ -1,27 +1,30 @@
 // 5th-generation tensor-core path of the multi-token attention kernel (prefill chunks, PARD verify).
 //
-// One 128-row query tile per CTA pass: S = Q K^T and O += P V are tcgen05.mma instructions issued
-// by one elected thread, operands in shared memory (K-major / MN-major, 128-byte swizzle, exactly
-// the layout the tiled TMA copies of K and V produce), accumulators in tensor memory.
-//
-// The chunks of a CTA's range are dealt alternately to two softmax warpgroups (A: even, B: odd).
-// Each group has its own running (max, sum) and O accumulator, so the two never wait for one another
-// while a unit part streams; the two accumulators are merged when the part ends.  Tensor memory:
+// S = Q K^T and O += P V are tcgen05.mma instructions issued by one elected thread of an issuer warp,
+// K and V in shared memory (K-major / MN-major, 128-byte swizzle, exactly the layout the tiled TMA
+// copies produce), accumulators in tensor memory.  Two softmax warpgroups, A and B, each with its own
+// running (max, sum), score / probability buffers and O accumulator, so that they never wait for one
+// another while a unit part streams.  Two forms:
+//   narrow  one 128-row query tile per unit; the chunks of a CTA's range are dealt alternately to the
+//           groups (A: even, B: odd) and the two accumulators are merged when the part ends;
+//   wide    256 query rows per unit = two 128-row tiles that share every K/V chunk the CTA fetches
+//           (half the L2 -> SM traffic per flop); group A owns tile A, group B tile B, both work on
+//           every chunk, nothing is merged inside the CTA.
+// Tensor memory:
 //     columns [0, 64) / [64, 128)    S_A / S_B: the scores of the chunk a group works on, 128 x 64 fp32
 //     columns [128, 160) / [160, 192) P_A / P_B: its probabilities, 128 x 64 bf16 (two per column)
-//     columns [192, 256)             the Q tile, 128 x D bf16 (two elements per column)
+//     columns [192, 256)             a Q tile, 128 x D bf16 (two elements per column)
 //     columns [256, 384) / [384, 512) O_A / O_B, 128 x D fp32
 // A softmax thread owns one query row (TMEM lane == row): tcgen05.ld the row of S - which hands the
 // score buffer back at once, so the QK of the group's next chunk runs while this one's softmax does -
 // online softmax in registers, P stored to the group's P buffer as packed bf16 pairs once the PV of its
-// previous chunk has completed; the second MMA takes it from there as its A operand.  Q sits in tensor memory as well (each softmax
-// thread stores its own row once per unit part) and is the A operand of the first MMA: with Q in
-// shared memory every chunk re-read the whole 32 KB tile, a third of the SM's shared-memory traffic
-// (Q 32 KB + K 16 KB + V 16 KB read, 32 KB written by the TMA unit per chunk), and shared-memory
-// bandwidth, not the tensor pipe, paced the MMAs (86 cycles per QK instruction against 32).
-// O is rescaled in TMEM
-// only when a row's running maximum grows by more than 2^8 (the result is exact either way:
-// numerator and denominator share whatever maximum was used).
+// previous chunk has completed; the second MMA takes it from there as its A operand.  Q sits in tensor
+// memory as well (each softmax thread stores its own row once per unit part) and is the A operand of the
+// first MMA: with Q in shared memory every chunk re-read the whole 32 KB tile, a third of the SM's
+// shared-memory traffic, and shared-memory bandwidth paced those MMAs.  (The wide form's second tile
+// does keep its Q in shared memory: tensor memory has room for one.)  O is rescaled in TMEM only when a
+// row's running maximum grows by more than 2^8 (the result is exact either way: numerator and
+// denominator share whatever maximum was used).
 //
 // Included by attn_mma.cu, which provides MmaParams, MetaM, the ring and its producer warp.
 #pragma once
