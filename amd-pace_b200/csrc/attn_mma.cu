@@ -36,9 +36,6 @@ namespace {
 __host__ __device__ constexpr int threads_of(bool umma, int nw = 8) { return nw * 32 + (umma ? 128 : 64); }
 constexpr int kChunk = 64;
 constexpr int kMaxStagesM = 8;
-#ifndef PACE_UMMA_FULL_TILE_PAIR_MODE
-#define PACE_UMMA_FULL_TILE_PAIR_MODE 0
-#endif
 constexpr int kMaxItems = 1024;
 
 struct MetaM {  // one 64-byte record per ring stage, written by the producer
@@ -344,18 +341,9 @@ __global__ void __launch_bounds__(threads_of(UMMA, UMMA ? 8 : MT * NS), (!UMMA &
   // groups, 22.6 us with four, 24.5 us with whole chunks per warp).  Decode with four warps (two CTAs per
   // SM, each with its own producer warp and a three-stage ring): one group, 16 keys per warp; the two
   // CTAs of an SM are the two groups, and they drift apart instead of marching in step - 19.3 us
-  // (PACE_DECODE_DEAL_HALF=2, two groups of two warps with 32 keys each, holds two of the three ring
+  // (1=2, two groups of two warps with 32 keys each, holds two of the three ring
   // stages at a time: 19.1 us where one group takes 18.0 us).
-#ifndef PACE_DECODE_DEAL
-#define PACE_DECODE_DEAL 2
-#endif
-#ifndef PACE_DECODE_TRANSPOSED
-#define PACE_DECODE_TRANSPOSED 1
-#endif
-#ifndef PACE_DECODE_DEAL_HALF
-#define PACE_DECODE_DEAL_HALF 1
-#endif
-  constexpr int DG = (MT >= 2 && NS >= 2) ? NS : (MT == 1 ? (NS == 4 ? PACE_DECODE_DEAL_HALF : PACE_DECODE_DEAL) : 1);
+  constexpr int DG = (MT >= 2 && NS >= 2) ? NS : (MT == 1 ? (NS == 4 ? 1 : 2) : 1);
   constexpr int SL = NS / DG;
   constexpr int TW = kChunk / SL;  // keys of a chunk one warp works on
   constexpr int NT = TW / 8;                              // score n-tiles per warp
@@ -399,20 +387,6 @@ __global__ void __launch_bounds__(threads_of(UMMA, UMMA ? 8 : MT * NS), (!UMMA &
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int Hkv = p.kv.n_kv_heads, P = p.kv.page_tokens, G = p.G;
-#ifdef PACE_TIMING
-  // (measurement builds only: the stamps land behind the partial records, so the caller must pass a
-  // workspace some 64 KB larger than pace_attn_workspace_bytes asks for)
-  unsigned long long* stamps = reinterpret_cast<unsigned long long*>(p.parts + (size_t)gridDim.x * 2 * REC) + blockIdx.x * 8;
-#define PACE_STAMP(i) do { unsigned long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_)); stamps[i] = t_; } while (0)
-  unsigned long long* trace = reinterpret_cast<unsigned long long*>(p.parts + (size_t)gridDim.x * 2 * REC) + gridDim.x * 8;
-#define PACE_TRACE(k, i) do { if (blockIdx.x == 7 && (i) < 64) { unsigned long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_)); trace[(k) * 64 + (i)] = t_; } } while (0)
-#define PACE_CLK(k, i) do { if (blockIdx.x == 7 && tid == 0 && (i) < 64) trace[(k) * 64 + (i)] = (unsigned long long)clock64(); } while (0)
-  if (tid == 0) PACE_STAMP(0);
-#else
-#define PACE_TRACE(k, i) do {} while (0)
-#define PACE_CLK(k, i) do {} while (0)
-#define PACE_STAMP(i) do {} while (0)
-#endif
 
   // ---- prologue, part 1: what depends on nothing an earlier kernel wrote.  Barrier set-up and the
   // zero fill of the V slots (rows no copy ever writes are multiplied by p = 0 and must not hold NaN
@@ -546,7 +520,6 @@ __global__ void __launch_bounds__(threads_of(UMMA, UMMA ? 8 : MT * NS), (!UMMA &
         }
         qs = n > 0;
       }
-      if (lane == 0) PACE_STAMP(6);
       if (lane == 0) {
         misc[3] = n;
         misc[7] = qs;
@@ -569,7 +542,6 @@ __global__ void __launch_bounds__(threads_of(UMMA, UMMA ? 8 : MT * NS), (!UMMA &
                                                         (size_t)h0s * p.pend_sh + (lane & 1) * 64));
       }
       gdc_wait();  // (early K/V: the page copies above are out; what follows reads the step's own inputs)
-      if (lane == 0) PACE_STAMP(7);
       if (qs) {
         const int q_rows = min(MR, p.q_len * G);
         for (int r = lane; r < q_rows; r += 32) {
@@ -706,9 +678,6 @@ __global__ void __launch_bounds__(threads_of(UMMA, UMMA ? 8 : MT * NS), (!UMMA &
       sb_S[b] = p.q_lens ? min(p.q_lens[b], p.q_len) : p.q_len;
     }
   }
-  if (tid == 0) PACE_TRACE(3, 0);
-  if (tid == 0) PACE_TRACE(3, 1);
-  if (tid == 0) PACE_TRACE(3, 2);
 #pragma unroll
   for (int r = 0; r < (kMaxItems + NTHR - 1) / NTHR; ++r) {
     const int b = tid + r * NTHR;
@@ -720,7 +689,6 @@ __global__ void __launch_bounds__(threads_of(UMMA, UMMA ? 8 : MT * NS), (!UMMA &
   fence_proxy_async();  // generic-proxy zero fill before async-proxy (TMA) writes to the same bytes
   // an earlier launch on this pool ran out of patience: nothing is attempted until the host clears that
   if (__syncthreads_or(pool_gave_up(status_word))) return;
-  if (tid == 0) PACE_TRACE(3, 3);
   int saw_empty = 0;
   for (int it = tid; it < n_items; it += NTHR) {
     const int b = p.n_qt == 1 ? it : it / p.n_qt, qt = it - b * p.n_qt;
@@ -739,7 +707,6 @@ __global__ void __launch_bounds__(threads_of(UMMA, UMMA ? 8 : MT * NS), (!UMMA &
     if (n > 0) atomicMax(&misc[2], n / Hkv);
   }
   const int any_empty = __syncthreads_or(saw_empty);
-  if (tid == 0) PACE_TRACE(3, 4);
   if (warp == 0) {
     int carry = 0;
     for (int base = 0; base < n_items; base += 32) {
@@ -756,7 +723,6 @@ __global__ void __launch_bounds__(threads_of(UMMA, UMMA ? 8 : MT * NS), (!UMMA &
     if (lane == 0) prefix[0] = 0;
   }
   __syncthreads();
-  if (tid == 0) PACE_TRACE(3, 5);
   T = prefix[n_items];
   NC = (long long)gridDim.x < T ? (int)gridDim.x : (int)T;
   small = (T + 1) * (NC + 1) < (1LL << 31);
@@ -800,8 +766,6 @@ __global__ void __launch_bounds__(threads_of(UMMA, UMMA ? 8 : MT * NS), (!UMMA &
   if (x1 <= x0) return;
   n_my = (int)(x1 - x0);
   }  // general prologue
-  if (tid == 0) PACE_STAMP(1);
-  if (tid == 0) PACE_TRACE(3, 6);
 
   if (warp == NW) {
     // ================================ producer ================================
@@ -828,7 +792,6 @@ __global__ void __launch_bounds__(threads_of(UMMA, UMMA ? 8 : MT * NS), (!UMMA &
     int h = rel / nch;
     int j = rel - h * nch;
     const bool whole_pages = p.pages_per_chunk > 0;
-    if (lane == 0) PACE_TRACE(3, 7);
     const int is_v = lane & 1;
     const int hf = (lane >> 1) % HALVES;
     const int pi = whole_pages ? lane / (2 * HALVES) : 0;
@@ -885,7 +848,6 @@ __global__ void __launch_bounds__(threads_of(UMMA, UMMA ? 8 : MT * NS), (!UMMA &
       const bool loaded = pw_slot == slot && lp == 0;  // (short prologue: the first window may be here already)
       pw_slot = -1;
       if (!loaded) pw.start(p.kv, slot, lp, win_step, lane);  // loads in flight while the arithmetic below runs
-      if (lane == 0 && i == 0) PACE_TRACE(3, 8);
       int mode = 0, parts = 1, first_cta = cta, first_slot = 0;
       {
         const long long ub = (long long)prefix[it] + (long long)h * nch, ue = ub + nch;
@@ -899,7 +861,6 @@ __global__ void __launch_bounds__(threads_of(UMMA, UMMA ? 8 : MT * NS), (!UMMA &
       }
       const int q_rows = min(MR, R - r_lo);
       const int c2h = h;
-      if (lane == 0 && i == 0) PACE_TRACE(3, 9);
       if (!UMMA && part_idx > 0) {
         flush_q();
         if (!mbar_wait(q_empty, (part_idx - 1) & 1, abort)) { ok = false; break; }
@@ -934,7 +895,6 @@ __global__ void __launch_bounds__(threads_of(UMMA, UMMA ? 8 : MT * NS), (!UMMA &
         }
         __syncwarp();
         const int pg = pw.get(sub ? lp : lp + pi, lp, lane);
-        if (lane == 0 && i == 0) PACE_TRACE(3, 10);
         if (pend && j == nch - 1) {
           // The unit's final chunk holds the pending row, which has to be in the pool before the copy
           // leaves.  Short prologue: the epilogue warp stored this CTA's rows at the start (one
@@ -973,8 +933,6 @@ __global__ void __launch_bounds__(threads_of(UMMA, UMMA ? 8 : MT * NS), (!UMMA &
             send_q_rows(b, h, r_lo, q_rows, &full_bar[s]);
           }
         }
-        if (lane == 0) PACE_TRACE(0, i);
-        if (lane == 0 && i == n_spec) PACE_STAMP(2);
         if (whole_pages) {
           lp += p.pages_per_chunk;
         } else {
@@ -1032,11 +990,7 @@ __global__ void __launch_bounds__(threads_of(UMMA, UMMA ? 8 : MT * NS), (!UMMA &
     uc.n_my = n_my;
     uc.n_stages = n_stages;
     uc.cta = cta;
-    uc.pair_mode = p.live_max >= kUmmaRows ? PACE_UMMA_FULL_TILE_PAIR_MODE : 1;  // (the wide form pairs nothing)
-#ifdef PACE_TIMING
-    uc.trace = trace;
-    uc.stamps = stamps;
-#endif
+    uc.pair_mode = p.live_max >= kUmmaRows ? 0 : 1;  // (the wide form pairs nothing)
     uc.qsw = qbuf;
     umma_consumer<D, WIDE>(p, uc, tid);
     return;
@@ -1098,14 +1052,11 @@ __global__ void __launch_bounds__(threads_of(UMMA, UMMA ? 8 : MT * NS), (!UMMA &
     const MetaM* meta = &metas[s];
     const int rows = meta->rows, tok0 = meta->tok0, flags = meta->flags, kvs = meta->kvs;
     if (flags & 8) return;  // (short prologue: the producer found nothing to stream)
-    if (tid == 0 && i == 0) PACE_STAMP(3);
-    if (tid == 0) PACE_TRACE(1, i);
-    if (tid == 0 && (flags & 4)) PACE_STAMP(4);
 
     if (flags & 1) {
       // ---- new unit part: Q fragments to registers, per-row visibility limits ----
       const int R = meta->R, r_lo = meta->r_lo, kv_len = meta->kv_len, S = meta->S;
-      tr = MT == 1 && PACE_DECODE_TRANSPOSED && R - r_lo <= 8 && !p.mask;
+      tr = MT == 1 && 1 && R - r_lo <= 8 && !p.mask;
       const uint32_t qb = smem_u32(qbuf) + (uint32_t)(mt * 16) * QS;
       if (tr) {
         // B fragments of Q^T (16 head dimensions x 8 query rows): thread holds row qr, dimensions 2 qc + {0, 1} (+ 8)
@@ -1154,14 +1105,9 @@ __global__ void __launch_bounds__(threads_of(UMMA, UMMA ? 8 : MT * NS), (!UMMA &
     int tw = TW;
     if (SL > 1 && NT > 1 && rows < kChunk) tw = min(TW, (((rows + SL - 1) / SL) + 7) & ~7);
     const int tw0 = (ns % SL) * tw;
-#ifdef PACE_SKIP_MATH
-    const bool mine = false;  // (measurement builds: the ring alone, no arithmetic)
-#else
     const bool mine = (i % DG) == (ns / SL);
-#endif
     if (mine && tw0 < rows && mt * 16 < fin.live) {
       const uint32_t kb = smem_u32(st), vb = kb + KVB;
-      PACE_CLK(4, i);
       if (tr) {
         // ---- S^T = K Q^T: my 16 keys x 8 query rows, two accumulators over the k-steps ----
         const int mi = lane >> 3;
@@ -1176,7 +1122,6 @@ __global__ void __launch_bounds__(threads_of(UMMA, UMMA ? 8 : MT * NS), (!UMMA &
             mma16816((k & 1) ? sb : sa, a, qa[k][0], qa[k][1]);
           }
         }
-        PACE_CLK(5, i);
         // sc[0], sc[1]: key qr, query rows 2 qc and 2 qc + 1; sc[2], sc[3]: key qr + 8
         float sc[4];
 #pragma unroll
@@ -1217,7 +1162,6 @@ __global__ void __launch_bounds__(threads_of(UMMA, UMMA ? 8 : MT * NS), (!UMMA &
         }
         // P (keys x query rows) -> B fragments of P^T: one 8x8 transpose per 8 keys
         const uint32_t pb0 = movmatrix_t(f2_to_bf2(p00, p01)), pb1 = movmatrix_t(f2_to_bf2(p10, p11));
-        PACE_CLK(6, i);
         // ---- O^T += V^T P^T: tiles of 16 head dimensions x 8 query rows ----
         {
           const int row = tw0 + (mi >> 1) * 8 + (lane & 7);
@@ -1261,7 +1205,6 @@ __global__ void __launch_bounds__(threads_of(UMMA, UMMA ? 8 : MT * NS), (!UMMA &
           sc[nt][0] = sc[nt][1] = sc[nt][2] = sc[nt][3] = -INFINITY;
         }
       }
-      PACE_CLK(5, i);
       // ---- scale, additive mask, visibility ----
       const int t_base = tok0 + tw0 + 2 * qc;  // key index of sc[0][0]
       const bool need_mask = (tw0 + tw > rows) || (tok0 + tw0 < kvs) || (tok0 + tw0 + tw > min(lim0, lim1));
@@ -1331,7 +1274,6 @@ __global__ void __launch_bounds__(threads_of(UMMA, UMMA ? 8 : MT * NS), (!UMMA &
         pk[nt][0] = f2_to_bf2(p00, p01);
         pk[nt][1] = f2_to_bf2(p10, p11);
       }
-      PACE_CLK(6, i);
       // ---- O += P V ----
       if constexpr (NT == 1) {
 #pragma unroll
@@ -1365,11 +1307,9 @@ __global__ void __launch_bounds__(threads_of(UMMA, UMMA ? 8 : MT * NS), (!UMMA &
       }
       }  // row-major path
     }
-    PACE_CLK(7, i);
     if (flags & 2) fin.last_part = (flags & 4) ? 1 : 0;
     __syncwarp();
     if (lane == 0) mbar_arrive(&empty_bar[s]);
-    if (tid == 0) PACE_TRACE(2, i);
 
     if (flags & 2) {
       // ================= end of a unit part: hand the result to the epilogue warp =================
@@ -1500,7 +1440,6 @@ __global__ void __launch_bounds__(threads_of(UMMA, UMMA ? 8 : MT * NS), (!UMMA &
         // wakes up to leave), which keeps the kernel's tail short
         csync<CTHR>();
         publish_part<D, MR, CTHR, false>(p, fin, rnum, rM, rden, tid, cta, misc);
-        if (tid == 0) PACE_STAMP(5);
       }
     }
     if (flags & 4) break;  // the CTA's last chunk (the short prologue gives the consumers no count)
@@ -1627,7 +1566,7 @@ int launch_mma(MmaParams& p, const CUtensorMap& tmK, const CUtensorMap& tmV, int
   // tcgen05 variant on full tiles: one QK covers the chunks of two neighbouring stages; with an odd ring
   // the last stage has no neighbour, every seventh chunk went alone and the two softmax groups fell out
   // of step for a thousand cycles each time
-  if (UMMA && PACE_UMMA_FULL_TILE_PAIR_MODE == 2 && p.live_max >= MR && (ns & 1)) --ns;
+  if (UMMA && 0 == 2 && p.live_max >= MR && (ns & 1)) --ns;
   p.n_stages = ns;
   const size_t smem_bytes = plan_smem(D, MT, NS, ns, p.live_max, p.batch, n_items, UMMA).total;
   // Early K/V streaming: only the short prologue of whole-unit decode has it, and only when this

@@ -42,17 +42,11 @@ constexpr int kTmemCols = 512;          // the whole tensor memory of the SM:
 constexpr uint32_t kTmemO = 256;        //   [0, 128) S_A S_B, [128, 192) P_A P_B, [192, 256) Q, [256, 512) O_A O_B
 constexpr uint32_t kTmemP = 128, kTmemQ = 192;
 constexpr float kLazyRescale = 8.0f;    // log2 units
-#ifndef PACE_WIDE_POLY_EVERY
-#define PACE_WIDE_POLY_EVERY 2
-#endif
 // Wide form: every n-th pair of a row's scores takes 2^x on the FMA pipe (0: none).  Both groups are in
 // their exp2 phase at the same time there (they wait for the same K/V chunk) and the one exp2 unit per
 // scheduler serves two warps: 1150 cycles per chunk for 2 x 64 exp2 per lane, measured.
-constexpr int kWidePolyEvery = PACE_WIDE_POLY_EVERY;
-#ifndef PACE_SOFTMAX_BACKOFF_NS
-#define PACE_SOFTMAX_BACKOFF_NS 100
-#endif
-constexpr unsigned kSoftmaxBackoffNs = PACE_SOFTMAX_BACKOFF_NS;  // a waiting softmax warp leaves its scheduler's issue slots to the MMA issuer
+constexpr int kWidePolyEvery = 2;
+constexpr unsigned kSoftmaxBackoffNs = 100;  // a waiting softmax warp leaves its scheduler's issue slots to the MMA issuer
 
 struct UmmaCtx {
   unsigned char* ring;    // [n_stages][K | V] as the TMA boxes land
@@ -74,20 +68,7 @@ struct UmmaCtx {
   volatile int* abort;
   int n_my, n_stages, cta;
   int pair_mode;          // QK issuer: 0 one chunk per QK, 1 two when the partner costs no waiting, 2 always two
-#ifdef PACE_TIMING
-  unsigned long long* trace;
-  unsigned long long* stamps;
-#endif
 };
-#ifdef PACE_TIMING
-#define PACE_UTRACE(c, k, i) do { if ((c).cta == 7 && (i) < 64) (c).trace[(k) * 64 + (i)] = (unsigned long long)clock64(); } while (0)
-#define PACE_USTAMP(c, k) do { unsigned long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_)); (c).stamps[k] = t_; } while (0)
-#define PACE_UCLK(c, k, i, v) do { if ((c).cta == 7 && (i) < 64) (c).trace[(k) * 64 + (i)] = (unsigned long long)(v); } while (0)
-#else
-#define PACE_USTAMP(c, k) do {} while (0)
-#define PACE_UCLK(c, k, i, v) do {} while (0)
-#define PACE_UTRACE(c, k, i) do {} while (0)
-#endif
 
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
@@ -304,14 +285,7 @@ __device__ __forceinline__ void umma_issue_qk(const UmmaCtx& c, uint32_t tmem, i
   int part = 0, left = 0;  // chunks left in the current unit part
   int used_a = 0, used_b = 0;  // QKs issued into S_A / S_B
   for (int i = 0; i < c.n_my;) {
-#ifdef PACE_TIMING
-    const long long cq0 = clock64();
-#endif
     if (!issuer_wait(c, &c.full_bar[s], ph)) break;
-#ifdef PACE_TIMING
-    if (lane == 0) PACE_UCLK(c, 12, i, clock64() - cq0);
-    const long long cq1 = clock64();
-#endif
     if (__all_sync(0xffffffffu, left == 0)) {  // first chunk of a unit part: its Q tile
       left = c.metas[s].pad;
       if (__any_sync(0xffffffffu, left < 1) || !issuer_wait(c, c.q_ready, part & 1)) {
@@ -347,9 +321,6 @@ __device__ __forceinline__ void umma_issue_qk(const UmmaCtx& c, uint32_t tmem, i
       }
       __syncwarp();
       ++used_b;
-#ifdef PACE_TIMING
-      if (lane == 0) PACE_UTRACE(c, 8, i);
-#endif
       ++i;
       --left;
       if (++s == c.n_stages) {
@@ -383,10 +354,6 @@ __device__ __forceinline__ void umma_issue_qk(const UmmaCtx& c, uint32_t tmem, i
     const int used_g = g ? used_b : used_a;
     if (used_g > 0 && !issuer_wait(c, &c.s_free[g], (used_g - 1) & 1)) break;
     tc_fence_after();  // the tcgen05.ld that read these buffers are done
-#ifdef PACE_TIMING
-    if (lane == 0) PACE_UCLK(c, 13, i, clock64() - cq1);
-    const long long ck0 = clock64();
-#endif
     const uint32_t k_lo = k_lo0 + (uint32_t)s * (HALF_B >> 4);
     const uint32_t tS = tmem + (uint32_t)g * kChunk;
     const uint32_t idesc = two ? IDESC_QK2 : IDESC_QK1;
@@ -398,10 +365,6 @@ __device__ __forceinline__ void umma_issue_qk(const UmmaCtx& c, uint32_t tmem, i
       if (two) umma_commit(&c.s_full[1]);
     }
     __syncwarp();
-#ifdef PACE_TIMING
-    if (lane == 0) PACE_UCLK(c, 1, i, clock64() - ck0);
-    if (lane == 0) PACE_UTRACE(c, 8, i);
-#endif
     const int n = two ? 2 : 1;
     if (g == 0) ++used_a;
     if (g == 1 || two) ++used_b;
@@ -445,9 +408,6 @@ __device__ __forceinline__ void umma_issue_pv(const UmmaCtx& c, uint32_t tmem, i
       }
     }
     --left;
-#ifdef PACE_TIMING
-    const long long cw0 = clock64();
-#endif
     const uint32_t v_lo = v_lo0 + (uint32_t)s * (KVB >> 4);
     bool ok = true;
     // narrow: the chunk's group; wide: both groups, A then B
@@ -458,10 +418,6 @@ __device__ __forceinline__ void umma_issue_pv(const UmmaCtx& c, uint32_t tmem, i
         break;
       }
       tc_fence_after();  // P was written with tcgen05.st
-#ifdef PACE_TIMING
-      if (lane == 0 && w == 0) PACE_UCLK(c, 3, i, clock64() - cw0);
-      if (lane == 0 && w == 0) PACE_UTRACE(c, 9, i);
-#endif
       const uint32_t tO = tmem + kTmemO + (uint32_t)w * 128, tP = tmem + kTmemP + (uint32_t)w * 32;
       const uint32_t acc0 = (W ? j < 1 : j < 2) ? 0u : 1u;  // a group's first chunk of the part overwrites O
       if (leader) {
@@ -477,9 +433,6 @@ __device__ __forceinline__ void umma_issue_pv(const UmmaCtx& c, uint32_t tmem, i
       else ++used_a;
     }
     if (!ok) break;
-#ifdef PACE_TIMING
-    if (lane == 0 && mine <= 0) PACE_UTRACE(c, 10, i);
-#endif
     ++j;
     if (++s == c.n_stages) {
       s = 0;
@@ -590,7 +543,6 @@ __device__ __forceinline__ void umma_softmax(const MmaParams& p, const UmmaCtx& 
   for (int i0 = 0; i0 < c.n_my;) {
     // ---- new unit part: its record, this thread's share of the Q tile ----
     if (!umma_wait(&c.full_bar[i0 % c.n_stages], (i0 / c.n_stages) & 1, c.abort)) return;
-    if (tid == 0 && i0 == 0) PACE_USTAMP(c, 2);
     ResMeta fin;
     int n_part, kvs, lim, tok0_part;
     bool live;
@@ -679,21 +631,14 @@ __device__ __forceinline__ void umma_softmax(const MmaParams& p, const UmmaCtx& 
         rows = c.metas[s].rows;
         tok0 = c.metas[s].tok0;
       }
-      if (tid == 0) PACE_UTRACE(c, 4, i);
       if (!umma_wait(&c.s_full[wg], cnt & 1, c.abort)) return;
       tc_fence_after();
-      if (tid == 0) PACE_UTRACE(c, 5, i);
-#ifdef PACE_UMMA_NO_SOFTMAX
-      if (false) {
-#else
       if (warp_live) {
-#endif
         // ---- the row's 64 scores: TMEM -> registers ----
         uint32_t sr[2][32];
         tmem_ld32(tS, sr[0]);
         tmem_ld32(tS + 32, sr[1]);
         tmem_wait_ld();
-        if (tid == 0) PACE_UTRACE(c, 14, i);
         // the scores are in registers: the buffer goes back to the QK issuer at once
         tc_fence_before();
         __syncwarp();
@@ -760,12 +705,10 @@ __device__ __forceinline__ void umma_softmax(const MmaParams& p, const UmmaCtx& 
             // The PV of the group's previous chunk has to have read the buffer (its completion is o_full's
             // phase) before the first store; asked for here, half a row's arithmetic after the scores came,
             // the answer is there without waiting.
-            if (tid == 0) PACE_UTRACE(c, 11, i);
             if (cnt > 0) {
               if (!umma_wait(&c.o_full[wg], (cnt - 1) & 1, c.abort)) return;
               tc_fence_after();
             }
-            if (tid == 0) PACE_UTRACE(c, 15, i);
           }
           tmem_st16(tP + hf * 16, pk[hf]);
         }
@@ -775,7 +718,6 @@ __device__ __forceinline__ void umma_softmax(const MmaParams& p, const UmmaCtx& 
           unpack64(l2[1], b0, b1);
           l += (__uint_as_float(a0) + __uint_as_float(a1)) + (__uint_as_float(b0) + __uint_as_float(b1));
         }
-        if (tid == 0) PACE_UTRACE(c, 0, i);
         tmem_wait_st();
       }
       else {
@@ -786,16 +728,13 @@ __device__ __forceinline__ void umma_softmax(const MmaParams& p, const UmmaCtx& 
         if (lane == 0) mbar_arrive(&c.s_free[wg]);
         if (cnt > 0 && !umma_wait(&c.o_full[wg], (cnt - 1) & 1, c.abort)) return;
       }
-      if (tid == 0) PACE_UTRACE(c, 6, i);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&c.p_full[wg]);
-      if (tid == 0) PACE_UTRACE(c, 7, i);
       ++cnt;
     }
 
     // ================= end of a unit part =================
-    if (tid == 0) PACE_USTAMP(c, 3);
     float M = m_used, den = l;
     float* rec = p.parts + ((size_t)c.cta * 2 + (fin.mode == 2 ? 1 : 0)) * REC;
     if constexpr (W) {
@@ -903,7 +842,6 @@ __device__ __forceinline__ void umma_softmax(const MmaParams& p, const UmmaCtx& 
     }
     tc_fence_before();
     i0 += n_part;
-    if (tid == 0) PACE_USTAMP(c, 4);
     if (fin.mode == 0) continue;
     // cut unit: the fp32 partial is in the workspace; arrival count, merge by the last arriver
     if (live && (W || wg == 0)) {
@@ -921,12 +859,10 @@ __device__ __forceinline__ void umma_softmax(const MmaParams& p, const UmmaCtx& 
     }
     if (!group_sync()) return;
     const int is_last = *flag;
-    if (tid == 0) PACE_USTAMP(c, 6);
     if (is_last) {
       __threadfence();
       umma_merge<D, W>(p, fin, tid);
     }
-    if (tid == 0) PACE_USTAMP(c, 7);
   }
 }
 
@@ -955,9 +891,6 @@ __device__ __forceinline__ void umma_consumer(const MmaParams& p, const UmmaCtx&
   } else if (warp == kUmmaPvWarp) umma_issue_pv<D, W>(c, tmem, lane, W ? 0 : -1);
   else umma_softmax<D, W>(p, c, tmem, tid);
   if (lane == 0 && *c.abort) raise_status(p.kv.status, PACE_DEV_WAIT_TIMEOUT);
-#ifdef PACE_TIMING
-  if (tid == 0) { unsigned long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_)); c.stamps[5] = t_; }
-#endif
   tc_fence_before();
   asm volatile("bar.sync 3, 352;" ::: "memory");
   if (owner) {

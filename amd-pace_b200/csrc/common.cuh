@@ -195,9 +195,6 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t by
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
-#ifndef PACE_WAIT_HINT_NS
-#define PACE_WAIT_HINT_NS 1000
-#endif
 // One potentially-blocking probe.  The suspend-time hint lets the hardware park the warp until the
 // phase completes (or the hint runs out) instead of having it spin: a spinning warp keeps taking
 // issue slots from the warps of its scheduler that have work.
@@ -208,7 +205,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
       "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
       "selp.u32 %0, 1, 0, p;\n\t}"
       : "=r"(ok)
-      : "r"(smem_u32(bar)), "r"(parity), "r"((uint32_t)PACE_WAIT_HINT_NS)
+      : "r"(smem_u32(bar)), "r"(parity), "r"((uint32_t)1000)
       : "memory");
   return ok != 0;
 }

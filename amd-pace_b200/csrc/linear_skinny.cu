@@ -38,15 +38,9 @@ constexpr int kLinTokens = 32;   // X rows
 constexpr int kLinWarps = 8;
 constexpr int kLinThreads = kLinWarps * 32 + 32;  // + producer warp
 constexpr int kLinStages = 5;
-#ifndef PACE_LIN_COLS
-#define PACE_LIN_COLS 128
-#endif
-constexpr int kLinCols = PACE_LIN_COLS;              // W columns per chunk: 128 (one CTA per SM) or 64 (two)
+constexpr int kLinCols = 128;              // W columns per chunk: 128 (one CTA per SM) or 64 (two)
 constexpr int kLinCtasPerSm = kLinCols == 128 ? 1 : 2;
-#ifndef PACE_LIN_EARLY
-#define PACE_LIN_EARLY 5
-#endif
-constexpr int kLinEarlyStages = PACE_LIN_EARLY;      // ring stages filled with W before the wait for the kernel in front
+constexpr int kLinEarlyStages = 5;      // ring stages filled with W before the wait for the kernel in front
 
 template <int COLS>
 struct LinShape {
@@ -64,20 +58,7 @@ struct LinParams {
   int32_t* status;    // optional sticky status word (PACE_DEV_WAIT_TIMEOUT)
   int M, N, K;
   int64_t y_stride;   // elements between rows of Y
-#ifdef PACE_LIN_TIMING
-  unsigned long long* dbg;  // [cta][8] globaltimer stamps (development builds only)
-#endif
 };
-#ifdef PACE_LIN_TIMING
-__device__ __forceinline__ void lin_stamp(const LinParams& p, int k) {
-  unsigned long long t;
-  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-  if (p.dbg) p.dbg[blockIdx.x * 8 + k] = t;
-}
-#define LIN_STAMP(k) lin_stamp(p, k)
-#else
-#define LIN_STAMP(k)
-#endif
 
 __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* tm, int c0, int c1, uint64_t* bar) {
   asm volatile(
@@ -139,7 +120,6 @@ __global__ void __launch_bounds__(kLinThreads, (COLS == 128 ? 1 : 2))
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmX)) : "memory");
   }
   __syncthreads();
-  if (tid == 0) LIN_STAMP(0);
   if (cta >= NC) {
     asm volatile("griddepcontrol.wait;" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
@@ -164,11 +144,9 @@ __global__ void __launch_bounds__(kLinThreads, (COLS == 128 ? 1 : 2))
     };
     if (lane == 0)
       for (int i = 0; i < early; ++i) issue_w(i);
-    if (lane == 0) LIN_STAMP(1);
     asm volatile("griddepcontrol.wait;" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     if (lane == 0) {
-      LIN_STAMP(2);
       for (int i = 0; i < ahead; ++i) {
         if (i >= early) issue_w(i);
         const int kc = (int)((x0 + i) % k_chunks);
@@ -221,7 +199,6 @@ __global__ void __launch_bounds__(kLinThreads, (COLS == 128 ? 1 : 2))
       if (lane == 0) raise_status(p.status, PACE_DEV_WAIT_TIMEOUT);
       break;  // the abort flag is up: every warp leaves its loop and meets the others at the barrier below
     }
-    if (tid == 0 && i == 0) LIN_STAMP(3);
     const long long x = x0 + i;
     const int nt = (int)(x / k_chunks), kc = (int)(x - (long long)nt * k_chunks);
     const uint32_t wb = smem_u32(ring + (size_t)s * S::kStage), xb = wb + S::kStageW;
@@ -281,7 +258,6 @@ __global__ void __launch_bounds__(kLinThreads, (COLS == 128 ? 1 : 2))
     seg_chunks = 0;
   }
   // ---- settle the row tiles this CTA holds a part of ----
-  if (tid == 0) LIN_STAMP(4);
   __threadfence();     // my reductions are performed before the counter says so
   consumer_barrier();  // ... and so are everybody else's of this CTA
   if (*abort) return;
@@ -294,7 +270,6 @@ __global__ void __launch_bounds__(kLinThreads, (COLS == 128 ? 1 : 2))
     }
   }
   consumer_barrier();
-  if (tid == 0) LIN_STAMP(5);
   // A complete tile sits in the workspace as 128 features x 32 tokens; a thread takes half a feature's
   // row.  Both tiles' loads are in flight before anything is stored: one round trip, not two.
   const bool conv0 = misc[1] != 0, conv1 = part_nt1 >= 0 && misc[2] != 0;
@@ -328,7 +303,6 @@ __global__ void __launch_bounds__(kLinThreads, (COLS == 128 ? 1 : 2))
       if (tok < p.M) p.y[(size_t)tok * p.y_stride + f] = __float2bfloat16(v[j][q]);
     }
   }
-  if (tid == 0) LIN_STAMP(6);
 }
 
 typedef CUresult (*EncodeFn2)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
@@ -382,10 +356,6 @@ int g_n_wmaps = 0, g_next_wmap = 0;
 
 using namespace pace;
 
-#ifdef PACE_LIN_TIMING
-static unsigned long long* g_lin_dbg = nullptr;
-extern "C" void pace_linear_debug_buffer(void* base) { g_lin_dbg = (unsigned long long*)base; }
-#endif
 
 extern "C" uint64_t pace_linear_workspace_bytes(int32_t n_max) {
   if (n_max <= 0) return 0;
@@ -429,10 +399,6 @@ extern "C" int pace_linear_skinny(const void* x, int64_t x_stride, const void* w
   p.status = status;
   p.M = M; p.N = N; p.K = K;
   p.y_stride = y_stride;
-#ifdef PACE_LIN_TIMING
-  p.dbg = g_lin_dbg;
-  if (g_lin_dbg) g_lin_dbg += 148 * 2 * 8;
-#endif
   int dev = 0, sms = 148;
   PACE_CUDA_TRY(cudaGetDevice(&dev));
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);

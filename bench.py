@@ -151,11 +151,34 @@ def run_reference(args, rank):
     print(json.dumps(line), flush=True)
 
 
+def gpu_local_cores(local_rank: int):
+    """Cores NVML reports as local to this rank's GPU (its NUMA node), or None when NVML cannot say.
+    Reading only: nothing on the GPU is set."""
+    try:
+        import pynvml
+        pynvml.nvmlInit()
+        visible = os.environ.get("CUDA_VISIBLE_DEVICES")
+        index = local_rank
+        if visible:
+            ids = [v.strip() for v in visible.split(",") if v.strip()]
+            if local_rank < len(ids) and ids[local_rank].isdigit():
+                index = int(ids[local_rank])
+        h = pynvml.nvmlDeviceGetHandleByIndex(index)
+        words = (os.cpu_count() + 63) // 64
+        mask = pynvml.nvmlDeviceGetCpuAffinity(h, words)
+        cores = [w * 64 + b for w, m in enumerate(mask) for b in range(64) if (int(m) >> b) & 1]
+        return cores or None
+    except Exception:
+        return None
+
+
 def pin_rank_to_cores(local_rank: int, world: int):
     """Each rank keeps its own slice of the cores this process may run on - set before the CUDA context
     and the pinned buffers exist, so that the rank's copies are driven from, and its pinned memory is
     allocated near, cores no other rank uses (the reference's workers pin themselves the same way,
-    pace/utils/worker.py:49-62).  Returns the slice."""
+    pace/utils/worker.py:49-62).  Where NVML names the cores local to the rank's GPU the slice is cut from
+    those (the GPUs of one NUMA node share them in rank order): pinned buffers first touched on the far
+    socket make every copy cross the inter-socket link.  Returns the slice."""
     try:
         allowed = sorted(os.sched_getaffinity(0))
     except AttributeError:
@@ -164,6 +187,19 @@ def pin_rank_to_cores(local_rank: int, world: int):
         return allowed
     per = len(allowed) // world
     mine = allowed[local_rank * per:(local_rank + 1) * per]
+    try:
+        local = gpu_local_cores(local_rank)
+        if local:
+            near = [c for c in allowed if c in set(local)]
+            # ranks whose GPUs report the same core set share it in rank order
+            same = [r for r in range(world) if (gpu_local_cores(r) or []) == local]
+            if len(near) >= len(same) >= 1 and local_rank in same:
+                share = len(near) // len(same)
+                k = same.index(local_rank)
+                if share >= 1:
+                    mine = near[k * share:(k + 1) * share]
+    except Exception:
+        pass
     try:
         os.sched_setaffinity(0, mine)
     except OSError:

@@ -148,6 +148,41 @@ def test_large_tiles_ragged_counts_and_left_padding():
     mgr.pool.check_status()
 
 
+@pytest.mark.parametrize("D,Hq,Hkv,S,lens,q_lens,pads", [
+    # 256-row units (two 128-row tiles share every K/V chunk): ragged query counts, left pads, a last unit whose
+    # second tile is empty (q_len 70 x G 4 = 280 rows), a sequence with a single query token
+    (128, 16, 4, 160, [700, 170, 330, 160], [160, 70, 1, 160], [0, 23, 100, 0]),
+    # head_dim 64, G = 8: 130 tokens = 1040 rows = four full units and 16 rows
+    (64, 16, 2, 130, [600, 131], [130, 97], [5, 0]),
+    # MHA (G = 1), exactly 256 rows, lengths at chunk boundaries
+    (128, 4, 4, 256, [256, 320, 1024], [256, 256, 64], [0, 64, 0]),
+])
+def test_wide_units_ragged_counts_and_left_padding(D, Hq, Hkv, S, lens, q_lens, pads):
+    from pace_b200.llm.cache import KVCacheManager, KVCacheType
+    from pace_b200.ops import MultiHeadAttention
+    g = torch.Generator().manual_seed(D + S + Hq)
+    B = len(lens)
+    ks = [torch.randn(Hkv, L, D, generator=g).bfloat16().to(DEV) for L in lens]
+    vs = [torch.randn(Hkv, L, D, generator=g).bfloat16().to(DEV) for L in lens]
+    q = torch.randn(B, S, Hq, D, generator=g).bfloat16().to(DEV).transpose(1, 2)
+    mgr = KVCacheManager(Cfg(1), max(lens) + 64, KVCacheType.BMC)
+    K, V = _fill(mgr, 0, ks, vs)
+    mha = MultiHeadAttention()
+    kw = dict(kv_start=torch.tensor(pads, dtype=torch.int32, device=DEV),
+              q_lens=torch.tensor(q_lens, dtype=torch.int32, device=DEV))
+    out = mha(q, K, V, **kw)
+    want = _oracle(q, ks, vs, left_pad=pads, q_lens=q_lens)
+    for b in range(B):
+        _check(out[b, :, : q_lens[b]], want[b])
+    # the same launch on a share of the GPU (units cut across few thread blocks, the cross-block merge of
+    # 256-row records) gives the same numbers within the parity budget
+    for ctas in (1, 5, 37):
+        part = mha(q, K, V, max_ctas=ctas, **kw)
+        for b in range(B):
+            _check(part[b, :, : q_lens[b]], want[b])
+    mgr.pool.check_status()
+
+
 def test_batch_larger_than_one_launch_on_unlisted_slots():
     """260 sequences x 5 query tiles are more work items than one launch takes: the batch goes out in two
     launches, and on a manager that owns its pool (slots 0..B-1, no slot list is passed) the second
