@@ -315,7 +315,7 @@ def run_ours(args, rank, world, local_rank):
     host_in = torch.empty(kvq.shape, dtype=kvq.dtype).pin_memory()
     host_in.copy_(kvq.cpu())
     host_out = torch.empty(out_all.shape, dtype=out_all.dtype).pin_memory()
-    n_chunks = int(os.environ.get("PACE_E2E_CHUNKS", "8")) if L % 8 == 0 else 1
+    n_chunks = 8 if L % 8 == 0 else 1   # (copies in growing chunks - 1, 2, 4, 8, 17 layers - measured slower: 1.17 ms per step)
     per = L // n_chunks
     copy_in, copy_out = torch.cuda.Stream(), torch.cuda.Stream()
 
