@@ -990,7 +990,6 @@ __global__ void __launch_bounds__(threads_of(UMMA, UMMA ? 8 : MT * NS), (!UMMA &
     uc.n_my = n_my;
     uc.n_stages = n_stages;
     uc.cta = cta;
-    uc.pair_mode = p.live_max >= kUmmaRows ? 0 : 1;  // (the wide form pairs nothing)
     uc.qsw = qbuf;
     umma_consumer<D, WIDE>(p, uc, tid);
     return;
@@ -1563,10 +1562,6 @@ int launch_mma(MmaParams& p, const CUtensorMap& tmK, const CUtensorMap& tmV, int
   int ns = kMaxStagesM;
   while (ns >= 2 && plan_smem(D, MT, NS, ns, p.live_max, p.batch, n_items, UMMA).total > budget) --ns;
   if (ns < 2) return PACE_ERR_UNSUPPORTED;
-  // tcgen05 variant on full tiles: one QK covers the chunks of two neighbouring stages; with an odd ring
-  // the last stage has no neighbour, every seventh chunk went alone and the two softmax groups fell out
-  // of step for a thousand cycles each time
-  if (UMMA && 0 == 2 && p.live_max >= MR && (ns & 1)) --ns;
   p.n_stages = ns;
   const size_t smem_bytes = plan_smem(D, MT, NS, ns, p.live_max, p.batch, n_items, UMMA).total;
   // Early K/V streaming: only the short prologue of whole-unit decode has it, and only when this

@@ -35,7 +35,7 @@ namespace {
 constexpr int kUmmaRows = 128;          // query rows per tile (UMMA M)
 constexpr int kUmmaSoftmaxThreads = 256;  // two warpgroups
 // Warps 0-7: softmax; 8: producer; 9: QK issuer (of group A's chunks when the work is split); 10: PV issuer;
-// 11: narrow form on full tiles: QK issuer of group B's chunks; wide form: PV issuer of group B.  (Issuers on warps 10 and 11, away from
+// 11: narrow form: QK issuer of group B's chunks; wide form: PV issuer of group B.  (Issuers on warps 10 and 11, away from
 // the schedulers of the softmax warps that hold a verify tile's live rows, measured the same.)
 constexpr int kUmmaQkWarp = 9, kUmmaPvWarp = 10, kUmmaWarpB = 11;
 constexpr int kTmemCols = 512;          // the whole tensor memory of the SM:
@@ -67,7 +67,6 @@ struct UmmaCtx {
   int* flag;              // "this CTA arrived last" broadcast
   volatile int* abort;
   int n_my, n_stages, cta;
-  int pair_mode;          // QK issuer: 0 one chunk per QK, 1 two when the partner costs no waiting, 2 always two
 };
 
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
@@ -252,27 +251,22 @@ __device__ __forceinline__ bool issuer_wait(const UmmaCtx& c, uint64_t* bar, uin
   *c.abort = 1;
   return false;
 }
-__device__ __forceinline__ bool issuer_probe(uint64_t* bar, uint32_t parity) {
-  return __all_sync(0xffffffffu, mbar_test_wait(bar, parity));
-}
 __device__ __forceinline__ bool elect_one() {
   uint32_t pred;
   asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(pred));
   return pred != 0;
 }
 
-// mine: -1 = this warp issues every QK (chunks may pair); 0 / 1 = only the chunks of group A / B, one
-// chunk per QK (full tiles: the loop's fixed cost - barrier probes, votes, fences, the commit - is about
-// as long as the MMAs themselves, and one warp walking every chunk paced the whole pipeline).
+// Narrow form: mine = 0 / 1, this warp issues the QK of group A's / B's chunks (the loop's fixed cost -
+// barrier waits, votes, fences, the commit - is about as long as the MMAs themselves, and one warp walking
+// every chunk paced the whole pipeline).
 // Wide form (W): warp 9 issues both tiles' QK of every chunk: tile A's Q from tensor memory into S_A, tile B's
 // from shared memory into S_B.
 template <int D, bool W>
 __device__ __forceinline__ void umma_issue_qk(const UmmaCtx& c, uint32_t tmem, int lane, int mine) {
   constexpr int HALF_B = kChunk * 128;
-  constexpr uint32_t IDESC_QK1 = umma_idesc(kChunk, false), IDESC_QK2 = umma_idesc(2 * kChunk, false);
-  // Ring layout: [K column block 0 of every stage][K column block 1 ...][V of every stage].  The K rows
-  // of stages s and s + 1 are contiguous, so one set of MMAs with N = 128 computes the scores of two
-  // chunks into two adjacent score buffers whenever neither the ring nor the buffers wrap in between.
+  constexpr uint32_t IDESC_QK1 = umma_idesc(kChunk, false);
+  // Ring layout: [K column block 0 of every stage][K column block 1 ...][V of every stage].
   // Descriptors differ from one instruction to the next only in the start-address field (units of
   // 16 bytes): everything else is folded into constants.
   const uint32_t k_lo0 = (smem_u32(c.ring) >> 4) | (1u << 16);  // K-major: LBO unused (1)
@@ -330,48 +324,29 @@ __device__ __forceinline__ void umma_issue_qk(const UmmaCtx& c, uint32_t tmem, i
       continue;
     }
     const int g = i & 1;
-    if (mine >= 0 && g != mine) {  // the other QK issuer's chunk: only keep the ring position in step
-      ++i;
-      --left;
-      if (++s == c.n_stages) {
-        s = 0;
-        ph ^= 1;
-      }
-      continue;
-    }
-    // An even chunk and its odd neighbour with one set of MMAs (N = 128 over S_A and S_B).  Short streams
-    // (verify: mostly padding rows, a dozen chunks) pair only when the second chunk costs no waiting: its K
-    // has landed and group B has taken its previous scores already.
-    bool two = mine < 0 && c.pair_mode != 0 && g == 0 && __all_sync(0xffffffffu, left >= 2) && s + 1 < c.n_stages;
-    if (two) {
-      if (c.pair_mode == 2) {
-        if (!issuer_wait(c, &c.full_bar[s + 1], ph)) break;
-        if (used_b > 0 && !issuer_wait(c, &c.s_free[1], (used_b - 1) & 1)) break;
-      } else {
-        two = issuer_probe(&c.full_bar[s + 1], ph) && (used_b == 0 || issuer_probe(&c.s_free[1], (used_b - 1) & 1));
-      }
-    }
-    const int used_g = g ? used_b : used_a;
-    if (used_g > 0 && !issuer_wait(c, &c.s_free[g], (used_g - 1) & 1)) break;
-    tc_fence_after();  // the tcgen05.ld that read these buffers are done
-    const uint32_t k_lo = k_lo0 + (uint32_t)s * (HALF_B >> 4);
-    const uint32_t tS = tmem + (uint32_t)g * kChunk;
-    const uint32_t idesc = two ? IDESC_QK2 : IDESC_QK1;
-    if (leader) {
+    if (g == mine) {
+      // narrow form: the chunk belongs to this issuer's group (the other issuer's chunks only move the
+      // ring position along).  Pairing two chunks per QK (N = 128 over S_A and S_B) was tried in three
+      // forms - always, when the partner costs no waiting, never - and never is the fastest on verify and
+      // prefill tiles alike.
+      const int used_g = g ? used_b : used_a;
+      if (used_g > 0 && !issuer_wait(c, &c.s_free[g], (used_g - 1) & 1)) break;
+      tc_fence_after();  // the tcgen05.ld that read this buffer are done
+      const uint32_t k_lo = k_lo0 + (uint32_t)s * (HALF_B >> 4);
+      const uint32_t tS = tmem + (uint32_t)g * kChunk;
+      if (leader) {
 #pragma unroll
-      for (int kk = 0; kk < D / 16; ++kk)
-        umma_bf16_ts(tS, tQ + kk * 8, pack64(k_lo + (kk >> 2) * k_half + (kk & 3) * 2, kDescHi), idesc, kk ? 1u : 0u);
-      umma_commit(&c.s_full[g]);
-      if (two) umma_commit(&c.s_full[1]);
+        for (int kk = 0; kk < D / 16; ++kk)
+          umma_bf16_ts(tS, tQ + kk * 8, pack64(k_lo + (kk >> 2) * k_half + (kk & 3) * 2, kDescHi), IDESC_QK1, kk ? 1u : 0u);
+        umma_commit(&c.s_full[g]);
+      }
+      __syncwarp();
+      if (g == 0) ++used_a;
+      else ++used_b;
     }
-    __syncwarp();
-    const int n = two ? 2 : 1;
-    if (g == 0) ++used_a;
-    if (g == 1 || two) ++used_b;
-    i += n;
-    left -= n;
-    s += n;
-    if (s >= c.n_stages) {
+    ++i;
+    --left;
+    if (++s == c.n_stages) {
       s = 0;
       ph ^= 1;
     }
@@ -883,11 +858,10 @@ __device__ __forceinline__ void umma_consumer(const MmaParams& p, const UmmaCtx&
   asm volatile("bar.sync 3, 352;" ::: "memory");
   tc_fence_after();
   const uint32_t tmem = *reinterpret_cast<volatile uint32_t*>(c.tmem_slot);
-  const bool split_qk = !W && c.pair_mode == 0;
-  if (warp == kUmmaQkWarp) umma_issue_qk<D, W>(c, tmem, lane, split_qk ? 0 : -1);
+  if (warp == kUmmaQkWarp) umma_issue_qk<D, W>(c, tmem, lane, 0);
   else if (warp == kUmmaWarpB) {
     if (W) umma_issue_pv<D, W>(c, tmem, lane, 1);
-    else if (split_qk) umma_issue_qk<D, W>(c, tmem, lane, 1);
+    else umma_issue_qk<D, W>(c, tmem, lane, 1);
   } else if (warp == kUmmaPvWarp) umma_issue_pv<D, W>(c, tmem, lane, W ? 0 : -1);
   else umma_softmax<D, W>(p, c, tmem, tid);
   if (lane == 0 && *c.abort) raise_status(p.kv.status, PACE_DEV_WAIT_TIMEOUT);
