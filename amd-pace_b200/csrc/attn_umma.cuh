@@ -222,7 +222,7 @@ __device__ __forceinline__ bool umma_wait(uint64_t* bar, uint32_t parity, volati
       break;
     }
     if (*abort) break;
-    __nanosleep(i > 64 ? 256 : kSoftmaxBackoffNs);
+    if (i >= 8) __nanosleep(i > 64 ? 256 : kSoftmaxBackoffNs);  // (the first probes back to back: most waits are nearly over)
   }
   if (!ok) *abort = 1;
   return __all_sync(0xffffffffu, ok);
