@@ -76,3 +76,33 @@ def test_continuous_batching_serves_every_request_and_returns_every_page():
     assert [o[0] for o in outs2] == [o[0] for o in outs[:3]]
     with pytest.raises(RuntimeError, match="does not fit the KV pool"):
         cb.run([torch.randint(1, 97, (590,))], 600)
+
+
+def test_router_in_front_of_the_continuous_batcher():
+    """Requests arrive concurrently at the batch-window router (the reference's router logic without its HTTP
+    hops, pace/server/router.py:112-225) and are served by the continuous batcher on the paged pool: every
+    request gets its own number of tokens, and the same tokens as when the batcher is called directly."""
+    import asyncio
+    from pace_b200.llm.router import BatchWindowRouter, CompletionRequest, batcher_backend
+    from pace_b200.llm.serving import ContinuousBatcher
+    model = _model()
+    g = torch.Generator().manual_seed(10)
+    lens, new = [120, 9, 260, 64, 33, 75], [5, 3, 7, 1, 4, 6]
+    prompts = [torch.randint(1, 97, (n,), generator=g) for n in lens]
+    cb = ContinuousBatcher(model, pool_tokens=64 * 16, max_batch=4, max_seq_len=400, prefill_chunk=128)
+    direct, _ = cb.run(prompts, max(new))
+
+    async def main():
+        r = BatchWindowRouter(batcher_backend(cb), ["llama"], max_batch_size=4, batch_timeout=0.2)
+        await r.start()
+        outs = await asyncio.gather(*(r.complete(CompletionRequest("llama", p.tolist(), max_tokens=n))
+                                      for p, n in zip(prompts, new)))
+        await r.stop()
+        return r.batches, outs
+    batches, outs = asyncio.run(main())
+    assert batches == [4, 2]
+    for i, o in enumerate(outs):
+        ids = o["choices"][0]["token_ids"]
+        assert len(ids) == new[i] and o["usage"]["prompt_tokens"] == lens[i], o["choices"][0]["text"]
+        assert ids[0] == direct[i][0]                         # the first token never depends on batch mates
+    assert cb.pool.query()[0] == 0 and cb.reserved_pages == 0
