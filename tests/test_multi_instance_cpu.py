@@ -94,14 +94,17 @@ def test_workers_pull_batches_and_a_dead_worker_is_noticed():
     assert agg > 0
 
 
-def _serve_dispatched(state, ip_queue, op_queue):
+def _serve_dispatched(state, ip_queue, op_queue, second_item_taken):
     seen = []
 
     def work(item):
         seen.append(item)
         if state["id"] == 0 and len(seen) == 2:
+            second_item_taken.set()
             time.sleep(0.3)                                # (its announcement of the item has left the process by now)
             os._exit(17)                                   # worker 0 is lost with its second item in hand
+        if state["id"] == 1 and len(seen) == 1:
+            second_item_taken.wait(60)                     # the survivor does not empty the queue before that happens
         time.sleep(0.05)
         return (state["id"], item * item)
     serve_items(state["id"], ip_queue, op_queue, work)
@@ -113,8 +116,8 @@ def test_dispatcher_hands_a_dead_workers_item_out_again():
     notices, hands the item it held to the survivor, and every item gets its one result; no wait is
     without a time limit."""
     ctx = mp.get_context("spawn")
-    ip, op = ctx.Queue(), ctx.Queue()
-    workers = [Worker(i, None, _init, (i,), _serve_dispatched, (ip, op), device_index=None, ctx=ctx) for i in range(2)]
+    ip, op, taken = ctx.Queue(), ctx.Queue(), ctx.Event()
+    workers = [Worker(i, None, _init, (i,), _serve_dispatched, (ip, op, taken), device_index=None, ctx=ctx) for i in range(2)]
     pool = MultipleProcesses(workers)
     pool.run()
     disp = Dispatcher(pool, ip, op, list(range(8)), poll_s=0.2)
