@@ -110,7 +110,7 @@ __device__ __forceinline__ uint32_t movmatrix_t(uint32_t a) {
   asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(d) : "r"(a));
   return d;
 }
-// tiled TMA load of one box, completion on an mbarrier (no multicast)
+// tiled TMA load of one box into this CTA, completion on an mbarrier
 __device__ __forceinline__ void tma_load_4d(void* smem_dst, const CUtensorMap* tm, int c0, int c1, int c2, int c3,
                                             uint64_t* bar) {
   asm volatile(
