@@ -140,3 +140,41 @@ def test_result_does_not_depend_on_the_partition_or_the_order_of_cached_tokens()
         _close(base[b].cpu(), want, ("oracle", b))
     mgr.pool.check_status()
     mgr.release()
+
+
+def test_chunked_prefill_equals_one_pass_at_size():
+    """Config-3 shape (batch 8, 32 / 8 heads of 128, 512-token chunks): a 1024-token stretch of the prompt
+    attended as two chunks of 512 (the second one sees the first through the cache) gives what one pass of
+    1024 query tokens gives, and a chunk's first rows do not depend on its later ones (causality) - the wide
+    tcgen05 form against itself across different unit boundaries, and against the launch cut over 5 thread
+    blocks."""
+    from pace_b200.llm.cache import KVCacheManager, KVCacheType
+    from pace_b200.ops import MultiHeadAttention
+    g = torch.Generator(device=DEV).manual_seed(24)
+    Bp, past, S = 8, 1536, 1024
+    mgr = KVCacheManager(Cfg(2), past + S + 8, KVCacheType.BMC)
+    mha = MultiHeadAttention()
+    k = torch.randn(Bp, HKV, past + S, D, device=DEV, generator=g, dtype=torch.float32).bfloat16()
+    v = torch.randn(Bp, HKV, past + S, D, device=DEV, generator=g, dtype=torch.float32).bfloat16()
+    q = torch.randn(Bp, S, HQ, D, device=DEV, generator=g, dtype=torch.float32).bfloat16().transpose(1, 2)
+    for lo in range(0, past, 512):
+        for l in range(2):
+            mgr[l].update_cache(k[:, :, lo:lo + 512], v[:, :, lo:lo + 512], concat_dim=2)
+    # layer 0: two chunks of 512; layer 1: one pass of 1024
+    outs = []
+    for c in range(2):
+        lo = past + 512 * c
+        K, V = mgr[0].update_cache(k[:, :, lo:lo + 512], v[:, :, lo:lo + 512], concat_dim=2)
+        outs.append(mha(q[:, :, 512 * c:512 * (c + 1)], K, V))
+    K, V = mgr[1].update_cache(k[:, :, past:], v[:, :, past:], concat_dim=2)
+    whole = mha(q, K, V)
+    _close(torch.cat(outs, dim=2), whole, "two chunks against one pass")
+    _close(mha(q, K, V, max_ctas=5), whole, "one pass on 5 thread blocks")
+    # causality: the first 300 query tokens alone (ragged count) see exactly what they saw inside the pass
+    q_lens = torch.full((Bp,), 300, dtype=torch.int32, device=DEV)
+    mgr.remove_cache(S - 300)
+    K0, V0 = mgr[1].key, mgr[1].value
+    head = mha(q[:, :, :300], K0, V0, q_lens=q_lens)
+    _close(head, whole[:, :, :300], "prefix of the pass")
+    mgr.pool.check_status()
+    mgr.release()
