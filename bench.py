@@ -519,7 +519,11 @@ def run_ours(args, rank, world, local_rank):
                        "tflops_best_single_launch": a["tensor"]["achieved_tflops_best_single_launch"],
                        "best_single_launch_frac_of_measured_burst": a["tensor"]["best_single_launch_frac_of_measured_burst"],
                        "shape": f"B={a['batch']} q_len={a['q_len']} kv_len={a['kv_len']}"}
+        lin = linear_measure()["shapes"]
+        aux["linear_skinny"] = {k: {"us": v["us_skinny"], "us_library_gemm": v["us_library"], "hbm_frac_of_measured": v["frac_skinny"],
+                                    "library_gemm_hbm_frac_of_measured": v["frac_library"]} for k, v in lin.items()}
         line["aux"] = {"verify_us": aux["verify"]["us_per_launch"], "prefill_tflops": aux["prefill"]["tflops"],
+                       "linear_skinny": aux["linear_skinny"],
                        "prefill_tflops_best_single_launch": aux["prefill"]["tflops_best_single_launch"],
                        "verify": aux["verify"], "prefill": aux["prefill"]}
     if world == 1 and not args.no_cpu_baseline:
@@ -808,15 +812,14 @@ def run_serving(args):
     print(json.dumps(res), flush=True)
 
 
-def run_linear(args):
+def linear_measure():
     """Side measurement of the weight-streaming linear kernel on the four layer shapes of a
     Llama-3.1-8B-shaped decode step (batch 32): fused QKV 4096 -> 6144, o_proj 4096 -> 4096, gate+up
     4096 -> 28672, down 14336 -> 4096.  Several weight matrices per shape are visited round-robin inside
     one CUDA graph (more bytes than L2 holds, every launch streams from DRAM; consecutive launches overlap
     the way they do inside a decoder layer); the same chain through the library GEMM beside it."""
     from pace_b200.ops.linear import linear_skinny as linear
-    dev = torch.device("cuda", 0)
-    torch.cuda.set_device(dev)
+    dev = torch.device("cuda", torch.cuda.current_device())
     peak, _ = measured_hbm_peak()
     g = torch.Generator(device=dev).manual_seed(3)
     out = {"workload": "linear", "tokens": 32, "peak_gbs": peak, "shapes": {}}
@@ -854,7 +857,11 @@ def run_linear(args):
                                "frac_library": nbytes / res["library"] / 1e3 / peak}
         del ws
         torch.cuda.empty_cache()
-    print(json.dumps(out), flush=True)
+    return out
+
+
+def run_linear(args):
+    print(json.dumps(linear_measure()), flush=True)
 
 
 def main():
