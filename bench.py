@@ -140,7 +140,7 @@ def cpu_reference_line(steps: int):
 def run_reference(args, rank):
     if rank != 0:
         return
-    steps = max(3, min(args.steps, 20))
+    steps = max(3, min(args.steps, 200))
     tps, step_s, cores, kind, sample = cpu_reference_line(steps)
     line = {"impl": "reference", "metric": "decode_tokens_per_s", "value": tps, "unit": "tokens/s",
             "n_gpus": args.gpus, "steps": steps, "warmup": args.warmup, "ms_per_step": step_s * 1e3,
