@@ -99,6 +99,7 @@ __device__ __forceinline__ void mma16816(float (&c)[4], const uint32_t (&a)[4], 
       : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
+// (m16n8k8: for consumer slices of eight keys, a form no current instantiation takes)
 __device__ __forceinline__ void mma1688(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t b0) {
   asm("mma.sync.aligned.m16n8k8.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5}, {%6}, {%0,%1,%2,%3};"
                : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
@@ -355,7 +356,6 @@ __global__ void __launch_bounds__(threads_of(UMMA, UMMA ? 8 : MT * NS), (!UMMA &
   constexpr int KVB = kChunk * D * 2;  // bytes of one K (or V) chunk slot
   constexpr int HALF_B = kChunk * 128;
   constexpr int STAGE = 2 * KVB;
-  constexpr int REC = MR * (D + 2);
 
   extern __shared__ __align__(1024) unsigned char smem[];
   const int n_stages = p.n_stages;

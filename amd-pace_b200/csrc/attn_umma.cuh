@@ -746,13 +746,10 @@ __device__ __forceinline__ void umma_softmax(const MmaParams& p, const UmmaCtx& 
     } else {
       const bool has_mine = j_first < n_part, has_other = (j_first ^ 1) < n_part;  // (a part of one chunk leaves a group empty-handed)
       if (has_mine && !umma_wait(&c.o_full[wg], (cnt - 1) & 1, c.abort)) return;
-      // Each row's (reference maximum, sum) crosses to the other group through tensor memory: columns 32
-      // and 33 of the score buffer of the group's own last chunk, which hold nothing any more (P, packed
-      // bf16, sits in columns 0..31 and its PV MMA has completed; the next QK into the buffer waits for the
-      // next part's Q).  Both groups' warp w own the same 32 TMEM lanes, so no shared memory is needed -
-      // the 2 KB it took are what a sixth ring stage was short of.
-      const int j_last_mine = ((n_part - 1) & 1) == j_first ? n_part - 1 : n_part - 2;
-      const int j_last_other = ((n_part - 1) & 1) == j_first ? n_part - 2 : n_part - 1;
+      // Each row's (reference maximum, sum) crosses to the other group through tensor memory: columns 0
+      // and 1 of the group's own score buffer, which holds nothing any more (the scores of its last chunk
+      // are long in registers; the next QK into the buffer waits for the next part's Q).  Both groups'
+      // warp w own the same 32 TMEM lanes, so no shared memory is needed.
       if (has_mine) {
         tmem_st2(t_lane + (uint32_t)wg * kChunk, __float_as_uint(m_used), __float_as_uint(l));
         tmem_wait_st();
