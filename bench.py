@@ -318,6 +318,18 @@ def run_ours(args, rank, world, local_rank):
     n_chunks = 8 if L % 8 == 0 else 1   # (copies in growing chunks - 1, 2, 4, 8, 17 layers - measured slower: 1.17 ms per step)
     per = L // n_chunks
     copy_in, copy_out = torch.cuda.Stream(), torch.cuda.Stream()
+    # how fast the copies in are next to the compute they feed, with every rank copying at once
+    barrier()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for _ in range(5):
+        with torch.cuda.stream(copy_in):
+            for c in range(n_chunks):
+                kvq[c * per:(c + 1) * per].copy_(host_in[c * per:(c + 1) * per], non_blocking=True)
+        copy_in.synchronize()
+    h2d_probe_ms = (time.perf_counter() - t0) * 1e3 / 5
+    barrier()
+    sparse_joins = h2d_probe_ms < 0.7 * (ms / args.steps)
 
     def step_e2e():
         main = torch.cuda.current_stream()
@@ -335,7 +347,10 @@ def run_ours(args, rank, world, local_rank):
         # wait, so the kernels join the copy stream only in front of chunks 0, 1, 2 and 4 (for the copies of
         # chunks 0 | 1 | 2-3 | 4-7) instead of in front of every chunk (0.677 -> 0.656 ms per step; splitting
         # the first chunk so that layer 0 waits for one layer's rows only gained nothing measurable).
-        join_for = {c: min(n_chunks, 2 * c if c else 1) - 1 for c in range(n_chunks) if c & (c - 1) == 0}
+        # Where the link is not that much faster (several ranks sharing the host's memory system), every chunk
+        # joins for its own copy: a late join for four chunks' copies would hold the kernels back.
+        join_for = ({c: min(n_chunks, 2 * c if c else 1) - 1 for c in range(n_chunks) if c & (c - 1) == 0}
+                    if sparse_joins else {c: c for c in range(n_chunks)})
         for c in range(n_chunks):
             if c in join_for:
                 main.wait_event(arrived[join_for[c]])
@@ -493,8 +508,8 @@ def run_ours(args, rank, world, local_rank):
                 "h2d_only_ms_per_step": h2d_ms, "d2h_only_ms_per_step": d2h_ms,
                 "block_ms_per_step": [b / e2e_steps for b in e2e_blocks],
                 "overlap": f"within a step only: copies in {n_chunks} chunks of {per} layers on side streams of the "
-                           "step's CUDA graph (the kernels join the copies in in front of chunks 0, 1, 2 and 4); the "
-                           "host synchronises after every step"},
+                           "step's CUDA graph (the kernels join the copies in in front of "
+                           + ("chunks 0, 1, 2 and 4" if sparse_joins else "every chunk") + "); the host synchronises after every step"},
         "gpu_launches": (own_launches_per_step * args.steps + timed_reserves) * world,
         "gpu_launches_note": (f"{own_launches_per_step} own kernels per step: {L} decode attention launches and the commit "
                               f"of the step's rows, plus the page reservation kernel in the {timed_reserves} of "
